@@ -1,0 +1,23 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+@pytest.fixture(scope="session")
+def checkers():
+    """The CPU checkers that are available: the reference build (if compiled) and the C restatement."""
+    from oracle import refapi
+    out = {}
+    for kind in ("ref", "oracle"):
+        if refapi.available(kind):
+            out[kind] = refapi.Checker(kind)
+    return out
