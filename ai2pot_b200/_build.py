@@ -1,0 +1,67 @@
+"""In-tree build of the native libraries (no JIT cache: the built files travel with the tree).
+
+  ai2pot_b200/_lib/libai2pot_b200.so   CUDA kernels + C ABI, sm_100a only
+
+Run ``python -m ai2pot_b200._build`` (or call build()). Needs nvcc; no GPU.
+"""
+import glob
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIBDIR = os.path.join(HERE, "_lib")
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
+
+
+def _nvcc():
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found")
+
+
+def _stale(target, sources):
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(s) > t for s in sources)
+
+
+def build_cuda(force=False, verbose=False):
+    os.makedirs(LIBDIR, exist_ok=True)
+    objdir = os.path.join(LIBDIR, "obj")
+    os.makedirs(objdir, exist_ok=True)
+    headers = glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(HERE, "..", "include", "*.h"))
+    objs = []
+    procs = []
+    for src in sorted(glob.glob(os.path.join(CSRC, "*.cu"))):
+        obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
+        objs.append(obj)
+        if force or _stale(obj, [src] + headers):
+            cmd = [_nvcc()] + NVCC_FLAGS + ["-c", src, "-o", obj]
+            log = open(obj + ".log", "w")
+            procs.append((src, subprocess.Popen(cmd, stdout=log, stderr=subprocess.STDOUT), log, obj))
+    for src, p, log, obj in procs:
+        rc = p.wait()
+        log.close()
+        out = open(obj + ".log").read()
+        if verbose or rc != 0:
+            sys.stderr.write(out)
+        if rc != 0:
+            raise RuntimeError(f"nvcc failed on {src}")
+    lib = os.path.join(LIBDIR, "libai2pot_b200.so")
+    if force or procs or _stale(lib, objs):
+        subprocess.check_call([_nvcc(), "-shared", "-o", lib] + objs + ["-lcudart"])
+    return lib
+
+
+def build(force=False, verbose=False):
+    return build_cuda(force, verbose)
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

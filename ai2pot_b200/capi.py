@@ -1,0 +1,157 @@
+"""ctypes binding of the C ABI declared in include/ai2pot_b200.h.
+
+PyTorch is used only as the owner of device memory and streams: every function here takes torch
+CUDA tensors, passes their raw pointers to libai2pot_b200.so and returns torch tensors. There is
+no CPU implementation behind these calls: a missing library or a non-CUDA tensor raises.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "_lib", "libai2pot_b200.so")
+_lib = None
+
+
+class Ai2bError(RuntimeError):
+    pass
+
+
+def lib():
+    """The loaded CUDA library. Raises if it has not been built (python -m ai2pot_b200._build)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise Ai2bError(f"{LIB_PATH} is missing: build it with `python -m ai2pot_b200._build` "
+                            "(there is no CPU fallback)")
+        _lib = C.CDLL(LIB_PATH)
+        _lib.ai2b_last_error_string.restype = C.c_char_p
+        _lib.ai2b_mtp_workspace_bytes.restype = C.c_size_t
+        if hasattr(_lib, "ai2b_nblist_workspace_bytes"):
+            _lib.ai2b_nblist_workspace_bytes.restype = C.c_size_t
+    return _lib
+
+
+def _check(rc):
+    if rc != 0:
+        raise Ai2bError(f"ai2pot_b200 error {rc}: {lib().ai2b_last_error_string().decode()}")
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise Ai2bError("expected a CUDA tensor (this library has no CPU path)")
+    if not t.is_contiguous():
+        raise Ai2bError("expected a contiguous tensor")
+    return C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _suf(dtype):
+    if dtype == torch.float64:
+        return "f64", C.c_double
+    if dtype == torch.float32:
+        return "f32", C.c_float
+    raise Ai2bError(f"unsupported float dtype {dtype}")
+
+
+def to_device(d, device="cuda", float_dtype=None):
+    """Copy the numpy arrays of a dict (model parameters or neighbour tensors) to the device."""
+    out = {}
+    for k, v in d.items():
+        if isinstance(v, np.ndarray):
+            t = torch.from_numpy(np.ascontiguousarray(v))
+            if float_dtype is not None and t.is_floating_point():
+                t = t.to(float_dtype)
+            out[k] = t.to(device)
+        else:
+            out[k] = v
+    return out
+
+
+class MtpProgram:
+    """Compiled alpha tables (ai2b_mtp_program). `tables` holds host int32 arrays."""
+
+    def __init__(self, tables):
+        self.tables = tables
+        b = np.ascontiguousarray(tables["alpha_index_basic"], np.int32)
+        t = np.ascontiguousarray(tables["alpha_index_times"], np.int32)
+        m = np.ascontiguousarray(tables["alpha_moment_mapping"], np.int32)
+        self.ns = len(m)
+        self.nmus = int(tables["nmus"])
+        self.handle = C.c_void_p()
+        _check(lib().ai2b_mtp_program_create(
+            C.c_int(int(tables["alpha_moments_count"])), C.c_int(len(b)), b.ctypes.data_as(C.c_void_p),
+            C.c_int(len(t)), t.ctypes.data_as(C.c_void_p), C.c_int(len(m)), m.ctypes.data_as(C.c_void_p),
+            C.c_int(self.nmus), C.byref(self.handle)))
+        self._ws = None
+
+    def workspace(self, B, npad, device):
+        need = lib().ai2b_mtp_workspace_bytes(self.handle, C.c_int(B), C.c_int(npad))
+        if self._ws is None or self._ws.numel() < need or self._ws.device != device:
+            self._ws = torch.empty(max(need, 256), dtype=torch.uint8, device=device)
+        return self._ws
+
+    def __del__(self):
+        try:
+            if self.handle:
+                lib().ai2b_mtp_program_destroy(self.handle)
+        except Exception:
+            pass
+
+
+def parse_almtp(path):
+    """Parse an MTP template file with the library's own parser -> tables dict."""
+    counts = np.zeros(5, np.int32)
+    _check(lib().ai2b_mtp_parse_almtp(path.encode(), counts.ctypes.data_as(C.c_void_p), None, None, None))
+    b = np.zeros((counts[1], 4), np.int32); t = np.zeros((counts[2], 4), np.int32); m = np.zeros(counts[3], np.int32)
+    _check(lib().ai2b_mtp_parse_almtp(path.encode(), counts.ctypes.data_as(C.c_void_p), b.ctypes.data_as(C.c_void_p),
+                                      t.ctypes.data_as(C.c_void_p), m.ctypes.data_as(C.c_void_p)))
+    return dict(alpha_moments_count=int(counts[0]), nmus=int(counts[4]), alpha_index_basic=b,
+                alpha_index_times=t, alpha_moment_mapping=m)
+
+
+def _nb_args(nb):
+    B, npad = nb["bilist"].shape
+    umax = nb["bfirstneigh"].shape[2]
+    return B, npad, umax, (C.c_int(B), C.c_int(npad), _ptr(nb["binum"]), _ptr(nb["bilist"]), _ptr(nb["bnumneigh"]),
+                           _ptr(nb["bfirstneigh"]), _ptr(nb["brcs"]), _ptr(nb["btypes"]), C.c_int(int(nb["ntypes"])),
+                           C.c_int(umax), C.c_int(int(nb.get("nghost", 0))))
+
+
+def mtp_efv(prog, model, nb, virial=True, out=None):
+    """Energy, forces (and virial) of a batch. `model` / `nb` hold device tensors (see to_device)."""
+    rcs = nb["brcs"]
+    suf, cf = _suf(rcs.dtype)
+    B, npad, umax, nbargs = _nb_args(nb)
+    ng = int(nb.get("nghost", 0))
+    if out is None:
+        e = torch.empty(B, dtype=rcs.dtype, device=rcs.device)
+        f = torch.empty(B, npad + ng, 3, dtype=rcs.dtype, device=rcs.device)
+        v = torch.empty(B, 9, dtype=rcs.dtype, device=rcs.device) if virial else None
+    else:
+        e, f, v = out
+    ws = prog.workspace(B, npad, rcs.device)
+    _check(getattr(lib(), "ai2b_mtp_efv_" + suf)(
+        prog.handle, _ptr(e), _ptr(f), _ptr(v), C.c_int(int(model["chebyshev_size"])), cf(model["scaling"]),
+        _ptr(model["coeffs"]), _ptr(model["linear_coeffs"]), _ptr(model["type_bias"]), *nbargs,
+        cf(model["rmax"]), cf(model["rmin"]), _ptr(model["q_scaler"]), _ptr(ws), C.c_size_t(ws.numel()), _stream()))
+    return (e, f, v) if virial else (e, f)
+
+
+def mtp_descriptors(prog, model, nb):
+    rcs = nb["brcs"]
+    suf, cf = _suf(rcs.dtype)
+    B, npad, umax, nbargs = _nb_args(nb)
+    d = torch.empty(B, npad, prog.ns, dtype=rcs.dtype, device=rcs.device)
+    ws = prog.workspace(B, npad, rcs.device)
+    _check(getattr(lib(), "ai2b_mtp_descriptors_" + suf)(
+        prog.handle, _ptr(d), C.c_int(int(model["chebyshev_size"])), cf(model["scaling"]), _ptr(model["coeffs"]),
+        *nbargs, cf(model["rmax"]), cf(model["rmin"]), _ptr(ws), C.c_size_t(ws.numel()), _stream()))
+    return d

@@ -1,0 +1,119 @@
+// Shared host/device helpers of the ai2pot_b200 CUDA library (sm_100a).
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdarg>
+#include <cstdio>
+#include <type_traits>
+#include "../../include/ai2pot_b200.h"
+
+namespace ai2b {
+
+// Records the calling thread's last error message (returned by ai2b_last_error_string()).
+void set_error(const char *fmt, ...);
+
+#define AI2B_CUDA(call)                                                                        \
+    do {                                                                                       \
+        cudaError_t e_ = (call);                                                               \
+        if (e_ != cudaSuccess) {                                                               \
+            ::ai2b::set_error("%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, \
+                              __LINE__);                                                       \
+            return AI2B_ERR_CUDA;                                                              \
+        }                                                                                      \
+    } while (0)
+
+#define AI2B_REQUIRE(cond, code, ...)                                                          \
+    do {                                                                                       \
+        if (!(cond)) {                                                                         \
+            ::ai2b::set_error(__VA_ARGS__);                                                    \
+            return (code);                                                                     \
+        }                                                                                      \
+    } while (0)
+
+constexpr unsigned FULL_MASK = 0xffffffffu;
+constexpr int WARP = 32;
+
+template <typename T>
+__device__ __forceinline__ T warp_sum(T v)
+{
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) v += __shfl_xor_sync(FULL_MASK, v, o);
+    return v;
+}
+
+// compile-time loop: f(std::integral_constant<int, I>) for I in [I0, N)
+template <int I, int N, typename F>
+__device__ __forceinline__ void static_for(F &&f)
+{
+    if constexpr (I < N) {
+        f(std::integral_constant<int, I>{});
+        static_for<I + 1, N>(f);
+    }
+}
+
+__host__ __device__ constexpr int pow2ceil(int n)
+{
+    int p = 1;
+    while (p < n) p <<= 1;
+    return p;
+}
+__host__ __device__ constexpr int ilog2(int n)
+{
+    int l = 0;
+    while ((1 << l) < n) ++l;
+    return l;
+}
+
+// Sum over the 32 lanes of N per-lane values at once ("transpose-reduce"): on return lane l
+// holds the warp total of v[l >> (5 - log2 N)]. N is a power of two <= 32. Uses N-1 exchange
+// shuffles plus (5 - log2 N) butterfly steps instead of 5 N.
+template <typename T, int N>
+__device__ __forceinline__ T warp_xreduce(T (&v)[N], int lane)
+{
+    int o = 16;
+#pragma unroll
+    for (int h = N / 2; h >= 1; h >>= 1, o >>= 1) {
+        const bool up = (lane & o) != 0;
+#pragma unroll
+        for (int i = 0; i < h; i++) {
+            T send = up ? v[i] : v[i + h];
+            T keep = up ? v[i + h] : v[i];
+            v[i] = keep + __shfl_xor_sync(FULL_MASK, send, o);
+        }
+    }
+    T r = v[0];
+    for (; o >= 1; o >>= 1) r += __shfl_xor_sync(FULL_MASK, r, o);
+    return r;
+}
+
+__device__ __forceinline__ double gsqrt(double x) { return sqrt(x); }
+__device__ __forceinline__ float gsqrt(float x) { return sqrtf(x); }
+
+// number of monomials x^a y^b z^c with a+b+c <= k, and of exact degree d
+__host__ __device__ constexpr int ncan(int k) { return k < 0 ? 0 : (k + 1) * (k + 2) * (k + 3) / 6; }
+__host__ __device__ constexpr int ndeg(int d) { return (d + 1) * (d + 2) / 2; }
+
+struct Exp3 {
+    int x, y, z;
+};
+// q-th monomial of exact degree D in canonical order: x exponent descending, then y descending
+__host__ __device__ constexpr Exp3 deg_exp(int D, int q)
+{
+    int ax = D;
+    while (q >= D - ax + 1) {
+        q -= (D - ax + 1);
+        --ax;
+    }
+    int ay = D - ax - q;
+    return Exp3{ax, ay, D - ax - ay};
+}
+// canonical index of (ax, ay, az) among all monomials, degree-major
+__host__ __device__ constexpr int canon_index(int ax, int ay, int az)
+{
+    int D = ax + ay + az;
+    int q = 0;
+    for (int x = D; x > ax; --x) q += D - x + 1;
+    q += (D - ax) - ay;
+    return ncan(D - 1) + q;
+}
+
+}  // namespace ai2b

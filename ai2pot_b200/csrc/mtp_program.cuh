@@ -1,0 +1,43 @@
+// Compiled form of the MTP alpha tables, shared by the MTP kernels.
+//
+// The reference walks alpha_index_basic / alpha_index_times row by row for every atom
+// (source/descriptor/mtpr/include/mtpBasis.h:472-528, linearMtp.h:292-306). Here the tables are
+// analysed once on the host:
+//  * basic moments (mu, ax, ay, az) are mapped onto a dense, degree-major canonical monomial
+//    numbering per mu, so the kernels evaluate them with compile-time exponents;
+//  * product rows (a, b, mult, dst) are grouped by destination and by dependency depth, so a
+//    warp runs all destinations of one depth in parallel (forward), and the adjoint sweep is
+//    turned into a gather per source moment (reverse).
+#pragma once
+#include "common.cuh"
+
+namespace ai2b {
+
+constexpr int MTP_MAX_MU = 8;
+constexpr int MTP_MAX_DEG = 8;
+constexpr int MTP_MAX_LEV = 16;
+
+struct MtpProgramDev {
+    int nm, nb, nt, ns, nmus, kmax, ndense, nlev;
+    int kmu[MTP_MAX_MU];            // highest monomial degree used with radial function mu
+    int doff[MTP_MAX_MU + 1];       // dense offset of mu: doff[mu] + canonical index
+    int fwd_lev_off[MTP_MAX_LEV + 1];  // destinations of depth 1..nlev
+    int rev_lev_off[MTP_MAX_LEV + 1];  // source moments of depth nlev-1..0
+    const int *basic_dense;         // [nb] dense index of basic row i
+    const int4 *e4g;                // [ndense] basic row holding {value, d/dx, d/dy, d/dz} source (-1: none)
+    const int *e4m;                 // [ndense] packed multipliers (ax+1) | (ay+1)<<8 | (az+1)<<16
+    const int4 *fwd_dst;            // {dst, row_begin, row_end, -}
+    const int2 *fwd_rows;           // {a | b<<16, mult}
+    const int4 *rev_mom;            // {m, entry_begin, entry_end, -}
+    const int2 *rev_ents;           // {other | dst<<16, mult}
+    const int *map;                 // [ns] alpha_moment_mapping
+};
+
+}  // namespace ai2b
+
+struct ai2b_mtp_program {
+    ai2b::MtpProgramDev dev;
+    void *d_blob;       // one device allocation holding every table
+    size_t blob_bytes;
+    int device;
+};

@@ -1,0 +1,103 @@
+/* ai2pot_b200 — C ABI of the B200 (sm_100a) per-atom evaluation path.
+ *
+ * Drop-in boundary: each entry point below takes what the reference's own raw-pointer
+ * launcher for the same step takes (cited per function, paths relative to the reference
+ * project root), plus a CUDA stream and — where the kernels need scratch — a caller-owned
+ * workspace. Plain pointers and sizes only; no torch types.
+ *
+ * Conventions
+ *  - Every function returns AI2B_OK (0) or a negative AI2B_ERR_* code and never throws;
+ *    ai2b_last_error_string() gives the message of the calling thread's last failure.
+ *  - Pointers named d_* are DEVICE pointers on the current device unless stated otherwise.
+ *  - Calls are stream-ordered and do not synchronise; `stream` is a cudaStream_t passed as
+ *    void* (NULL = the legacy default stream).
+ *  - The hot calls allocate nothing: outputs and workspace come from the caller. Handles
+ *    (ai2b_mtp_program) own small device tables allocated at create time.
+ *  - Suffix _f32 / _f64 selects the float type of rcs, parameters and outputs, exactly as the
+ *    reference dispatches on brcs.scalar_type().
+ *  - Batched neighbour tensors use the reference layout: binum[B], bilist[B,Np],
+ *    bnumneigh[B,Np], bfirstneigh[B,Np,umax] (padding -1), brcs[B,Np,umax,3] (r_j - r_i),
+ *    btypes[B,Np+nghost]; forces [B,Np+nghost,3] indexed by atom id; virial [B,9] row-major.
+ */
+#ifndef AI2POT_B200_H
+#define AI2POT_B200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AI2B_OK 0
+#define AI2B_ERR_INVALID (-1)      /* bad argument (NULL pointer, negative size, unsupported value) */
+#define AI2B_ERR_UNSUPPORTED (-2)  /* valid in the reference but outside this build's limits       */
+#define AI2B_ERR_CUDA (-3)         /* a CUDA runtime call failed                                    */
+#define AI2B_ERR_WORKSPACE (-4)    /* workspace missing or too small                                */
+#define AI2B_ERR_OVERFLOW (-5)     /* a neighbour row would exceed umax (list truncated)            */
+#define AI2B_ERR_TIMEOUT (-6)      /* a bounded device-side wait gave up                            */
+
+const char *ai2b_last_error_string(void);
+int ai2b_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Linear MTP
+ * ---------------------------------------------------------------------------------------- */
+
+/* Compiled form of the alpha tables (replaces passing d_alpha_index_basic / _times /
+ * _moment_mapping to every launch: source/descriptor/mtpr/gpu/include/
+ * linearMtp_torch_launcher.h:24-55 takes them per call; source/descriptor/mtpr/src/
+ * mtpParam.cc:80-200 produces them). Tables are HOST pointers, int32, row-major [n][4].
+ * Limits: monomial degree <= 8 (template level <= 20), nmus <= 8. */
+typedef struct ai2b_mtp_program ai2b_mtp_program;
+int ai2b_mtp_program_create(int alpha_moments_count, int alpha_index_basic_count,
+                            const int *alpha_index_basic, int alpha_index_times_count,
+                            const int *alpha_index_times, int alpha_scalar_moments,
+                            const int *alpha_moment_mapping, int nmus,
+                            ai2b_mtp_program **out);
+void ai2b_mtp_program_destroy(ai2b_mtp_program *prog);
+
+/* Parser of the .almtp template files (source/descriptor/mtpr/src/mtpParam.cc:80-200).
+ * Two-call protocol: with the array pointers NULL only counts[5] = {alpha_moments_count,
+ * alpha_index_basic_count, alpha_index_times_count, alpha_scalar_moments, nmus} is filled. */
+int ai2b_mtp_parse_almtp(const char *filename, int *counts, int *alpha_index_basic,
+                         int *alpha_index_times, int *alpha_moment_mapping);
+
+/* Scratch bytes the MTP calls below need for a batch of `batch_size` structures. */
+size_t ai2b_mtp_workspace_bytes(const ai2b_mtp_program *prog, int batch_size, int natoms_pad);
+
+/* Energy + force + virial. Replaces find_efv_torch_launcher<T>
+ * (source/descriptor/mtpr/gpu/include/linearMtp_torch_launcher.h:24-55, .cuh:27-100) and the
+ * CPU launcher (source/descriptor/mtpr/include/linearMtp_cpu_launcher.h:128-203).
+ * Outputs are overwritten (zeroed, then accumulated). d_bvirial may be NULL: energy + force
+ * only (find_ef_torch_launcher, linearMtp_torch_launcher.h:58-88). */
+#define AI2B_DECL_MTP_EFV(SUF, T)                                                              \
+    int ai2b_mtp_efv_##SUF(const ai2b_mtp_program *prog, T *d_betot, T *d_bforce, T *d_bvirial, \
+                           int chebyshev_size, T scaling, const T *d_coeffs,                   \
+                           const T *d_linear_coeffs, const T *d_type_bias, int batch_size,     \
+                           int natoms_pad, const int *d_binum, const int *d_bilist,            \
+                           const int *d_bnumneigh, const int *d_bfirstneigh, const T *d_brcs,  \
+                           const int *d_btypes, int ntypes, int umax, int nghost, T rmax,      \
+                           T rmin, const T *d_q_scaler, void *d_workspace,                     \
+                           size_t workspace_bytes, void *stream);
+AI2B_DECL_MTP_EFV(f64, double)
+AI2B_DECL_MTP_EFV(f32, float)
+
+/* Scalar basis values [B, Np, alpha_scalar_moments] (not divided by q_scaler). Replaces
+ * find_descriptors_torch_launcher<T> (linearMtp_torch_launcher.h:90-118) /
+ * find_descriptors_cpu_launcher (linearMtp_cpu_launcher.h:284-345). */
+#define AI2B_DECL_MTP_DESC(SUF, T)                                                             \
+    int ai2b_mtp_descriptors_##SUF(const ai2b_mtp_program *prog, T *d_bdescriptors,            \
+                                   int chebyshev_size, T scaling, const T *d_coeffs,           \
+                                   int batch_size, int natoms_pad, const int *d_binum,         \
+                                   const int *d_bilist, const int *d_bnumneigh,                \
+                                   const int *d_bfirstneigh, const T *d_brcs,                  \
+                                   const int *d_btypes, int ntypes, int umax, int nghost,      \
+                                   T rmax, T rmin, void *d_workspace, size_t workspace_bytes,  \
+                                   void *stream);
+AI2B_DECL_MTP_DESC(f64, double)
+AI2B_DECL_MTP_DESC(f32, float)
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AI2POT_B200_H */
