@@ -155,3 +155,49 @@ def mtp_descriptors(prog, model, nb):
         prog.handle, _ptr(d), C.c_int(int(model["chebyshev_size"])), cf(model["scaling"]), _ptr(model["coeffs"]),
         *nbargs, cf(model["rmax"]), cf(model["rmin"]), _ptr(ws), C.c_size_t(ws.numel()), _stream()))
     return d
+
+
+class NeighborBuilder:
+    """Device neighbour-list builder for one structure (ai2b_nblist_build_*). Keeps its workspace
+    and output tensors between calls, so repeated builds of same-sized systems allocate nothing."""
+
+    def __init__(self):
+        self._ws = None
+        self._out = None
+
+    def build(self, cell, coords, rcut, umax, is_cart=True, pbc=(True, True, True)):
+        """cell: host array [3,3]; coords: CUDA tensor [N,3] (float32/float64).
+        Returns (numneigh[N], firstneigh[N,umax], rcs[N,umax,3], status[2]) device tensors."""
+        if not coords.is_cuda:
+            raise Ai2bError("coords must be a CUDA tensor")
+        suf, _ = _suf(coords.dtype)
+        n = coords.shape[0]
+        npdt = np.float64 if suf == "f64" else np.float32
+        hcell = np.ascontiguousarray(np.asarray(cell, dtype=npdt).reshape(9))
+        hpbc = np.ascontiguousarray([1 if p else 0 for p in pbc], np.int32)
+        need = lib().ai2b_nblist_workspace_bytes(C.c_int(n), C.c_int(1 if suf == "f64" else 0))
+        dev = coords.device
+        if self._ws is None or self._ws.numel() < need or self._ws.device != dev:
+            self._ws = torch.empty(need, dtype=torch.uint8, device=dev)
+        key = (n, umax, coords.dtype, dev)
+        if self._out is None or self._out[0] != key:
+            self._out = (key, torch.empty(n, dtype=torch.int32, device=dev),
+                         torch.empty(n, umax, dtype=torch.int32, device=dev),
+                         torch.empty(n, umax, 3, dtype=coords.dtype, device=dev),
+                         torch.empty(2, dtype=torch.int32, device=dev))
+        _, nn, fn, rcs, status = self._out
+        coords = coords.contiguous()
+        _check(getattr(lib(), "ai2b_nblist_build_" + suf)(
+            C.c_int(n), hcell.ctypes.data_as(C.c_void_p), _ptr(coords), C.c_int(1 if is_cart else 0), C.c_double(rcut),
+            hpbc.ctypes.data_as(C.c_void_p), C.c_int(umax), _ptr(nn), _ptr(fn), _ptr(rcs), _ptr(status), _ptr(self._ws),
+            C.c_size_t(self._ws.numel()), _stream()))
+        return nn, fn, rcs, status
+
+
+def sort_rows_by_distance(numneigh, firstneigh, rcs):
+    """In-place distance ordering of every row (ai2b_nblist_sort_rows_*)."""
+    suf, _ = _suf(rcs.dtype)
+    n, umax = firstneigh.shape
+    _check(getattr(lib(), "ai2b_nblist_sort_rows_" + suf)(C.c_int(n), C.c_int(umax), _ptr(numneigh), _ptr(firstneigh),
+                                                          _ptr(rcs), _stream()))
+    return numneigh, firstneigh, rcs

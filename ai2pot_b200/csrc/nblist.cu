@@ -1,0 +1,599 @@
+// Cell-list neighbour build on sm_100a, bit-compatible with the reference's CPU list.
+//
+// Reference semantics (source/nblist/include/structure.h:589-710, binLinkedList.h:658-696,983-1031,
+// neighborList.h:532-578): the cell is replicated over images n_k in [-e_k, e_k],
+// e_k = ceil(rcut / interplanar distance) on periodic axes; image position
+// ((r_j + a0*nx) + a1*ny) + a2*nz; (j, n) is a neighbour of i iff 1e-3 < d2 < rcut^2 with
+// d = image - r_i (squares accumulated in double when T = float); row = index j, rcs = d;
+// padding -1 / 0. The order inside a row is not part of the contract.
+//
+// Here: atoms are binned once by their fractional coordinates wrapped into the cell (bins at
+// least rcut thick), each centre atom is handled by one warp that walks the neighbouring bins
+// with lanes over candidate atoms, applies the reference's predicate with the reference's
+// operation order (no FMA contraction), and compacts hits with a warp ballot. The padded row
+// is written once, by the same warp.
+#include "common.cuh"
+
+#include <cmath>
+#include <cstring>
+
+namespace ai2b {
+
+template <typename T> struct Vec4;
+template <> struct Vec4<double> { using type = double4; };
+template <> struct Vec4<float> { using type = float4; };
+
+struct NbGrid {          // lives in the workspace; written by nb_grid_kernel
+    int nb[3];           // bins per fractional axis
+    int R[3];            // bins to search on each side
+    int total;
+    int pad;
+    double lo[3];        // non-periodic axes: lowest fractional coordinate
+    double scale[3];     // bin = (s - lo) * scale
+};
+
+template <typename T>
+struct NbParams {
+    T cell[9];           // rows = lattice vectors (as given, type T)
+    double inv[9];       // inverse cell: frac_k = sum_c r_c * inv[3*c + k]
+    double dplane[3];    // interplanar distances (double, for bin sizing only)
+    int per[3], e[3];
+    int nbh[3];          // bins of the periodic axes (host-computed); cap for the others
+    double rcut_m;       // rcut with a safety margin, for bin sizing
+    double rc2;          // rcut^2 as the reference forms it
+    int n, umax, maxbins;
+};
+
+__device__ __forceinline__ double mul_rn(double a, double b) { return __dmul_rn(a, b); }
+__device__ __forceinline__ double add_rn(double a, double b) { return __dadd_rn(a, b); }
+__device__ __forceinline__ double sub_rn(double a, double b) { return __dsub_rn(a, b); }
+__device__ __forceinline__ float mul_rn(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ float add_rn(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ float sub_rn(float a, float b) { return __fsub_rn(a, b); }
+
+// fractional -> Cartesian with the reference's operation order (structure.h:561-581)
+template <typename T>
+__global__ void nb_frac2cart_kernel(NbParams<T> P, const T *__restrict__ frac, T *__restrict__ cart)
+{
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= P.n) return;
+    T f0 = frac[3 * i], f1 = frac[3 * i + 1], f2 = frac[3 * i + 2];
+#pragma unroll
+    for (int c = 0; c < 3; c++)
+        cart[3 * i + c] = add_rn(add_rn(mul_rn(f0, P.cell[c]), mul_rn(f1, P.cell[3 + c])), mul_rn(f2, P.cell[6 + c]));
+}
+
+template <typename T>
+__device__ __forceinline__ void frac_of(const NbParams<T> &P, const T *pos, int i, double *s)
+{
+    double x = pos[3 * i], y = pos[3 * i + 1], z = pos[3 * i + 2];
+#pragma unroll
+    for (int k = 0; k < 3; k++) s[k] = x * P.inv[k] + y * P.inv[3 + k] + z * P.inv[6 + k];
+}
+
+__device__ __forceinline__ unsigned long long enc_double(double d)
+{
+    unsigned long long u = (unsigned long long)__double_as_longlong(d);
+    return (u >> 63) ? ~u : (u | 0x8000000000000000ull);
+}
+__device__ __forceinline__ double dec_double(unsigned long long u)
+{
+    u = (u >> 63) ? (u & 0x7fffffffffffffffull) : ~u;
+    return __longlong_as_double((long long)u);
+}
+
+// extents of the fractional coordinates (only launched when an axis is not periodic)
+template <typename T>
+__global__ void nb_extent_kernel(NbParams<T> P, const T *__restrict__ pos, unsigned long long *__restrict__ ext)
+{
+    double lo[3] = {1e300, 1e300, 1e300}, hi[3] = {-1e300, -1e300, -1e300};
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < P.n; i += gridDim.x * blockDim.x) {
+        double s[3];
+        frac_of(P, pos, i, s);
+#pragma unroll
+        for (int k = 0; k < 3; k++) { lo[k] = fmin(lo[k], s[k]); hi[k] = fmax(hi[k], s[k]); }
+    }
+#pragma unroll
+    for (int k = 0; k < 3; k++) {
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) {
+            lo[k] = fmin(lo[k], __shfl_xor_sync(FULL_MASK, lo[k], o));
+            hi[k] = fmax(hi[k], __shfl_xor_sync(FULL_MASK, hi[k], o));
+        }
+        if ((threadIdx.x & 31) == 0) {
+            atomicMin(ext + k, enc_double(lo[k]));
+            atomicMax(ext + 3 + k, enc_double(hi[k]));
+        }
+    }
+}
+
+__global__ void nb_init_kernel(unsigned long long *ext, int *status)
+{
+    if (threadIdx.x < 3) { ext[threadIdx.x] = ~0ull; ext[3 + threadIdx.x] = 0ull; }
+    if (threadIdx.x < 2) status[threadIdx.x] = 0;
+}
+
+template <typename T>
+__global__ void nb_grid_kernel(NbParams<T> P, const unsigned long long *__restrict__ ext, NbGrid *__restrict__ g)
+{
+    if (threadIdx.x != 0) return;
+    long total = 1;
+    for (int k = 0; k < 3; k++) {
+        if (P.per[k]) {
+            g->nb[k] = P.nbh[k];
+            double t = P.dplane[k] / P.nbh[k];
+            g->R[k] = (int)ceil(P.rcut_m / t);
+            g->lo[k] = 0.0;
+            g->scale[k] = (double)P.nbh[k];
+        } else {
+            double lo = dec_double(ext[k]), hi = dec_double(ext[3 + k]);
+            double span = fmax(hi - lo, 1e-12);
+            int nb = (int)floor(span * P.dplane[k] / P.rcut_m);
+            nb = max(1, min(nb, P.nbh[k]));
+            g->nb[k] = nb;
+            g->R[k] = 1;
+            g->lo[k] = lo;
+            g->scale[k] = nb / span;
+        }
+        total *= g->nb[k];
+    }
+    g->total = (int)total;   // <= maxbins by construction of nbh
+}
+
+template <typename T>
+__device__ __forceinline__ void bin_of(const NbParams<T> &P, const NbGrid &g, const double *s, int *b, int *w)
+{
+#pragma unroll
+    for (int k = 0; k < 3; k++) {
+        if (P.per[k]) {
+            double fl = floor(s[k]);
+            w[k] = (int)fl;
+            int bb = (int)((s[k] - fl) * g.scale[k]);
+            b[k] = min(max(bb, 0), g.nb[k] - 1);
+        } else {
+            w[k] = 0;
+            int bb = (int)((s[k] - g.lo[k]) * g.scale[k]);
+            b[k] = min(max(bb, 0), g.nb[k] - 1);
+        }
+    }
+}
+
+// pass 1: bin index + lattice wrap of every atom, bin populations
+template <typename T>
+__global__ void nb_count_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const T *__restrict__ pos,
+                                int4 *__restrict__ ainfo, int *__restrict__ bin_count)
+{
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= P.n) return;
+    const NbGrid g = *gp;
+    double s[3];
+    int b[3], w[3];
+    frac_of(P, pos, i, s);
+    bin_of(P, g, s, b, w);
+    int bin = (b[0] * g.nb[1] + b[1]) * g.nb[2] + b[2];
+    ainfo[i] = make_int4(bin, w[0], w[1], w[2]);
+    atomicAdd(bin_count + bin, 1);
+}
+
+// exclusive scan of bin_count[0..total) -> bin_start[0..total], three small kernels
+constexpr int SCAN_BLOCK = 1024;
+__global__ void nb_scan1_kernel(const NbGrid *__restrict__ gp, const int *__restrict__ in, int *__restrict__ out, int *__restrict__ bsum)
+{
+    __shared__ int ws[32];
+    const int total = gp->total;
+    int i = blockIdx.x * SCAN_BLOCK + threadIdx.x;
+    if (blockIdx.x * SCAN_BLOCK >= total + 1) return;
+    int v = i < total ? in[i] : 0, inc = v;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { int n = __shfl_up_sync(FULL_MASK, inc, o); if (lane >= o) inc += n; }
+    if (lane == 31) ws[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        int w = ws[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { int n = __shfl_up_sync(FULL_MASK, w, o); if (lane >= o) w += n; }
+        ws[lane] = w;
+    }
+    __syncthreads();
+    int excl = inc - v + (warp > 0 ? ws[warp - 1] : 0);
+    if (i <= total) out[i] = excl;
+    if (threadIdx.x == SCAN_BLOCK - 1) bsum[blockIdx.x] = excl + v;
+}
+__global__ void nb_scan2_kernel(const NbGrid *__restrict__ gp, int *__restrict__ bsum)
+{
+    // serial-by-chunks exclusive scan of the block sums (at most a few thousand entries)
+    __shared__ int ws[32];
+    __shared__ int carry;
+    const int nblk = (gp->total + 1 + SCAN_BLOCK - 1) / SCAN_BLOCK;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    for (int base = 0; base < nblk; base += SCAN_BLOCK) {
+        int i = base + threadIdx.x;
+        int v = i < nblk ? bsum[i] : 0, inc = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { int n = __shfl_up_sync(FULL_MASK, inc, o); if (lane >= o) inc += n; }
+        if (lane == 31) ws[warp] = inc;
+        __syncthreads();
+        if (warp == 0) {
+            int w = ws[lane];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { int n = __shfl_up_sync(FULL_MASK, w, o); if (lane >= o) w += n; }
+            ws[lane] = w;
+        }
+        __syncthreads();
+        int excl = carry + inc - v + (warp > 0 ? ws[warp - 1] : 0);
+        if (i < nblk) bsum[i] = excl;
+        __syncthreads();
+        if (threadIdx.x == SCAN_BLOCK - 1) carry = excl + v;
+        __syncthreads();
+    }
+}
+__global__ void nb_scan3_kernel(const NbGrid *__restrict__ gp, int *__restrict__ out, const int *__restrict__ bsum, int *__restrict__ cursor)
+{
+    const int total = gp->total;
+    int i = blockIdx.x * SCAN_BLOCK + threadIdx.x;
+    if (i > total) return;
+    int v = out[i] + bsum[blockIdx.x];
+    out[i] = v;
+    if (i < total) cursor[i] = v;
+}
+
+// pass 2: atoms into bin order: position (type T) + {original index, wrap}
+template <typename T>
+__global__ void nb_fill_kernel(NbParams<T> P, const T *__restrict__ pos, const int4 *__restrict__ ainfo,
+                               int *__restrict__ cursor, typename Vec4<T>::type *__restrict__ spos, int4 *__restrict__ sinfo)
+{
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= P.n) return;
+    const int4 a = ainfo[i];
+    int k = atomicAdd(cursor + a.x, 1);
+    typename Vec4<T>::type p;
+    p.x = pos[3 * i]; p.y = pos[3 * i + 1]; p.z = pos[3 * i + 2]; p.w = T(0);
+    spos[k] = p;
+    sinfo[k] = make_int4(i, a.y, a.z, a.w);
+}
+
+constexpr int NB_WARPS = 8;
+
+// pass 3: one warp per centre atom (taken in bin order, so neighbouring warps share bins)
+template <typename T>
+__global__ void __launch_bounds__(NB_WARPS * 32)
+nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restrict__ bin_start,
+                const int4 *__restrict__ ainfo, const typename Vec4<T>::type *__restrict__ spos,
+                const int4 *__restrict__ sinfo, int *__restrict__ numneigh, int *__restrict__ firstneigh,
+                T *__restrict__ rcs, int *__restrict__ status)
+{
+    __shared__ int s_start[NB_WARPS][32], s_pre[NB_WARPS][33], s_shift[NB_WARPS][32];
+    const NbGrid g = *gp;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = gridDim.x * NB_WARPS;
+    const int nx = 2 * g.R[0] + 1, ny = 2 * g.R[1] + 1, nz = 2 * g.R[2] + 1, nnb = nx * ny * nz;
+    const unsigned lt_mask = (1u << lane) - 1u;
+    int local_max = 0;
+
+    for (int a = blockIdx.x * NB_WARPS + warp; a < P.n; a += nwarps) {
+        const typename Vec4<T>::type pi = spos[a];
+        const int4 si = sinfo[a];
+        const int i = si.x;
+        const int bin_i = ainfo[i].x;
+        const int bz = bin_i % g.nb[2], by = (bin_i / g.nb[2]) % g.nb[1], bx = bin_i / (g.nb[2] * g.nb[1]);
+        int count = 0;
+        int *frow = firstneigh + (size_t)i * P.umax;
+        T *rrow = rcs + (size_t)i * P.umax * 3;
+
+        for (int base = 0; base < nnb; base += 32) {
+            // lanes = neighbouring bins of this group
+            const int k = base + lane;
+            int start = 0, len = 0, shift = 0;
+            if (k < nnb) {
+                int d[3] = {k / (ny * nz) - g.R[0], (k / nz) % ny - g.R[1], k % nz - g.R[2]};
+                int b[3] = {bx + d[0], by + d[1], bz + d[2]}, m[3];
+                bool ok = true;
+#pragma unroll
+                for (int c = 0; c < 3; c++) {
+                    if (P.per[c]) {
+                        int q = b[c] >= 0 ? b[c] / g.nb[c] : -((-b[c] + g.nb[c] - 1) / g.nb[c]);
+                        m[c] = q; b[c] -= q * g.nb[c];
+                    } else {
+                        m[c] = 0;
+                        ok = ok && b[c] >= 0 && b[c] < g.nb[c];
+                    }
+                }
+                if (ok) {
+                    int bin = (b[0] * g.nb[1] + b[1]) * g.nb[2] + b[2];
+                    start = bin_start[bin];
+                    len = bin_start[bin + 1] - start;
+                    shift = (m[0] + 512) | ((m[1] + 512) << 10) | ((m[2] + 512) << 20);
+                }
+            }
+            int inc = len;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { int n = __shfl_up_sync(FULL_MASK, inc, o); if (lane >= o) inc += n; }
+            const int total = __shfl_sync(FULL_MASK, inc, 31);
+            __syncwarp();
+            s_start[warp][lane] = start;
+            s_pre[warp][lane] = inc - len;
+            s_shift[warp][lane] = shift;
+            if (lane == 31) s_pre[warp][32] = total;
+            __syncwarp();
+
+            // lanes = candidate atoms of the whole group of bins
+            for (int c0 = 0; c0 < total; c0 += 32) {
+                const int c = c0 + lane;
+                bool hit = false;
+                int jidx = 0;
+                T d0 = 0, d1 = 0, d2 = 0;
+                if (c < total) {
+                    int lo = 0, hi = 32;    // largest slot with pre[slot] <= c
+                    while (hi - lo > 1) { int mid = (lo + hi) >> 1; if (s_pre[warp][mid] <= c) lo = mid; else hi = mid; }
+                    const int aj = s_start[warp][lo] + (c - s_pre[warp][lo]);
+                    const int sh = s_shift[warp][lo];
+                    const typename Vec4<T>::type pj = spos[aj];
+                    const int4 sj = sinfo[aj];
+                    const int n0 = (sh & 1023) - 512 - sj.y + si.y;
+                    const int n1 = ((sh >> 10) & 1023) - 512 - sj.z + si.z;
+                    const int n2 = ((sh >> 20) & 1023) - 512 - sj.w + si.w;
+                    if (abs(n0) <= P.e[0] && abs(n1) <= P.e[1] && abs(n2) <= P.e[2]) {
+                        const T f0 = T(n0), f1 = T(n1), f2 = T(n2);
+                        const T ix = add_rn(add_rn(add_rn(pj.x, mul_rn(P.cell[0], f0)), mul_rn(P.cell[3], f1)), mul_rn(P.cell[6], f2));
+                        const T iy = add_rn(add_rn(add_rn(pj.y, mul_rn(P.cell[1], f0)), mul_rn(P.cell[4], f1)), mul_rn(P.cell[7], f2));
+                        const T iz = add_rn(add_rn(add_rn(pj.z, mul_rn(P.cell[2], f0)), mul_rn(P.cell[5], f1)), mul_rn(P.cell[8], f2));
+                        d0 = sub_rn(ix, pi.x); d1 = sub_rn(iy, pi.y); d2 = sub_rn(iz, pi.z);
+                        // squares accumulate in double for both types (pow(T,int) promotes float), then round to T
+                        const double dd = add_rn(add_rn(mul_rn((double)d0, (double)d0), mul_rn((double)d1, (double)d1)),
+                                                 mul_rn((double)d2, (double)d2));
+                        const double ddT = (double)(T)dd;
+                        hit = (ddT < P.rc2) && (ddT > 1e-3);
+                        jidx = sj.x;
+                    }
+                }
+                const unsigned bal = __ballot_sync(FULL_MASK, hit);
+                if (hit) {
+                    const int p = count + __popc(bal & lt_mask);
+                    if (p < P.umax) {
+                        frow[p] = jidx;
+                        rrow[3 * p] = d0; rrow[3 * p + 1] = d1; rrow[3 * p + 2] = d2;
+                    }
+                }
+                count += __popc(bal);
+            }
+            __syncwarp();
+        }
+        for (int k = count + lane; k < P.umax; k += 32) {
+            frow[k] = -1;
+            rrow[3 * k] = T(0); rrow[3 * k + 1] = T(0); rrow[3 * k + 2] = T(0);
+        }
+        if (lane == 0) numneigh[i] = min(count, P.umax);
+        local_max = max(local_max, count);
+    }
+    if (lane == 0 && local_max > 0) {
+        atomicMax(status, local_max);
+        if (local_max > P.umax) status[1] = 1;
+    }
+}
+
+
+// optional pass 4: order each row by distance (the reference's sort=true, neighborList.h:290-335:
+// std::sort on sqrt(dx^2+dy^2+dz^2)). Stable rank sort, one warp per row; ties keep build order.
+template <typename T>
+__global__ void nb_sort_rows_kernel(int n, int umax, const int *__restrict__ numneigh, int *__restrict__ firstneigh, T *__restrict__ rcs)
+{
+    extern __shared__ __align__(16) unsigned char sort_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+    T *key = reinterpret_cast<T *>(sort_smem) + (size_t)warp * umax * 4;
+    T *val = key + umax;                                   // 3 * umax
+    int *idx = reinterpret_cast<int *>(reinterpret_cast<T *>(sort_smem) + (size_t)wpb * umax * 4) + (size_t)warp * umax;
+    for (int i = blockIdx.x * wpb + warp; i < n; i += gridDim.x * wpb) {
+        const int nn = min(numneigh[i], umax);
+        int *frow = firstneigh + (size_t)i * umax;
+        T *rrow = rcs + (size_t)i * umax * 3;
+        for (int k = lane; k < nn; k += 32) {
+            T a = rrow[3 * k], b = rrow[3 * k + 1], c = rrow[3 * k + 2];
+            val[3 * k] = a; val[3 * k + 1] = b; val[3 * k + 2] = c;
+            idx[k] = frow[k];
+            key[k] = (T)sqrt((double)a * (double)a + (double)b * (double)b + (double)c * (double)c);
+        }
+        __syncwarp();
+        for (int k = lane; k < nn; k += 32) {
+            const T kk = key[k];
+            int rank = 0;
+            for (int m = 0; m < nn; m++) rank += (key[m] < kk || (key[m] == kk && m < k)) ? 1 : 0;
+            frow[rank] = idx[k];
+            rrow[3 * rank] = val[3 * k]; rrow[3 * rank + 1] = val[3 * k + 1]; rrow[3 * rank + 2] = val[3 * k + 2];
+        }
+        __syncwarp();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+struct NbLayout {
+    size_t grid, ext, status_unused, cart, ainfo, count, start, cursor, bsum, spos, sinfo, total;
+};
+template <typename T>
+static NbLayout nb_layout(int n, int maxbins)
+{
+    NbLayout L;
+    size_t o = 0;
+    auto take = [&](size_t bytes) { size_t r = o; o += (bytes + 255) & ~size_t(255); return r; };
+    L.grid = take(sizeof(NbGrid));
+    L.ext = take(6 * sizeof(unsigned long long));
+    L.status_unused = take(16);
+    L.cart = take(sizeof(T) * 3 * (size_t)n);
+    L.ainfo = take(sizeof(int4) * (size_t)n);
+    L.count = take(sizeof(int) * ((size_t)maxbins + 1));
+    L.start = take(sizeof(int) * ((size_t)maxbins + 2));
+    L.cursor = take(sizeof(int) * ((size_t)maxbins + 1));
+    L.bsum = take(sizeof(int) * ((size_t)maxbins / SCAN_BLOCK + 2));
+    L.spos = take(sizeof(typename Vec4<T>::type) * (size_t)n);
+    L.sinfo = take(sizeof(int4) * (size_t)n);
+    L.total = o;
+    return L;
+}
+static int nb_maxbins(int n) { return 2 * (n > 0 ? n : 0) + 4096; }
+
+template <typename T>
+static void plane_distances(const T *cell, T *d)
+{
+    // interplanar distances in type T, same operations as structure.h:818-843
+    for (int k = 0; k < 3; k++) {
+        const T *a = cell + 3 * ((k == 0) ? 1 : 0), *b = cell + 3 * ((k == 2) ? 1 : 2);
+        T n[3] = {a[1] * b[2] - a[2] * b[1], a[2] * b[0] - a[0] * b[2], a[0] * b[1] - a[1] * b[0]};
+        T len = (T)std::sqrt((double)(n[0] * n[0] + n[1] * n[1] + n[2] * n[2]));
+        T u[3] = {n[0] / len, n[1] / len, n[2] / len};
+        const T *c = cell + 3 * k;
+        d[k] = (T)std::fabs((double)(c[0] * u[0] + c[1] * u[1] + c[2] * u[2]));
+    }
+}
+
+template <typename T>
+static int nblist_build(int n, const T *h_cell, const T *d_coords, int is_cart, double rcut_in, const int *pbc, int umax,
+                        int *d_numneigh, int *d_firstneigh, T *d_rcs, int *d_status, void *ws, size_t ws_bytes, cudaStream_t st)
+{
+    AI2B_REQUIRE(h_cell && pbc && d_status, AI2B_ERR_INVALID, "ai2b_nblist_build: NULL argument");
+    AI2B_REQUIRE(n >= 0 && umax >= 0 && rcut_in > 0, AI2B_ERR_INVALID, "ai2b_nblist_build: bad size or cutoff");
+    if (n == 0) return AI2B_OK;
+    AI2B_REQUIRE(d_coords && d_numneigh && d_firstneigh && d_rcs, AI2B_ERR_INVALID, "ai2b_nblist_build: NULL argument");
+    const int maxbins = nb_maxbins(n);
+    const NbLayout L = nb_layout<T>(n, maxbins);
+    AI2B_REQUIRE(ws && ws_bytes >= L.total, AI2B_ERR_WORKSPACE, "nblist workspace too small: %zu < %zu bytes", ws_bytes, L.total);
+
+    NbParams<T> P;
+    memset(&P, 0, sizeof(P));
+    const T rcut = (T)rcut_in;                 // the float build casts rcut first (nblist_bind.cc:133)
+    for (int k = 0; k < 9; k++) P.cell[k] = h_cell[k];
+    // inverse cell in double
+    double a[9];
+    for (int k = 0; k < 9; k++) a[k] = (double)h_cell[k];
+    double det = a[0] * (a[4] * a[8] - a[5] * a[7]) - a[1] * (a[3] * a[8] - a[5] * a[6]) + a[2] * (a[3] * a[7] - a[4] * a[6]);
+    AI2B_REQUIRE(std::fabs(det) > 1e-300, AI2B_ERR_INVALID, "ai2b_nblist_build: singular cell");
+    // inv = A^{-1}, with r = f A  =>  f = r A^{-1}
+    double c[9] = {a[4] * a[8] - a[5] * a[7], a[2] * a[7] - a[1] * a[8], a[1] * a[5] - a[2] * a[4],
+                   a[5] * a[6] - a[3] * a[8], a[0] * a[8] - a[2] * a[6], a[2] * a[3] - a[0] * a[5],
+                   a[3] * a[7] - a[4] * a[6], a[1] * a[6] - a[0] * a[7], a[0] * a[4] - a[1] * a[3]};
+    for (int k = 0; k < 9; k++) P.inv[k] = c[k] / det;
+    T dT[3];
+    plane_distances<T>(h_cell, dT);
+    P.rcut_m = (double)rcut * 1.0001 + 1e-6;
+    P.rc2 = (double)rcut * (double)rcut;
+    if (sizeof(T) == 8) { volatile double r2 = (double)rcut * (double)rcut; P.rc2 = r2; }
+    P.n = n; P.umax = umax; P.maxbins = maxbins;
+    bool any_open = false;
+    long prod = 1;
+    for (int k = 0; k < 3; k++) {
+        P.per[k] = pbc[k] ? 1 : 0;
+        P.dplane[k] = (double)dT[k];
+        P.e[k] = pbc[k] ? (int)std::ceil((double)(rcut / dT[k])) : 0;
+        AI2B_REQUIRE(P.e[k] < 500, AI2B_ERR_UNSUPPORTED, "cell far smaller than the cutoff (%d images on axis %d)", P.e[k], k);
+        if (pbc[k]) {
+            int nb = (int)std::floor(P.dplane[k] / P.rcut_m);
+            P.nbh[k] = nb < 1 ? 1 : nb;
+        } else {
+            any_open = true;
+            P.nbh[k] = 1;
+        }
+        prod *= P.nbh[k];
+    }
+    // shrink periodic bin counts if the grid would not fit, then hand the rest to the open axes
+    while (prod > maxbins) {
+        int big = 0;
+        for (int k = 1; k < 3; k++) if (P.nbh[k] > P.nbh[big]) big = k;
+        prod /= P.nbh[big];
+        P.nbh[big] = (P.nbh[big] + 1) / 2;
+        prod *= P.nbh[big];
+    }
+    if (any_open) {
+        int nopen = 0;
+        for (int k = 0; k < 3; k++) nopen += pbc[k] ? 0 : 1;
+        int cap = (int)std::floor(std::pow((double)maxbins / (double)prod, 1.0 / nopen));
+        for (int k = 0; k < 3; k++) if (!pbc[k]) P.nbh[k] = cap < 1 ? 1 : cap;
+    }
+
+    unsigned char *w = (unsigned char *)ws;
+    NbGrid *grid = (NbGrid *)(w + L.grid);
+    unsigned long long *ext = (unsigned long long *)(w + L.ext);
+    T *cart = (T *)(w + L.cart);
+    int4 *ainfo = (int4 *)(w + L.ainfo);
+    int *count = (int *)(w + L.count), *start = (int *)(w + L.start), *cursor = (int *)(w + L.cursor), *bsum = (int *)(w + L.bsum);
+    auto *spos = (typename Vec4<T>::type *)(w + L.spos);
+    int4 *sinfo = (int4 *)(w + L.sinfo);
+
+    const int tb = 256, nblk = (n + tb - 1) / tb;
+    nb_init_kernel<<<1, 32, 0, st>>>(ext, d_status);
+    const T *pos = d_coords;
+    if (!is_cart) {
+        nb_frac2cart_kernel<T><<<nblk, tb, 0, st>>>(P, d_coords, cart);
+        pos = cart;
+    }
+    if (any_open) nb_extent_kernel<T><<<(nblk < 1024 ? nblk : 1024), tb, 0, st>>>(P, pos, ext);
+    nb_grid_kernel<T><<<1, 32, 0, st>>>(P, ext, grid);
+    AI2B_CUDA(cudaMemsetAsync(count, 0, sizeof(int) * ((size_t)maxbins + 1), st));
+    nb_count_kernel<T><<<nblk, tb, 0, st>>>(P, grid, pos, ainfo, count);
+    const int sblk = (maxbins + 1 + SCAN_BLOCK - 1) / SCAN_BLOCK;
+    nb_scan1_kernel<<<sblk, SCAN_BLOCK, 0, st>>>(grid, count, start, bsum);
+    nb_scan2_kernel<<<1, SCAN_BLOCK, 0, st>>>(grid, bsum);
+    nb_scan3_kernel<<<sblk, SCAN_BLOCK, 0, st>>>(grid, start, bsum, cursor);
+    nb_fill_kernel<T><<<nblk, tb, 0, st>>>(P, pos, ainfo, cursor, spos, sinfo);
+    int sms = 148;
+    {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    long blocks = ((long)n + NB_WARPS - 1) / NB_WARPS;
+    if (blocks > (long)sms * 8) blocks = (long)sms * 8;
+    nb_build_kernel<T><<<(unsigned)blocks, NB_WARPS * 32, 0, st>>>(P, grid, start, ainfo, spos, sinfo, d_numneigh, d_firstneigh, d_rcs, d_status);
+    AI2B_CUDA(cudaGetLastError());
+    return AI2B_OK;
+}
+
+}  // namespace ai2b
+
+using namespace ai2b;
+
+extern "C" size_t ai2b_nblist_workspace_bytes(int natoms, int is_f64)
+{
+    return is_f64 ? nb_layout<double>(natoms, nb_maxbins(natoms)).total : nb_layout<float>(natoms, nb_maxbins(natoms)).total;
+}
+
+extern "C" int ai2b_nblist_build_f64(int natoms, const double *h_cell, const double *d_coords, int is_cart, double rcut,
+                                     const int *h_pbc, int umax, int *d_numneigh, int *d_firstneigh, double *d_rcs,
+                                     int *d_status, void *d_workspace, size_t workspace_bytes, void *stream)
+{
+    return nblist_build<double>(natoms, h_cell, d_coords, is_cart, rcut, h_pbc, umax, d_numneigh, d_firstneigh, d_rcs,
+                                d_status, d_workspace, workspace_bytes, (cudaStream_t)stream);
+}
+extern "C" int ai2b_nblist_build_f32(int natoms, const float *h_cell, const float *d_coords, int is_cart, double rcut,
+                                     const int *h_pbc, int umax, int *d_numneigh, int *d_firstneigh, float *d_rcs,
+                                     int *d_status, void *d_workspace, size_t workspace_bytes, void *stream)
+{
+    return nblist_build<float>(natoms, h_cell, d_coords, is_cart, rcut, h_pbc, umax, d_numneigh, d_firstneigh, d_rcs,
+                               d_status, d_workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+template <typename T>
+static int nblist_sort(int n, int umax, const int *numneigh, int *firstneigh, T *rcs, cudaStream_t st)
+{
+    AI2B_REQUIRE(n >= 0 && umax >= 0, AI2B_ERR_INVALID, "ai2b_nblist_sort_rows: negative size");
+    if (n == 0 || umax == 0) return AI2B_OK;
+    AI2B_REQUIRE(numneigh && firstneigh && rcs, AI2B_ERR_INVALID, "ai2b_nblist_sort_rows: NULL argument");
+    const int wpb = 4;
+    const size_t smem = (size_t)wpb * umax * (4 * sizeof(T) + sizeof(int));
+    AI2B_REQUIRE(smem <= 200 * 1024, AI2B_ERR_UNSUPPORTED, "umax %d too large to sort rows in shared memory", umax);
+    auto kern = nb_sort_rows_kernel<T>;
+    if (smem > 48 * 1024) AI2B_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    long blocks = ((long)n + wpb - 1) / wpb;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    kern<<<(unsigned)blocks, wpb * 32, smem, st>>>(n, umax, numneigh, firstneigh, rcs);
+    AI2B_CUDA(cudaGetLastError());
+    return AI2B_OK;
+}
+extern "C" int ai2b_nblist_sort_rows_f64(int natoms, int umax, const int *d_numneigh, int *d_firstneigh, double *d_rcs, void *stream)
+{
+    return nblist_sort<double>(natoms, umax, d_numneigh, d_firstneigh, d_rcs, (cudaStream_t)stream);
+}
+extern "C" int ai2b_nblist_sort_rows_f32(int natoms, int umax, const int *d_numneigh, int *d_firstneigh, float *d_rcs, void *stream)
+{
+    return nblist_sort<float>(natoms, umax, d_numneigh, d_firstneigh, d_rcs, (cudaStream_t)stream);
+}

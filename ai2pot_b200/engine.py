@@ -1,0 +1,172 @@
+"""Host-side driver of the evaluation path: positions -> neighbour list -> E/F/V on one GPU,
+and the measurement loop bench.py uses. Everything on the device goes through the C ABI."""
+import ctypes as C
+import json
+import os
+
+import numpy as np
+import torch
+
+from . import capi
+
+MEASURED_PEAKS = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+
+
+class Evaluator:
+    """One structure, one model, one GPU: compute(coords) -> (etot[1], force[1,N,3], virial[1,9]).
+    Mirrors what the reference's calculators do per call (neighbour list, then predict_efv:
+    ai2pot/models/potential_utils.py:217-268), with every step on the device."""
+
+    def __init__(self, model, cell, types, rcut, umax, dtype):
+        self.kind = model["kind"]
+        self.dtype = dtype
+        self.cell = np.asarray(cell)
+        self.rcut, self.umax = float(rcut), int(umax)
+        n = len(types)
+        self.n = n
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.model = capi.to_device({k: v for k, v in model.items() if k != "tables"}, dev, dtype)
+        self.prog = capi.MtpProgram(model["tables"]) if self.kind == "mtp" else None
+        self.builder = capi.NeighborBuilder()
+        self.nb_static = dict(binum=torch.tensor([n], dtype=torch.int32, device=dev),
+                              bilist=torch.arange(n, dtype=torch.int32, device=dev)[None].contiguous(),
+                              btypes=torch.from_numpy(np.ascontiguousarray(types, np.int32)).to(dev)[None].contiguous(),
+                              ntypes=int(model["ntypes"]), nghost=0)
+        self.out = (torch.empty(1, dtype=dtype, device=dev), torch.empty(1, n, 3, dtype=dtype, device=dev),
+                    torch.empty(1, 9, dtype=dtype, device=dev))
+        self.status = None
+
+    def build_list(self, coords):
+        nn, fn, rcs, status = self.builder.build(self.cell, coords, self.rcut, self.umax)
+        self.status = status
+        return dict(self.nb_static, bnumneigh=nn[None], bfirstneigh=fn[None], brcs=rcs[None])
+
+    def evaluate(self, nb):
+        if self.kind == "mtp":
+            return capi.mtp_efv(self.prog, self.model, nb, out=self.out)
+        return capi.nep_efv(self.model, nb, out=self.out)
+
+    def compute(self, coords):
+        return self.evaluate(self.build_list(coords))
+
+    # kernels of this library launched by one compute() (memsets not counted)
+    def launches_per_step(self):
+        return 8 + 2
+
+
+def fma_peak_tflops(is_f64, sms):
+    """Measured FMA-pipe throughput of this GPU (microbenchmark, best of 5)."""
+    blocks, iters = sms * 16, 4096
+    out = torch.empty(blocks * 256, dtype=torch.float64 if is_f64 else torch.float32, device="cuda")
+    best = 0.0
+    for _ in range(6):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        capi._check(capi.lib().ai2b_fma_chain(C.c_int(1 if is_f64 else 0), C.c_int(blocks), C.c_int(iters),
+                                              capi._ptr(out), capi._stream()))
+        e1.record()
+        torch.cuda.synchronize()
+        best = max(best, blocks * 256 * 8 * iters * 2 / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+    return best
+
+
+def _timed(fn, steps, warmup, flush, barrier=None):
+    """Sum of per-step device times (CUDA events on the current stream), L2 flushed between steps."""
+    for _ in range(warmup):
+        flush.zero_()
+        fn()
+    torch.cuda.synchronize()
+    if barrier is not None:
+        barrier()
+        torch.cuda.synchronize()
+    evs = []
+    for _ in range(steps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        evs.append((e0, e1))
+    torch.cuda.synchronize()
+    if barrier is not None:
+        barrier()
+    return sum(a.elapsed_time(b) for a, b in evs) * 1e-3
+
+
+def run_benchmark(w, steps, warmup, dist, sampler):
+    from bench import flops_mtp, flops_nep   # formulas live beside the JSON contract
+    dtype = torch.float64 if w["dtype"] == "f64" else torch.float32
+    ev = Evaluator(w["model"], w["cell"], w["types"], w["rcut"], w["umax"], dtype)
+    n = ev.n
+    host_coords = torch.from_numpy(np.ascontiguousarray(w["coords"])).to(dtype).pin_memory()
+    coords = host_coords.cuda()
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    barrier = (lambda: dist.barrier()) if dist is not None else None
+    props = torch.cuda.get_device_properties(torch.cuda.current_device())
+
+    # device-resident throughput: positions already in HBM
+    nb = ev.build_list(coords)
+    ev.evaluate(nb)
+    torch.cuda.synchronize()
+    st = ev.status.cpu().numpy()
+    if st[1]:
+        raise RuntimeError(f"umax {ev.umax} too small (max {st[0]})")
+    mean_nn = float(nb["bnumneigh"].float().mean())
+    sampler.start()
+    t_dev = _timed(lambda: ev.compute(coords), steps, warmup, flush, barrier)
+    clocks = sampler.stop()
+
+    # end to end: host positions in, host E/F/V out, every step
+    h_e = torch.empty(1, dtype=dtype).pin_memory()
+    h_f = torch.empty(1, n, 3, dtype=dtype).pin_memory()
+    h_v = torch.empty(1, 9, dtype=dtype).pin_memory()
+    dcoords = torch.empty_like(coords)
+
+    def e2e_step():
+        dcoords.copy_(host_coords, non_blocking=True)
+        e, f, v = ev.compute(dcoords)
+        h_e.copy_(e, non_blocking=True); h_f.copy_(f, non_blocking=True); h_v.copy_(v, non_blocking=True)
+    t_e2e = _timed(e2e_step, steps, warmup, flush, barrier)
+    h2d = host_coords.numel() * host_coords.element_size()
+    d2h = sum(t.numel() * t.element_size() for t in (h_e, h_f, h_v))
+
+    # the two parts separately (same timing rules), for the roofline of the dominant kernel
+    k = max(3, min(steps, 10))
+    t_nb = _timed(lambda: ev.build_list(coords), k, 3, flush) / k
+    t_ev = _timed(lambda: ev.evaluate(nb), k, 3, flush) / k
+
+    m = w["model"]
+    if m["kind"] == "mtp":
+        tb = m["tables"]
+        kmax = int(tb["alpha_index_basic"][:, 1:].sum(1).max())
+        fl = flops_mtp(mean_nn, len(tb["alpha_index_basic"]), len(tb["alpha_index_times"]), len(tb["alpha_moment_mapping"]),
+                       tb["nmus"], m["chebyshev_size"], kmax)
+        bound = "fp64"
+    else:
+        nn_a = float((torch.linalg.norm(nb["brcs"][0], dim=-1) <= m["rmax_angular"]).logical_and(
+            torch.arange(ev.umax, device="cuda")[None] < nb["bnumneigh"][0][:, None]).sum(1).float().mean())
+        fl = flops_nep(mean_nn, nn_a, m["chebyshev_size"], m["n_radial"], m["n_angular"], m["num_neurons"],
+                       m["n_radial"] + m["n_angular"] * m["l_max"])
+        bound = "fp32"
+    is64 = dtype == torch.float64
+    peak_meas = fma_peak_tflops(is64, props.multi_processor_count)
+    sm_max = clocks.get("sm_max_mhz") or 1965.0
+    peak_nom = props.multi_processor_count * (64 if is64 else 128) * 2 * sm_max * 1e6 / 1e12
+    achieved = n * fl / t_ev / 1e12
+    sz = 8 if is64 else 4
+    nb_bytes = n * (3 * sz + 4 + ev.umax * (4 + 3 * sz) + 4)
+    hbm = None
+    if os.path.exists(MEASURED_PEAKS):
+        hbm = json.load(open(MEASURED_PEAKS)).get("hbm_gbs")
+    roofline = {"kernel": "mtp_atom_kernel" if m["kind"] == "mtp" else "nep_atom_kernel", "bound": bound,
+                "achieved": achieved, "peak": peak_meas, "unit": "TFLOP/s", "frac": achieved / peak_meas,
+                "peak_source": "FMA-chain microbenchmark in this run (of measured)", "peak_nominal": peak_nom,
+                "frac_of_nominal": achieved / peak_nom, "flops_per_atom": fl, "mean_neighbours": mean_nn,
+                "traffic": None, "kernel_ms": 1e3 * t_ev,
+                "nblist": {"bound": "hbm", "achieved": nb_bytes / t_nb / 1e9, "peak": hbm or 6650.0, "unit": "GB/s",
+                           "frac": nb_bytes / t_nb / 1e9 / (hbm or 6650.0),
+                           "peak_source": "MEASURED_PEAKS.json (of measured)" if hbm else "6.65 TB/s (of fallback)",
+                           "bytes_per_atom": nb_bytes / n, "ms": 1e3 * t_nb}}
+    return dict(t_dev=t_dev, t_e2e=t_e2e, clocks=clocks, launches=ev.launches_per_step() * steps, h2d=h2d, d2h=d2h,
+                e2e_path="pinned host positions -> H2D -> ai2b_nblist_build -> ai2b_*_efv -> D2H E,F,V (C ABI via ctypes)",
+                roofline=roofline, parts_ms={"nblist": 1e3 * t_nb, "efv": 1e3 * t_ev})

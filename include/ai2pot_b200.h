@@ -97,6 +97,43 @@ AI2B_DECL_MTP_EFV(f32, float)
 AI2B_DECL_MTP_DESC(f64, double)
 AI2B_DECL_MTP_DESC(f32, float)
 
+/* ------------------------------------------------------------------------------------------
+ * Neighbour list
+ * ---------------------------------------------------------------------------------------- */
+
+/* Builds the padded neighbour tensors of ONE structure from positions. Replaces the CPU-only
+ * chain Structure -> NeighborList -> find_info4mlff that the Python module calls
+ * (source/nblist/bind/nblist_bind.cc:35-207; source/nblist/include/neighborList.h:178-189,
+ * 532-578; binLinkedList.h:983-1031). Same membership rule and the same rcs bits as the
+ * reference; the order inside a row is unspecified.
+ *   h_cell[9]   HOST, rows = lattice vectors          h_pbc[3]  HOST, periodic flags
+ *   d_coords    [natoms,3] Cartesian (is_cart != 0) or fractional
+ *   outputs     d_numneigh[natoms], d_firstneigh[natoms,umax] (pad -1), d_rcs[natoms,umax,3] (pad 0)
+ *   d_status    int[2]: {largest neighbour count found, 1 if a row exceeded umax}. A row that
+ *               would exceed umax is truncated to umax entries (the reference overruns its
+ *               buffers there, neighborList.h:550); the caller reads d_status to detect it.
+ * Workspace: ai2b_nblist_workspace_bytes(natoms, is_f64). */
+size_t ai2b_nblist_workspace_bytes(int natoms, int is_f64);
+int ai2b_nblist_build_f64(int natoms, const double *h_cell, const double *d_coords, int is_cart,
+                          double rcut, const int *h_pbc, int umax, int *d_numneigh,
+                          int *d_firstneigh, double *d_rcs, int *d_status, void *d_workspace,
+                          size_t workspace_bytes, void *stream);
+int ai2b_nblist_build_f32(int natoms, const float *h_cell, const float *d_coords, int is_cart,
+                          double rcut, const int *h_pbc, int umax, int *d_numneigh,
+                          int *d_firstneigh, float *d_rcs, int *d_status, void *d_workspace,
+                          size_t workspace_bytes, void *stream);
+
+/* Orders every row by distance, in place (the reference's sort=true argument,
+ * source/nblist/include/neighborList.h:290-335). Ties keep their build order. */
+int ai2b_nblist_sort_rows_f64(int natoms, int umax, const int *d_numneigh, int *d_firstneigh,
+                              double *d_rcs, void *stream);
+int ai2b_nblist_sort_rows_f32(int natoms, int umax, const int *d_numneigh, int *d_firstneigh,
+                              float *d_rcs, void *stream);
+
+/* FMA-pipe microbenchmark used for the roofline denominator (no counterpart in the reference):
+ * blocks x 256 threads, 8 independent chains of `iters` fused multiply-adds each. */
+int ai2b_fma_chain(int is_f64, int blocks, int iters, void *d_out, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

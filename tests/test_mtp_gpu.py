@@ -108,7 +108,11 @@ def test_errors():
     bad["alpha_index_basic"][3, 1] = 12    # degree beyond the supported maximum
     with pytest.raises(capi.Ai2bError):
         capi.MtpProgram(bad)
+    # host tensors are refused: there is no CPU path behind the C ABI
     w = util.small_mtp_case(6, 3)
+    from oracle import refapi
+    nb = util.nblist_batch(refapi.Checker("oracle"), w)
+    nb_host = {k: (torch.from_numpy(v) if isinstance(v, np.ndarray) else v) for k, v in nb.items()}
+    md = capi.to_device({k: v for k, v in w["model"].items() if k != "tables"})
     with pytest.raises(capi.Ai2bError):
-        capi.mtp_efv(capi.MtpProgram(w["model"]["tables"]), w["model"], {"brcs": torch.zeros(1, 1, 1, 3, dtype=torch.float64),
-                     "bilist": torch.zeros(1, 1), "bfirstneigh": torch.zeros(1, 1, 1)})
+        capi.mtp_efv(capi.MtpProgram(w["model"]["tables"]), md, nb_host)

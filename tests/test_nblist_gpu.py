@@ -1,0 +1,117 @@
+"""Neighbour lists from the CUDA builder: bit-exact with the CPU checkers after canonical sort."""
+import os
+import numpy as np
+import pytest
+import torch
+
+import util
+from ai2pot_b200 import capi, synth
+from ai2pot_b200.fromcc import nblist as nblist_mod
+
+pytestmark = pytest.mark.gpu
+G = np.load(os.path.join(util.GOLDEN, "golden_small.npz"))
+
+
+def _chk(checkers):
+    return checkers.get("ref") or checkers["oracle"]
+
+
+def _gpu(cell, types, coords, rcut, umax, is_cart=True, pbc=(1, 1, 1), sort=False):
+    out = nblist_mod.find_info4mlff(np.ascontiguousarray(cell, dtype=coords.dtype), np.asarray(types), coords, rcut, umax,
+                                    is_cart, [bool(p) for p in pbc], sort)
+    inum, ilist, nn, fn, rc, ty, ng = out
+    assert inum == len(coords) and ng == 0 and np.array_equal(ilist, np.arange(inum)) and ty.dtype == np.int32
+    return nn, fn, rc
+
+
+def test_mos2_fixture():
+    z = np.load(os.path.join(util.GOLDEN, "mos2_fixture.npz"))
+    nn, fn, rc = _gpu(z["cell"].astype(np.float32), z["z"], z["frac"].astype(np.float32), 3.2, 16, is_cart=False, pbc=(1, 1, 0))
+    assert nn.max() == 12
+    util.assert_nblist_equal((nn, fn, rc), (G["mos2_numneigh"], G["mos2_first"], G["mos2_rcs"]))
+
+
+def test_g0_golden():
+    w = synth.g0(util.tables(10))
+    nn, fn, rc = _gpu(w["cell"], w["types"].astype(np.int64), w["coords"], w["rcut"], w["umax"])
+    assert np.array_equal(nn, G["g0_numneigh"])
+    fs, rs = util.canonical_nblist(nn, fn, rc)
+    assert np.array_equal(fs, G["g0_first_sorted"]) and np.array_equal(rs.view(np.uint64), G["g0_rcs_sorted"].view(np.uint64))
+    # padding convention
+    pad = np.arange(fn.shape[1])[None] >= nn[:, None]
+    assert np.all(fn[pad] == -1) and np.all(rc[pad] == 0)
+
+
+@pytest.mark.parametrize("dt", [np.float64, np.float32])
+def test_triclinic_unwrapped_open_axes(checkers, dt):
+    chk = _chk(checkers)
+    rng = np.random.default_rng(5)
+    cell = np.array([[7.0, 0.3, 0.1], [1.5, 6.5, 0.2], [-0.7, 0.9, 8.0]]).astype(dt)
+    frac = rng.random((60, 3))
+    pos = (frac @ cell.astype(np.float64) + rng.normal(0, 3.0, (60, 3))).astype(dt)
+    types = rng.integers(0, 2, 60).astype(np.int32)
+    for pbc in ((1, 1, 1), (1, 0, 1), (0, 0, 0), (0, 1, 0)):
+        a = _gpu(cell, types, pos, 5.5, 160, pbc=pbc)
+        b = chk.nblist(cell, types, pos, 5.5, 160, pbc=pbc)
+        util.assert_nblist_equal(a, b[:3])
+    a = _gpu(cell, types, frac.astype(dt), 5.5, 160, is_cart=False, sort=True)
+    b = chk.nblist(cell, types, frac.astype(dt), 5.5, 160, is_cart=False, sort=True)
+    util.assert_nblist_equal(a, b[:3])
+    # sorted rows: distances ascending
+    d = np.sqrt((a[2].astype(np.float64) ** 2).sum(-1))
+    for i in range(len(a[0])):
+        assert np.all(np.diff(d[i, :a[0][i]]) >= 0)
+
+
+def test_tiny_cell_many_images(checkers):
+    chk = _chk(checkers)
+    rng = np.random.default_rng(9)
+    cell = np.eye(3) * 4.0
+    pos = rng.random((3, 3)) * 4.0
+    a = _gpu(cell, np.array([0, 1, 0]), pos, 6.0, 256)
+    b = chk.nblist(cell, [0, 1, 0], pos, 6.0, 256)
+    util.assert_nblist_equal(a, b[:3])
+    # one atom alone sees only its own images
+    a = _gpu(cell, np.array([0]), pos[:1], 6.0, 64)
+    b = chk.nblist(cell, [0], pos[:1], 6.0, 64)
+    util.assert_nblist_equal(a, b[:3])
+
+
+@pytest.mark.parametrize("dt", [np.float64, np.float32])
+def test_g1_full_size_vs_checker(checkers, dt):
+    """13,824 atoms, rcut 6 (the benchmark structure), both float types."""
+    w = synth.g1(util.tables(16))
+    chk = _chk(checkers)
+    pos = w["coords"].astype(dt); cell = w["cell"].astype(dt)
+    a = _gpu(cell, w["types"], pos, 6.0, 64)
+    b = chk.nblist(cell, w["types"], pos, 6.0, 64)
+    util.assert_nblist_equal(a, b[:3])
+
+
+def test_g4_slice_float(checkers):
+    w = synth.g4(ncell=8)
+    chk = _chk(checkers)
+    a = _gpu(w["cell"], w["types"], w["coords"], 6.0, 32)
+    b = chk.nblist(w["cell"], w["types"], w["coords"], 6.0, 32)
+    util.assert_nblist_equal(a, b[:3])
+
+
+def test_overflow_and_errors():
+    w = synth.g0(util.tables(10))
+    with pytest.raises(ValueError):
+        _gpu(w["cell"], w["types"], w["coords"], 5.0, 8)
+    with pytest.raises(TypeError):
+        nblist_mod.find_info4mlff(w["cell"].tolist(), w["types"], w["coords"], 5.0, 64, True, [True] * 3, False)
+    with pytest.raises(TypeError):
+        nblist_mod.find_info4mlff(w["cell"], w["types"], w["coords"].astype(np.float32), 5.0, 64, True, [True] * 3, False)
+    # device-level status of a truncated build
+    nb = capi.NeighborBuilder()
+    nn, fn, rc, st = nb.build(w["cell"], torch.from_numpy(w["coords"]).cuda(), 5.0, 8)
+    st = st.cpu().numpy()
+    assert st[1] == 1 and st[0] == G["g0_numneigh"].max() and nn.max().item() == 8
+
+
+def test_empty_structure():
+    nb = capi.NeighborBuilder()
+    nn, fn, rc, st = nb.build(np.eye(3) * 5, torch.zeros(0, 3, dtype=torch.float64, device="cuda"), 3.0, 8)
+    assert nn.numel() == 0
