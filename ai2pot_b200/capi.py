@@ -29,8 +29,8 @@ def lib():
         _lib = C.CDLL(LIB_PATH)
         _lib.ai2b_last_error_string.restype = C.c_char_p
         _lib.ai2b_mtp_workspace_bytes.restype = C.c_size_t
-        if hasattr(_lib, "ai2b_nblist_workspace_bytes"):
-            _lib.ai2b_nblist_workspace_bytes.restype = C.c_size_t
+        _lib.ai2b_nblist_workspace_bytes.restype = C.c_size_t
+        _lib.ai2b_nep_workspace_bytes.restype = C.c_size_t
     return _lib
 
 
@@ -201,3 +201,53 @@ def sort_rows_by_distance(numneigh, firstneigh, rcs):
     _check(getattr(lib(), "ai2b_nblist_sort_rows_" + suf)(C.c_int(n), C.c_int(umax), _ptr(numneigh), _ptr(firstneigh),
                                                           _ptr(rcs), _stream()))
     return numneigh, firstneigh, rcs
+
+
+_nep_ws = {}
+
+
+def _nep_workspace(model, B, dtype, device):
+    need = lib().ai2b_nep_workspace_bytes(C.c_int(B), C.c_int(int(model["ntypes"])), C.c_int(int(model["n_radial"])),
+                                          C.c_int(int(model["n_angular"])), C.c_int(int(model["chebyshev_size"])),
+                                          C.c_int(1 if dtype == torch.float64 else 0))
+    ws = _nep_ws.get(device)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(need, dtype=torch.uint8, device=device)
+        _nep_ws[device] = ws
+    return ws
+
+
+def nep_efv(model, nb, virial=True, out=None):
+    """NEP energy, forces (and virial) of a batch; `model` / `nb` hold device tensors."""
+    rcs = nb["brcs"]
+    suf, cf = _suf(rcs.dtype)
+    B, npad, umax, nbargs = _nb_args(nb)
+    ng = int(nb.get("nghost", 0))
+    if out is None:
+        e = torch.empty(B, dtype=rcs.dtype, device=rcs.device)
+        f = torch.empty(B, npad + ng, 3, dtype=rcs.dtype, device=rcs.device)
+        v = torch.empty(B, 9, dtype=rcs.dtype, device=rcs.device) if virial else None
+    else:
+        e, f, v = out
+    ws = _nep_workspace(model, B, rcs.dtype, rcs.device)
+    _check(getattr(lib(), "ai2b_nep_efv_" + suf)(
+        _ptr(e), _ptr(f), _ptr(v), C.c_int(int(model["chebyshev_size"])), C.c_int(int(model["n_radial"])),
+        C.c_int(int(model["n_angular"])), C.c_int(int(model["l_max"])), C.c_int(int(model["num_neurons"])),
+        _ptr(model["coeffs"]), _ptr(model["w0"]), _ptr(model["b0"]), _ptr(model["w1"]), _ptr(model["type_bias"]),
+        *nbargs, cf(model["rmax_radial"]), cf(model["rmax_angular"]), _ptr(model["q_scaler"]), _ptr(ws),
+        C.c_size_t(ws.numel()), _stream()))
+    return (e, f, v) if virial else (e, f)
+
+
+def nep_descriptors(model, nb):
+    rcs = nb["brcs"]
+    suf, cf = _suf(rcs.dtype)
+    B, npad, umax, nbargs = _nb_args(nb)
+    nd = int(model["n_radial"]) + int(model["n_angular"]) * int(model["l_max"])
+    d = torch.empty(B, npad, nd, dtype=rcs.dtype, device=rcs.device)
+    ws = _nep_workspace(model, B, rcs.dtype, rcs.device)
+    _check(getattr(lib(), "ai2b_nep_descriptors_" + suf)(
+        _ptr(d), C.c_int(int(model["chebyshev_size"])), C.c_int(int(model["n_radial"])), C.c_int(int(model["n_angular"])),
+        C.c_int(int(model["l_max"])), _ptr(model["coeffs"]), *nbargs, cf(model["rmax_radial"]), cf(model["rmax_angular"]),
+        _ptr(ws), C.c_size_t(ws.numel()), _stream()))
+    return d

@@ -134,6 +134,40 @@ int ai2b_nblist_sort_rows_f32(int natoms, int umax, const int *d_numneigh, int *
  * blocks x 256 threads, 8 independent chains of `iters` fused multiply-adds each. */
 int ai2b_fma_chain(int is_f64, int blocks, int iters, void *d_out, void *stream);
 
+/* ------------------------------------------------------------------------------------------
+ * NEP (3-body terms, l_max <= 4, chebyshev_size <= 16)
+ * ---------------------------------------------------------------------------------------- */
+
+size_t ai2b_nep_workspace_bytes(int batch_size, int ntypes, int n_radial, int n_angular,
+                                int chebyshev_size, int is_f64);
+
+/* Energy + force + virial. Replaces nep::find_efv_torch_launcher<T>
+ * (source/descriptor/nep/gpu/include/nep_torch_launcher.cuh:34-103) and the CPU launcher
+ * (source/descriptor/nep/include/nep_cpu_launcher.h:186-257). Parameter layouts as in the
+ * reference: coeffs[ntypes,ntypes,n_radial+n_angular,chebyshev_size], w0[ntypes,neurons,nd],
+ * b0[ntypes,neurons], w1[ntypes,neurons], nd = n_radial + n_angular*l_max. Outputs are
+ * overwritten. d_bvirial may be NULL: energy + force only (find_ef, nep_cpu_launcher.h:116-184). */
+#define AI2B_DECL_NEP(SUF, T)                                                                    \
+    int ai2b_nep_efv_##SUF(T *d_betot, T *d_bforce, T *d_bvirial, int chebyshev_size,            \
+                           int n_radial, int n_angular, int l_max, int num_neurons,              \
+                           const T *d_coeffs, const T *d_w0, const T *d_b0, const T *d_w1,       \
+                           const T *d_type_bias, int batch_size, int natoms_pad,                 \
+                           const int *d_binum, const int *d_bilist, const int *d_bnumneigh,      \
+                           const int *d_bfirstneigh, const T *d_brcs, const int *d_btypes,       \
+                           int ntypes, int umax, int nghost, T rmax_radial, T rmax_angular,      \
+                           const T *d_q_scaler, void *d_workspace, size_t workspace_bytes,       \
+                           void *stream);                                                        \
+    /* descriptors [B,Np,nd]: find_descriptors launcher, nep_cpu_launcher.h:259-317 */           \
+    int ai2b_nep_descriptors_##SUF(T *d_bdescriptors, int chebyshev_size, int n_radial,          \
+                                   int n_angular, int l_max, const T *d_coeffs, int batch_size,  \
+                                   int natoms_pad, const int *d_binum, const int *d_bilist,      \
+                                   const int *d_bnumneigh, const int *d_bfirstneigh,             \
+                                   const T *d_brcs, const int *d_btypes, int ntypes, int umax,   \
+                                   int nghost, T rmax_radial, T rmax_angular, void *d_workspace, \
+                                   size_t workspace_bytes, void *stream);
+AI2B_DECL_NEP(f64, double)
+AI2B_DECL_NEP(f32, float)
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,92 @@
+"""Parity of the CUDA NEP path (through the C ABI) with the CPU checkers.
+Tolerance: fp32 rel 1e-5, fp64 rel 1e-10 of the tensor's max magnitude."""
+import os
+import numpy as np
+import pytest
+import torch
+
+import util
+from ai2pot_b200 import capi, synth
+
+pytestmark = pytest.mark.gpu
+G = np.load(os.path.join(util.GOLDEN, "golden_small.npz"))
+TOL = {np.float64: 1e-10, np.float32: 1e-5}
+
+
+def _chk(checkers):
+    return checkers.get("ref") or checkers["oracle"]
+
+
+def _run(model, nb, virial=True):
+    dt = torch.float64 if nb["brcs"].dtype == np.float64 else torch.float32
+    md = capi.to_device(model, float_dtype=dt)
+    nbd = capi.to_device(nb)
+    out = capi.nep_efv(md, nbd, virial=virial)
+    torch.cuda.synchronize()
+    return [o.cpu().numpy() for o in out], md, nbd
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+def test_small_golden(checkers, dt):
+    w = util.small_nep_case(5, dt)
+    nb = util.nblist_batch(_chk(checkers), w)
+    (e, f, v), md, nbd = _run(w["model"], nb)
+    tag = f"nep_{np.dtype(dt).name}"
+    for a, k in ((e, "_e"), (f, "_f"), (v, "_v")):
+        assert util.relerr(a, G[tag + k]) < TOL[dt], k
+    e2, f2 = capi.nep_efv(md, nbd, virial=False)
+    assert util.relerr(f2.cpu().numpy(), G[tag + "_f"]) < TOL[dt]
+    d = capi.nep_descriptors(md, nbd).cpu().numpy()
+    assert util.relerr(d[0, :8], G[tag + "_desc_head"]) < TOL[dt]
+    assert util.relerr(d, _chk(checkers).nep_descriptors(w["model"], nb)) < TOL[dt]
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+def test_g2_full_size_vs_checker(checkers, dt):
+    """The benchmark structure (13,824 atoms, rc 6/4) against the CPU checker."""
+    w = synth.g2()
+    chk = _chk(checkers)
+    w["coords"] = w["coords"].astype(dt); w["cell"] = w["cell"].astype(dt)
+    model = {k: (v.astype(dt) if isinstance(v, np.ndarray) else v) for k, v in w["model"].items()}
+    nn, fn, rc, ty, mx = chk.nblist(w["cell"], w["types"], w["coords"], w["rcut"], w["umax"])
+    nb = synth.batch_from_nblist(nn, fn, rc, ty, 3)
+    (e, f, v), *_ = _run(model, nb)
+    er, fr, vr = chk.nep_efv(model, nb)
+    tol = TOL[dt] * (3 if dt == np.float32 else 1)   # the fp32 reference itself sums 13,824 site energies in fp32
+    assert util.relerr(e, er) < tol and util.relerr(f, fr) < tol and util.relerr(v, vr) < tol
+
+
+@pytest.mark.parametrize("cfg", [dict(n_radial=6, n_angular=3, l_max=2, chebyshev_size=5, num_neurons=17),
+                                 dict(n_radial=3, n_angular=5, l_max=3, chebyshev_size=12, num_neurons=40),
+                                 dict(n_radial=5, n_angular=2, l_max=0, chebyshev_size=8, num_neurons=9),
+                                 dict(n_radial=2, n_angular=2, l_max=1, chebyshev_size=3, num_neurons=4)])
+def test_other_shapes_fp64(checkers, cfg):
+    chk = _chk(checkers)
+    rng = np.random.default_rng(17)
+    cell, pos = synth.cubic_lattice(4, 2.6, 0.12, rng)
+    types = rng.integers(0, 2, len(pos)).astype(np.int32)
+    model = synth.nep_model(2, rng, np.float64, rmax_radial=5.0, rmax_angular=3.5, **cfg)
+    model["q_scaler"] = rng.uniform(0.5, 2.0, len(model["q_scaler"]))
+    model["type_bias"] = rng.normal(0, 0.1, 2)
+    nn, fn, rc, ty, mx = chk.nblist(cell, types, pos, 5.0, 96)
+    nb = synth.batch_from_nblist(nn, fn, rc, ty, 2)
+    (e, f, v), md, nbd = _run(model, nb)
+    er, fr, vr = chk.nep_efv(model, nb)
+    assert util.relerr(e, er) < 1e-10 and util.relerr(f, fr) < 1e-10 and util.relerr(v, vr) < 1e-10
+    assert util.relerr(capi.nep_descriptors(md, nbd).cpu().numpy(), chk.nep_descriptors(model, nb)) < 1e-10
+
+
+def test_ragged_batch(checkers):
+    chk = _chk(checkers)
+    rng = np.random.default_rng(4)
+    lists = []
+    for n, a in ((3, 2.8), (4, 2.4), (2, 3.0)):
+        cell, pos = synth.cubic_lattice(n, a, 0.1, rng, np.float32)
+        ty = rng.integers(0, 3, len(pos)).astype(np.int32)
+        nn, fn, rc, _, mx = chk.nblist(cell, ty, pos, 6.0, 160)
+        lists.append((nn, fn, rc, ty))
+    nb = synth.pad_batch(lists, 3, 160)
+    model = synth.nep_model(3, rng)
+    (e, f, v), *_ = _run(model, nb)
+    er, fr, vr = chk.nep_efv(model, nb)
+    assert util.relerr(e, er) < 1e-5 and util.relerr(f, fr) < 1e-5 and util.relerr(v, vr) < 1e-5
