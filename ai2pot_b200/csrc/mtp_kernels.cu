@@ -20,6 +20,7 @@ template <typename T>
 struct MtpArgs {
     T *etot, *force, *virial, *desc;
     const T *coeffs, *lin, *bias, *qs;
+    const T *coeffs_pad;   // [ntypes*ntypes][nmus][CSP] zero-padded copy of coeffs (workspace)
     const int *binum, *bilist, *numneigh, *firstneigh, *types;
     const T *rcs;
     const int *prefix;   // [B+1] exclusive prefix sum of binum (workspace)
@@ -71,9 +72,19 @@ __host__ __device__ inline int mtp_warp_elems(const MtpProgramDev &P)
     return 4 * r4(P.ndense) + 2 * r4(P.nm) + r4(P.ndense) + 2 * MTP_MAX_MU * 32;
 }
 
-template <typename T, int MODE>
-__global__ void __launch_bounds__(MTP_WARPS * 32) mtp_atom_kernel(const MtpProgramDev P, const MtpArgs<T> A)
+template <typename T>
+__global__ void mtp_pad_coeffs_kernel(const T *__restrict__ c, T *__restrict__ out, int rows, int cs, int csp)
 {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * csp) return;
+    int r = i / csp, k = i % csp;
+    out[i] = k < cs ? c[r * cs + k] : T(0);
+}
+
+template <typename T, int MODE, int KD, int CSP>
+__global__ void __launch_bounds__(MTP_WARPS * 32, 3) mtp_atom_kernel(const MtpProgramDev P, const MtpArgs<T> A)
+{
+    using V2 = typename Vec2<T>::type;
     extern __shared__ __align__(32) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     auto r4 = [](int n) { return (n + 3) & ~3; };
@@ -154,23 +165,28 @@ __global__ void __launch_bounds__(MTP_WARPS * 32) mtp_atom_kernel(const MtpProgr
             int tj = 0;
             if (act) { tj = types[nj]; rinv = T(1) / r; } else { rinv = T(0); }
             ux = x * rinv; uy = y * rinv; uz = z * rinv;
-            T f[MTP_MAX_MU], fd[MTP_MAX_MU];
-            mtp_radial<T>(act ? r : A.rmax, A.rmax, A.rmin, A.cs, P.nmus, A.scaling,
-                          A.coeffs + (size_t)(ti * A.ntypes + tj) * P.nmus * A.cs, f, fd);
+            T q[CSP], dq[CSP];
+            mtp_radial_basis<T, CSP>(act ? r : A.rmax, A.rmax, A.rmin, A.scaling, q, dq);
+            const T *crow = A.coeffs_pad + (size_t)(ti * A.ntypes + tj) * P.nmus * CSP;
+            for (int m = 0; m < P.nmus; m++) {
+                T f = T(0), fd = T(0);
 #pragma unroll
-            for (int m = 0; m < MTP_MAX_MU; m++)
-                if (m < P.nmus) {
-                    fr[m * 32 + lane] = act ? f[m] : T(0);
-                    fdv[m * 32 + lane] = act ? fd[m] : T(0);
+                for (int k = 0; k < CSP; k += 2) {
+                    const V2 c2 = *reinterpret_cast<const V2 *>(crow + m * CSP + k);
+                    f = fma(c2.x, q[k], f); fd = fma(c2.x, dq[k], fd);
+                    f = fma(c2.y, q[k + 1], f); fd = fma(c2.y, dq[k + 1], fd);
                 }
+                fr[m * 32 + lane] = act ? f : T(0);
+                fdv[m * 32 + lane] = act ? fd : T(0);
+            }
         };
 
         // ---- forward: dense basic-moment sums ------------------------------------------------
         for (int j0 = 0; j0 < nn || j0 == 0; j0 += 32) {
             pair_setup(j0);
-            Powers<T> pw;
+            Powers<T, KD> pw;
             pw.set(ux, uy, uz);
-            for (int m = 0; m < P.nmus; m++) fwd_mu<T>(P.kmu[m], fr[m * 32 + lane], pw, Md + P.doff[m], lane);
+            for (int m = 0; m < P.nmus; m++) fwd_mu<T, KD>(P.kmu[m], fr[m * 32 + lane], pw, Md + P.doff[m], lane);
         }
         __syncwarp();
         for (int i = lane; i < P.nb; i += 32) M[i] = Md[P.basic_dense[i]];
@@ -180,12 +196,21 @@ __global__ void __launch_bounds__(MTP_WARPS * 32) mtp_atom_kernel(const MtpProgr
         for (int lev = 0; lev < P.nlev; lev++) {
             for (int d = P.fwd_lev_off[lev] + lane; d < P.fwd_lev_off[lev + 1]; d += 32) {
                 const int4 ds = P.fwd_dst[d];
-                T acc = T(0);
-                for (int r = ds.y; r < ds.z; r++) {
-                    const int2 row = P.fwd_rows[r];
-                    acc = fma(T(row.y) * M[row.x & 0xffff], M[row.x >> 16], acc);
+                const int *ab = P.fwd_ab;
+                const T *mult = fwd_mult<T>(P);
+                T acc0 = T(0), acc1 = T(0);
+                int r = ds.y;
+                for (; r + 1 < ds.z; r += 2) {
+                    const int x0 = ab[r], x1 = ab[r + 1];
+                    const T m0 = mult[r], m1 = mult[r + 1];
+                    acc0 = fma(m0 * M[x0 & 0xffff], M[x0 >> 16], acc0);
+                    acc1 = fma(m1 * M[x1 & 0xffff], M[x1 >> 16], acc1);
                 }
-                M[ds.x] += acc;
+                if (r < ds.z) {
+                    const int x0 = ab[r];
+                    acc0 = fma(mult[r] * M[x0 & 0xffff], M[x0 >> 16], acc0);
+                }
+                M[ds.x] += acc0 + acc1;
             }
             __syncwarp();
         }
@@ -214,12 +239,21 @@ __global__ void __launch_bounds__(MTP_WARPS * 32) mtp_atom_kernel(const MtpProgr
         for (int k = 0; k < P.nlev; k++) {
             for (int d = P.rev_lev_off[k] + lane; d < P.rev_lev_off[k + 1]; d += 32) {
                 const int4 ms = P.rev_mom[d];
-                T acc = T(0);
-                for (int e = ms.y; e < ms.z; e++) {
-                    const int2 en = P.rev_ents[e];
-                    acc = fma(T(en.y) * Eb[en.x >> 16], M[en.x & 0xffff], acc);
+                const int *od = P.rev_od;
+                const T *mult = rev_mult<T>(P);
+                T acc0 = T(0), acc1 = T(0);
+                int e = ms.y;
+                for (; e + 1 < ms.z; e += 2) {
+                    const int x0 = od[e], x1 = od[e + 1];
+                    const T m0 = mult[e], m1 = mult[e + 1];
+                    acc0 = fma(m0 * Eb[x0 >> 16], M[x0 & 0xffff], acc0);
+                    acc1 = fma(m1 * Eb[x1 >> 16], M[x1 & 0xffff], acc1);
                 }
-                Eb[ms.x] += acc;
+                if (e < ms.z) {
+                    const int x0 = od[e];
+                    acc0 = fma(mult[e] * Eb[x0 >> 16], M[x0 & 0xffff], acc0);
+                }
+                Eb[ms.x] += acc0 + acc1;
             }
             __syncwarp();
         }
@@ -240,12 +274,12 @@ __global__ void __launch_bounds__(MTP_WARPS * 32) mtp_atom_kernel(const MtpProgr
         T fcx = T(0), fcy = T(0), fcz = T(0);
         for (int j0 = 0; j0 < nn; j0 += 32) {
             if (nn > 32) pair_setup(j0);
-            Powers<T> pw;
+            Powers<T, KD> pw;
             pw.set(ux, uy, uz);
             T gx = T(0), gy = T(0), gz = T(0);
             for (int m = 0; m < P.nmus; m++) {
                 T Pv = T(0), Gx = T(0), Gy = T(0), Gz = T(0);
-                eval_mu<T>(P.kmu[m], E4 + 4 * P.doff[m], pw, Pv, Gx, Gy, Gz);
+                eval_mu<T, KD>(P.kmu[m], E4 + 4 * P.doff[m], pw, Pv, Gx, Gy, Gz);
                 const T f = fr[m * 32 + lane], fd = fdv[m * 32 + lane];
                 const T ug = ux * Gx + uy * Gy + uz * Gz;
                 const T a = fd * Pv - f * rinv * ug, c = f * rinv;
@@ -291,31 +325,37 @@ static int sm_count()
     return g_sm_count;
 }
 
-template <typename T, int MODE>
-static int launch_mtp(const ai2b_mtp_program *prog, MtpArgs<T> A, void *ws, size_t ws_bytes, cudaStream_t st)
+static size_t mtp_ws_bytes(const MtpProgramDev &P, int B, int ntypes, size_t elem)
+{
+    size_t pre = (((size_t)(B > 0 ? B : 0) + 1) * sizeof(int) + 255) & ~size_t(255);
+    size_t co = ((size_t)ntypes * ntypes * P.nmus * 16 * elem + 255) & ~size_t(255);
+    return pre + co;
+}
+
+template <typename T, int MODE, int KD, int CSP>
+static int launch_mtp_v(const ai2b_mtp_program *prog, MtpArgs<T> A, void *ws, cudaStream_t st)
 {
     const MtpProgramDev &P = prog->dev;
-    AI2B_REQUIRE(A.cs >= 1 && A.cs <= 64, AI2B_ERR_INVALID, "chebyshev_size %d outside 1..64", A.cs);
-    AI2B_REQUIRE(A.B >= 0 && A.npad >= 0 && A.umax >= 0 && A.ntypes >= 1 && A.nghost >= 0, AI2B_ERR_INVALID, "negative size");
-    if (A.B == 0 || A.npad == 0) return AI2B_OK;
-    AI2B_REQUIRE(ws && ws_bytes >= ai2b_mtp_workspace_bytes(prog, A.B, A.npad), AI2B_ERR_WORKSPACE,
-                 "MTP workspace too small: %zu < %zu bytes", ws_bytes, ai2b_mtp_workspace_bytes(prog, A.B, A.npad));
     int *prefix = reinterpret_cast<int *>(ws);
+    T *cpad = reinterpret_cast<T *>(reinterpret_cast<unsigned char *>(ws) + ((((size_t)A.B + 1) * sizeof(int) + 255) & ~size_t(255)));
     A.prefix = prefix;
+    A.coeffs_pad = cpad;
     prefix_binum_kernel<<<1, 256, 0, st>>>(A.binum, A.B, prefix);
+    const int rows = A.ntypes * A.ntypes * P.nmus;
+    mtp_pad_coeffs_kernel<T><<<(rows * CSP + 255) / 256, 256, 0, st>>>(A.coeffs, cpad, rows, A.cs, CSP);
     AI2B_CUDA(cudaGetLastError());
 
     const size_t smem = sizeof(T) * (size_t)mtp_warp_elems(P) * MTP_WARPS;
     AI2B_REQUIRE(smem <= 227 * 1024, AI2B_ERR_UNSUPPORTED, "MTP tables need %zu bytes of shared memory per block", smem);
-    auto kern = mtp_atom_kernel<T, MODE>;
+    auto kern = mtp_atom_kernel<T, MODE, KD, CSP>;
     static size_t configured = 0;   // per instantiation
-    if (smem > configured) {
+    static int per_sm = 0;
+    if (smem > configured || per_sm == 0) {
         AI2B_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        AI2B_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, MTP_WARPS * 32, smem));
+        if (per_sm < 1) per_sm = 1;
         configured = smem;
     }
-    int per_sm = 0;
-    AI2B_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, MTP_WARPS * 32, smem));
-    if (per_sm < 1) per_sm = 1;
     const long slots = (long)A.B * A.npad;
     long blocks = (long)sm_count() * per_sm;
     const long need = (slots + MTP_WARPS - 1) / MTP_WARPS;
@@ -325,14 +365,28 @@ static int launch_mtp(const ai2b_mtp_program *prog, MtpArgs<T> A, void *ws, size
     return AI2B_OK;
 }
 
+template <typename T, int MODE>
+static int launch_mtp(const ai2b_mtp_program *prog, MtpArgs<T> A, void *ws, size_t ws_bytes, cudaStream_t st)
+{
+    const MtpProgramDev &P = prog->dev;
+    AI2B_REQUIRE(A.cs >= 1 && A.cs <= 16, AI2B_ERR_UNSUPPORTED, "chebyshev_size %d outside 1..16", A.cs);
+    AI2B_REQUIRE(A.B >= 0 && A.npad >= 0 && A.umax >= 0 && A.ntypes >= 1 && A.nghost >= 0, AI2B_ERR_INVALID, "negative size");
+    if (A.B == 0 || A.npad == 0) return AI2B_OK;
+    const size_t need = mtp_ws_bytes(P, A.B, A.ntypes, sizeof(T));
+    AI2B_REQUIRE(ws && ws_bytes >= need, AI2B_ERR_WORKSPACE, "MTP workspace too small: %zu < %zu bytes", ws_bytes, need);
+    // fast variant: monomial degree <= 6 (template level <= 16) and <= 8 radial basis functions
+    if (P.kmax <= 6 && A.cs <= 8) return launch_mtp_v<T, MODE, 6, 8>(prog, A, ws, st);
+    return launch_mtp_v<T, MODE, 8, 16>(prog, A, ws, st);
+}
+
 }  // namespace ai2b
 
 using namespace ai2b;
 
-extern "C" size_t ai2b_mtp_workspace_bytes(const ai2b_mtp_program *prog, int batch_size, int natoms_pad)
+extern "C" size_t ai2b_mtp_workspace_bytes(const ai2b_mtp_program *prog, int batch_size, int ntypes)
 {
-    (void)prog; (void)natoms_pad;
-    return (((size_t)(batch_size > 0 ? batch_size : 0) + 1) * sizeof(int) + 255) & ~size_t(255);
+    if (!prog) return 0;
+    return mtp_ws_bytes(prog->dev, batch_size, ntypes > 0 ? ntypes : 1, sizeof(double));
 }
 
 #define AI2B_DEF_MTP(SUF, T)                                                                                   \
@@ -351,7 +405,7 @@ extern "C" size_t ai2b_mtp_workspace_bytes(const ai2b_mtp_program *prog, int bat
             AI2B_CUDA(cudaMemsetAsync(force, 0, sizeof(T) * 3 * (size_t)B * (npad + nghost), st));             \
             if (virial) AI2B_CUDA(cudaMemsetAsync(virial, 0, sizeof(T) * 9 * B, st));                          \
         }                                                                                                      \
-        MtpArgs<T> A{etot, force, virial, nullptr, coeffs, lin, bias, qs, binum, bilist, numneigh, firstneigh, \
+        MtpArgs<T> A{etot, force, virial, nullptr, coeffs, lin, bias, qs, nullptr, binum, bilist, numneigh, firstneigh, \
                      types, rcs, nullptr, B, npad, ntypes, umax, nghost, cs, scaling, rmax, rmin};             \
         return virial ? launch_mtp<T, MODE_EFV>(prog, A, ws, ws_bytes, st)                                     \
                       : launch_mtp<T, MODE_EF>(prog, A, ws, ws_bytes, st);                                     \
@@ -368,7 +422,7 @@ extern "C" size_t ai2b_mtp_workspace_bytes(const ai2b_mtp_program *prog, int bat
         cudaStream_t st = (cudaStream_t)stream;                                                                \
         if (B > 0 && npad > 0)                                                                                 \
             AI2B_CUDA(cudaMemsetAsync(desc, 0, sizeof(T) * (size_t)B * npad * prog->dev.ns, st));              \
-        MtpArgs<T> A{nullptr, nullptr, nullptr, desc, coeffs, nullptr, nullptr, nullptr, binum, bilist,        \
+        MtpArgs<T> A{nullptr, nullptr, nullptr, desc, coeffs, nullptr, nullptr, nullptr, nullptr, binum, bilist,        \
                      numneigh, firstneigh, types, rcs, nullptr, B, npad, ntypes, umax, nghost, cs, scaling,    \
                      rmax, rmin};                                                                              \
         return launch_mtp<T, MODE_DESC>(prog, A, ws, ws_bytes, st);                                            \

@@ -17,11 +17,10 @@ template <> struct Vec2<double> { using type = double2; };
 template <> struct Vec2<float> { using type = float2; };
 
 // Q_xi = s(r) T_xi(u), Q'_xi = s' T_xi + s T'_xi  (source/descriptor/mtpr/include/basis.h:155-181,
-// 352-380, 621-637), contracted on the fly with the radial coefficients of NMU radial functions:
-// f[mu] = scaling * sum_xi c[mu*cs + xi] Q_xi, fd[mu] likewise with Q'.
-template <typename T>
-__device__ __forceinline__ void mtp_radial(T r, T rmax, T rmin, int cs, int nmus, T scaling, const T *__restrict__ c,
-                                           T (&f)[MTP_MAX_MU], T (&fd)[MTP_MAX_MU])
+// 352-380, 621-637), scaled by `scaling`. CSP >= chebyshev_size entries are produced; the ones
+// past chebyshev_size meet zero coefficients (the coefficient rows are zero-padded to CSP).
+template <typename T, int CSP>
+__device__ __forceinline__ void mtp_radial_basis(T r, T rmax, T rmin, T scaling, T (&q)[CSP], T (&dq)[CSP])
 {
     const T inv = T(1) / (rmax - rmin);
     const T w = (r - rmin) * inv;
@@ -31,12 +30,12 @@ __device__ __forceinline__ void mtp_radial(T r, T rmax, T rmin, int cs, int nmus
         s = w2 * w * (T(-6) * w2 + T(15) * w - T(10)) + T(1);
         ds = inv * (T(-30) * w2 * w2 + T(60) * w2 * w - T(30) * w2);
     }
+    s *= scaling; ds *= scaling;
     const T u = (T(2) * r - (rmax + rmin)) * inv;
     const T uc = T(2) * inv;
-#pragma unroll
-    for (int m = 0; m < MTP_MAX_MU; m++) { f[m] = T(0); fd[m] = T(0); }
     T t0 = T(1), t1 = u, d0 = T(0), d1 = T(1);
-    for (int xi = 0; xi < cs; xi++) {
+#pragma unroll
+    for (int xi = 0; xi < CSP; xi++) {
         T t, d;
         if (xi == 0) { t = T(1); d = T(0); }
         else if (xi == 1) { t = u; d = T(1); }
@@ -45,26 +44,19 @@ __device__ __forceinline__ void mtp_radial(T r, T rmax, T rmin, int cs, int nmus
             d = T(2) * t1 + T(2) * u * d1 - d0;
             t0 = t1; t1 = t; d0 = d1; d1 = d;
         }
-        const T q = s * t * scaling;
-        const T dq = (ds * t + s * (d * uc)) * scaling;
-#pragma unroll
-        for (int m = 0; m < MTP_MAX_MU; m++)
-            if (m < nmus) {
-                const T cc = c[m * cs + xi];
-                f[m] = fma(cc, q, f[m]);
-                fd[m] = fma(cc, dq, fd[m]);
-            }
+        q[xi] = s * t;
+        dq[xi] = ds * t + s * (d * uc);
     }
 }
 
-template <typename T>
+template <typename T, int KD>
 struct Powers {
-    T x[MTP_MAX_DEG + 1], y[MTP_MAX_DEG + 1], z[MTP_MAX_DEG + 1];
+    T x[KD + 1], y[KD + 1], z[KD + 1];
     __device__ __forceinline__ void set(T ux, T uy, T uz)
     {
         x[0] = y[0] = z[0] = T(1);
 #pragma unroll
-        for (int k = 1; k <= MTP_MAX_DEG; k++) {
+        for (int k = 1; k <= KD; k++) {
             x[k] = x[k - 1] * ux;
             y[k] = y[k - 1] * uy;
             z[k] = z[k - 1] * uz;
@@ -72,8 +64,8 @@ struct Powers {
     }
 };
 
-template <typename T, int D, int Q>
-__device__ __forceinline__ T mono(const Powers<T> &p)
+template <typename T, int KD, int D, int Q>
+__device__ __forceinline__ T mono(const Powers<T, KD> &p)
 {
     constexpr Exp3 e = deg_exp(D, Q);
     if constexpr (e.y == 0 && e.z == 0) return p.x[e.x];
@@ -87,47 +79,39 @@ __device__ __forceinline__ T mono(const Powers<T> &p)
 
 // Forward: acc[q] += sum over lanes of f * mono_q for the ndeg(D) monomials of degree D.
 // `acc` points at this degree's slice of the warp's dense moment array in shared memory.
-template <typename T, int D>
-__device__ __forceinline__ void fwd_degree(T f, const Powers<T> &p, T *acc, int lane)
+template <typename T, int KD, int D>
+__device__ __forceinline__ void fwd_degree(T f, const Powers<T, KD> &p, T *acc, int lane)
 {
     constexpr int ND = ndeg(D);
-    static_for<0, (ND + 31) / 32>([&](auto g) {
+    constexpr int GS = 16;   // values reduced together: 16 keeps the staging array at 32 registers (fp64)
+    static_for<0, (ND + GS - 1) / GS>([&](auto g) {
         constexpr int G = decltype(g)::value;
-        constexpr int CNT = (ND - 32 * G) < 32 ? (ND - 32 * G) : 32;
+        constexpr int CNT = (ND - GS * G) < GS ? (ND - GS * G) : GS;
         constexpr int N = pow2ceil(CNT);
         T v[N];
         static_for<0, N>([&](auto i) {
             constexpr int I = decltype(i)::value;
-            if constexpr (I < CNT) v[I] = f * mono<T, D, 32 * G + I>(p);
+            if constexpr (I < CNT) v[I] = f * mono<T, KD, D, GS * G + I>(p);
             else v[I] = T(0);
         });
         const T r = warp_xreduce<T, N>(v, lane);
         constexpr int SH = 5 - ilog2(N);
         const int idx = lane >> SH;
-        if ((lane & ((1 << SH) - 1)) == 0 && idx < CNT) acc[32 * G + idx] += r;
+        if ((lane & ((1 << SH) - 1)) == 0 && idx < CNT) acc[GS * G + idx] += r;
     });
 }
 
-template <typename T>
-__device__ __forceinline__ void fwd_mu(int kmu, T f, const Powers<T> &p, T *acc, int lane)
+template <typename T, int KD>
+__device__ __forceinline__ void fwd_mu(int kmu, T f, const Powers<T, KD> &p, T *acc, int lane)
 {
-    fwd_degree<T, 0>(f, p, acc + ncan(-1), lane);
-    if (kmu < 1) return;
-    fwd_degree<T, 1>(f, p, acc + ncan(0), lane);
-    if (kmu < 2) return;
-    fwd_degree<T, 2>(f, p, acc + ncan(1), lane);
-    if (kmu < 3) return;
-    fwd_degree<T, 3>(f, p, acc + ncan(2), lane);
-    if (kmu < 4) return;
-    fwd_degree<T, 4>(f, p, acc + ncan(3), lane);
-    if (kmu < 5) return;
-    fwd_degree<T, 5>(f, p, acc + ncan(4), lane);
-    if (kmu < 6) return;
-    fwd_degree<T, 6>(f, p, acc + ncan(5), lane);
-    if (kmu < 7) return;
-    fwd_degree<T, 7>(f, p, acc + ncan(6), lane);
-    if (kmu < 8) return;
-    fwd_degree<T, 8>(f, p, acc + ncan(7), lane);
+#define AI2B_FWD_DEG(D)                                                  \
+    if constexpr (D <= KD) {                                             \
+        if (kmu < D) return;                                             \
+        fwd_degree<T, KD, D>(f, p, acc + ncan(D - 1), lane);             \
+    }
+    AI2B_FWD_DEG(0) AI2B_FWD_DEG(1) AI2B_FWD_DEG(2) AI2B_FWD_DEG(3) AI2B_FWD_DEG(4)
+    AI2B_FWD_DEG(5) AI2B_FWD_DEG(6) AI2B_FWD_DEG(7) AI2B_FWD_DEG(8)
+#undef AI2B_FWD_DEG
 }
 
 // Polynomial evaluation for one neighbour: with coefficient quadruples e4[q] = {e, cx, cy, cz}
@@ -135,13 +119,13 @@ __device__ __forceinline__ void fwd_mu(int kmu, T f, const Powers<T> &p, T *acc,
 //   P += sum e mono,  G{x,y,z} += sum c{x,y,z} mono   (G = gradient of the polynomial w.r.t. u)
 // Every lane reads the same addresses (shared-memory broadcast). GRAD = false for the top
 // degree of a mu, whose gradient coefficients are zero.
-template <typename T, int D, bool GRAD>
-__device__ __forceinline__ void eval_degree(const T *__restrict__ e4, const Powers<T> &p, T &P, T &Gx, T &Gy, T &Gz)
+template <typename T, int KD, int D, bool GRAD>
+__device__ __forceinline__ void eval_degree(const T *__restrict__ e4, const Powers<T, KD> &p, T &P, T &Gx, T &Gy, T &Gz)
 {
     using V2 = typename Vec2<T>::type;
     static_for<0, ndeg(D)>([&](auto qq) {
         constexpr int Q = decltype(qq)::value;
-        const T m = mono<T, D, Q>(p);
+        const T m = mono<T, KD, D, Q>(p);
         if constexpr (GRAD) {
             const V2 a = *reinterpret_cast<const V2 *>(e4 + 4 * Q);
             const V2 b = *reinterpret_cast<const V2 *>(e4 + 4 * Q + 2);
@@ -155,21 +139,19 @@ __device__ __forceinline__ void eval_degree(const T *__restrict__ e4, const Powe
     });
 }
 
-template <typename T>
-__device__ __forceinline__ void eval_mu(int kmu, const T *__restrict__ e4, const Powers<T> &p, T &P, T &Gx, T &Gy, T &Gz)
+template <typename T, int KD>
+__device__ __forceinline__ void eval_mu(int kmu, const T *__restrict__ e4, const Powers<T, KD> &p, T &P, T &Gx, T &Gy, T &Gz)
 {
-#define AI2B_EVAL_DEG(D)                                                               \
-    if (kmu > D) eval_degree<T, D, true>(e4 + 4 * ncan(D - 1), p, P, Gx, Gy, Gz);      \
-    else { eval_degree<T, D, false>(e4 + 4 * ncan(D - 1), p, P, Gx, Gy, Gz); return; }
-    AI2B_EVAL_DEG(0)
-    AI2B_EVAL_DEG(1)
-    AI2B_EVAL_DEG(2)
-    AI2B_EVAL_DEG(3)
-    AI2B_EVAL_DEG(4)
-    AI2B_EVAL_DEG(5)
-    AI2B_EVAL_DEG(6)
-    AI2B_EVAL_DEG(7)
-    eval_degree<T, 8, false>(e4 + 4 * ncan(7), p, P, Gx, Gy, Gz);
+#define AI2B_EVAL_DEG(D)                                                                         \
+    if constexpr (D < KD) {                                                                      \
+        if (kmu > D) eval_degree<T, KD, D, true>(e4 + 4 * ncan(D - 1), p, P, Gx, Gy, Gz);        \
+        else { eval_degree<T, KD, D, false>(e4 + 4 * ncan(D - 1), p, P, Gx, Gy, Gz); return; }   \
+    } else if constexpr (D == KD) {                                                              \
+        eval_degree<T, KD, D, false>(e4 + 4 * ncan(D - 1), p, P, Gx, Gy, Gz);                    \
+        return;                                                                                  \
+    }
+    AI2B_EVAL_DEG(0) AI2B_EVAL_DEG(1) AI2B_EVAL_DEG(2) AI2B_EVAL_DEG(3) AI2B_EVAL_DEG(4)
+    AI2B_EVAL_DEG(5) AI2B_EVAL_DEG(6) AI2B_EVAL_DEG(7) AI2B_EVAL_DEG(8)
 #undef AI2B_EVAL_DEG
 }
 

@@ -199,7 +199,9 @@ extern "C" int ai2b_mtp_program_create(int nm, int nb, const int *basic, int nt,
         occ_of[times[4 * t + 1]].push_back(2 * t + 1);  // this moment is `b`, other = a
     }
     std::vector<int4> fwd_dst, rev_mom;
-    std::vector<int2> fwd_rows, rev_ents;
+    std::vector<int> fwd_ab, rev_od;
+    std::vector<float> fwd_mf, rev_mf;
+    std::vector<double> fwd_md, rev_md;
     P.fwd_lev_off[0] = 0;
     for (int lev = 1; lev <= P.nlev; lev++) {
         std::vector<int> ds;
@@ -207,9 +209,13 @@ extern "C" int ai2b_mtp_program_create(int nm, int nb, const int *basic, int nt,
             if (depth[m] == lev && !rows_of[m].empty()) ds.push_back(m);
         std::stable_sort(ds.begin(), ds.end(), [&](int a, int b) { return rows_of[a].size() > rows_of[b].size(); });
         for (int m : ds) {
-            int rb = (int)fwd_rows.size();
-            for (int t : rows_of[m]) fwd_rows.push_back(make_int2(times[4 * t] | (times[4 * t + 1] << 16), times[4 * t + 2]));
-            fwd_dst.push_back(make_int4(m, rb, (int)fwd_rows.size(), 0));
+            int rb = (int)fwd_ab.size();
+            for (int t : rows_of[m]) {
+                fwd_ab.push_back(times[4 * t] | (times[4 * t + 1] << 16));
+                fwd_mf.push_back((float)times[4 * t + 2]);
+                fwd_md.push_back((double)times[4 * t + 2]);
+            }
+            fwd_dst.push_back(make_int4(m, rb, (int)fwd_ab.size(), 0));
         }
         P.fwd_lev_off[lev] = (int)fwd_dst.size();
     }
@@ -223,13 +229,15 @@ extern "C" int ai2b_mtp_program_create(int nm, int nb, const int *basic, int nt,
             if (depth[m] == lev && !occ_of[m].empty()) ms.push_back(m);
         std::stable_sort(ms.begin(), ms.end(), [&](int a, int b) { return occ_of[a].size() > occ_of[b].size(); });
         for (int m : ms) {
-            int eb = (int)rev_ents.size();
+            int eb = (int)rev_od.size();
             for (int o : occ_of[m]) {
                 int t = o >> 1;
                 int other = (o & 1) ? times[4 * t] : times[4 * t + 1];
-                rev_ents.push_back(make_int2(other | (times[4 * t + 3] << 16), times[4 * t + 2]));
+                rev_od.push_back(other | (times[4 * t + 3] << 16));
+                rev_mf.push_back((float)times[4 * t + 2]);
+                rev_md.push_back((double)times[4 * t + 2]);
             }
-            rev_mom.push_back(make_int4(m, eb, (int)rev_ents.size(), 0));
+            rev_mom.push_back(make_int4(m, eb, (int)rev_od.size(), 0));
         }
         P.rev_lev_off[k + 1] = (int)rev_mom.size();
     }
@@ -241,7 +249,8 @@ extern "C" int ai2b_mtp_program_create(int nm, int nb, const int *basic, int nt,
 
     Blob blob;
     size_t o_bd = blob.add(basic_dense), o_g = blob.add(e4g), o_m = blob.add(e4m), o_fd = blob.add(fwd_dst),
-           o_fr = blob.add(fwd_rows), o_rm = blob.add(rev_mom), o_re = blob.add(rev_ents), o_map = blob.add(map);
+           o_fr = blob.add(fwd_ab), o_fmf = blob.add(fwd_mf), o_fmd = blob.add(fwd_md), o_rm = blob.add(rev_mom),
+           o_re = blob.add(rev_od), o_rmf = blob.add(rev_mf), o_rmd = blob.add(rev_md), o_map = blob.add(map);
     ai2b_mtp_program *prog = new ai2b_mtp_program;
     prog->blob_bytes = blob.bytes.size();
     prog->d_blob = nullptr;
@@ -259,9 +268,13 @@ extern "C" int ai2b_mtp_program_create(int nm, int nb, const int *basic, int nt,
     P.e4g = (const int4 *)(b + o_g);
     P.e4m = (const int *)(b + o_m);
     P.fwd_dst = (const int4 *)(b + o_fd);
-    P.fwd_rows = (const int2 *)(b + o_fr);
+    P.fwd_ab = (const int *)(b + o_fr);
+    P.fwd_mult_f = (const float *)(b + o_fmf);
+    P.fwd_mult_d = (const double *)(b + o_fmd);
     P.rev_mom = (const int4 *)(b + o_rm);
-    P.rev_ents = (const int2 *)(b + o_re);
+    P.rev_od = (const int *)(b + o_re);
+    P.rev_mult_f = (const float *)(b + o_rmf);
+    P.rev_mult_d = (const double *)(b + o_rmd);
     P.map = (const int *)(b + o_map);
     prog->dev = P;
     *out = prog;

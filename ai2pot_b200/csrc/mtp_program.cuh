@@ -27,11 +27,22 @@ struct MtpProgramDev {
     const int4 *e4g;                // [ndense] basic row holding {value, d/dx, d/dy, d/dz} source (-1: none)
     const int *e4m;                 // [ndense] packed multipliers (ax+1) | (ay+1)<<8 | (az+1)<<16
     const int4 *fwd_dst;            // {dst, row_begin, row_end, -}
-    const int2 *fwd_rows;           // {a | b<<16, mult}
+    const int *fwd_ab;              // [nt] a | b<<16, rows grouped by destination
+    const float *fwd_mult_f;        // [nt] multiplier, float / double copies (no int->fp conversion on the device)
+    const double *fwd_mult_d;
     const int4 *rev_mom;            // {m, entry_begin, entry_end, -}
-    const int2 *rev_ents;           // {other | dst<<16, mult}
+    const int *rev_od;              // [2 nt] other | dst<<16
+    const float *rev_mult_f;
+    const double *rev_mult_d;
     const int *map;                 // [ns] alpha_moment_mapping
 };
+
+template <typename T> __device__ __forceinline__ const T *fwd_mult(const MtpProgramDev &P);
+template <> __device__ __forceinline__ const float *fwd_mult<float>(const MtpProgramDev &P) { return P.fwd_mult_f; }
+template <> __device__ __forceinline__ const double *fwd_mult<double>(const MtpProgramDev &P) { return P.fwd_mult_d; }
+template <typename T> __device__ __forceinline__ const T *rev_mult(const MtpProgramDev &P);
+template <> __device__ __forceinline__ const float *rev_mult<float>(const MtpProgramDev &P) { return P.rev_mult_f; }
+template <> __device__ __forceinline__ const double *rev_mult<double>(const MtpProgramDev &P) { return P.rev_mult_d; }
 
 }  // namespace ai2b
 

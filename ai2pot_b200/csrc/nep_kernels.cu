@@ -124,18 +124,20 @@ __device__ __forceinline__ void nep_blm(T x, T y, T z, T (&b)[NEP_NLM], T (&g)[G
 #undef NEP_SET
 }
 
-// sum over the 8 lanes of a group
+// Sum over the 8 lanes of a group. `gmask` names exactly the group's lanes: the four groups of a
+// warp run loops of different trip counts (their atoms have different neighbour counts), so a
+// full-warp mask inside those loops would wait for lanes that never arrive.
 template <typename T>
-__device__ __forceinline__ T group_sum(T v)
+__device__ __forceinline__ T group_sum(T v, unsigned gmask)
 {
-    v += __shfl_xor_sync(FULL_MASK, v, 4);
-    v += __shfl_xor_sync(FULL_MASK, v, 2);
-    v += __shfl_xor_sync(FULL_MASK, v, 1);
+    v += __shfl_xor_sync(gmask, v, 4);
+    v += __shfl_xor_sync(gmask, v, 2);
+    v += __shfl_xor_sync(gmask, v, 1);
     return v;
 }
 // 8 values per lane -> lane `sub` of each group holds the group total of v[sub]
 template <typename T>
-__device__ __forceinline__ T group_xreduce8(T (&v)[8], int sub)
+__device__ __forceinline__ T group_xreduce8(T (&v)[8], int sub, unsigned gmask)
 {
     int o = 4;
 #pragma unroll
@@ -145,7 +147,7 @@ __device__ __forceinline__ T group_xreduce8(T (&v)[8], int sub)
         for (int i = 0; i < h; i++) {
             T send = up ? v[i] : v[i + h];
             T keep = up ? v[i + h] : v[i];
-            v[i] = keep + __shfl_xor_sync(FULL_MASK, send, o);
+            v[i] = keep + __shfl_xor_sync(gmask, send, o);
         }
     }
     return v[0];
@@ -186,6 +188,7 @@ __global__ void __launch_bounds__(NEP_WARPS * 32) nep_atom_kernel(const NepArgs<
     const int sub = lane & (NEP_GROUP - 1), grp = lane / NEP_GROUP;
     const int slot_in_block = warp * NEP_APW + grp;
     const unsigned gmask_shift = grp * NEP_GROUP;
+    const unsigned gmask = 0xffu << gmask_shift;
     auto r4 = [](int n) { return (n + 3) & ~3; };
     const int per_atom = nep_atom_elems(A.nd, A.nS, A.nneu);
     T *q = reinterpret_cast<T *>(nep_smem) + (size_t)slot_in_block * per_atom;
@@ -250,11 +253,11 @@ __global__ void __launch_bounds__(NEP_WARPS * 32) nep_atom_kernel(const NepArgs<
                 T g = T(0);
 #pragma unroll
                 for (int k = 0; k < CSP; k++) g = fma(crow[n * CSP + k], f[k], g);
-                g = group_sum(on ? g : T(0));
+                g = group_sum(on ? g : T(0), gmask);
                 if (sub == (n & (NEP_GROUP - 1))) q[n] += g;
             }
             const bool ang = on && r <= A.rc_a && A.l_max > 0;
-            const unsigned bal = (__ballot_sync(FULL_MASK, ang) >> gmask_shift) & 0xffu;
+            const unsigned bal = (__ballot_sync(gmask, ang) >> gmask_shift) & 0xffu;
             if (ang) alist[nang + __popc(bal & ((1u << sub) - 1u))] = (unsigned short)j;
             nang += __popc(bal);
         }
@@ -287,7 +290,7 @@ __global__ void __launch_bounds__(NEP_WARPS * 32) nep_atom_kernel(const NepArgs<
                         T v[8];
 #pragma unroll
                         for (int i = 0; i < 8; i++) v[i] = g * bl[8 * c + i];
-                        const T s = group_xreduce8<T>(v, sub);
+                        const T s = group_xreduce8<T>(v, sub, gmask);
                         if (8 * c + sub < nlm) S[mu * nlm + 8 * c + sub] += s;
                     }
                 }
@@ -323,7 +326,7 @@ __global__ void __launch_bounds__(NEP_WARPS * 32) nep_atom_kernel(const NepArgs<
             es += W1[p] * th;
             act[p] = W1[p] * (T(1) - th * th);
         }
-        es = group_sum(es);
+        es = group_sum(es, gmask);
         __syncwarp();
         for (int k = sub; k < A.nd; k += NEP_GROUP) {
             T acc = T(0);
@@ -425,10 +428,10 @@ __global__ void __launch_bounds__(NEP_WARPS * 32) nep_atom_kernel(const NepArgs<
             }
             scatter(on, nj, gx, gy, gz, x, y, z);
         }
-        fcx = group_sum(fcx); fcy = group_sum(fcy); fcz = group_sum(fcz);
+        fcx = group_sum(fcx, gmask); fcy = group_sum(fcy, gmask); fcz = group_sum(fcz, gmask);
         if (MODE == NEP_EFV) {
 #pragma unroll
-            for (int k = 0; k < 9; k++) vir[k] = group_sum(vir[k]);
+            for (int k = 0; k < 9; k++) vir[k] = group_sum(vir[k], gmask);
         }
         if (sub == 0 && valid) {
             atomicAdd(frc + 3 * ci + 0, fcx);
