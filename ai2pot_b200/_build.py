@@ -59,8 +59,48 @@ def build_cuda(force=False, verbose=False):
     return lib
 
 
+GLUE = {"libmtpr_bind.so": ["mtpr_bind.cpp"], "libnep_bind.so": ["nep_bind.cpp"], "libfvt_sr_op_bind.so": ["fvt_sr_op_bind.cpp"]}
+
+
+def build_glue(force=False, verbose=False):
+    """Torch-op libraries with the reference's file names (what ai2pot.fromcc loads and what the
+    LAMMPS interface links: -lmtpr_bind -lnep_bind). Plain g++ against the installed torch."""
+    import torch
+    from torch.utils import cpp_extension
+    gdir = os.path.join(CSRC, "torch_glue")
+    tlib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    inc = []
+    for p in cpp_extension.include_paths("cuda"):
+        inc += ["-isystem", p]
+    abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
+    cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else (shutil.which("g++") or "g++")
+    headers = glob.glob(os.path.join(gdir, "*.h")) + glob.glob(os.path.join(gdir, "*.inc")) + \
+        glob.glob(os.path.join(HERE, "..", "include", "*.h"))
+    procs, outs = [], []
+    for lib, srcs in GLUE.items():
+        out = os.path.join(LIBDIR, lib)
+        outs.append(out)
+        paths = [os.path.join(gdir, s) for s in srcs]
+        if force or _stale(out, paths + headers + [os.path.join(LIBDIR, "libai2pot_b200.so")]):
+            cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", f"-D_GLIBCXX_USE_CXX11_ABI={abi}", "-w"] + inc + paths + \
+                  ["-o", out, "-L" + LIBDIR, "-lai2pot_b200", "-L" + tlib, "-ltorch", "-ltorch_cpu", "-lc10", "-ltorch_cuda",
+                   "-lc10_cuda", "-L/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + tlib]
+            log = open(out + ".log", "w")
+            procs.append((lib, subprocess.Popen(cmd, stdout=log, stderr=subprocess.STDOUT), log, out))
+    for lib, p, log, out in procs:
+        rc = p.wait()
+        log.close()
+        if rc != 0 or verbose:
+            sys.stderr.write(open(out + ".log").read())
+        if rc != 0:
+            raise RuntimeError(f"g++ failed on {lib}")
+    return outs
+
+
 def build(force=False, verbose=False):
-    return build_cuda(force, verbose)
+    lib = build_cuda(force, verbose)
+    build_glue(force, verbose)
+    return lib
 
 
 if __name__ == "__main__":

@@ -132,6 +132,34 @@ int ai2b_nblist_sort_rows_f64(int natoms, int umax, const int *d_numneigh, int *
 int ai2b_nblist_sort_rows_f32(int natoms, int umax, const int *d_numneigh, int *d_firstneigh,
                               float *d_rcs, void *stream);
 
+/* ------------------------------------------------------------------------------------------
+ * fvt: scatter of per-pair energy gradients dE_i/dr_ij [B,Np,umax,3] into forces / virial
+ * ---------------------------------------------------------------------------------------- */
+
+/* force[B,Np+nghost,3]: F[i] += d, F[nbr] -= d (fvt::ForceSr<T>::find_val_der,
+ * source/fvt/include/force_sr.h:50-81); _bwd gives dL/d(dei_drij) from dL/dforce without the
+ * dense Jacobian the reference stores (find_der_backward, force_sr.h:99-123).
+ * virial[B,9]: V[a,b] -= d_a r_b (fvt::VirialSr<T>::find_val_der, virial_sr.h:24-51); _bwd gives
+ * dL/d(dei_drij) and, if d_grcs != NULL, dL/d(rcs). Outputs are overwritten. */
+#define AI2B_DECL_FVT(SUF, T)                                                                    \
+    int ai2b_fvt_force_fwd_##SUF(T *d_bforce, int batch_size, int natoms_pad, int nghost,        \
+                                 int umax, const int *d_binum, const int *d_bilist,              \
+                                 const int *d_bnumneigh, const int *d_bfirstneigh,               \
+                                 const T *d_bdei_drij, void *stream);                            \
+    int ai2b_fvt_force_bwd_##SUF(T *d_grad_dei_drij, int batch_size, int natoms_pad, int nghost, \
+                                 int umax, const int *d_binum, const int *d_bilist,              \
+                                 const int *d_bnumneigh, const int *d_bfirstneigh,               \
+                                 const T *d_grad_force, void *stream);                           \
+    int ai2b_fvt_virial_fwd_##SUF(T *d_bvirial, int batch_size, int natoms_pad, int umax,        \
+                                  const int *d_bnumneigh, const T *d_brcs, const T *d_bdei_drij, \
+                                  void *stream);                                                 \
+    int ai2b_fvt_virial_bwd_##SUF(T *d_grad_dei_drij, T *d_grad_rcs, int batch_size,             \
+                                  int natoms_pad, int umax, const int *d_bnumneigh,              \
+                                  const T *d_brcs, const T *d_bdei_drij, const T *d_grad_virial, \
+                                  void *stream);
+AI2B_DECL_FVT(f64, double)
+AI2B_DECL_FVT(f32, float)
+
 /* FMA-pipe microbenchmark used for the roofline denominator (no counterpart in the reference):
  * blocks x 256 threads, 8 independent chains of `iters` fused multiply-adds each. */
 int ai2b_fma_chain(int is_f64, int blocks, int iters, void *d_out, void *stream);
