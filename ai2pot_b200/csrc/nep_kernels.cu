@@ -559,3 +559,68 @@ extern "C" size_t ai2b_nep_workspace_bytes(int batch_size, int ntypes, int n_rad
 
 AI2B_DEF_NEP(f64, double)
 AI2B_DEF_NEP(f32, float)
+
+// ---------------------------------------------------------------------------------------------
+// NEP energy/force/virial for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot hand it a workspace: a molecular-dynamics driver that calls
+// the potential from inside its timestep loop, where a cudaMalloc would stall every stream on
+// the device; or a program whose device memory belongs entirely to its own pool and which has
+// no hook for a plugin's scratch buffer. For them the scratch of ai2b_nep_efv_f32 (the
+// per-structure atom offsets and the zero-padded radial coefficients) lives in a fixed array
+// that is part of the library image: every GPU that loads the library carries these 128 KiB
+// until the process exits.
+constexpr size_t NEP_STATIC_SCRATCH_BYTES = 128 * 1024;
+static __device__ __align__(256) unsigned char g_nep_static_scratch[NEP_STATIC_SCRATCH_BYTES];
+
+// Same arguments and results as ai2b_nep_efv_f32 minus the workspace pair.
+//  * The first call on each device looks up the array's device address (cudaGetSymbolAddress with
+//    that device current) and keeps it; make that first call outside any stream capture.
+//  * Sizes whose scratch exceeds the array are refused with AI2B_ERR_WORKSPACE:
+//    4 * (batch_size + 1) + 4 * ntypes^2 * (n_radial + n_angular) * (chebyshev_size <= 8 ? 8 : 16),
+//    each term rounded up to 256 bytes, must fit in 128 KiB.
+//  * No cudaMalloc / cudaFree or allocating library routine is called. Both scratch regions are
+//    fully rewritten by every call before they are read, so nothing has to start at zero; the
+//    array keeps the last call's contents in between.
+//  * All calls on a device share the one array: two calls whose kernels overlap on the GPU
+//    (different streams, no ordering between them) race on it. Order them, or use
+//    ai2b_nep_efv_f32 with separate workspaces.
+extern "C" int ai2b_nep_efv_static_scratch_f32(float *etot, float *force, float *virial, int cs, int n_r, int n_a, int l_max,
+                                               int nneu, const float *coeffs, const float *w0, const float *b0, const float *w1,
+                                               const float *bias, int B, int npad, const int *binum, const int *bilist,
+                                               const int *numneigh, const int *firstneigh, const float *rcs, const int *types,
+                                               int ntypes, int umax, int nghost, float rc_r, float rc_a, const float *qs,
+                                               void *stream)
+{
+    constexpr int MAX_DEVICES = 64;
+    static void *scratch_of_device[MAX_DEVICES] = {nullptr};
+    AI2B_REQUIRE(etot && force && coeffs && w0 && b0 && w1 && bias && qs && binum && bilist && numneigh && firstneigh && rcs && types,
+                 AI2B_ERR_INVALID, "ai2b_nep_efv_static_scratch_f32: NULL argument");
+    AI2B_REQUIRE(B >= 0 && ntypes >= 1 && n_r >= 0 && n_a >= 0 && cs >= 1 && cs <= 16, AI2B_ERR_INVALID,
+                 "ai2b_nep_efv_static_scratch_f32: bad sizes");
+    const size_t need = nep_ws_bytes(B, ntypes, n_r, n_a, cs <= 8 ? 8 : 16, sizeof(float));
+    AI2B_REQUIRE(need <= NEP_STATIC_SCRATCH_BYTES, AI2B_ERR_WORKSPACE,
+                 "ai2b_nep_efv_static_scratch_f32: this batch/model needs %zu bytes of scratch, the built-in array holds %zu; "
+                 "use ai2b_nep_efv_f32 with a caller-owned workspace",
+                 need, NEP_STATIC_SCRATCH_BYTES);
+    int dev = 0;
+    AI2B_CUDA(cudaGetDevice(&dev));
+    AI2B_REQUIRE(dev >= 0 && dev < MAX_DEVICES, AI2B_ERR_UNSUPPORTED, "device ordinal %d not supported", dev);
+    if (!scratch_of_device[dev]) {
+        // in host code the array's name is only a handle: the kernels need its device address
+        void *p = nullptr;
+        AI2B_CUDA(cudaGetSymbolAddress(&p, g_nep_static_scratch));
+        scratch_of_device[dev] = p;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    if (B > 0 && npad >= 0) {
+        AI2B_CUDA(cudaMemsetAsync(etot, 0, sizeof(float) * B, st));
+        AI2B_CUDA(cudaMemsetAsync(force, 0, sizeof(float) * 3 * (size_t)B * (npad + nghost), st));
+        if (virial) AI2B_CUDA(cudaMemsetAsync(virial, 0, sizeof(float) * 9 * B, st));
+    }
+    NepArgs<float> A{etot, force, virial, nullptr, nullptr, w0, b0, w1, bias, qs, binum, bilist, numneigh,
+                     firstneigh, types, rcs, nullptr, B, npad, ntypes, umax, nghost, cs, n_r, n_a, l_max, nneu,
+                     0, 0, rc_r, rc_a};
+    return virial ? launch_nep<float, NEP_EFV>(A, coeffs, scratch_of_device[dev], NEP_STATIC_SCRATCH_BYTES, st)
+                  : launch_nep<float, NEP_EF>(A, coeffs, scratch_of_device[dev], NEP_STATIC_SCRATCH_BYTES, st);
+}

@@ -132,6 +132,29 @@ int ai2b_nblist_sort_rows_f64(int natoms, int umax, const int *d_numneigh, int *
 int ai2b_nblist_sort_rows_f32(int natoms, int umax, const int *d_numneigh, int *d_firstneigh,
                               float *d_rcs, void *stream);
 
+/* NEP energy + force + virial without a workspace argument (no counterpart in the reference).
+ * For hosts that cannot give this library device memory of its own: an MD driver calling from
+ * inside its timestep loop, where an allocation would stall the whole device, or a program
+ * whose device memory is owned by its own pool. The scratch of ai2b_nep_efv_f32 lives in a
+ * 128 KiB array inside the library image (held by every GPU that loads the library until the
+ * process exits). Same arguments and results as ai2b_nep_efv_f32 otherwise.
+ *  - allocates nothing; the first call on a device resolves the array's device address and
+ *    should be made outside any stream capture;
+ *  - returns AI2B_ERR_WORKSPACE when  256-rounded 4*(batch_size+1)  +  256-rounded
+ *    4*ntypes^2*(n_radial+n_angular)*(chebyshev_size <= 8 ? 8 : 16)  exceeds 128 KiB;
+ *  - every call rewrites the scratch it reads, so nothing needs clearing between calls;
+ *  - all calls on a device share the array: calls that overlap on the GPU race. */
+int ai2b_nep_efv_static_scratch_f32(float *d_betot, float *d_bforce, float *d_bvirial,
+                                    int chebyshev_size, int n_radial, int n_angular, int l_max,
+                                    int num_neurons, const float *d_coeffs, const float *d_w0,
+                                    const float *d_b0, const float *d_w1, const float *d_type_bias,
+                                    int batch_size, int natoms_pad, const int *d_binum,
+                                    const int *d_bilist, const int *d_bnumneigh,
+                                    const int *d_bfirstneigh, const float *d_brcs,
+                                    const int *d_btypes, int ntypes, int umax, int nghost,
+                                    float rmax_radial, float rmax_angular, const float *d_q_scaler,
+                                    void *stream);
+
 /* ------------------------------------------------------------------------------------------
  * fvt: scatter of per-pair energy gradients dE_i/dr_ij [B,Np,umax,3] into forces / virial
  * ---------------------------------------------------------------------------------------- */
