@@ -92,8 +92,8 @@ class MtpProgram:
             C.c_int(self.nmus), C.byref(self.handle)))
         self._ws = None
 
-    def workspace(self, B, ntypes, device):
-        need = lib().ai2b_mtp_workspace_bytes(self.handle, C.c_int(B), C.c_int(ntypes))
+    def workspace(self, B, npad, ntypes, device):
+        need = lib().ai2b_mtp_workspace_bytes(self.handle, C.c_int(B), C.c_int(npad), C.c_int(ntypes))
         if self._ws is None or self._ws.numel() < need or self._ws.device != device:
             self._ws = torch.empty(max(need, 256), dtype=torch.uint8, device=device)
         return self._ws
@@ -137,7 +137,7 @@ def mtp_efv(prog, model, nb, virial=True, out=None):
         v = torch.empty(B, 9, dtype=rcs.dtype, device=rcs.device) if virial else None
     else:
         e, f, v = out
-    ws = prog.workspace(B, int(nb["ntypes"]), rcs.device)
+    ws = prog.workspace(B, npad, int(nb["ntypes"]), rcs.device)
     _check(getattr(lib(), "ai2b_mtp_efv_" + suf)(
         prog.handle, _ptr(e), _ptr(f), _ptr(v), C.c_int(int(model["chebyshev_size"])), cf(model["scaling"]),
         _ptr(model["coeffs"]), _ptr(model["linear_coeffs"]), _ptr(model["type_bias"]), *nbargs,
@@ -150,7 +150,7 @@ def mtp_descriptors(prog, model, nb):
     suf, cf = _suf(rcs.dtype)
     B, npad, umax, nbargs = _nb_args(nb)
     d = torch.empty(B, npad, prog.ns, dtype=rcs.dtype, device=rcs.device)
-    ws = prog.workspace(B, int(nb["ntypes"]), rcs.device)
+    ws = prog.workspace(B, npad, int(nb["ntypes"]), rcs.device)
     _check(getattr(lib(), "ai2b_mtp_descriptors_" + suf)(
         prog.handle, _ptr(d), C.c_int(int(model["chebyshev_size"])), cf(model["scaling"]), _ptr(model["coeffs"]),
         *nbargs, cf(model["rmax"]), cf(model["rmin"]), _ptr(ws), C.c_size_t(ws.numel()), _stream()))

@@ -1,18 +1,23 @@
-// Linear MTP: energy, force, virial and descriptors on sm_100a.
+// Linear MTP: energy, force, virial and descriptors on sm_100a, as three kernels per call.
 //
-// One warp evaluates one centre atom at a time; lanes are the atom's neighbours.
-//   1. pair set-up: r, unit vector, radial functions f_mu / f'_mu (registers -> shared memory)
-//   2. forward: dense moment sums per mu (compile-time monomials + warp transpose-reduce)
-//   3. product rows by dependency depth (lanes = destinations), site energy
-//   4. adjoint sweep as a gather per source moment (lanes = sources), deepest first
-//   5. adjoints of the basic moments -> polynomial coefficients, evaluated per neighbour with
-//      their gradient; pair force g = f' P u + f/r (G - (u.G) u); F_i += g, F_j -= g, V -= g (x) r
+//   mtp_fwd_kernel      one warp per atom, lanes = neighbours: r, unit vector, radial functions
+//                       f_mu, dense basic-moment sums per mu (compile-time monomials + warp
+//                       transpose-reduce) -> Mb[atom][dense] in the workspace
+//   mtp_contract_kernel one block per tile of atoms, LANES = ATOMS: the product rows and the
+//                       adjoint sweep run out of shared memory with the row tables uniform across
+//                       the warp (no divergence, no per-lane table loads); site energies;
+//                       adjoints of the basic moments -> Eb[atom][dense] (or the descriptors)
+//   mtp_force_kernel    one warp per atom, lanes = neighbours: adjoints -> polynomial coefficient
+//                       quadruples in shared memory, evaluated per neighbour with their gradient;
+//                       pair force g = f' P u + f/r (G - (u.G) u); F_i += g, F_j -= g, V -= g (x) r
+//
 // Reference semantics: source/descriptor/mtpr/include/mtpBasis.h:400-534, linearMtp.h:190-352.
 #include "mtp_poly.cuh"
 
 namespace ai2b {
 
-constexpr int MTP_WARPS = 4;   // warps (atoms in flight) per block
+constexpr int MTP_WARPS = 4;      // warps (atoms in flight) per block of the per-atom kernels
+constexpr int MTP_CWARPS = 16;    // warps per block of the contraction kernel
 
 enum MtpMode { MODE_EFV = 0, MODE_EF = 1, MODE_DESC = 2 };
 
@@ -23,8 +28,9 @@ struct MtpArgs {
     const T *coeffs_pad;   // [ntypes*ntypes][nmus][CSP] zero-padded copy of coeffs (workspace)
     const int *binum, *bilist, *numneigh, *firstneigh, *types;
     const T *rcs;
-    const int *prefix;   // [B+1] exclusive prefix sum of binum (workspace)
-    int B, npad, ntypes, umax, nghost, cs;
+    const int *prefix;     // [B+1] exclusive prefix sum of binum (workspace)
+    T *Mb, *Eb;            // [atoms][nbp] basic moments / their adjoints, in alpha_index_basic order (workspace)
+    int B, npad, ntypes, umax, nghost, cs, ndp, nbp;
     T scaling, rmax, rmin;
 };
 
@@ -65,13 +71,6 @@ __global__ void prefix_binum_kernel(const int *__restrict__ binum, int B, int *_
     }
 }
 
-__host__ __device__ inline int mtp_warp_elems(const MtpProgramDev &P)
-{
-    // per-warp shared memory, in elements of T: E4[4*ndense] M[nm] Eb[nm] Md[ndense] fr,fd[2*nmus*32]
-    auto r4 = [](int n) { return (n + 3) & ~3; };
-    return 4 * r4(P.ndense) + 2 * r4(P.nm) + r4(P.ndense) + 2 * MTP_MAX_MU * 32;
-}
-
 template <typename T>
 __global__ void mtp_pad_coeffs_kernel(const T *__restrict__ c, T *__restrict__ out, int rows, int cs, int csp)
 {
@@ -81,18 +80,261 @@ __global__ void mtp_pad_coeffs_kernel(const T *__restrict__ c, T *__restrict__ o
     out[i] = k < cs ? c[r * cs + k] : T(0);
 }
 
-template <typename T, int MODE, int KD, int CSP>
-__global__ void __launch_bounds__(MTP_WARPS * 32, 3) mtp_atom_kernel(const MtpProgramDev P, const MtpArgs<T> A)
+// structure index of flat atom t: largest b with prefix[b] <= t
+__device__ __forceinline__ int find_structure(const int *__restrict__ prefix, int B, int t)
 {
-    using V2 = typename Vec2<T>::type;
+    int lo = 0, hi = B;
+    while (hi - lo > 1) {
+        int mid = (lo + hi) >> 1;
+        if (prefix[mid] <= t) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+// One neighbour per lane: geometry and the radial functions of all mu (into shared memory).
+template <typename T, int CSP, bool DERIV>
+struct PairState {
+    T x, y, z, ux, uy, uz, rinv;
+    int nj;
+    bool act;
+    __device__ __forceinline__ void setup(const MtpProgramDev &P, const MtpArgs<T> &A, const T *rc, const int *fn, const int *types,
+                                          int ti, int nn, int j, int lane, T *fr, T *fdv)
+    {
+        using V2 = typename Vec2<T>::type;
+        act = j < nn;
+        x = y = z = T(0);
+        nj = 0;
+        if (act) {
+            x = rc[3 * j]; y = rc[3 * j + 1]; z = rc[3 * j + 2];
+            nj = fn[j];
+        }
+        const T r = gsqrt(x * x + y * y + z * z);
+        act = act && (r <= A.rmax) && (r > T(0));
+        int tj = 0;
+        if (act) { tj = types[nj]; rinv = T(1) / r; } else { rinv = T(0); }
+        ux = x * rinv; uy = y * rinv; uz = z * rinv;
+        T q[CSP], dq[CSP];
+        mtp_radial_basis<T, CSP>(act ? r : A.rmax, A.rmax, A.rmin, A.scaling, q, dq);
+        const T *crow = A.coeffs_pad + (size_t)(ti * A.ntypes + tj) * P.nmus * CSP;
+        for (int m = 0; m < P.nmus; m++) {
+            T f = T(0), fd = T(0);
+#pragma unroll
+            for (int k = 0; k < CSP; k += 2) {
+                const V2 c2 = *reinterpret_cast<const V2 *>(crow + m * CSP + k);
+                f = fma(c2.x, q[k], f);
+                f = fma(c2.y, q[k + 1], f);
+                if (DERIV) { fd = fma(c2.x, dq[k], fd); fd = fma(c2.y, dq[k + 1], fd); }
+            }
+            fr[m * 32 + lane] = act ? f : T(0);
+            if (DERIV) fdv[m * 32 + lane] = act ? fd : T(0);
+        }
+    }
+};
+
+// ---- kernel A: dense basic-moment sums ---------------------------------------------------------
+template <typename T, int KD, int CSP>
+__global__ void __launch_bounds__(MTP_WARPS * 32, 4) mtp_fwd_kernel(const MtpProgramDev P, const MtpArgs<T> A)
+{
     extern __shared__ __align__(32) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    auto r4 = [](int n) { return (n + 3) & ~3; };
-    T *E4 = reinterpret_cast<T *>(smem_raw) + (size_t)warp * mtp_warp_elems(P);
-    T *M = E4 + 4 * r4(P.ndense);
-    T *Eb = M + r4(P.nm);
-    T *Md = Eb + r4(P.nm);
-    T *fr = Md + r4(P.ndense);
+    T *Md = reinterpret_cast<T *>(smem_raw) + (size_t)warp * (A.ndp + MTP_MAX_MU * 32);
+    T *fr = Md + A.ndp;
+    const int ntot = A.prefix[A.B];
+    const int nw = gridDim.x * MTP_WARPS;
+    for (int t = blockIdx.x * MTP_WARPS + warp; t < ntot; t += nw) {
+        const int b = find_structure(A.prefix, A.B, t);
+        const size_t slot = (size_t)b * A.npad + (t - A.prefix[b]);
+        const int ci = A.bilist[slot];
+        const int nn = min(A.numneigh[slot], A.umax);
+        // descriptor launches index types with row stride Np (linearMtp_cpu_launcher.h:284-345)
+        const int *types = A.types + (size_t)b * (A.npad + (A.desc ? 0 : A.nghost));
+        const int ti = types[ci];
+        for (int i = lane; i < A.ndp; i += 32) Md[i] = T(0);
+        __syncwarp();
+        for (int j0 = 0; j0 < nn; j0 += 32) {
+            PairState<T, CSP, false> ps;
+            ps.setup(P, A, A.rcs + slot * A.umax * 3, A.firstneigh + slot * A.umax, types, ti, nn, j0 + lane, lane, fr, nullptr);
+            Powers<T, KD> pw;
+            pw.set(ps.ux, ps.uy, ps.uz);
+            for (int m = 0; m < P.nmus; m++) fwd_mu<T, KD>(P.kmu[m], fr[m * 32 + lane], pw, Md + P.doff[m], lane);
+        }
+        __syncwarp();
+        T *out = A.Mb + (size_t)t * A.nbp;
+        for (int i = lane; i < A.nbp; i += 32) out[i] = i < P.nb ? Md[P.basic_dense[i]] : T(0);
+        __syncwarp();
+    }
+}
+
+// ---- kernel B: products and adjoint sweep, lanes = atoms ----------------------------------------
+// TA atoms per tile (32, 16 or 8); with TA < 32 the 32/TA lane groups of a warp work on different
+// destination moments. Shared memory: M[nm][TA+1] and (unless DESC) E[nm][TA+1].
+template <typename T, int TA, int MODE, bool SMEMTAB>
+__global__ void __launch_bounds__(MTP_CWARPS * 32, 1) mtp_contract_kernel(const MtpProgramDev P, const MtpArgs<T> A)
+{
+    extern __shared__ __align__(32) unsigned char smem_raw[];
+    constexpr int LD = TA + 1;
+    constexpr int G = 32 / TA;
+    constexpr int NWORK = MTP_CWARPS * G;
+    __shared__ T esum[NWORK][TA];
+    T *M = reinterpret_cast<T *>(smem_raw);
+    T *E = M + (size_t)P.nm * LD;
+    // row tables staged in shared memory: every lane of a group reads the same row (broadcast)
+    const size_t arr_bytes = (sizeof(T) * (size_t)P.nm * LD * (MODE == MODE_DESC ? 1 : 2) + 15) & ~size_t(15);
+    int2 *s_fwd = reinterpret_cast<int2 *>(smem_raw + arr_bytes);
+    int2 *s_rev = s_fwd + P.nt;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int a = lane % TA, wid = warp * G + lane / TA;
+    const T *Ma = M + a, *Ea = E + a;
+    const int ntot = A.prefix[A.B];
+    const int t0 = blockIdx.x * TA;
+    if (t0 >= ntot) return;
+    const int nthreads = MTP_CWARPS * 32;
+
+    for (int i = threadIdx.x; i < P.nm * LD; i += nthreads) {
+        M[i] = T(0);
+        if (MODE != MODE_DESC) E[i] = T(0);
+    }
+    // staged with the moment indices already scaled to element offsets (index * LD fits 16 bits)
+    auto scale = [](int2 r) { return make_int2(((r.x & 0xffff) * LD) | (((r.x >> 16) & 0xffff) * LD) << 16, r.y); };
+    if (SMEMTAB) {
+#pragma unroll 4
+        for (int i = threadIdx.x; i < P.nt; i += nthreads) s_fwd[i] = scale(P.fwd_rows[i]);
+        if (MODE != MODE_DESC)
+#pragma unroll 4
+            for (int i = threadIdx.x; i < 2 * P.nt; i += nthreads) s_rev[i] = scale(P.rev_ents[i]);
+    }
+    // large tables (template levels above 16) stay in global memory
+    auto frow = [&](int r) { return SMEMTAB ? s_fwd[r] : scale(P.fwd_rows[r]); };
+    auto rrow = [&](int r) { return SMEMTAB ? s_rev[r] : scale(P.rev_ents[r]); };
+    __syncthreads();
+    // rows of the tile -> M[basic][atom] (coalesced global reads, padded rows in shared memory)
+#pragma unroll 4
+    for (int idx = threadIdx.x; idx < TA * A.nbp; idx += nthreads) {
+        const int at = idx / A.nbp, i = idx - at * A.nbp;
+        if (i < P.nb && t0 + at < ntot) M[i * LD + at] = A.Mb[(size_t)(t0 + at) * A.nbp + i];
+    }
+    __syncthreads();
+
+    for (int lev = 0; lev < P.nlev; lev++) {
+        const int dend = P.fwd_lev_off[lev + 1];
+        int d = P.fwd_lev_off[lev] + wid;
+        int4 nxt = d < dend ? P.fwd_dst[d] : make_int4(0, 0, 0, 0);
+        for (; d < dend; d += NWORK) {
+            const int4 ds = nxt;
+            if (d + NWORK < dend) nxt = P.fwd_dst[d + NWORK];   // header of the next destination, in flight during this one
+            T acc0 = T(0), acc1 = T(0), acc2 = T(0), acc3 = T(0);
+            int r = ds.y;
+            for (; r + 3 < ds.z; r += 4) {
+                const int2 r0 = frow(r), r1 = frow(r + 1), r2 = frow(r + 2), r3 = frow(r + 3);
+                acc0 = fma(T(__int_as_float(r0.y)) * Ma[r0.x & 0xffff], Ma[(unsigned)r0.x >> 16], acc0);
+                acc1 = fma(T(__int_as_float(r1.y)) * Ma[r1.x & 0xffff], Ma[(unsigned)r1.x >> 16], acc1);
+                acc2 = fma(T(__int_as_float(r2.y)) * Ma[r2.x & 0xffff], Ma[(unsigned)r2.x >> 16], acc2);
+                acc3 = fma(T(__int_as_float(r3.y)) * Ma[r3.x & 0xffff], Ma[(unsigned)r3.x >> 16], acc3);
+            }
+            for (; r < ds.z; r++) {
+                const int2 r0 = frow(r);
+                acc0 = fma(T(__int_as_float(r0.y)) * Ma[r0.x & 0xffff], Ma[(unsigned)r0.x >> 16], acc0);
+            }
+            M[ds.x * LD + a] += (acc0 + acc1) + (acc2 + acc3);
+        }
+        __syncthreads();
+    }
+
+    // per-atom bookkeeping (all lanes of a column agree)
+    const int t = t0 + a;
+    const bool valid = t < ntot;
+    int b = 0;
+    size_t slot = 0;
+    if (valid) {
+        b = find_structure(A.prefix, A.B, t);
+        slot = (size_t)b * A.npad + (t - A.prefix[b]);
+    }
+
+    if (MODE == MODE_DESC) {
+        if (valid)
+            for (int s = wid; s < P.ns; s += NWORK) A.desc[slot * P.ns + s] = M[P.map[s] * LD + a];
+        return;
+    }
+
+    // site energy and adjoint seeds (linearMtp.h:281-295)
+    T es = T(0);
+#pragma unroll 4
+    for (int s = wid; s < P.ns; s += NWORK) {
+        const int m = P.map[s];
+        const T w = A.lin[s] / A.qs[s];
+        es = fma(w, M[m * LD + a], es);
+        E[m * LD + a] = w;
+    }
+    esum[wid][a] = es;
+    __syncthreads();
+    if (wid == 0) {
+        T e = T(0);
+#pragma unroll
+        for (int k = 0; k < NWORK; k++) e += esum[k][a];
+        if (valid) {
+            const int *types = A.types + (size_t)b * (A.npad + A.nghost);
+            e += A.bias[types[A.bilist[slot]]];
+        } else {
+            e = T(0);
+        }
+        // one atomic per structure present in these TA atoms. Every lane of the group walks all TA
+        // lanes (a fixed trip count: the shuffles must be executed by the whole group together)
+        const unsigned grp = (TA == 32) ? FULL_MASK : (((1u << TA) - 1u) << (lane / TA * TA));
+        const int base = lane / TA * TA;
+        const int key = valid ? b : -1;
+        T tot = T(0);
+        int leader = TA;
+        for (int k = 0; k < TA; k++) {
+            const T ek = __shfl_sync(grp, e, base + k);
+            const int bk = __shfl_sync(grp, key, base + k);
+            if (bk == key) { tot += ek; leader = min(leader, k); }
+        }
+        if (valid && a == leader) atomicAdd(A.etot + b, tot);
+    }
+
+    for (int k = 0; k < P.nlev; k++) {
+        const int dend = P.rev_lev_off[k + 1];
+        int d = P.rev_lev_off[k] + wid;
+        int4 nxt = d < dend ? P.rev_mom[d] : make_int4(0, 0, 0, 0);
+        for (; d < dend; d += NWORK) {
+            const int4 ms = nxt;
+            if (d + NWORK < dend) nxt = P.rev_mom[d + NWORK];
+            T acc0 = T(0), acc1 = T(0), acc2 = T(0), acc3 = T(0);
+            int e = ms.y;
+            for (; e + 3 < ms.z; e += 4) {
+                const int2 r0 = rrow(e), r1 = rrow(e + 1), r2 = rrow(e + 2), r3 = rrow(e + 3);
+                acc0 = fma(T(__int_as_float(r0.y)) * Ea[(unsigned)r0.x >> 16], Ma[r0.x & 0xffff], acc0);
+                acc1 = fma(T(__int_as_float(r1.y)) * Ea[(unsigned)r1.x >> 16], Ma[r1.x & 0xffff], acc1);
+                acc2 = fma(T(__int_as_float(r2.y)) * Ea[(unsigned)r2.x >> 16], Ma[r2.x & 0xffff], acc2);
+                acc3 = fma(T(__int_as_float(r3.y)) * Ea[(unsigned)r3.x >> 16], Ma[r3.x & 0xffff], acc3);
+            }
+            for (; e < ms.z; e++) {
+                const int2 r0 = rrow(e);
+                acc0 = fma(T(__int_as_float(r0.y)) * Ea[(unsigned)r0.x >> 16], Ma[r0.x & 0xffff], acc0);
+            }
+            E[ms.x * LD + a] += (acc0 + acc1) + (acc2 + acc3);
+        }
+        __syncthreads();
+    }
+
+    // adjoints of the basic moments, back to per-atom rows
+#pragma unroll 4
+    for (int idx = threadIdx.x; idx < TA * A.nbp; idx += nthreads) {
+        const int at = idx / A.nbp, i = idx - at * A.nbp;
+        if (t0 + at < ntot) A.Eb[(size_t)(t0 + at) * A.nbp + i] = i < P.nb ? E[i * LD + at] : T(0);
+    }
+}
+
+// ---- kernel C: force and virial -----------------------------------------------------------------
+template <typename T, int MODE, int KD, int CSP>
+__global__ void __launch_bounds__(MTP_WARPS * 32, 4) mtp_force_kernel(const MtpProgramDev P, const MtpArgs<T> A)
+{
+    extern __shared__ __align__(32) unsigned char smem_raw[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // per warp: E4[4*ndp] Ed[nbp] fr, fd[2 * MU * 32]
+    T *E4 = reinterpret_cast<T *>(smem_raw) + (size_t)warp * (4 * A.ndp + A.nbp + 2 * MTP_MAX_MU * 32);
+    T *Ed = E4 + 4 * A.ndp;
+    T *fr = Ed + A.nbp;
     T *fdv = fr + MTP_MAX_MU * 32;
 
     const int ntot = A.prefix[A.B];
@@ -101,201 +343,79 @@ __global__ void __launch_bounds__(MTP_WARPS * 32, 3) mtp_atom_kernel(const MtpPr
     const int t0 = gw * chunk, t1 = min(ntot, t0 + chunk);
 
     int cur_b = -1, b_end = 0;
-    T eacc = T(0);
     T vir[9];
 #pragma unroll
     for (int k = 0; k < 9; k++) vir[k] = T(0);
-
     auto flush = [&]() {
-        if (cur_b < 0) return;
-        if (MODE != MODE_DESC) {
-            if (lane == 0) atomicAdd(A.etot + cur_b, eacc);
-            if (MODE == MODE_EFV) {
+        if (cur_b < 0 || MODE != MODE_EFV) return;
 #pragma unroll
-                for (int k = 0; k < 9; k++) {
-                    T s = warp_sum(vir[k]);
-                    if (lane == 0) atomicAdd(A.virial + 9 * cur_b + k, s);
-                    vir[k] = T(0);
-                }
-            }
+        for (int k = 0; k < 9; k++) {
+            T s = warp_sum(vir[k]);
+            if (lane == 0) atomicAdd(A.virial + 9 * cur_b + k, s);
+            vir[k] = T(0);
         }
-        eacc = T(0);
     };
 
     for (int t = t0; t < t1; t++) {
         if (t >= b_end || cur_b < 0) {
             flush();
-            int lo = 0, hi = A.B;   // largest b with prefix[b] <= t
-            while (hi - lo > 1) {
-                int mid = (lo + hi) >> 1;
-                if (A.prefix[mid] <= t) lo = mid; else hi = mid;
-            }
-            cur_b = lo;
-            b_end = A.prefix[lo + 1];
+            cur_b = find_structure(A.prefix, A.B, t);
+            b_end = A.prefix[cur_b + 1];
         }
         const int b = cur_b;
-        const int ii = t - A.prefix[b];
-        const size_t slot = (size_t)b * A.npad + ii;
+        const size_t slot = (size_t)b * A.npad + (t - A.prefix[b]);
         const int ci = A.bilist[slot];
         const int nn = min(A.numneigh[slot], A.umax);
-        const int *types = A.types + (size_t)b * (A.npad + (MODE == MODE_DESC ? 0 : A.nghost));
+        const int *types = A.types + (size_t)b * (A.npad + A.nghost);
         const int ti = types[ci];
         const int *fn = A.firstneigh + slot * A.umax;
         const T *rc = A.rcs + slot * A.umax * 3;
 
-        for (int i = lane; i < P.ndense; i += 32) Md[i] = T(0);
-        for (int i = P.nb + lane; i < P.nm; i += 32) M[i] = T(0);
+        // adjoints of this atom -> coefficient quadruples {e, (ax+1) e[+x], (ay+1) e[+y], (az+1) e[+z]}
+        const T *ein = A.Eb + (size_t)t * A.nbp;
+        for (int i = lane; i < A.nbp; i += 32) Ed[i] = ein[i];
         __syncwarp();
-
-        // pair state of the (last) chunk, reused by the force pass when the atom has <= 32 neighbours
-        T x = 0, y = 0, z = 0, ux = 0, uy = 0, uz = 0, rinv = 0;
-        int nj = 0;
-        bool act = false;
-        auto pair_setup = [&](int j0) {
-            const int j = j0 + lane;
-            act = j < nn;
-            x = y = z = T(0);
-            nj = 0;
-            if (act) {
-                x = rc[3 * j]; y = rc[3 * j + 1]; z = rc[3 * j + 2];
-                nj = fn[j];
-            }
-            const T r = gsqrt(x * x + y * y + z * z);
-            act = act && (r <= A.rmax) && (r > T(0));
-            int tj = 0;
-            if (act) { tj = types[nj]; rinv = T(1) / r; } else { rinv = T(0); }
-            ux = x * rinv; uy = y * rinv; uz = z * rinv;
-            T q[CSP], dq[CSP];
-            mtp_radial_basis<T, CSP>(act ? r : A.rmax, A.rmax, A.rmin, A.scaling, q, dq);
-            const T *crow = A.coeffs_pad + (size_t)(ti * A.ntypes + tj) * P.nmus * CSP;
-            for (int m = 0; m < P.nmus; m++) {
-                T f = T(0), fd = T(0);
-#pragma unroll
-                for (int k = 0; k < CSP; k += 2) {
-                    const V2 c2 = *reinterpret_cast<const V2 *>(crow + m * CSP + k);
-                    f = fma(c2.x, q[k], f); fd = fma(c2.x, dq[k], fd);
-                    f = fma(c2.y, q[k + 1], f); fd = fma(c2.y, dq[k + 1], fd);
-                }
-                fr[m * 32 + lane] = act ? f : T(0);
-                fdv[m * 32 + lane] = act ? fd : T(0);
-            }
-        };
-
-        // ---- forward: dense basic-moment sums ------------------------------------------------
-        for (int j0 = 0; j0 < nn || j0 == 0; j0 += 32) {
-            pair_setup(j0);
-            Powers<T, KD> pw;
-            pw.set(ux, uy, uz);
-            for (int m = 0; m < P.nmus; m++) fwd_mu<T, KD>(P.kmu[m], fr[m * 32 + lane], pw, Md + P.doff[m], lane);
-        }
-        __syncwarp();
-        for (int i = lane; i < P.nb; i += 32) M[i] = Md[P.basic_dense[i]];
-        __syncwarp();
-
-        // ---- products, by dependency depth ---------------------------------------------------
-        for (int lev = 0; lev < P.nlev; lev++) {
-            for (int d = P.fwd_lev_off[lev] + lane; d < P.fwd_lev_off[lev + 1]; d += 32) {
-                const int4 ds = P.fwd_dst[d];
-                const int *ab = P.fwd_ab;
-                const T *mult = fwd_mult<T>(P);
-                T acc0 = T(0), acc1 = T(0);
-                int r = ds.y;
-                for (; r + 1 < ds.z; r += 2) {
-                    const int x0 = ab[r], x1 = ab[r + 1];
-                    const T m0 = mult[r], m1 = mult[r + 1];
-                    acc0 = fma(m0 * M[x0 & 0xffff], M[x0 >> 16], acc0);
-                    acc1 = fma(m1 * M[x1 & 0xffff], M[x1 >> 16], acc1);
-                }
-                if (r < ds.z) {
-                    const int x0 = ab[r];
-                    acc0 = fma(mult[r] * M[x0 & 0xffff], M[x0 >> 16], acc0);
-                }
-                M[ds.x] += acc0 + acc1;
-            }
-            __syncwarp();
-        }
-
-        if (MODE == MODE_DESC) {
-            for (int s = lane; s < P.ns; s += 32) A.desc[slot * P.ns + s] = M[P.map[s]];
-            __syncwarp();
-            continue;
-        }
-
-        // ---- site energy and adjoint seeds ------------------------------------------------------
-        for (int i = lane; i < P.nm; i += 32) Eb[i] = T(0);
-        __syncwarp();
-        T es = T(0);
-        for (int s = lane; s < P.ns; s += 32) {
-            const int m = P.map[s];
-            const T l = A.lin[s], q = A.qs[s];
-            es += l * M[m] / q;
-            Eb[m] = l / q;
-        }
-        es = warp_sum(es);
-        eacc += es + A.bias[ti];
-        __syncwarp();
-
-        // ---- adjoint sweep (gather per source moment, deepest sources first) --------------------
-        for (int k = 0; k < P.nlev; k++) {
-            for (int d = P.rev_lev_off[k] + lane; d < P.rev_lev_off[k + 1]; d += 32) {
-                const int4 ms = P.rev_mom[d];
-                const int *od = P.rev_od;
-                const T *mult = rev_mult<T>(P);
-                T acc0 = T(0), acc1 = T(0);
-                int e = ms.y;
-                for (; e + 1 < ms.z; e += 2) {
-                    const int x0 = od[e], x1 = od[e + 1];
-                    const T m0 = mult[e], m1 = mult[e + 1];
-                    acc0 = fma(m0 * Eb[x0 >> 16], M[x0 & 0xffff], acc0);
-                    acc1 = fma(m1 * Eb[x1 >> 16], M[x1 & 0xffff], acc1);
-                }
-                if (e < ms.z) {
-                    const int x0 = od[e];
-                    acc0 = fma(mult[e] * Eb[x0 >> 16], M[x0 & 0xffff], acc0);
-                }
-                Eb[ms.x] += acc0 + acc1;
-            }
-            __syncwarp();
-        }
-
-        // ---- adjoints of the basic moments -> polynomial coefficient quadruples -----------------
         for (int c = lane; c < P.ndense; c += 32) {
+            using V2 = typename Vec2<T>::type;
             const int4 g = P.e4g[c];
             const int mu = P.e4m[c];
-            E4[4 * c + 0] = g.x >= 0 ? Eb[g.x] : T(0);
-            E4[4 * c + 1] = g.y >= 0 ? T(mu & 255) * Eb[g.y] : T(0);
-            E4[4 * c + 2] = g.z >= 0 ? T((mu >> 8) & 255) * Eb[g.z] : T(0);
-            E4[4 * c + 3] = g.w >= 0 ? T((mu >> 16) & 255) * Eb[g.w] : T(0);
+            V2 lo, hi;
+            lo.x = g.x >= 0 ? Ed[g.x] : T(0);
+            lo.y = g.y >= 0 ? T(mu & 255) * Ed[g.y] : T(0);
+            hi.x = g.z >= 0 ? T((mu >> 8) & 255) * Ed[g.z] : T(0);
+            hi.y = g.w >= 0 ? T((mu >> 16) & 255) * Ed[g.w] : T(0);
+            *reinterpret_cast<V2 *>(E4 + 4 * c) = lo;
+            *reinterpret_cast<V2 *>(E4 + 4 * c + 2) = hi;
         }
         __syncwarp();
 
-        // ---- force / virial pass ------------------------------------------------------------------
         T *frc = A.force + (size_t)b * (A.npad + A.nghost) * 3;
         T fcx = T(0), fcy = T(0), fcz = T(0);
         for (int j0 = 0; j0 < nn; j0 += 32) {
-            if (nn > 32) pair_setup(j0);
+            PairState<T, CSP, true> ps;
+            ps.setup(P, A, rc, fn, types, ti, nn, j0 + lane, lane, fr, fdv);
             Powers<T, KD> pw;
-            pw.set(ux, uy, uz);
+            pw.set(ps.ux, ps.uy, ps.uz);
             T gx = T(0), gy = T(0), gz = T(0);
             for (int m = 0; m < P.nmus; m++) {
                 T Pv = T(0), Gx = T(0), Gy = T(0), Gz = T(0);
                 eval_mu<T, KD>(P.kmu[m], E4 + 4 * P.doff[m], pw, Pv, Gx, Gy, Gz);
                 const T f = fr[m * 32 + lane], fd = fdv[m * 32 + lane];
-                const T ug = ux * Gx + uy * Gy + uz * Gz;
-                const T a = fd * Pv - f * rinv * ug, c = f * rinv;
-                gx += a * ux + c * Gx;
-                gy += a * uy + c * Gy;
-                gz += a * uz + c * Gz;
+                const T ug = ps.ux * Gx + ps.uy * Gy + ps.uz * Gz;
+                const T aa = fd * Pv - f * ps.rinv * ug, cc = f * ps.rinv;
+                gx += aa * ps.ux + cc * Gx;
+                gy += aa * ps.uy + cc * Gy;
+                gz += aa * ps.uz + cc * Gz;
             }
-            if (act) {
+            if (ps.act) {
                 fcx += gx; fcy += gy; fcz += gz;
-                atomicAdd(frc + 3 * nj + 0, -gx);
-                atomicAdd(frc + 3 * nj + 1, -gy);
-                atomicAdd(frc + 3 * nj + 2, -gz);
+                atomicAdd(frc + 3 * ps.nj + 0, -gx);
+                atomicAdd(frc + 3 * ps.nj + 1, -gy);
+                atomicAdd(frc + 3 * ps.nj + 2, -gz);
                 if (MODE == MODE_EFV) {
-                    vir[0] -= gx * x; vir[1] -= gx * y; vir[2] -= gx * z;
-                    vir[3] -= gy * x; vir[4] -= gy * y; vir[5] -= gy * z;
-                    vir[6] -= gz * x; vir[7] -= gz * y; vir[8] -= gz * z;
+                    vir[0] -= gx * ps.x; vir[1] -= gx * ps.y; vir[2] -= gx * ps.z;
+                    vir[3] -= gy * ps.x; vir[4] -= gy * ps.y; vir[5] -= gy * ps.z;
+                    vir[6] -= gz * ps.x; vir[7] -= gz * ps.y; vir[8] -= gz * ps.z;
                 }
             }
         }
@@ -325,43 +445,128 @@ static int sm_count()
     return g_sm_count;
 }
 
-static size_t mtp_ws_bytes(const MtpProgramDev &P, int B, int ntypes, size_t elem)
+static inline size_t up256(size_t n) { return (n + 255) & ~size_t(255); }
+static inline int ndense_pad(const MtpProgramDev &P) { return (P.ndense + 3) & ~3; }
+static inline int nbasic_pad(const MtpProgramDev &P) { return (P.nb + 3) & ~3; }
+
+struct MtpWs {
+    size_t prefix, cpad, mb, eb, total;
+};
+static MtpWs mtp_ws_layout(const MtpProgramDev &P, int B, int npad, int ntypes, size_t elem)
 {
-    size_t pre = (((size_t)(B > 0 ? B : 0) + 1) * sizeof(int) + 255) & ~size_t(255);
-    size_t co = ((size_t)ntypes * ntypes * P.nmus * 16 * elem + 255) & ~size_t(255);
-    return pre + co;
+    MtpWs L;
+    const size_t atoms = (size_t)(B > 0 ? B : 0) * (npad > 0 ? npad : 0);
+    L.prefix = 0;
+    L.cpad = up256(((size_t)(B > 0 ? B : 0) + 1) * sizeof(int));
+    L.mb = L.cpad + up256((size_t)ntypes * ntypes * P.nmus * 16 * elem);
+    L.eb = L.mb + up256(atoms * nbasic_pad(P) * elem);
+    L.total = L.eb + up256(atoms * nbasic_pad(P) * elem);
+    return L;
+}
+
+template <typename Kern>
+static int set_smem(Kern kern, size_t smem, size_t *configured)
+{
+    if (smem > *configured) {
+        AI2B_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        *configured = smem;
+    }
+    return AI2B_OK;
+}
+
+template <typename T, int MODE>
+static size_t contract_smem(const MtpProgramDev &P, int ta, bool tables)
+{
+    const size_t arrays = sizeof(T) * (size_t)P.nm * (ta + 1) * (MODE == MODE_DESC ? 1 : 2);
+    const size_t tab = tables ? sizeof(int2) * (size_t)P.nt * (MODE == MODE_DESC ? 1 : 3) : 0;
+    return ((arrays + 15) & ~size_t(15)) + tab + 16;
+}
+
+template <typename T, int TA, int MODE, bool SMEMTAB>
+static int launch_contract(const MtpProgramDev &P, const MtpArgs<T> &A, long atoms_upper, cudaStream_t st)
+{
+    const size_t smem = contract_smem<T, MODE>(P, TA, SMEMTAB);
+    auto kern = mtp_contract_kernel<T, TA, MODE, SMEMTAB>;
+    static size_t configured = 0;
+    if (int rc = set_smem(kern, smem, &configured)) return rc;
+    const long tiles = (atoms_upper + TA - 1) / TA;
+    kern<<<(unsigned)tiles, MTP_CWARPS * 32, smem, st>>>(P, A);
+    AI2B_CUDA(cudaGetLastError());
+    return AI2B_OK;
+}
+
+// largest tile (and shared-memory row tables if they fit too) within the 227 KiB opt-in limit;
+// moment offsets are packed as index * (TA + 1) in 16 bits
+template <typename T, int MODE>
+static int dispatch_contract(const MtpProgramDev &P, const MtpArgs<T> &A, long atoms_upper, cudaStream_t st)
+{
+    const size_t cap = 222 * 1024;
+#define AI2B_TRY(TA_)                                                                                       \
+    if ((long)P.nm * (TA_ + 1) <= 65535) {                                                                  \
+        if (contract_smem<T, MODE>(P, TA_, true) <= cap) return launch_contract<T, TA_, MODE, true>(P, A, atoms_upper, st);   \
+        if (contract_smem<T, MODE>(P, TA_, false) <= cap) return launch_contract<T, TA_, MODE, false>(P, A, atoms_upper, st); \
+    }
+    AI2B_TRY(32) AI2B_TRY(16) AI2B_TRY(8)
+#undef AI2B_TRY
+    set_error("MTP tables with %d moments do not fit the contraction kernel's shared memory", P.nm);
+    return AI2B_ERR_UNSUPPORTED;
 }
 
 template <typename T, int MODE, int KD, int CSP>
 static int launch_mtp_v(const ai2b_mtp_program *prog, MtpArgs<T> A, void *ws, cudaStream_t st)
 {
     const MtpProgramDev &P = prog->dev;
-    int *prefix = reinterpret_cast<int *>(ws);
-    T *cpad = reinterpret_cast<T *>(reinterpret_cast<unsigned char *>(ws) + ((((size_t)A.B + 1) * sizeof(int) + 255) & ~size_t(255)));
+    const MtpWs L = mtp_ws_layout(P, A.B, A.npad, A.ntypes, sizeof(T));
+    unsigned char *w = reinterpret_cast<unsigned char *>(ws);
+    int *prefix = reinterpret_cast<int *>(w + L.prefix);
+    T *cpad = reinterpret_cast<T *>(w + L.cpad);
     A.prefix = prefix;
     A.coeffs_pad = cpad;
+    A.Mb = reinterpret_cast<T *>(w + L.mb);
+    A.Eb = reinterpret_cast<T *>(w + L.eb);
+    A.ndp = ndense_pad(P);
+    A.nbp = nbasic_pad(P);
     prefix_binum_kernel<<<1, 256, 0, st>>>(A.binum, A.B, prefix);
     const int rows = A.ntypes * A.ntypes * P.nmus;
     mtp_pad_coeffs_kernel<T><<<(rows * CSP + 255) / 256, 256, 0, st>>>(A.coeffs, cpad, rows, A.cs, CSP);
     AI2B_CUDA(cudaGetLastError());
 
-    const size_t smem = sizeof(T) * (size_t)mtp_warp_elems(P) * MTP_WARPS;
-    AI2B_REQUIRE(smem <= 227 * 1024, AI2B_ERR_UNSUPPORTED, "MTP tables need %zu bytes of shared memory per block", smem);
-    auto kern = mtp_atom_kernel<T, MODE, KD, CSP>;
-    static size_t configured = 0;   // per instantiation
-    static int per_sm = 0;
-    if (smem > configured || per_sm == 0) {
-        AI2B_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        AI2B_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, MTP_WARPS * 32, smem));
-        if (per_sm < 1) per_sm = 1;
-        configured = smem;
+    const long atoms_upper = (long)A.B * A.npad;
+    const long need = (atoms_upper + MTP_WARPS - 1) / MTP_WARPS;
+    {   // A: forward
+        const size_t smem = sizeof(T) * (size_t)(A.ndp + MTP_MAX_MU * 32) * MTP_WARPS;
+        auto kern = mtp_fwd_kernel<T, KD, CSP>;
+        static size_t configured = 0;
+        static int per_sm = 0;
+        if (smem > configured || per_sm == 0) {
+            if (int rc = set_smem(kern, smem, &configured)) return rc;
+            AI2B_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, MTP_WARPS * 32, smem));
+            if (per_sm < 1) per_sm = 1;
+        }
+        long blocks = (long)sm_count() * per_sm;
+        if (blocks > need) blocks = need;
+        kern<<<(unsigned)blocks, MTP_WARPS * 32, smem, st>>>(P, A);
+        AI2B_CUDA(cudaGetLastError());
     }
-    const long slots = (long)A.B * A.npad;
-    long blocks = (long)sm_count() * per_sm;
-    const long need = (slots + MTP_WARPS - 1) / MTP_WARPS;
-    if (blocks > need) blocks = need;
-    kern<<<(unsigned)blocks, MTP_WARPS * 32, smem, st>>>(P, A);
-    AI2B_CUDA(cudaGetLastError());
+    {   // B: products / adjoints with lanes = atoms; tile size by shared-memory footprint
+        int rc = dispatch_contract<T, MODE>(P, A, atoms_upper, st);
+        if (rc) return rc;
+    }
+    if (MODE != MODE_DESC) {   // C: forces / virial
+        const size_t smem = sizeof(T) * (size_t)(4 * A.ndp + A.nbp + 2 * MTP_MAX_MU * 32) * MTP_WARPS;
+        auto kern = mtp_force_kernel<T, MODE, KD, CSP>;
+        static size_t configured = 0;
+        static int per_sm = 0;
+        if (smem > configured || per_sm == 0) {
+            if (int rc = set_smem(kern, smem, &configured)) return rc;
+            AI2B_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, MTP_WARPS * 32, smem));
+            if (per_sm < 1) per_sm = 1;
+        }
+        long blocks = (long)sm_count() * per_sm;
+        if (blocks > need) blocks = need;
+        kern<<<(unsigned)blocks, MTP_WARPS * 32, smem, st>>>(P, A);
+        AI2B_CUDA(cudaGetLastError());
+    }
     return AI2B_OK;
 }
 
@@ -372,7 +577,7 @@ static int launch_mtp(const ai2b_mtp_program *prog, MtpArgs<T> A, void *ws, size
     AI2B_REQUIRE(A.cs >= 1 && A.cs <= 16, AI2B_ERR_UNSUPPORTED, "chebyshev_size %d outside 1..16", A.cs);
     AI2B_REQUIRE(A.B >= 0 && A.npad >= 0 && A.umax >= 0 && A.ntypes >= 1 && A.nghost >= 0, AI2B_ERR_INVALID, "negative size");
     if (A.B == 0 || A.npad == 0) return AI2B_OK;
-    const size_t need = mtp_ws_bytes(P, A.B, A.ntypes, sizeof(T));
+    const size_t need = mtp_ws_layout(P, A.B, A.npad, A.ntypes, sizeof(T)).total;
     AI2B_REQUIRE(ws && ws_bytes >= need, AI2B_ERR_WORKSPACE, "MTP workspace too small: %zu < %zu bytes", ws_bytes, need);
     // fast variant: monomial degree <= 6 (template level <= 16) and <= 8 radial basis functions
     if (P.kmax <= 6 && A.cs <= 8) return launch_mtp_v<T, MODE, 6, 8>(prog, A, ws, st);
@@ -383,10 +588,10 @@ static int launch_mtp(const ai2b_mtp_program *prog, MtpArgs<T> A, void *ws, size
 
 using namespace ai2b;
 
-extern "C" size_t ai2b_mtp_workspace_bytes(const ai2b_mtp_program *prog, int batch_size, int ntypes)
+extern "C" size_t ai2b_mtp_workspace_bytes(const ai2b_mtp_program *prog, int batch_size, int natoms_pad, int ntypes)
 {
     if (!prog) return 0;
-    return mtp_ws_bytes(prog->dev, batch_size, ntypes > 0 ? ntypes : 1, sizeof(double));
+    return mtp_ws_layout(prog->dev, batch_size, natoms_pad, ntypes > 0 ? ntypes : 1, sizeof(double)).total;
 }
 
 #define AI2B_DEF_MTP(SUF, T)                                                                                   \
@@ -405,8 +610,9 @@ extern "C" size_t ai2b_mtp_workspace_bytes(const ai2b_mtp_program *prog, int bat
             AI2B_CUDA(cudaMemsetAsync(force, 0, sizeof(T) * 3 * (size_t)B * (npad + nghost), st));             \
             if (virial) AI2B_CUDA(cudaMemsetAsync(virial, 0, sizeof(T) * 9 * B, st));                          \
         }                                                                                                      \
-        MtpArgs<T> A{etot, force, virial, nullptr, coeffs, lin, bias, qs, nullptr, binum, bilist, numneigh, firstneigh, \
-                     types, rcs, nullptr, B, npad, ntypes, umax, nghost, cs, scaling, rmax, rmin};             \
+        MtpArgs<T> A{etot, force, virial, nullptr, coeffs, lin, bias, qs, nullptr, binum, bilist, numneigh,    \
+                     firstneigh, types, rcs, nullptr, nullptr, nullptr, B, npad, ntypes, umax, nghost, cs, 0, 0, \
+                     scaling, rmax, rmin};                                                                     \
         return virial ? launch_mtp<T, MODE_EFV>(prog, A, ws, ws_bytes, st)                                     \
                       : launch_mtp<T, MODE_EF>(prog, A, ws, ws_bytes, st);                                     \
     }                                                                                                          \
@@ -422,9 +628,9 @@ extern "C" size_t ai2b_mtp_workspace_bytes(const ai2b_mtp_program *prog, int bat
         cudaStream_t st = (cudaStream_t)stream;                                                                \
         if (B > 0 && npad > 0)                                                                                 \
             AI2B_CUDA(cudaMemsetAsync(desc, 0, sizeof(T) * (size_t)B * npad * prog->dev.ns, st));              \
-        MtpArgs<T> A{nullptr, nullptr, nullptr, desc, coeffs, nullptr, nullptr, nullptr, nullptr, binum, bilist,        \
-                     numneigh, firstneigh, types, rcs, nullptr, B, npad, ntypes, umax, nghost, cs, scaling,    \
-                     rmax, rmin};                                                                              \
+        MtpArgs<T> A{nullptr, nullptr, nullptr, desc, coeffs, nullptr, nullptr, nullptr, nullptr, binum,       \
+                     bilist, numneigh, firstneigh, types, rcs, nullptr, nullptr, nullptr, B, npad, ntypes,     \
+                     umax, nghost, cs, 0, 0, scaling, rmax, rmin};                                             \
         return launch_mtp<T, MODE_DESC>(prog, A, ws, ws_bytes, st);                                            \
     }
 

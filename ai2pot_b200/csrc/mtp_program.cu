@@ -171,6 +171,14 @@ extern "C" int ai2b_mtp_program_create(int nm, int nb, const int *basic, int nt,
                 }
             }
 
+    std::vector<int> dense_basic(P.ndense, -1);
+    std::vector<int4> e4d(P.ndense, make_int4(-1, -1, -1, -1));
+    for (int i = 0; i < nb; i++) dense_basic[basic_dense[i]] = i;
+    for (int d = 0; d < P.ndense; d++) {
+        auto dn = [&](int bi) { return bi >= 0 ? basic_dense[bi] : -1; };
+        e4d[d] = make_int4(dn(e4g[d].x), dn(e4g[d].y), dn(e4g[d].z), dn(e4g[d].w));
+    }
+
     // product rows: dependency depth, and the requirement that sources are final before use
     std::vector<int> depth(nm, 0), last_write(nm, -1);
     for (int t = 0; t < nt; t++) {
@@ -243,14 +251,18 @@ extern "C" int ai2b_mtp_program_create(int nm, int nb, const int *basic, int nt,
     }
     for (int k = P.nlev + 1; k <= MTP_MAX_LEV; k++) P.rev_lev_off[k] = P.rev_lev_off[P.nlev];
 
+    std::vector<int2> fwd_rows(fwd_ab.size()), rev_ents(rev_od.size());
+    for (size_t i = 0; i < fwd_ab.size(); i++) { int bits; memcpy(&bits, &fwd_mf[i], 4); fwd_rows[i] = make_int2(fwd_ab[i], bits); }
+    for (size_t i = 0; i < rev_od.size(); i++) { int bits; memcpy(&bits, &rev_mf[i], 4); rev_ents[i] = make_int2(rev_od[i], bits); }
     std::vector<int> map(mapping, mapping + ns);
     for (int s = 0; s < ns; s++)
         AI2B_REQUIRE(map[s] >= 0 && map[s] < nm, AI2B_ERR_INVALID, "alpha_moment_mapping[%d] out of range", s);
 
     Blob blob;
-    size_t o_bd = blob.add(basic_dense), o_g = blob.add(e4g), o_m = blob.add(e4m), o_fd = blob.add(fwd_dst),
+    size_t o_bd = blob.add(basic_dense), o_db = blob.add(dense_basic), o_e4d = blob.add(e4d), o_g = blob.add(e4g), o_m = blob.add(e4m), o_fd = blob.add(fwd_dst),
            o_fr = blob.add(fwd_ab), o_fmf = blob.add(fwd_mf), o_fmd = blob.add(fwd_md), o_rm = blob.add(rev_mom),
            o_re = blob.add(rev_od), o_rmf = blob.add(rev_mf), o_rmd = blob.add(rev_md), o_map = blob.add(map);
+    size_t o_frow = blob.add(fwd_rows), o_rent = blob.add(rev_ents);
     ai2b_mtp_program *prog = new ai2b_mtp_program;
     prog->blob_bytes = blob.bytes.size();
     prog->d_blob = nullptr;
@@ -265,6 +277,8 @@ extern "C" int ai2b_mtp_program_create(int nm, int nb, const int *basic, int nt,
     }
     unsigned char *b = (unsigned char *)prog->d_blob;
     P.basic_dense = (const int *)(b + o_bd);
+    P.dense_basic = (const int *)(b + o_db);
+    P.e4d = (const int4 *)(b + o_e4d);
     P.e4g = (const int4 *)(b + o_g);
     P.e4m = (const int *)(b + o_m);
     P.fwd_dst = (const int4 *)(b + o_fd);
@@ -276,6 +290,8 @@ extern "C" int ai2b_mtp_program_create(int nm, int nb, const int *basic, int nt,
     P.rev_mult_f = (const float *)(b + o_rmf);
     P.rev_mult_d = (const double *)(b + o_rmd);
     P.map = (const int *)(b + o_map);
+    P.fwd_rows = (const int2 *)(b + o_frow);
+    P.rev_ents = (const int2 *)(b + o_rent);
     prog->dev = P;
     *out = prog;
     return AI2B_OK;

@@ -24,12 +24,16 @@ struct MtpProgramDev {
     int fwd_lev_off[MTP_MAX_LEV + 1];  // destinations of depth 1..nlev
     int rev_lev_off[MTP_MAX_LEV + 1];  // source moments of depth nlev-1..0
     const int *basic_dense;         // [nb] dense index of basic row i
+    const int *dense_basic;         // [ndense] basic row of dense index d (-1: the tables have no such moment)
+    const int4 *e4d;                // [ndense] dense indices holding {value, d/dx, d/dy, d/dz} sources (-1: none)
     const int4 *e4g;                // [ndense] basic row holding {value, d/dx, d/dy, d/dz} source (-1: none)
     const int *e4m;                 // [ndense] packed multipliers (ax+1) | (ay+1)<<8 | (az+1)<<16
     const int4 *fwd_dst;            // {dst, row_begin, row_end, -}
     const int *fwd_ab;              // [nt] a | b<<16, rows grouped by destination
     const float *fwd_mult_f;        // [nt] multiplier, float / double copies (no int->fp conversion on the device)
     const double *fwd_mult_d;
+    const int2 *fwd_rows;           // [nt] {a | b<<16, multiplier as float bits}: one 8-byte load per row
+    const int2 *rev_ents;           // [2 nt] {other | dst<<16, multiplier as float bits}
     const int4 *rev_mom;            // {m, entry_begin, entry_end, -}
     const int *rev_od;              // [2 nt] other | dst<<16
     const float *rev_mult_f;

@@ -85,7 +85,7 @@ variable_list efv_impl(bool with_virial, int64_t cs, double scaling, const at::T
     // outputs shaped as the reference allocates them (src/linearMtpOp.cc:2890-2892)
     at::Tensor e = at::empty({B}, brcs.options()), f = at::empty({B, npad + nghost, 3}, brcs.options());
     at::Tensor v = with_virial ? at::empty({B, 9}, brcs.options()) : at::Tensor();
-    at::Tensor ws = workspace(ai2b_mtp_workspace_bytes(prog, B, ntypes), brcs);
+    at::Tensor ws = workspace(ai2b_mtp_workspace_bytes(prog, B, npad, ntypes), brcs);
     auto fn = [&](auto tag) {
         using U = decltype(tag);
         if constexpr (std::is_same<U, double>::value)
@@ -135,7 +135,7 @@ variable_list descriptors_dispatch(int64_t cs, double scaling, const at::Tensor 
     const int B = (int)binum.size(0), npad = (int)bnumneigh.size(1), umax = (int)bfirstneigh.size(2), ntypes = (int)type_map.size(0);
     const ai2b_mtp_program *prog = program_for((int)nm, basic, times, map, (int)nmus, brcs.get_device());
     at::Tensor d = at::empty({B, npad, map.size(0)}, brcs.options());
-    at::Tensor ws = workspace(ai2b_mtp_workspace_bytes(prog, B, ntypes), brcs);
+    at::Tensor ws = workspace(ai2b_mtp_workspace_bytes(prog, B, npad, ntypes), brcs);
     int rc;
     if (brcs.scalar_type() == at::kDouble)
         rc = ai2b_mtp_descriptors_f64(prog, d.data_ptr<double>(), (int)cs, scaling, fptr<double>(coeffs, brcs, "coeffs"), B, npad,

@@ -62,10 +62,12 @@ void ai2b_mtp_program_destroy(ai2b_mtp_program *prog);
 int ai2b_mtp_parse_almtp(const char *filename, int *counts, int *alpha_index_basic,
                          int *alpha_index_times, int *alpha_moment_mapping);
 
-/* Scratch bytes the MTP calls below need for a batch of `batch_size` structures of a model
- * with `ntypes` species (holds the per-structure atom offsets and a zero-padded copy of the
- * radial coefficients). */
-size_t ai2b_mtp_workspace_bytes(const ai2b_mtp_program *prog, int batch_size, int ntypes);
+/* Scratch bytes the MTP calls below need for a batch of `batch_size` structures padded to
+ * `natoms_pad` atoms, for a model with `ntypes` species: per-structure atom offsets, a
+ * zero-padded copy of the radial coefficients, and two [atoms][dense moments] arrays that carry
+ * the basic moments and their adjoints between the three kernels of a call. */
+size_t ai2b_mtp_workspace_bytes(const ai2b_mtp_program *prog, int batch_size, int natoms_pad,
+                                int ntypes);
 
 /* Energy + force + virial. Replaces find_efv_torch_launcher<T>
  * (source/descriptor/mtpr/gpu/include/linearMtp_torch_launcher.h:24-55, .cuh:27-100) and the
