@@ -31,6 +31,7 @@ def lib():
         _lib.ai2b_mtp_workspace_bytes.restype = C.c_size_t
         _lib.ai2b_nblist_workspace_bytes.restype = C.c_size_t
         _lib.ai2b_nep_workspace_bytes.restype = C.c_size_t
+        _lib.ai2b_mtp_loss_workspace_bytes.restype = C.c_size_t
     return _lib
 
 
@@ -165,9 +166,10 @@ class NeighborBuilder:
         self._ws = None
         self._out = None
 
-    def build(self, cell, coords, rcut, umax, is_cart=True, pbc=(True, True, True)):
-        """cell: host array [3,3]; coords: CUDA tensor [N,3] (float32/float64).
-        Returns (numneigh[N], firstneigh[N,umax], rcs[N,umax,3], status[2]) device tensors."""
+    def build(self, cell, coords, rcut, umax, is_cart=True, pbc=(True, True, True), ncentres=None):
+        """cell: host array [3,3]; coords: CUDA tensor [N,3] (float32/float64). With `ncentres`
+        rows are built for the first ncentres atoms only (the rest are ghosts).
+        Returns (numneigh[Nc], firstneigh[Nc,umax], rcs[Nc,umax,3], status[2]) device tensors."""
         if not coords.is_cuda:
             raise Ai2bError("coords must be a CUDA tensor")
         suf, _ = _suf(coords.dtype)
@@ -179,16 +181,17 @@ class NeighborBuilder:
         dev = coords.device
         if self._ws is None or self._ws.numel() < need or self._ws.device != dev:
             self._ws = torch.empty(need, dtype=torch.uint8, device=dev)
-        key = (n, umax, coords.dtype, dev)
+        nc = n if ncentres is None else int(ncentres)
+        key = (nc, umax, coords.dtype, dev)
         if self._out is None or self._out[0] != key:
-            self._out = (key, torch.empty(n, dtype=torch.int32, device=dev),
-                         torch.empty(n, umax, dtype=torch.int32, device=dev),
-                         torch.empty(n, umax, 3, dtype=coords.dtype, device=dev),
-                         torch.empty(2, dtype=torch.int32, device=dev))
+            self._out = (key, torch.empty(nc, dtype=torch.int32, device=dev),
+                         torch.empty(nc, umax, dtype=torch.int32, device=dev),
+                         torch.empty(nc, umax, 3, dtype=coords.dtype, device=dev),
+                         torch.zeros(2, dtype=torch.int32, device=dev))
         _, nn, fn, rcs, status = self._out
         coords = coords.contiguous()
-        _check(getattr(lib(), "ai2b_nblist_build_" + suf)(
-            C.c_int(n), hcell.ctypes.data_as(C.c_void_p), _ptr(coords), C.c_int(1 if is_cart else 0), C.c_double(rcut),
+        _check(getattr(lib(), "ai2b_nblist_build_ghost_" + suf)(
+            C.c_int(n), C.c_int(nc), hcell.ctypes.data_as(C.c_void_p), _ptr(coords), C.c_int(1 if is_cart else 0), C.c_double(rcut),
             hpbc.ctypes.data_as(C.c_void_p), C.c_int(umax), _ptr(nn), _ptr(fn), _ptr(rcs), _ptr(status), _ptr(self._ws),
             C.c_size_t(self._ws.numel()), _stream()))
         return nn, fn, rcs, status
@@ -251,3 +254,36 @@ def nep_descriptors(model, nb):
         C.c_int(int(model["l_max"])), _ptr(model["coeffs"]), *nbargs, cf(model["rmax_radial"]), cf(model["rmax_angular"]),
         _ptr(ws), C.c_size_t(ws.numel()), _stream()))
     return d
+
+
+def mtp_loss(nb, weights, e_ml, e_dft, f_ml, f_dft, v_ml=None, v_dft=None):
+    """Per-structure loss [B] and rmse[3] = (energy, force, virial)."""
+    suf, cf = _suf(e_ml.dtype)
+    B, npad = nb["bilist"].shape
+    loss = torch.empty(B, dtype=e_ml.dtype, device=e_ml.device)
+    rmse = torch.empty(3, dtype=e_ml.dtype, device=e_ml.device)
+    ws = torch.empty(256, dtype=torch.uint8, device=e_ml.device)
+    _check(getattr(lib(), "ai2b_mtp_loss_" + suf)(
+        _ptr(loss), _ptr(rmse), C.c_int(B), C.c_int(npad), C.c_int(int(nb.get("nghost", 0))), _ptr(nb["binum"]), _ptr(nb["bilist"]),
+        cf(weights[0]), cf(weights[1]), cf(weights[2]), _ptr(e_ml), _ptr(e_dft), _ptr(f_ml), _ptr(f_dft), _ptr(v_ml), _ptr(v_dft),
+        _ptr(ws), C.c_size_t(ws.numel()), _stream()))
+    return loss, rmse
+
+
+def mtp_loss_backward(prog, model, nb, weights, e_ml, e_dft, f_ml, f_dft, v_ml=None, v_dft=None):
+    """Per-structure gradients (dcoeffs [B,ncoef], dlinear [B,ns], dbias [B,ntypes])."""
+    rcs = nb["brcs"]
+    suf, cf = _suf(rcs.dtype)
+    B, npad, umax, nbargs = _nb_args(nb)
+    ntypes = int(nb["ntypes"])
+    dco = torch.empty(B, model["coeffs"].numel(), dtype=rcs.dtype, device=rcs.device)
+    dli = torch.empty(B, prog.ns, dtype=rcs.dtype, device=rcs.device)
+    dbi = torch.empty(B, ntypes, dtype=rcs.dtype, device=rcs.device)
+    need = lib().ai2b_mtp_loss_workspace_bytes(prog.handle, C.c_int(B), C.c_int(npad), C.c_int(ntypes))
+    ws = torch.empty(need, dtype=torch.uint8, device=rcs.device)
+    _check(getattr(lib(), "ai2b_mtp_loss_backward_" + suf)(
+        prog.handle, _ptr(dco), _ptr(dli), _ptr(dbi), cf(weights[0]), cf(weights[1]), cf(weights[2]), _ptr(e_ml), _ptr(e_dft),
+        _ptr(f_ml), _ptr(f_dft), _ptr(v_ml), _ptr(v_dft), C.c_int(int(model["chebyshev_size"])), cf(model["scaling"]),
+        _ptr(model["coeffs"]), _ptr(model["linear_coeffs"]), _ptr(model["type_bias"]), *nbargs, cf(model["rmax"]), cf(model["rmin"]),
+        _ptr(model["q_scaler"]), _ptr(ws), C.c_size_t(ws.numel()), _stream()))
+    return dco, dli, dbi

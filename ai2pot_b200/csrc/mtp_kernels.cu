@@ -12,124 +12,9 @@
 //                       pair force g = f' P u + f/r (G - (u.G) u); F_i += g, F_j -= g, V -= g (x) r
 //
 // Reference semantics: source/descriptor/mtpr/include/mtpBasis.h:400-534, linearMtp.h:190-352.
-#include "mtp_poly.cuh"
+#include "mtp_device.cuh"
 
 namespace ai2b {
-
-constexpr int MTP_WARPS = 4;      // warps (atoms in flight) per block of the per-atom kernels
-constexpr int MTP_CWARPS = 16;    // warps per block of the contraction kernel
-
-enum MtpMode { MODE_EFV = 0, MODE_EF = 1, MODE_DESC = 2 };
-
-template <typename T>
-struct MtpArgs {
-    T *etot, *force, *virial, *desc;
-    const T *coeffs, *lin, *bias, *qs;
-    const T *coeffs_pad;   // [ntypes*ntypes][nmus][CSP] zero-padded copy of coeffs (workspace)
-    const int *binum, *bilist, *numneigh, *firstneigh, *types;
-    const T *rcs;
-    const int *prefix;     // [B+1] exclusive prefix sum of binum (workspace)
-    T *Mb, *Eb;            // [atoms][nbp] basic moments / their adjoints, in alpha_index_basic order (workspace)
-    int B, npad, ntypes, umax, nghost, cs, ndp, nbp;
-    T scaling, rmax, rmin;
-};
-
-// exclusive prefix sum of binum -> prefix[0..B]; one block
-__global__ void prefix_binum_kernel(const int *__restrict__ binum, int B, int *__restrict__ prefix)
-{
-    __shared__ int carry;
-    __shared__ int wsum[32];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (threadIdx.x == 0) { carry = 0; prefix[0] = 0; }
-    __syncthreads();
-    for (int base = 0; base < B; base += blockDim.x) {
-        int i = base + threadIdx.x;
-        int v = i < B ? binum[i] : 0;
-        int inc = v;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            int n = __shfl_up_sync(FULL_MASK, inc, o);
-            if (lane >= o) inc += n;
-        }
-        if (lane == 31) wsum[warp] = inc;
-        __syncthreads();
-        if (warp == 0) {
-            int w = lane < (int)(blockDim.x >> 5) ? wsum[lane] : 0;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                int n = __shfl_up_sync(FULL_MASK, w, o);
-                if (lane >= o) w += n;
-            }
-            wsum[lane] = w;
-        }
-        __syncthreads();
-        int off = carry + (warp > 0 ? wsum[warp - 1] : 0);
-        if (i < B) prefix[i + 1] = off + inc;
-        __syncthreads();
-        if (threadIdx.x == blockDim.x - 1) carry = off + inc;
-        __syncthreads();
-    }
-}
-
-template <typename T>
-__global__ void mtp_pad_coeffs_kernel(const T *__restrict__ c, T *__restrict__ out, int rows, int cs, int csp)
-{
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= rows * csp) return;
-    int r = i / csp, k = i % csp;
-    out[i] = k < cs ? c[r * cs + k] : T(0);
-}
-
-// structure index of flat atom t: largest b with prefix[b] <= t
-__device__ __forceinline__ int find_structure(const int *__restrict__ prefix, int B, int t)
-{
-    int lo = 0, hi = B;
-    while (hi - lo > 1) {
-        int mid = (lo + hi) >> 1;
-        if (prefix[mid] <= t) lo = mid; else hi = mid;
-    }
-    return lo;
-}
-
-// One neighbour per lane: geometry and the radial functions of all mu (into shared memory).
-template <typename T, int CSP, bool DERIV>
-struct PairState {
-    T x, y, z, ux, uy, uz, rinv;
-    int nj;
-    bool act;
-    __device__ __forceinline__ void setup(const MtpProgramDev &P, const MtpArgs<T> &A, const T *rc, const int *fn, const int *types,
-                                          int ti, int nn, int j, int lane, T *fr, T *fdv)
-    {
-        using V2 = typename Vec2<T>::type;
-        act = j < nn;
-        x = y = z = T(0);
-        nj = 0;
-        if (act) {
-            x = rc[3 * j]; y = rc[3 * j + 1]; z = rc[3 * j + 2];
-            nj = fn[j];
-        }
-        const T r = gsqrt(x * x + y * y + z * z);
-        act = act && (r <= A.rmax) && (r > T(0));
-        int tj = 0;
-        if (act) { tj = types[nj]; rinv = T(1) / r; } else { rinv = T(0); }
-        ux = x * rinv; uy = y * rinv; uz = z * rinv;
-        T q[CSP], dq[CSP];
-        mtp_radial_basis<T, CSP>(act ? r : A.rmax, A.rmax, A.rmin, A.scaling, q, dq);
-        const T *crow = A.coeffs_pad + (size_t)(ti * A.ntypes + tj) * P.nmus * CSP;
-        for (int m = 0; m < P.nmus; m++) {
-            T f = T(0), fd = T(0);
-#pragma unroll
-            for (int k = 0; k < CSP; k += 2) {
-                const V2 c2 = *reinterpret_cast<const V2 *>(crow + m * CSP + k);
-                f = fma(c2.x, q[k], f);
-                f = fma(c2.y, q[k + 1], f);
-                if (DERIV) { fd = fma(c2.x, dq[k], fd); fd = fma(c2.y, dq[k + 1], fd); }
-            }
-            fr[m * 32 + lane] = act ? f : T(0);
-            if (DERIV) fdv[m * 32 + lane] = act ? fd : T(0);
-        }
-    }
-};
 
 // ---- kernel A: dense basic-moment sums ---------------------------------------------------------
 template <typename T, int KD, int CSP>
@@ -433,47 +318,6 @@ __global__ void __launch_bounds__(MTP_WARPS * 32, 4) mtp_force_kernel(const MtpP
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
-static int g_sm_count = 0;
-static int sm_count()
-{
-    if (!g_sm_count) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (g_sm_count <= 0) g_sm_count = 148;
-    }
-    return g_sm_count;
-}
-
-static inline size_t up256(size_t n) { return (n + 255) & ~size_t(255); }
-static inline int ndense_pad(const MtpProgramDev &P) { return (P.ndense + 3) & ~3; }
-static inline int nbasic_pad(const MtpProgramDev &P) { return (P.nb + 3) & ~3; }
-
-struct MtpWs {
-    size_t prefix, cpad, mb, eb, total;
-};
-static MtpWs mtp_ws_layout(const MtpProgramDev &P, int B, int npad, int ntypes, size_t elem)
-{
-    MtpWs L;
-    const size_t atoms = (size_t)(B > 0 ? B : 0) * (npad > 0 ? npad : 0);
-    L.prefix = 0;
-    L.cpad = up256(((size_t)(B > 0 ? B : 0) + 1) * sizeof(int));
-    L.mb = L.cpad + up256((size_t)ntypes * ntypes * P.nmus * 16 * elem);
-    L.eb = L.mb + up256(atoms * nbasic_pad(P) * elem);
-    L.total = L.eb + up256(atoms * nbasic_pad(P) * elem);
-    return L;
-}
-
-template <typename Kern>
-static int set_smem(Kern kern, size_t smem, size_t *configured)
-{
-    if (smem > *configured) {
-        AI2B_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        *configured = smem;
-    }
-    return AI2B_OK;
-}
-
 template <typename T, int MODE>
 static size_t contract_smem(const MtpProgramDev &P, int ta, bool tables)
 {

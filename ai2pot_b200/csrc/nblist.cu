@@ -42,6 +42,7 @@ struct NbParams {
     double rcut_m;       // rcut with a safety margin, for bin sizing
     double rc2;          // rcut^2 as the reference forms it
     int n, umax, maxbins;
+    int ncentre;         // rows are built for atoms [0, ncentre); the rest are neighbours only (ghosts)
 };
 
 __device__ __forceinline__ double mul_rn(double a, double b) { return __dmul_rn(a, b); }
@@ -277,6 +278,7 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
         const typename Vec4<T>::type pi = spos[a];
         const int4 si = sinfo[a];
         const int i = si.x;
+        if (i >= P.ncentre) continue;
         const int bin_i = ainfo[i].x;
         const int bz = bin_i % g.nb[2], by = (bin_i / g.nb[2]) % g.nb[1], bx = bin_i / (g.nb[2] * g.nb[1]);
         int count = 0;
@@ -448,12 +450,13 @@ static void plane_distances(const T *cell, T *d)
 }
 
 template <typename T>
-static int nblist_build(int n, const T *h_cell, const T *d_coords, int is_cart, double rcut_in, const int *pbc, int umax,
+static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, int is_cart, double rcut_in, const int *pbc, int umax,
                         int *d_numneigh, int *d_firstneigh, T *d_rcs, int *d_status, void *ws, size_t ws_bytes, cudaStream_t st)
 {
     AI2B_REQUIRE(h_cell && pbc && d_status, AI2B_ERR_INVALID, "ai2b_nblist_build: NULL argument");
-    AI2B_REQUIRE(n >= 0 && umax >= 0 && rcut_in > 0, AI2B_ERR_INVALID, "ai2b_nblist_build: bad size or cutoff");
-    if (n == 0) return AI2B_OK;
+    AI2B_REQUIRE(n >= 0 && umax >= 0 && rcut_in > 0 && ncentre >= 0 && ncentre <= n, AI2B_ERR_INVALID,
+                 "ai2b_nblist_build: bad size or cutoff");
+    if (n == 0 || ncentre == 0) return AI2B_OK;
     AI2B_REQUIRE(d_coords && d_numneigh && d_firstneigh && d_rcs, AI2B_ERR_INVALID, "ai2b_nblist_build: NULL argument");
     const int maxbins = nb_maxbins(n);
     const NbLayout L = nb_layout<T>(n, maxbins);
@@ -478,7 +481,7 @@ static int nblist_build(int n, const T *h_cell, const T *d_coords, int is_cart, 
     P.rcut_m = (double)rcut * 1.0001 + 1e-6;
     P.rc2 = (double)rcut * (double)rcut;
     if (sizeof(T) == 8) { volatile double r2 = (double)rcut * (double)rcut; P.rc2 = r2; }
-    P.n = n; P.umax = umax; P.maxbins = maxbins;
+    P.n = n; P.umax = umax; P.maxbins = maxbins; P.ncentre = ncentre;
     bool any_open = false;
     long prod = 1;
     for (int k = 0; k < 3; k++) {
@@ -561,14 +564,14 @@ extern "C" int ai2b_nblist_build_f64(int natoms, const double *h_cell, const dou
                                      const int *h_pbc, int umax, int *d_numneigh, int *d_firstneigh, double *d_rcs,
                                      int *d_status, void *d_workspace, size_t workspace_bytes, void *stream)
 {
-    return nblist_build<double>(natoms, h_cell, d_coords, is_cart, rcut, h_pbc, umax, d_numneigh, d_firstneigh, d_rcs,
+    return nblist_build<double>(natoms, natoms, h_cell, d_coords, is_cart, rcut, h_pbc, umax, d_numneigh, d_firstneigh, d_rcs,
                                 d_status, d_workspace, workspace_bytes, (cudaStream_t)stream);
 }
 extern "C" int ai2b_nblist_build_f32(int natoms, const float *h_cell, const float *d_coords, int is_cart, double rcut,
                                      const int *h_pbc, int umax, int *d_numneigh, int *d_firstneigh, float *d_rcs,
                                      int *d_status, void *d_workspace, size_t workspace_bytes, void *stream)
 {
-    return nblist_build<float>(natoms, h_cell, d_coords, is_cart, rcut, h_pbc, umax, d_numneigh, d_firstneigh, d_rcs,
+    return nblist_build<float>(natoms, natoms, h_cell, d_coords, is_cart, rcut, h_pbc, umax, d_numneigh, d_firstneigh, d_rcs,
                                d_status, d_workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
@@ -596,4 +599,23 @@ extern "C" int ai2b_nblist_sort_rows_f64(int natoms, int umax, const int *d_numn
 extern "C" int ai2b_nblist_sort_rows_f32(int natoms, int umax, const int *d_numneigh, int *d_firstneigh, float *d_rcs, void *stream)
 {
     return nblist_sort<float>(natoms, umax, d_numneigh, d_firstneigh, d_rcs, (cudaStream_t)stream);
+}
+
+// Same build for a local domain with ghost atoms: rows are produced for the first `ncentres`
+// atoms only, all `natoms` atoms (centres + ghosts) are candidates. Indices in d_firstneigh are
+// positions in d_coords, so ghosts appear as indices >= ncentres (the LAMMPS convention the
+// evaluation ops expect with nghost = natoms - ncentres).
+extern "C" int ai2b_nblist_build_ghost_f64(int natoms, int ncentres, const double *h_cell, const double *d_coords, int is_cart,
+                                           double rcut, const int *h_pbc, int umax, int *d_numneigh, int *d_firstneigh,
+                                           double *d_rcs, int *d_status, void *d_workspace, size_t workspace_bytes, void *stream)
+{
+    return nblist_build<double>(natoms, ncentres, h_cell, d_coords, is_cart, rcut, h_pbc, umax, d_numneigh, d_firstneigh, d_rcs,
+                                d_status, d_workspace, workspace_bytes, (cudaStream_t)stream);
+}
+extern "C" int ai2b_nblist_build_ghost_f32(int natoms, int ncentres, const float *h_cell, const float *d_coords, int is_cart,
+                                           double rcut, const int *h_pbc, int umax, int *d_numneigh, int *d_firstneigh,
+                                           float *d_rcs, int *d_status, void *d_workspace, size_t workspace_bytes, void *stream)
+{
+    return nblist_build<float>(natoms, ncentres, h_cell, d_coords, is_cart, rcut, h_pbc, umax, d_numneigh, d_firstneigh, d_rcs,
+                               d_status, d_workspace, workspace_bytes, (cudaStream_t)stream);
 }

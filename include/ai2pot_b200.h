@@ -101,6 +101,40 @@ AI2B_DECL_MTP_EFV(f32, float)
 AI2B_DECL_MTP_DESC(f64, double)
 AI2B_DECL_MTP_DESC(f32, float)
 
+/* Training path. ai2b_mtp_loss_*: per-structure weighted MSE loss[B] and the batch RMSEs
+ * rmse[3] = {energy, force, virial} (LinearMtpLoss<T>::find_loss / find_ef_loss,
+ * source/descriptor/mtpr/include/linearMtpLoss.h:138-210; RMSE definitions
+ * source/descriptor/mtpr/src/linearMtpOp.cc:885-911). d_bvirial_ml / d_bvirial_dft NULL gives
+ * the energy + force variant. Needs 32 bytes of workspace.
+ * ai2b_mtp_loss_backward_*: analytic gradient of every structure's loss w.r.t. coeffs
+ * [B,ntypes*ntypes*nmus*chebyshev_size], linear_coeffs [B,alpha_scalar_moments] and type_bias
+ * [B,ntypes] (find_loss_backward / find_ef_loss_backward, linearMtpLoss.h:212-569; CUDA
+ * launcher gpu/include/linearMtpLoss.cuh:1015). The model E/F/V of the same inputs are passed
+ * in (the reference recomputes them inside its backward). Outputs are overwritten.
+ * d_bforce_ml has row stride natoms_pad + nghost, d_bforce_dft natoms_pad; nghost must be 0
+ * for the gradient. Workspace: ai2b_mtp_loss_workspace_bytes. */
+size_t ai2b_mtp_loss_workspace_bytes(const ai2b_mtp_program *prog, int batch_size, int natoms_pad,
+                                     int ntypes);
+#define AI2B_DECL_MTP_LOSS(SUF, T)                                                               \
+    int ai2b_mtp_loss_##SUF(T *d_bloss, T *d_rmse, int batch_size, int natoms_pad, int nghost,   \
+                            const int *d_binum, const int *d_bilist, T e_weight, T f_weight,     \
+                            T v_weight, const T *d_betot_ml, const T *d_betot_dft,               \
+                            const T *d_bforce_ml, const T *d_bforce_dft, const T *d_bvirial_ml,  \
+                            const T *d_bvirial_dft, void *d_workspace, size_t workspace_bytes,   \
+                            void *stream);                                                       \
+    int ai2b_mtp_loss_backward_##SUF(                                                            \
+        const ai2b_mtp_program *prog, T *d_bloss_der2coeffs, T *d_bloss_der2linear_coeffs,       \
+        T *d_bloss_der2type_bias, T e_weight, T f_weight, T v_weight, const T *d_betot_ml,       \
+        const T *d_betot_dft, const T *d_bforce_ml, const T *d_bforce_dft,                       \
+        const T *d_bvirial_ml, const T *d_bvirial_dft, int chebyshev_size, T scaling,            \
+        const T *d_coeffs, const T *d_linear_coeffs, const T *d_type_bias, int batch_size,       \
+        int natoms_pad, const int *d_binum, const int *d_bilist, const int *d_bnumneigh,         \
+        const int *d_bfirstneigh, const T *d_brcs, const int *d_btypes, int ntypes, int umax,    \
+        int nghost, T rmax, T rmin, const T *d_q_scaler, void *d_workspace,                      \
+        size_t workspace_bytes, void *stream);
+AI2B_DECL_MTP_LOSS(f64, double)
+AI2B_DECL_MTP_LOSS(f32, float)
+
 /* ------------------------------------------------------------------------------------------
  * Neighbour list
  * ---------------------------------------------------------------------------------------- */
@@ -126,6 +160,22 @@ int ai2b_nblist_build_f32(int natoms, const float *h_cell, const float *d_coords
                           double rcut, const int *h_pbc, int umax, int *d_numneigh,
                           int *d_firstneigh, float *d_rcs, int *d_status, void *d_workspace,
                           size_t workspace_bytes, void *stream);
+
+/* Neighbour build for a local domain with ghost atoms (what the LAMMPS pair style assembles on
+ * the host from its full list, interface/lammps/AI2POT/pair_ai2pot.cpp:175-249): rows for the
+ * first `ncentres` atoms, all `natoms` atoms as candidates; neighbour indices are positions in
+ * d_coords (ghosts >= ncentres). Outputs sized [ncentres, ...]. Same workspace size as the
+ * plain build for `natoms`. */
+int ai2b_nblist_build_ghost_f64(int natoms, int ncentres, const double *h_cell,
+                                const double *d_coords, int is_cart, double rcut,
+                                const int *h_pbc, int umax, int *d_numneigh, int *d_firstneigh,
+                                double *d_rcs, int *d_status, void *d_workspace,
+                                size_t workspace_bytes, void *stream);
+int ai2b_nblist_build_ghost_f32(int natoms, int ncentres, const float *h_cell,
+                                const float *d_coords, int is_cart, double rcut,
+                                const int *h_pbc, int umax, int *d_numneigh, int *d_firstneigh,
+                                float *d_rcs, int *d_status, void *d_workspace,
+                                size_t workspace_bytes, void *stream);
 
 /* Orders every row by distance, in place (the reference's sort=true argument,
  * source/nblist/include/neighborList.h:290-335). Ties keep their build order. */
