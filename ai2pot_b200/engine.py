@@ -94,6 +94,150 @@ def _timed(fn, steps, warmup, flush, barrier=None):
 
 
 def run_benchmark(w, steps, warmup, dist, sampler):
+    if w.get("kind") == "train":
+        return run_training_benchmark(w, steps, warmup, dist, sampler)
+    if w.get("kind") == "slab":
+        return run_slab_benchmark(w, steps, warmup, dist, sampler)
+    return run_single_benchmark(w, steps, warmup, dist, sampler)
+
+
+def _mtp_flops(m, mean_nn, training=False):
+    from bench import flops_mtp
+    tb = m["tables"]
+    kmax = int(tb["alpha_index_basic"][:, 1:].sum(1).max())
+    nb_, nt_, ns_ = len(tb["alpha_index_basic"]), len(tb["alpha_index_times"]), len(tb["alpha_moment_mapping"])
+    fl = flops_mtp(mean_nn, nb_, nt_, ns_, tb["nmus"], m["chebyshev_size"], kmax)
+    if training:   # F_train = F_MTP + nn (55 n_basic + R) + 18 n_times + 6 n_scalar
+        R = 9 * m["chebyshev_size"] + 20 + 4 * tb["nmus"] * m["chebyshev_size"]
+        fl += mean_nn * (55 * nb_ + R) + 18 * nt_ + 6 * ns_
+    return fl
+
+
+def run_training_benchmark(w, steps, warmup, dist, sampler):
+    """configs[3]: one step = forward E/F/V + loss + analytic gradient w.r.t. the MTP coefficients for
+    this rank's share of the batch (structures dealt round-robin), then one all-reduce of the summed
+    gradient when there is more than one rank. Neighbour tensors are built once (as the reference's
+    dataset does at load time) and are resident."""
+    rank = dist.get_rank() if dist is not None else 0
+    world = dist.get_world_size() if dist is not None else 1
+    dtype = torch.float64
+    dev = torch.device("cuda", torch.cuda.current_device())
+    structs = w["structs"][rank::world]
+    model = w["model"]
+    prog = capi.MtpProgram(model["tables"])
+    md = capi.to_device({k: v for k, v in model.items() if k != "tables"}, dev, dtype)
+    builder = capi.NeighborBuilder()
+    npad = max(len(s_["types"]) for s_ in w["structs"])
+    B = len(structs)
+    nbt = dict(binum=torch.zeros(B, dtype=torch.int32, device=dev), bilist=torch.zeros(B, npad, dtype=torch.int32, device=dev),
+               bnumneigh=torch.zeros(B, npad, dtype=torch.int32, device=dev),
+               bfirstneigh=torch.full((B, npad, w["umax"]), -1, dtype=torch.int32, device=dev),
+               brcs=torch.zeros(B, npad, w["umax"], 3, dtype=dtype, device=dev), btypes=torch.zeros(B, npad, dtype=torch.int32, device=dev),
+               ntypes=int(model["ntypes"]), nghost=0)
+    for b, s_ in enumerate(structs):
+        n = len(s_["types"])
+        nn, fn, rcs, st = builder.build(s_["cell"], torch.from_numpy(s_["coords"]).to(dev), w["rcut"], w["umax"])
+        if int(st[1]):
+            raise RuntimeError("umax too small for the training batch")
+        nbt["binum"][b] = n
+        nbt["bilist"][b, :n] = torch.arange(n, dtype=torch.int32, device=dev)
+        nbt["bnumneigh"][b, :n] = nn; nbt["bfirstneigh"][b, :n] = fn; nbt["brcs"][b, :n] = rcs
+        nbt["btypes"][b, :n] = torch.from_numpy(s_["types"]).to(dev)
+    t = w["targets"]
+    sel = slice(rank, None, world)
+    E = torch.from_numpy(t["E"][sel]).to(dev); F = torch.from_numpy(np.ascontiguousarray(t["F"][sel, :npad])).to(dev)
+    V = torch.from_numpy(np.ascontiguousarray(t["V"][sel])).to(dev)
+    natoms = int(nbt["binum"].sum())
+    mean_nn = float(nbt["bnumneigh"].sum()) / natoms
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    grad = torch.zeros(md["coeffs"].numel() + prog.ns + int(model["ntypes"]) + 1, dtype=dtype, device=dev)
+
+    def step():
+        e, f, v = capi.mtp_efv(prog, md, nbt)
+        loss, rmse = capi.mtp_loss(nbt, w["weights"], e, E, f, F, v, V)
+        dco, dli, dbi = capi.mtp_loss_backward(prog, md, nbt, w["weights"], e, E, f, F, v, V)
+        torch.cat([dco.sum(0), dli.sum(0), dbi.sum(0), loss.sum(0, keepdim=True)], out=grad)
+        if dist is not None:
+            dist.all_reduce(grad)
+        return grad
+    barrier = (lambda: dist.barrier()) if dist is not None else None
+    sampler.start()
+    t_dev = _timed(step, steps, warmup, flush, barrier)
+    clocks = sampler.stop()
+    hgrad = torch.empty_like(grad, device="cpu").pin_memory()
+
+    def e2e_step():
+        step()
+        hgrad.copy_(grad, non_blocking=True)
+    t_e2e = _timed(e2e_step, steps, warmup, flush, barrier)
+    props = torch.cuda.get_device_properties(torch.cuda.current_device())
+    peak = fma_peak_tflops(True, props.multi_processor_count)
+    fl = _mtp_flops(model, mean_nn, training=True)
+    achieved = natoms * fl / (t_dev / steps) / 1e12
+    roofline = {"kernel": "mtp E/F/V + loss-gradient kernels (whole step)", "bound": "fp64", "achieved": achieved, "peak": peak,
+                "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": "FMA-chain microbenchmark in this run (of measured)",
+                "flops_per_atom": fl, "mean_neighbours": mean_nn, "traffic": None}
+    return dict(t_dev=t_dev, t_e2e=t_e2e, clocks=clocks, launches=(5 + 2 + 5) * steps, h2d=0, d2h=hgrad.numel() * 8, units=natoms,
+                e2e_path="resident neighbour tensors -> ai2b_mtp_efv -> ai2b_mtp_loss -> ai2b_mtp_loss_backward -> D2H summed gradient",
+                roofline=roofline, parts_ms=None)
+
+
+def run_slab_benchmark(w, steps, warmup, dist, sampler):
+    """configs[4]: x-slab decomposition, halo exchange, ghost-force reduction (ai2pot_b200/slab.py).
+    Strong scaling: the system is fixed, each rank owns 1/N of it."""
+    from . import slab
+    from bench import flops_nep
+    rank = dist.get_rank() if dist is not None else 0
+    world = dist.get_world_size() if dist is not None else 1
+    dtype = torch.float32 if w["dtype"] == "f32" else torch.float64
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dom = slab.SlabDomain(w["cell"], w["coords"], w["types"], w["rcut"], rank, world, dev, dist)
+    compute = slab.LocalCompute(w["model"], w["cell"], w["rcut"], w["umax"], dtype)
+    e, f, v = dom.evaluate(compute)
+    torch.cuda.synchronize()
+    st = compute.status.cpu().numpy()
+    if st[1]:
+        raise RuntimeError(f"umax {w['umax']} too small (max {st[0]})")
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    barrier = (lambda: dist.barrier()) if dist is not None else None
+    sampler.start()
+    t_dev = _timed(lambda: dom.evaluate(compute), steps, warmup, flush, barrier)
+    clocks = sampler.stop()
+    host_owned = dom.owned.cpu().pin_memory()
+    h_f = torch.empty(dom.nlocal, 3, dtype=dtype).pin_memory()
+    h_ev = torch.empty(10, dtype=dtype).pin_memory()
+
+    def e2e_step():
+        dom.owned.copy_(host_owned, non_blocking=True)
+        e_, f_, v_ = dom.evaluate(compute)
+        h_f.copy_(f_, non_blocking=True)
+        h_ev[:1].copy_(e_.reshape(1), non_blocking=True); h_ev[1:].copy_(v_, non_blocking=True)
+    t_e2e = _timed(e2e_step, steps, warmup, flush, barrier)
+    k = max(3, min(steps, 5))
+    local = dom.halo_exchange()
+    t_halo = _timed(lambda: dom.halo_exchange(), k, 2, flush) / k
+    t_comp = _timed(lambda: compute(local, dom.types, dom.nlocal, dom.pbc), k, 2, flush) / k
+    m = w["model"]
+    props = torch.cuda.get_device_properties(torch.cuda.current_device())
+    peak = fma_peak_tflops(dtype == torch.float64, props.multi_processor_count)
+    nn = compute.builder._out[1]
+    mean_nn = float(nn.float().mean())
+    rcs = compute.builder._out[3]
+    nn_a = float(((torch.linalg.norm(rcs, dim=-1) <= m["rmax_angular"]) &
+                  (torch.arange(rcs.shape[1], device=dev)[None] < nn[:, None])).sum(1).float().mean())
+    fl = flops_nep(mean_nn, nn_a, m["chebyshev_size"], m["n_radial"], m["n_angular"], m["num_neurons"], m["n_radial"] + m["n_angular"] * m["l_max"])
+    achieved = dom.nlocal * fl / t_comp / 1e12
+    roofline = {"kernel": "nep_atom_kernel (+ neighbour build) on this rank's slab", "bound": "fp32", "achieved": achieved, "peak": peak,
+                "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": "FMA-chain microbenchmark in this run (of measured)",
+                "flops_per_atom": fl, "mean_neighbours": mean_nn, "traffic": None, "owned_atoms": dom.nlocal, "ghost_atoms": dom.nghost}
+    return dict(t_dev=t_dev, t_e2e=t_e2e, clocks=clocks, launches=(8 + 3) * steps, h2d=host_owned.numel() * host_owned.element_size(),
+                d2h=h_f.numel() * h_f.element_size() + 40, units=len(w["types"]) / world,
+                e2e_path="pinned host positions of the slab -> H2D -> halo exchange (NCCL p2p) -> ai2b_nblist_build_ghost -> ai2b_nep_efv "
+                         "-> ghost-force return -> all-reduce(E, virial) -> D2H forces, E, virial",
+                roofline=roofline, parts_ms={"halo_exchange": 1e3 * t_halo, "nblist+efv": 1e3 * t_comp})
+
+
+def run_single_benchmark(w, steps, warmup, dist, sampler):
     from bench import flops_mtp, flops_nep   # formulas live beside the JSON contract
     dtype = torch.float64 if w["dtype"] == "f64" else torch.float32
     ev = Evaluator(w["model"], w["cell"], w["types"], w["rcut"], w["umax"], dtype)

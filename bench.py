@@ -90,6 +90,18 @@ def make_workload(name):
         w = synth.g2()
         w["label"] = "configs[2]: NEP fp32 (3-body), 13,824 atoms, rc 6.0/4.0"
         w["dtype"] = "f32"
+    elif name == "train":
+        w = synth.g3(load_tables(16))
+        w["kind"] = "train"
+        w["label"] = "configs[3]: MTP level 16 training step, fp64, 64 structures of 64-256 atoms, E/F/V + loss + coefficient gradient"
+        w["dtype"] = "f64"
+        w["types"] = np.concatenate([s["types"] for s in w["structs"]])
+    elif name.startswith("nep1m"):
+        ncell = int(name.split(":")[1]) if ":" in name else 64
+        w = synth.g4(ncell=ncell)
+        w["kind"] = "slab"
+        w["label"] = f"configs[4]: NEP fp32 (3-body), {4 * ncell ** 3:,} atoms, x-slabs with 6 A halos, ghost-force reduction"
+        w["dtype"] = "f32"
     else:
         raise SystemExit(f"unknown workload {name}")
     return w
@@ -117,6 +129,33 @@ def cpu_reference_run(w, kind_pref, budget_s, threads):
     return kind, t_nb, min(times), len(times), float(nn.mean())
 
 
+def cpu_reference_train(w, budget_s, threads):
+    """CPU arm of the training step: forward E/F/V + loss + analytic gradient on the whole batch
+    (the reference evaluates E/F/V a second time inside its backward; that repeat is not timed).
+    Neighbour lists are built before the timed part, as the reference's dataset does."""
+    from oracle import refapi
+    from ai2pot_b200 import synth
+    kind = "ref" if refapi.available("ref") else "oracle"
+    os.environ["OMP_NUM_THREADS"] = str(threads)
+    chk = refapi.Checker(kind)
+    lists = []
+    for s in w["structs"]:
+        nn, fn, rc, ty, mx = chk.nblist(s["cell"], s["types"], s["coords"], w["rcut"], w["umax"])
+        lists.append((nn, fn, rc, ty))
+    nb = synth.pad_batch(lists, w["model"]["ntypes"], w["umax"])
+    t = w["targets"]
+    npad = nb["bilist"].shape[1]
+    times = []
+    t_start = time.perf_counter()
+    while len(times) < 3 and (time.perf_counter() - t_start < budget_s or not times):
+        t0 = time.perf_counter()
+        e, f, v = chk.mtp_efv(w["model"], nb)
+        chk.mtp_loss(nb, w["weights"], e, t["E"], f, t["F"][:, :npad], v, t["V"])
+        chk.mtp_loss_backward(w["model"], nb, w["weights"], e, t["E"], f, t["F"][:, :npad], v, t["V"])
+        times.append(time.perf_counter() - t0)
+    return kind, 0.0, min(times), len(times)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -133,18 +172,23 @@ def main():
     w = make_workload(args.workload)
     natoms = len(w["types"])
     metric = "atoms/sec for E+F+virial"
-    config = {"workload": w["label"], "atoms_per_gpu": natoms, "l2": "256 MiB buffer written between timed steps"}
+    strong = w.get("kind") in ("train", "slab")           # a fixed batch / system divided over the ranks
+    config = {"workload": w["label"], "atoms_per_gpu": natoms // world if strong else natoms,
+              "l2": "256 MiB buffer written between timed steps"}
 
     if args.impl == "reference":
         if rank != 0:
             return
-        kind, t_nb, t_efv, nrep, mean_nn = cpu_reference_run(w, "ref", 60.0, ncores)
+        if w.get("kind") == "train":
+            kind, t_nb, t_efv, nrep = cpu_reference_train(w, 60.0, ncores)
+        else:
+            kind, t_nb, t_efv, nrep, mean_nn = cpu_reference_run(w, "ref", 60.0, ncores)
         steps = max(1, args.steps)
         t_step = t_nb + t_efv
         val = natoms / t_step
         line = {"impl": "reference", "metric": metric, "value": val, "unit": "atoms/s", "n_gpus": args.gpus,
                 "steps": steps, "warmup": args.warmup, "ms_per_step": 1e3 * t_step, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic", "config": config,
+                "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic", "config": config,
                 "cpu_baseline": {"value": val, "unit": "atoms/s", "cores": ncores,
                                  "kind": "reference" if kind == "ref" else "port",
                                  "sample": f"full workload, nblist {t_nb:.3f}s (serial) + E/F/V best of {nrep} = {t_efv:.3f}s"},
@@ -165,16 +209,23 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         res["t_dev"], res["t_e2e"] = float(t[0]), float(t[1])
     if rank == 0:
-        total_atoms = natoms * world
+        total_atoms = natoms if strong else natoms * world
         value = total_atoms * args.steps / res["t_dev"]
         line = {"metric": metric, "value": value, "unit": "atoms/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": 1e3 * res["t_dev"] / args.steps, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic", "config": config,
+                "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic", "config": config,
                 "clocks": res["clocks"], "gpu_launches": res["launches"],
                 "e2e": {"value": total_atoms * args.steps / res["t_e2e"], "unit": "atoms/s",
                         "h2d_bytes_per_step": res["h2d"], "d2h_bytes_per_step": res["d2h"], "path": res["e2e_path"]},
                 "roofline": res["roofline"], "parts_ms": res.get("parts_ms")}
-        if world == 1 and not args.no_cpu_baseline:
+        if world > 1:
+            config["parallelism"] = ("replicas only: %d independent copies, no data-path collective" % world) if not strong else \
+                ("structures dealt over %d ranks + one gradient all-reduce" % world if w["kind"] == "train" else "%d x-slabs, halo exchange + ghost-force reduction over NCCL" % world)
+        if world == 1 and not args.no_cpu_baseline and w.get("kind") == "train":
+            kind, t_nb, t_efv, nrep = cpu_reference_train(w, 20.0, ncores)
+            line["cpu_baseline"] = {"value": natoms / t_efv, "unit": "atoms/s", "cores": ncores, "kind": "reference" if kind == "ref" else "port",
+                                    "sample": f"whole batch: E/F/V + loss + gradient, best of {nrep} = {t_efv:.3f}s"}
+        elif world == 1 and not args.no_cpu_baseline and (w.get("kind") is None or natoms <= 200000):
             kind, t_nb, t_efv, nrep, mean_nn = cpu_reference_run(w, "ref", 20.0, ncores)
             line["cpu_baseline"] = {"value": natoms / (t_nb + t_efv), "unit": "atoms/s", "cores": ncores,
                                     "kind": "reference" if kind == "ref" else "port",
