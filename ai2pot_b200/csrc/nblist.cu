@@ -241,6 +241,61 @@ __global__ void nb_scan3_kernel(const NbGrid *__restrict__ gp, int *__restrict__
     if (i < total) cursor[i] = v;
 }
 
+
+// all axes periodic: grid parameters are known on the host, so one kernel zeroes the bin counters,
+// resets the status words and writes the grid description
+template <typename T>
+__global__ void nb_setup_periodic_kernel(NbParams<T> P, NbGrid *__restrict__ g, int *__restrict__ count, int ncount, int *__restrict__ status)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < ncount) count[i] = 0;
+    if (i == 0) {
+        status[0] = 0; status[1] = 0;
+        long total = 1;
+        for (int k = 0; k < 3; k++) {
+            g->nb[k] = P.nbh[k];
+            g->R[k] = (int)ceil(P.rcut_m / (P.dplane[k] / P.nbh[k]));
+            g->lo[k] = 0.0;
+            g->scale[k] = (double)P.nbh[k];
+            total *= P.nbh[k];
+        }
+        g->total = (int)total;
+    }
+}
+
+// exclusive scan by one block (grids of up to a few hundred thousand bins): bin_start and cursor
+__global__ void nb_scan_small_kernel(const NbGrid *__restrict__ gp, const int *__restrict__ in, int *__restrict__ out, int *__restrict__ cursor)
+{
+    __shared__ int ws[32];
+    __shared__ int carry;
+    const int total = gp->total;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    for (int base = 0; base <= total; base += SCAN_BLOCK) {
+        const int i = base + threadIdx.x;
+        const int v = i < total ? in[i] : 0;
+        int inc = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { int n = __shfl_up_sync(FULL_MASK, inc, o); if (lane >= o) inc += n; }
+        if (lane == 31) ws[warp] = inc;
+        __syncthreads();
+        if (warp == 0) {
+            int w = ws[lane];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { int n = __shfl_up_sync(FULL_MASK, w, o); if (lane >= o) w += n; }
+            ws[lane] = w;
+        }
+        __syncthreads();
+        const int excl = carry + inc - v + (warp > 0 ? ws[warp - 1] : 0);
+        if (i <= total) out[i] = excl;
+        if (i < total) cursor[i] = excl;
+        __syncthreads();
+        if (threadIdx.x == SCAN_BLOCK - 1) carry = excl + v;
+        __syncthreads();
+    }
+}
+
 // pass 2: atoms into bin order: position (type T) + {original index, wrap}
 template <typename T>
 __global__ void nb_fill_kernel(NbParams<T> P, const T *__restrict__ pos, const int4 *__restrict__ ainfo,
@@ -338,10 +393,15 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
                     const int n1 = ((sh >> 10) & 1023) - 512 - sj.z + si.z;
                     const int n2 = ((sh >> 20) & 1023) - 512 - sj.w + si.w;
                     if (abs(n0) <= P.e[0] && abs(n1) <= P.e[1] && abs(n2) <= P.e[2]) {
-                        const T f0 = T(n0), f1 = T(n1), f2 = T(n2);
-                        const T ix = add_rn(add_rn(add_rn(pj.x, mul_rn(P.cell[0], f0)), mul_rn(P.cell[3], f1)), mul_rn(P.cell[6], f2));
-                        const T iy = add_rn(add_rn(add_rn(pj.y, mul_rn(P.cell[1], f0)), mul_rn(P.cell[4], f1)), mul_rn(P.cell[7], f2));
-                        const T iz = add_rn(add_rn(add_rn(pj.z, mul_rn(P.cell[2], f0)), mul_rn(P.cell[5], f1)), mul_rn(P.cell[8], f2));
+                        T ix = pj.x, iy = pj.y, iz = pj.z;
+                        // the home image needs no arithmetic: x + a*0 is x bit for bit, except for x = -0.0
+                        // (whose sum with +0 is +0), so exact zeros take the full path
+                        if ((n0 | n1 | n2) != 0 || pj.x == T(0) || pj.y == T(0) || pj.z == T(0)) {
+                            const T f0 = T(n0), f1 = T(n1), f2 = T(n2);
+                            ix = add_rn(add_rn(add_rn(pj.x, mul_rn(P.cell[0], f0)), mul_rn(P.cell[3], f1)), mul_rn(P.cell[6], f2));
+                            iy = add_rn(add_rn(add_rn(pj.y, mul_rn(P.cell[1], f0)), mul_rn(P.cell[4], f1)), mul_rn(P.cell[7], f2));
+                            iz = add_rn(add_rn(add_rn(pj.z, mul_rn(P.cell[2], f0)), mul_rn(P.cell[5], f1)), mul_rn(P.cell[8], f2));
+                        }
                         d0 = sub_rn(ix, pi.x); d1 = sub_rn(iy, pi.y); d2 = sub_rn(iz, pi.z);
                         // squares accumulate in double for both types (pow(T,int) promotes float), then round to T
                         const double dd = add_rn(add_rn(mul_rn((double)d0, (double)d0), mul_rn((double)d1, (double)d1)),
@@ -523,20 +583,28 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
     int4 *sinfo = (int4 *)(w + L.sinfo);
 
     const int tb = 256, nblk = (n + tb - 1) / tb;
-    nb_init_kernel<<<1, 32, 0, st>>>(ext, d_status);
     const T *pos = d_coords;
     if (!is_cart) {
         nb_frac2cart_kernel<T><<<nblk, tb, 0, st>>>(P, d_coords, cart);
         pos = cart;
     }
-    if (any_open) nb_extent_kernel<T><<<(nblk < 1024 ? nblk : 1024), tb, 0, st>>>(P, pos, ext);
-    nb_grid_kernel<T><<<1, 32, 0, st>>>(P, ext, grid);
-    AI2B_CUDA(cudaMemsetAsync(count, 0, sizeof(int) * ((size_t)maxbins + 1), st));
-    nb_count_kernel<T><<<nblk, tb, 0, st>>>(P, grid, pos, ainfo, count);
-    const int sblk = (maxbins + 1 + SCAN_BLOCK - 1) / SCAN_BLOCK;
-    nb_scan1_kernel<<<sblk, SCAN_BLOCK, 0, st>>>(grid, count, start, bsum);
-    nb_scan2_kernel<<<1, SCAN_BLOCK, 0, st>>>(grid, bsum);
-    nb_scan3_kernel<<<sblk, SCAN_BLOCK, 0, st>>>(grid, start, bsum, cursor);
+    const bool small_grid = !any_open && prod + 1 <= 256 * 1024;
+    if (small_grid) {
+        const int ncount = (int)prod + 1;
+        nb_setup_periodic_kernel<T><<<(ncount + 255) / 256, 256, 0, st>>>(P, grid, count, ncount, d_status);
+        nb_count_kernel<T><<<nblk, tb, 0, st>>>(P, grid, pos, ainfo, count);
+        nb_scan_small_kernel<<<1, SCAN_BLOCK, 0, st>>>(grid, count, start, cursor);
+    } else {
+        nb_init_kernel<<<1, 32, 0, st>>>(ext, d_status);
+        if (any_open) nb_extent_kernel<T><<<(nblk < 1024 ? nblk : 1024), tb, 0, st>>>(P, pos, ext);
+        nb_grid_kernel<T><<<1, 32, 0, st>>>(P, ext, grid);
+        AI2B_CUDA(cudaMemsetAsync(count, 0, sizeof(int) * ((size_t)maxbins + 1), st));
+        nb_count_kernel<T><<<nblk, tb, 0, st>>>(P, grid, pos, ainfo, count);
+        const int sblk = (maxbins + 1 + SCAN_BLOCK - 1) / SCAN_BLOCK;
+        nb_scan1_kernel<<<sblk, SCAN_BLOCK, 0, st>>>(grid, count, start, bsum);
+        nb_scan2_kernel<<<1, SCAN_BLOCK, 0, st>>>(grid, bsum);
+        nb_scan3_kernel<<<sblk, SCAN_BLOCK, 0, st>>>(grid, start, bsum, cursor);
+    }
     nb_fill_kernel<T><<<nblk, tb, 0, st>>>(P, pos, ainfo, cursor, spos, sinfo);
     int sms = 148;
     {

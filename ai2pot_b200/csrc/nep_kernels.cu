@@ -184,6 +184,7 @@ __global__ void __launch_bounds__(NEP_WARPS * 32) nep_atom_kernel(const NepArgs<
     extern __shared__ __align__(16) unsigned char nep_smem[];
     __shared__ T blk_acc[10];   // energy + virial of the structure most of this block's atoms belong to
     __shared__ int blk_b;
+    __shared__ T iqs[96];       // 1 / q_scaler (descriptor count <= 20 + 12*4 = 68)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int sub = lane & (NEP_GROUP - 1), grp = lane / NEP_GROUP;
     const int slot_in_block = warp * NEP_APW + grp;
@@ -200,6 +201,10 @@ __global__ void __launch_bounds__(NEP_WARPS * 32) nep_atom_kernel(const NepArgs<
                             (size_t)slot_in_block * A.umax;
     const int ntot_n = A.n_r + A.n_a;
     const int nlm = A.l_max * A.l_max + 2 * A.l_max;
+    if (MODE != NEP_DESC) {
+        for (int k = threadIdx.x; k < A.nd; k += blockDim.x) iqs[k] = T(1) / A.qs[k];
+        __syncthreads();
+    }
 
     const int ntot = A.prefix[A.B];
     const int ngroups = gridDim.x * NEP_APB;
@@ -317,21 +322,34 @@ __global__ void __launch_bounds__(NEP_WARPS * 32) nep_atom_kernel(const NepArgs<
             continue;
         }
         const T *W0 = A.w0 + (size_t)ti * A.nneu * A.nd, *B0 = A.b0 + (size_t)ti * A.nneu, *W1 = A.w1 + (size_t)ti * A.nneu;
+        // network on the scaled descriptors q_k / q_scaler_k (kept in Eq until the backward pass overwrites it)
+        for (int k = sub; k < A.nd; k += NEP_GROUP) Eq[k] = q[k] * iqs[k];
+        __syncwarp();
         T es = T(0);
         for (int p = sub; p < A.nneu; p += NEP_GROUP) {
-            T h = T(0);
-            for (int k = 0; k < A.nd; k++) h += W0[p * A.nd + k] * q[k] / A.qs[k];
-            h += B0[p];
-            const T th = gtanh(h);
+            const T *wrow = W0 + p * A.nd;
+            T h0 = T(0), h1 = T(0);
+            int k = 0;
+            for (; k + 1 < A.nd; k += 2) {
+                h0 = fma(wrow[k], Eq[k], h0);
+                h1 = fma(wrow[k + 1], Eq[k + 1], h1);
+            }
+            if (k < A.nd) h0 = fma(wrow[k], Eq[k], h0);
+            const T th = gtanh(h0 + h1 + B0[p]);
             es += W1[p] * th;
             act[p] = W1[p] * (T(1) - th * th);
         }
         es = group_sum(es, gmask);
         __syncwarp();
         for (int k = sub; k < A.nd; k += NEP_GROUP) {
-            T acc = T(0);
-            for (int p = 0; p < A.nneu; p++) acc += act[p] * W0[p * A.nd + k];
-            Eq[k] = acc / A.qs[k];
+            T a0 = T(0), a1 = T(0);
+            int p = 0;
+            for (; p + 1 < A.nneu; p += 2) {
+                a0 = fma(act[p], W0[p * A.nd + k], a0);
+                a1 = fma(act[p + 1], W0[(p + 1) * A.nd + k], a1);
+            }
+            if (p < A.nneu) a0 = fma(act[p], W0[p * A.nd + k], a0);
+            Eq[k] = (a0 + a1) * iqs[k];
         }
         __syncwarp();
         for (int i = sub; i < A.nS; i += NEP_GROUP) {
