@@ -85,30 +85,6 @@ __device__ __forceinline__ T warp_xreduce(T (&v)[N], int lane)
     return r;
 }
 
-// Same job through shared memory: lane l stores its CNT (<= 16) values into a 16 x 33 tile (one
-// column per lane), then lane l sums half of row l >> 1; even lanes return the warp total of
-// v[l >> 1]. Costs CNT stores + 16 loads per lane instead of ~7 shuffle/select pairs per value.
-// `tile` must hold 16 * 33 elements and belong to this warp.
-template <typename T, int CNT>
-__device__ __forceinline__ T warp_tile_reduce16(const T (&v)[CNT], T *tile, int lane)
-{
-    static_assert(CNT <= 16, "at most 16 values per pass");
-#pragma unroll
-    for (int i = 0; i < CNT; i++) tile[i * 33 + lane] = v[i];
-    __syncwarp();
-    const int row = lane >> 1, half = lane & 1;
-    T s0 = T(0), s1 = T(0);
-    if (row < CNT) {
-        const T *p = tile + row * 33 + half * 16;
-#pragma unroll
-        for (int k = 0; k < 16; k += 2) { s0 += p[k]; s1 += p[k + 1]; }
-    }
-    T s = s0 + s1;
-    s += __shfl_xor_sync(FULL_MASK, s, 1);
-    __syncwarp();
-    return s;
-}
-
 __device__ __forceinline__ double gsqrt(double x) { return sqrt(x); }
 __device__ __forceinline__ float gsqrt(float x) { return sqrtf(x); }
 

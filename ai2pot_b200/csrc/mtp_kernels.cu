@@ -22,9 +22,8 @@ __global__ void __launch_bounds__(MTP_WARPS * 32, 4) mtp_fwd_kernel(const MtpPro
 {
     extern __shared__ __align__(32) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    T *Md = reinterpret_cast<T *>(smem_raw) + (size_t)warp * (A.ndp + MTP_MAX_MU * 32 + 16 * 33 + 3);
+    T *Md = reinterpret_cast<T *>(smem_raw) + (size_t)warp * (A.ndp + MTP_MAX_MU * 32);
     T *fr = Md + A.ndp;
-    T *tile = fr + MTP_MAX_MU * 32;
     const int ntot = A.prefix[A.B];
     const int nw = gridDim.x * MTP_WARPS;
     for (int t = blockIdx.x * MTP_WARPS + warp; t < ntot; t += nw) {
@@ -42,7 +41,7 @@ __global__ void __launch_bounds__(MTP_WARPS * 32, 4) mtp_fwd_kernel(const MtpPro
             ps.setup(P, A, A.rcs + slot * A.umax * 3, A.firstneigh + slot * A.umax, types, ti, nn, j0 + lane, lane, fr, nullptr);
             Powers<T, KD> pw;
             pw.set(ps.ux, ps.uy, ps.uz);
-            for (int m = 0; m < P.nmus; m++) fwd_mu<T, KD>(P.kmu[m], fr[m * 32 + lane], pw, Md + P.doff[m], tile, lane);
+            for (int m = 0; m < P.nmus; m++) fwd_mu<T, KD>(P.kmu[m], fr[m * 32 + lane], pw, Md + P.doff[m], lane);
         }
         __syncwarp();
         T *out = A.Mb + (size_t)t * A.nbp;
@@ -379,7 +378,7 @@ static int launch_mtp_v(const ai2b_mtp_program *prog, MtpArgs<T> A, void *ws, cu
     const long atoms_upper = (long)A.B * A.npad;
     const long need = (atoms_upper + MTP_WARPS - 1) / MTP_WARPS;
     {   // A: forward
-        const size_t smem = sizeof(T) * (size_t)(A.ndp + MTP_MAX_MU * 32 + 16 * 33 + 3) * MTP_WARPS;
+        const size_t smem = sizeof(T) * (size_t)(A.ndp + MTP_MAX_MU * 32) * MTP_WARPS;
         auto kern = mtp_fwd_kernel<T, KD, CSP>;
         static size_t configured = 0;
         static int per_sm = 0;

@@ -100,40 +100,48 @@ __device__ __forceinline__ void pair_weight(const MtpArgs<T> &A, const LossArgs<
 //   accM[q] += sum_lanes f mono_q
 //   accD[q] += sum_lanes ( a mono_q + bx ax mono(q - ex) + by ay mono(q - ey) + bz az mono(q - ez) )
 template <typename T, int KD, int D>
-__device__ __forceinline__ void fwd2_degree(T f, T a, T bx, T by, T bz, const Powers<T, KD> &p, T *accM, T *accD, T *tile, int lane)
+__device__ __forceinline__ void fwd2_degree(T f, T a, T bx, T by, T bz, const Powers<T, KD> &p, T *accM, T *accD, int lane)
 {
     constexpr int ND = ndeg(D);
     constexpr int GS = 16;
     static_for<0, (ND + GS - 1) / GS>([&](auto g) {
         constexpr int G = decltype(g)::value;
         constexpr int CNT = (ND - GS * G) < GS ? (ND - GS * G) : GS;
-        T v[CNT], w[CNT];
-        static_for<0, CNT>([&](auto i) {
+        constexpr int N = pow2ceil(CNT);
+        T v[N], w[N];
+        static_for<0, N>([&](auto i) {
             constexpr int I = decltype(i)::value;
-            constexpr Exp3 e = deg_exp(D, GS * G + I);
-            const T m = mono<T, KD, D, GS * G + I>(p);
-            v[I] = f * m;
-            T d = a * m;
-            if constexpr (e.x > 0) d = fma(bx * T(e.x), p.x[e.x - 1] * p.y[e.y] * p.z[e.z], d);
-            if constexpr (e.y > 0) d = fma(by * T(e.y), p.x[e.x] * p.y[e.y - 1] * p.z[e.z], d);
-            if constexpr (e.z > 0) d = fma(bz * T(e.z), p.x[e.x] * p.y[e.y] * p.z[e.z - 1], d);
-            w[I] = d;
+            if constexpr (I < CNT) {
+                constexpr Exp3 e = deg_exp(D, GS * G + I);
+                const T m = mono<T, KD, D, GS * G + I>(p);
+                v[I] = f * m;
+                T d = a * m;
+                if constexpr (e.x > 0) d = fma(bx * T(e.x), p.x[e.x - 1] * p.y[e.y] * p.z[e.z], d);
+                if constexpr (e.y > 0) d = fma(by * T(e.y), p.x[e.x] * p.y[e.y - 1] * p.z[e.z], d);
+                if constexpr (e.z > 0) d = fma(bz * T(e.z), p.x[e.x] * p.y[e.y] * p.z[e.z - 1], d);
+                w[I] = d;
+            } else {
+                v[I] = T(0);
+                w[I] = T(0);
+            }
         });
-        const T rv = warp_tile_reduce16<T, CNT>(v, tile, lane);
-        const T rw = warp_tile_reduce16<T, CNT>(w, tile, lane);
-        if ((lane & 1) == 0 && (lane >> 1) < CNT) {
-            accM[GS * G + (lane >> 1)] += rv;
-            accD[GS * G + (lane >> 1)] += rw;
+        const T rv = warp_xreduce<T, N>(v, lane);
+        const T rw = warp_xreduce<T, N>(w, lane);
+        constexpr int SH = 5 - ilog2(N);
+        const int idx = lane >> SH;
+        if ((lane & ((1 << SH) - 1)) == 0 && idx < CNT) {
+            accM[GS * G + idx] += rv;
+            accD[GS * G + idx] += rw;
         }
     });
 }
 template <typename T, int KD>
-__device__ __forceinline__ void fwd2_mu(int kmu, T f, T a, T bx, T by, T bz, const Powers<T, KD> &p, T *accM, T *accD, T *tile, int lane)
+__device__ __forceinline__ void fwd2_mu(int kmu, T f, T a, T bx, T by, T bz, const Powers<T, KD> &p, T *accM, T *accD, int lane)
 {
 #define AI2B_FWD2_DEG(D)                                                                          \
     if constexpr (D <= KD) {                                                                      \
         if (kmu < D) return;                                                                      \
-        fwd2_degree<T, KD, D>(f, a, bx, by, bz, p, accM + ncan(D - 1), accD + ncan(D - 1), tile, lane); \
+        fwd2_degree<T, KD, D>(f, a, bx, by, bz, p, accM + ncan(D - 1), accD + ncan(D - 1), lane); \
     }
     AI2B_FWD2_DEG(0) AI2B_FWD2_DEG(1) AI2B_FWD2_DEG(2) AI2B_FWD2_DEG(3) AI2B_FWD2_DEG(4)
     AI2B_FWD2_DEG(5) AI2B_FWD2_DEG(6) AI2B_FWD2_DEG(7) AI2B_FWD2_DEG(8)
@@ -163,11 +171,10 @@ __global__ void __launch_bounds__(MTP_WARPS * 32, 3) mtp_loss_fwd_kernel(const M
 {
     extern __shared__ __align__(32) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    T *Md = reinterpret_cast<T *>(smem_raw) + (size_t)warp * (2 * A.ndp + 2 * MTP_MAX_MU * 32 + 16 * 33 + 3);
+    T *Md = reinterpret_cast<T *>(smem_raw) + (size_t)warp * (2 * A.ndp + 2 * MTP_MAX_MU * 32);
     T *Dd = Md + A.ndp;
     T *fr = Dd + A.ndp;
     T *fdv = fr + MTP_MAX_MU * 32;
-    T *tile = fdv + MTP_MAX_MU * 32;
     const int ntot = A.prefix[A.B];
     const int nw = gridDim.x * MTP_WARPS;
     for (int t = blockIdx.x * MTP_WARPS + warp; t < ntot; t += nw) {
@@ -190,7 +197,7 @@ __global__ void __launch_bounds__(MTP_WARPS * 32, 3) mtp_loss_fwd_kernel(const M
             pw.set(ps.ux, ps.uy, ps.uz);
             for (int m = 0; m < P.nmus; m++) {
                 const T f = fr[m * 32 + lane], fd = fdv[m * 32 + lane];
-                fwd2_mu<T, KD>(P.kmu[m], f, fd * ppar, f * qx, f * qy, f * qz, pw, Md + P.doff[m], Dd + P.doff[m], tile, lane);
+                fwd2_mu<T, KD>(P.kmu[m], f, fd * ppar, f * qx, f * qy, f * qz, pw, Md + P.doff[m], Dd + P.doff[m], lane);
             }
         }
         __syncwarp();
@@ -543,7 +550,7 @@ static int launch_loss_bwd_v(const ai2b_mtp_program *prog, MtpArgs<T> A, LossArg
     const long atoms_upper = (long)A.B * A.npad;
     const long need = (atoms_upper + MTP_WARPS - 1) / MTP_WARPS;
     {
-        const size_t smem = sizeof(T) * (size_t)(2 * A.ndp + 2 * MTP_MAX_MU * 32 + 16 * 33 + 3) * MTP_WARPS;
+        const size_t smem = sizeof(T) * (size_t)(2 * A.ndp + 2 * MTP_MAX_MU * 32) * MTP_WARPS;
         auto kern = mtp_loss_fwd_kernel<T, KD, CSP>;
         static size_t configured = 0;
         static int per_sm = 0;

@@ -78,33 +78,36 @@ __device__ __forceinline__ T mono(const Powers<T, KD> &p)
 }
 
 // Forward: acc[q] += sum over lanes of f * mono_q for the ndeg(D) monomials of degree D.
-// `acc` points at this degree's slice of the warp's dense moment array in shared memory, `tile`
-// at the warp's 16 x 33 reduction tile.
+// `acc` points at this degree's slice of the warp's dense moment array in shared memory.
 template <typename T, int KD, int D>
-__device__ __forceinline__ void fwd_degree(T f, const Powers<T, KD> &p, T *acc, T *tile, int lane)
+__device__ __forceinline__ void fwd_degree(T f, const Powers<T, KD> &p, T *acc, int lane)
 {
     constexpr int ND = ndeg(D);
-    constexpr int GS = 16;
+    constexpr int GS = 16;   // values reduced together: 16 keeps the staging array at 32 registers (fp64)
     static_for<0, (ND + GS - 1) / GS>([&](auto g) {
         constexpr int G = decltype(g)::value;
         constexpr int CNT = (ND - GS * G) < GS ? (ND - GS * G) : GS;
-        T v[CNT];
-        static_for<0, CNT>([&](auto i) {
+        constexpr int N = pow2ceil(CNT);
+        T v[N];
+        static_for<0, N>([&](auto i) {
             constexpr int I = decltype(i)::value;
-            v[I] = f * mono<T, KD, D, GS * G + I>(p);
+            if constexpr (I < CNT) v[I] = f * mono<T, KD, D, GS * G + I>(p);
+            else v[I] = T(0);
         });
-        const T r = warp_tile_reduce16<T, CNT>(v, tile, lane);
-        if ((lane & 1) == 0 && (lane >> 1) < CNT) acc[GS * G + (lane >> 1)] += r;
+        const T r = warp_xreduce<T, N>(v, lane);
+        constexpr int SH = 5 - ilog2(N);
+        const int idx = lane >> SH;
+        if ((lane & ((1 << SH) - 1)) == 0 && idx < CNT) acc[GS * G + idx] += r;
     });
 }
 
 template <typename T, int KD>
-__device__ __forceinline__ void fwd_mu(int kmu, T f, const Powers<T, KD> &p, T *acc, T *tile, int lane)
+__device__ __forceinline__ void fwd_mu(int kmu, T f, const Powers<T, KD> &p, T *acc, int lane)
 {
 #define AI2B_FWD_DEG(D)                                                  \
     if constexpr (D <= KD) {                                             \
         if (kmu < D) return;                                             \
-        fwd_degree<T, KD, D>(f, p, acc + ncan(D - 1), tile, lane);       \
+        fwd_degree<T, KD, D>(f, p, acc + ncan(D - 1), lane);             \
     }
     AI2B_FWD_DEG(0) AI2B_FWD_DEG(1) AI2B_FWD_DEG(2) AI2B_FWD_DEG(3) AI2B_FWD_DEG(4)
     AI2B_FWD_DEG(5) AI2B_FWD_DEG(6) AI2B_FWD_DEG(7) AI2B_FWD_DEG(8)
