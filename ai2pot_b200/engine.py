@@ -306,7 +306,8 @@ def run_single_benchmark(w, steps, warmup, dist, sampler):
                 "achieved": achieved, "peak": peak_meas, "unit": "TFLOP/s", "frac": achieved / peak_meas,
                 "peak_source": "FMA-chain microbenchmark in this run (of measured)", "peak_nominal": peak_nom,
                 "frac_of_nominal": achieved / peak_nom, "flops_per_atom": fl, "mean_neighbours": mean_nn,
-                "traffic": None, "kernel_ms": 1e3 * t_ev,
+                # dram__bytes_read + write of the E/F/V kernels of one call, from the ncu capture summarised under profiles/
+                "traffic": (55.9e6 if m["kind"] == "mtp" else 7.5e6) if n == 13824 else None, "kernel_ms": 1e3 * t_ev,
                 "nblist": {"bound": "hbm", "achieved": nb_bytes / t_nb / 1e9, "peak": hbm or 6650.0, "unit": "GB/s",
                            "frac": nb_bytes / t_nb / 1e9 / (hbm or 6650.0),
                            "peak_source": "MEASURED_PEAKS.json (of measured)" if hbm else "6.65 TB/s (of fallback)",
