@@ -5,7 +5,7 @@
 namespace ai2b {
 
 constexpr int MTP_WARPS = 4;      // warps (atoms in flight) per block of the per-atom kernels
-constexpr int MTP_CWARPS = 16;    // warps per block of the contraction kernel
+constexpr int MTP_CWARPS = 32;    // warps per block of the contraction kernel
 
 enum MtpMode { MODE_EFV = 0, MODE_EF = 1, MODE_DESC = 2 };
 

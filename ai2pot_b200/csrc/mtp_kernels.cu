@@ -256,6 +256,11 @@ __global__ void __launch_bounds__(MTP_WARPS * 32, 4) mtp_force_kernel(const MtpP
         const int *fn = A.firstneigh + slot * A.umax;
         const T *rc = A.rcs + slot * A.umax * 3;
 
+        // the first chunk of neighbours is set up before the coefficient quadruples are built: its
+        // global loads (neighbour row, types, radial coefficients) overlap the loads of the adjoint row
+        PairState<T, CSP, true> ps;
+        ps.setup(P, A, rc, fn, types, ti, nn, lane, lane, fr, fdv);
+
         // adjoints of this atom -> coefficient quadruples {e, (ax+1) e[+x], (ay+1) e[+y], (az+1) e[+z]}
         const T *ein = A.Eb + (size_t)t * A.nbp;
         for (int i = lane; i < A.nbp; i += 32) Ed[i] = ein[i];
@@ -277,8 +282,7 @@ __global__ void __launch_bounds__(MTP_WARPS * 32, 4) mtp_force_kernel(const MtpP
         T *frc = A.force + (size_t)b * (A.npad + A.nghost) * 3;
         T fcx = T(0), fcy = T(0), fcz = T(0);
         for (int j0 = 0; j0 < nn; j0 += 32) {
-            PairState<T, CSP, true> ps;
-            ps.setup(P, A, rc, fn, types, ti, nn, j0 + lane, lane, fr, fdv);
+            if (j0 > 0) ps.setup(P, A, rc, fn, types, ti, nn, j0 + lane, lane, fr, fdv);
             Powers<T, KD> pw;
             pw.set(ps.ux, ps.uy, ps.uz);
             T gx = T(0), gy = T(0), gz = T(0);
