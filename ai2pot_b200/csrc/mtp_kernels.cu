@@ -52,7 +52,12 @@ __global__ void __launch_bounds__(MTP_WARPS * 32, 4) mtp_fwd_kernel(const MtpPro
 
 // ---- kernel B: products and adjoint sweep, lanes = atoms ----------------------------------------
 // TA atoms per tile (32, 16 or 8); with TA < 32 the 32/TA lane groups of a warp work on different
-// destination moments. Shared memory: M[nm][TA+1] and (unless DESC) E[nm][TA+1].
+// rows. Shared memory: M[nm][TA+1] and (unless DESC) E[nm][TA+1], then the row tables.
+// Persistent: one block per SM walks over tiles; the row tables are staged once, and the next
+// tile's moment rows are fetched into registers while the current tile is being processed, so
+// no global-memory latency sits between two tiles.
+constexpr int MTP_PREF = 8;   // prefetch registers per thread: basic moments <= 32 * MTP_PREF
+
 template <typename T, int TA, int MODE, bool SMEMTAB>
 __global__ void __launch_bounds__(MTP_CWARPS * 32, 1) mtp_contract_kernel(const MtpProgramDev P, const MtpArgs<T> A)
 {
@@ -63,7 +68,6 @@ __global__ void __launch_bounds__(MTP_CWARPS * 32, 1) mtp_contract_kernel(const 
     __shared__ T esum[NWORK][TA];
     T *M = reinterpret_cast<T *>(smem_raw);
     T *E = M + (size_t)P.nm * LD;
-    // row tables staged in shared memory: every lane of a group reads the same row (broadcast)
     const size_t arr_bytes = (sizeof(T) * (size_t)P.nm * LD * (MODE == MODE_DESC ? 1 : 2) + 15) & ~size_t(15);
     int2 *s_fwd = reinterpret_cast<int2 *>(smem_raw + arr_bytes);
     int2 *s_rev = s_fwd + P.nt;
@@ -71,142 +75,156 @@ __global__ void __launch_bounds__(MTP_CWARPS * 32, 1) mtp_contract_kernel(const 
     const int a = lane % TA, wid = warp * G + lane / TA;
     const T *Ma = M + a, *Ea = E + a;
     const int ntot = A.prefix[A.B];
-    const int t0 = blockIdx.x * TA;
-    if (t0 >= ntot) return;
+    const int ntiles = (ntot + TA - 1) / TA;
     const int nthreads = MTP_CWARPS * 32;
+    if ((int)blockIdx.x >= ntiles) return;
 
-    for (int i = threadIdx.x; i < P.nm * LD; i += nthreads) {
-        M[i] = T(0);
-        if (MODE != MODE_DESC) E[i] = T(0);
-    }
-    // staged with the moment indices already scaled to element offsets (index * LD fits 16 bits)
-    auto scale = [](int2 r) { return make_int2(((r.x & 0xffff) * LD) | (((r.x >> 16) & 0xffff) * LD) << 16, r.y); };
+    // row tables, staged once, with the moment indices already scaled to element offsets (index * LD fits 16 bits)
+    auto scale = [](int2 r) {
+        return make_int2(((r.x & 0xffff) * LD) | (((r.x >> 16) & 0xffff) * LD) << 16, (r.y & 0xffff) | (((r.y >> 16) & 0xffff) * LD) << 16);
+    };
     if (SMEMTAB) {
 #pragma unroll 4
-        for (int i = threadIdx.x; i < P.nt; i += nthreads) s_fwd[i] = scale(P.fwd_rows[i]);
+        for (int i = threadIdx.x; i < P.nt; i += nthreads) s_fwd[i] = scale(P.fwd_flat[i]);
         if (MODE != MODE_DESC)
 #pragma unroll 4
-            for (int i = threadIdx.x; i < 2 * P.nt; i += nthreads) s_rev[i] = scale(P.rev_ents[i]);
+            for (int i = threadIdx.x; i < 2 * P.nt; i += nthreads) s_rev[i] = scale(P.rev_flat[i]);
     }
     // large tables (template levels above 16) stay in global memory
-    auto frow = [&](int r) { return SMEMTAB ? s_fwd[r] : scale(P.fwd_rows[r]); };
-    auto rrow = [&](int r) { return SMEMTAB ? s_rev[r] : scale(P.rev_ents[r]); };
-    __syncthreads();
-    // rows of the tile -> M[basic][atom] (coalesced global reads, padded rows in shared memory)
-#pragma unroll 4
-    for (int idx = threadIdx.x; idx < TA * A.nbp; idx += nthreads) {
-        const int at = idx / A.nbp, i = idx - at * A.nbp;
-        if (i < P.nb && t0 + at < ntot) M[i * LD + at] = A.Mb[(size_t)(t0 + at) * A.nbp + i];
-    }
-    __syncthreads();
+    auto frow = [&](int r) { return SMEMTAB ? s_fwd[r] : scale(P.fwd_flat[r]); };
+    auto rrow = [&](int r) { return SMEMTAB ? s_rev[r] : scale(P.rev_flat[r]); };
 
-    for (int lev = 0; lev < P.nlev; lev++) {
-        const int dend = P.fwd_lev_off[lev + 1];
-        int d = P.fwd_lev_off[lev] + wid;
-        int4 nxt = d < dend ? P.fwd_dst[d] : make_int4(0, 0, 0, 0);
-        for (; d < dend; d += NWORK) {
-            const int4 ds = nxt;
-            if (d + NWORK < dend) nxt = P.fwd_dst[d + NWORK];   // header of the next destination, in flight during this one
-            T acc0 = T(0), acc1 = T(0), acc2 = T(0), acc3 = T(0);
-            int r = ds.y;
-            for (; r + 3 < ds.z; r += 4) {
-                const int2 r0 = frow(r), r1 = frow(r + 1), r2 = frow(r + 2), r3 = frow(r + 3);
-                acc0 = fma(T(__int_as_float(r0.y)) * Ma[r0.x & 0xffff], Ma[(unsigned)r0.x >> 16], acc0);
-                acc1 = fma(T(__int_as_float(r1.y)) * Ma[r1.x & 0xffff], Ma[(unsigned)r1.x >> 16], acc1);
-                acc2 = fma(T(__int_as_float(r2.y)) * Ma[r2.x & 0xffff], Ma[(unsigned)r2.x >> 16], acc2);
-                acc3 = fma(T(__int_as_float(r3.y)) * Ma[r3.x & 0xffff], Ma[(unsigned)r3.x >> 16], acc3);
-            }
-            for (; r < ds.z; r++) {
-                const int2 r0 = frow(r);
-                acc0 = fma(T(__int_as_float(r0.y)) * Ma[r0.x & 0xffff], Ma[(unsigned)r0.x >> 16], acc0);
-            }
-            M[ds.x * LD + a] += (acc0 + acc1) + (acc2 + acc3);
-        }
-        __syncthreads();
-    }
-
-    // per-atom bookkeeping (all lanes of a column agree)
-    const int t = t0 + a;
-    const bool valid = t < ntot;
-    int b = 0;
-    size_t slot = 0;
-    if (valid) {
-        b = find_structure(A.prefix, A.B, t);
-        slot = (size_t)b * A.npad + (t - A.prefix[b]);
-    }
-
-    if (MODE == MODE_DESC) {
-        if (valid)
-            for (int s = wid; s < P.ns; s += NWORK) A.desc[slot * P.ns + s] = M[P.map[s] * LD + a];
-        return;
-    }
-
-    // site energy and adjoint seeds (linearMtp.h:281-295)
-    T es = T(0);
-#pragma unroll 4
-    for (int s = wid; s < P.ns; s += NWORK) {
-        const int m = P.map[s];
-        const T w = A.lin[s] / A.qs[s];
-        es = fma(w, M[m * LD + a], es);
-        E[m * LD + a] = w;
-    }
-    esum[wid][a] = es;
-    __syncthreads();
-    if (wid == 0) {
-        T e = T(0);
+    // moment rows of a tile: warp w fetches atom w (and w + nwarps, ..), lanes run over the row
+    const bool can_prefetch = P.nb <= 32 * MTP_PREF && TA <= MTP_CWARPS;
+    T pre[MTP_PREF];
+    auto fetch = [&](int tile) {
 #pragma unroll
-        for (int k = 0; k < NWORK; k++) e += esum[k][a];
-        if (valid) {
-            const int *types = A.types + (size_t)b * (A.npad + A.nghost);
-            e += A.bias[types[A.bilist[slot]]];
-        } else {
-            e = T(0);
+        for (int k = 0; k < MTP_PREF; k++) {
+            const int i = lane + 32 * k, t = tile * TA + warp;
+            pre[k] = (warp < TA && t < ntot && i < P.nb) ? A.Mb[(size_t)t * A.nbp + i] : T(0);
         }
-        // one atomic per structure present in these TA atoms. Every lane of the group walks all TA
-        // lanes (a fixed trip count: the shuffles must be executed by the whole group together)
-        const unsigned grp = (TA == 32) ? FULL_MASK : (((1u << TA) - 1u) << (lane / TA * TA));
-        const int base = lane / TA * TA;
-        const int key = valid ? b : -1;
-        T tot = T(0);
-        int leader = TA;
-        for (int k = 0; k < TA; k++) {
-            const T ek = __shfl_sync(grp, e, base + k);
-            const int bk = __shfl_sync(grp, key, base + k);
-            if (bk == key) { tot += ek; leader = min(leader, k); }
-        }
-        if (valid && a == leader) atomicAdd(A.etot + b, tot);
-    }
+    };
+    if (can_prefetch) fetch(blockIdx.x);
 
-    for (int k = 0; k < P.nlev; k++) {
-        const int dend = P.rev_lev_off[k + 1];
-        int d = P.rev_lev_off[k] + wid;
-        int4 nxt = d < dend ? P.rev_mom[d] : make_int4(0, 0, 0, 0);
-        for (; d < dend; d += NWORK) {
-            const int4 ms = nxt;
-            if (d + NWORK < dend) nxt = P.rev_mom[d + NWORK];
-            T acc0 = T(0), acc1 = T(0), acc2 = T(0), acc3 = T(0);
-            int e = ms.y;
-            for (; e + 3 < ms.z; e += 4) {
-                const int2 r0 = rrow(e), r1 = rrow(e + 1), r2 = rrow(e + 2), r3 = rrow(e + 3);
-                acc0 = fma(T(__int_as_float(r0.y)) * Ea[(unsigned)r0.x >> 16], Ma[r0.x & 0xffff], acc0);
-                acc1 = fma(T(__int_as_float(r1.y)) * Ea[(unsigned)r1.x >> 16], Ma[r1.x & 0xffff], acc1);
-                acc2 = fma(T(__int_as_float(r2.y)) * Ea[(unsigned)r2.x >> 16], Ma[r2.x & 0xffff], acc2);
-                acc3 = fma(T(__int_as_float(r3.y)) * Ea[(unsigned)r3.x >> 16], Ma[r3.x & 0xffff], acc3);
-            }
-            for (; e < ms.z; e++) {
-                const int2 r0 = rrow(e);
-                acc0 = fma(T(__int_as_float(r0.y)) * Ea[(unsigned)r0.x >> 16], Ma[r0.x & 0xffff], acc0);
-            }
-            E[ms.x * LD + a] += (acc0 + acc1) + (acc2 + acc3);
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const int t0 = tile * TA;
+        for (int i = threadIdx.x; i < P.nm * LD; i += nthreads) {
+            M[i] = T(0);
+            if (MODE != MODE_DESC) E[i] = T(0);
         }
         __syncthreads();
-    }
+        if (can_prefetch) {
+            if (warp < TA) {
+#pragma unroll
+                for (int k = 0; k < MTP_PREF; k++) {
+                    const int i = lane + 32 * k;
+                    if (i < P.nb) M[i * LD + warp] = pre[k];
+                }
+            }
+            if (tile + (int)gridDim.x < ntiles) fetch(tile + gridDim.x);   // in flight during this tile
+        } else {
+            for (int at = warp; at < TA && t0 + at < ntot; at += MTP_CWARPS) {
+                const T *src = A.Mb + (size_t)(t0 + at) * A.nbp;
+                for (int i = lane; i < P.nb; i += 32) M[i * LD + at] = src[i];
+            }
+        }
+        __syncthreads();
 
-    // adjoints of the basic moments, back to per-atom rows
+        // product rows: every depth's rows are one contiguous stream; each worker takes an equal share
+        // of it and adds a destination's partial sum when the stream leaves that destination
+        // (shared-memory atomic add: a destination may straddle two workers)
+        for (int lev = 0; lev < P.nlev; lev++) {
+            const int R0 = P.fwd_lev_row[lev], len = P.fwd_lev_row[lev + 1] - R0;
+            const int rb = R0 + (int)((long)len * wid / NWORK), re = R0 + (int)((long)len * (wid + 1) / NWORK);
+            T acc = T(0);
 #pragma unroll 4
-    for (int idx = threadIdx.x; idx < TA * A.nbp; idx += nthreads) {
-        const int at = idx / A.nbp, i = idx - at * A.nbp;
-        if (t0 + at < ntot) A.Eb[(size_t)(t0 + at) * A.nbp + i] = i < P.nb ? E[i * LD + at] : T(0);
+            for (int r = rb; r < re; r++) {
+                const int2 row = frow(r);
+                acc = fma(T(row.y & 0xff) * Ma[row.x & 0xffff], Ma[(unsigned)row.x >> 16], acc);
+                if ((row.y & 0x100) || r == re - 1) {
+                    atomicAdd(M + ((unsigned)row.y >> 16) + a, acc);
+                    acc = T(0);
+                }
+            }
+            __syncthreads();
+        }
+
+        // per-atom bookkeeping (all lanes of a column agree)
+        const int t = t0 + a;
+        const bool valid = t < ntot;
+        int b = 0;
+        size_t slot = 0;
+        if (valid) {
+            b = find_structure(A.prefix, A.B, t);
+            slot = (size_t)b * A.npad + (t - A.prefix[b]);
+        }
+
+        if (MODE == MODE_DESC) {
+            if (valid)
+                for (int s = wid; s < P.ns; s += NWORK) A.desc[slot * P.ns + s] = M[P.map[s] * LD + a];
+            __syncthreads();
+            continue;
+        }
+
+        // site energy and adjoint seeds (linearMtp.h:281-295)
+        T es = T(0);
+#pragma unroll 4
+        for (int s = wid; s < P.ns; s += NWORK) {
+            const int m = P.map[s];
+            const T w = A.lin[s] / A.qs[s];
+            es = fma(w, M[m * LD + a], es);
+            E[m * LD + a] = w;
+        }
+        esum[wid][a] = es;
+        __syncthreads();
+        if (wid == 0) {
+            T e = T(0);
+#pragma unroll
+            for (int k = 0; k < NWORK; k++) e += esum[k][a];
+            if (valid) {
+                const int *types = A.types + (size_t)b * (A.npad + A.nghost);
+                e += A.bias[types[A.bilist[slot]]];
+            } else {
+                e = T(0);
+            }
+            // one atomic per structure present in these TA atoms. Every lane of the group walks all TA
+            // lanes (a fixed trip count: the shuffles must be executed by the whole group together)
+            const unsigned grp = (TA == 32) ? FULL_MASK : (((1u << TA) - 1u) << (lane / TA * TA));
+            const int base = lane / TA * TA;
+            const int key = valid ? b : -1;
+            T tot = T(0);
+            int leader = TA;
+            for (int k = 0; k < TA; k++) {
+                const T ek = __shfl_sync(grp, e, base + k);
+                const int bk = __shfl_sync(grp, key, base + k);
+                if (bk == key) { tot += ek; leader = min(leader, k); }
+            }
+            if (valid && a == leader) atomicAdd(A.etot + b, tot);
+        }
+
+        // adjoint sweep, deepest sources first: E[source] += sum mult E[dst] M[other]
+        for (int k = 0; k < P.nlev; k++) {
+            const int R0 = P.rev_lev_row[k], len = P.rev_lev_row[k + 1] - R0;
+            const int rb = R0 + (int)((long)len * wid / NWORK), re = R0 + (int)((long)len * (wid + 1) / NWORK);
+            T acc = T(0);
+#pragma unroll 4
+            for (int r = rb; r < re; r++) {
+                const int2 row = rrow(r);
+                acc = fma(T(row.y & 0xff) * Ea[(unsigned)row.x >> 16], Ma[row.x & 0xffff], acc);
+                if ((row.y & 0x100) || r == re - 1) {
+                    atomicAdd(E + ((unsigned)row.y >> 16) + a, acc);
+                    acc = T(0);
+                }
+            }
+            __syncthreads();
+        }
+
+        // adjoints of the basic moments, back to per-atom rows
+        for (int at = warp; at < TA && t0 + at < ntot; at += MTP_CWARPS) {
+            T *dstp = A.Eb + (size_t)(t0 + at) * A.nbp;
+            for (int i = lane; i < A.nbp; i += 32) dstp[i] = i < P.nb ? E[i * LD + at] : T(0);
+        }
+        __syncthreads();
     }
 }
 
@@ -337,7 +355,8 @@ static int launch_contract(const MtpProgramDev &P, const MtpArgs<T> &A, long ato
     auto kern = mtp_contract_kernel<T, TA, MODE, SMEMTAB>;
     static size_t configured = 0;
     if (int rc = set_smem(kern, smem, &configured)) return rc;
-    const long tiles = (atoms_upper + TA - 1) / TA;
+    long tiles = (atoms_upper + TA - 1) / TA;
+    if (tiles > sm_count()) tiles = sm_count();      // persistent: one block per SM walks over the tiles
     kern<<<(unsigned)tiles, MTP_CWARPS * 32, smem, st>>>(P, A);
     AI2B_CUDA(cudaGetLastError());
     return AI2B_OK;

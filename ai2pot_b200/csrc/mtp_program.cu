@@ -254,6 +254,30 @@ extern "C" int ai2b_mtp_program_create(int nm, int nb, const int *basic, int nt,
     std::vector<int2> fwd_rows(fwd_ab.size()), rev_ents(rev_od.size());
     for (size_t i = 0; i < fwd_ab.size(); i++) { int bits; memcpy(&bits, &fwd_mf[i], 4); fwd_rows[i] = make_int2(fwd_ab[i], bits); }
     for (size_t i = 0; i < rev_od.size(); i++) { int bits; memcpy(&bits, &rev_mf[i], 4); rev_ents[i] = make_int2(rev_od[i], bits); }
+    // flat streams (same row order as fwd_ab / rev_od)
+    std::vector<int2> fwd_flat(fwd_ab.size()), rev_flat(rev_od.size());
+    int maxmult = 0;
+    for (int lev = 0; lev <= MTP_MAX_LEV; lev++) {
+        const int di = P.fwd_lev_off[lev];
+        P.fwd_lev_row[lev] = di < (int)fwd_dst.size() ? fwd_dst[di].y : (int)fwd_ab.size();
+        const int mi = P.rev_lev_off[lev];
+        P.rev_lev_row[lev] = mi < (int)rev_mom.size() ? rev_mom[mi].y : (int)rev_od.size();
+    }
+    for (const int4 &d : fwd_dst)
+        for (int r = d.y; r < d.z; r++) {
+            const int mult = (int)fwd_md[r];
+            maxmult = std::max(maxmult, mult);
+            fwd_flat[r] = make_int2(fwd_ab[r], (mult & 0xff) | ((r == d.z - 1) ? 0x100 : 0) | (d.x << 16));
+        }
+    for (const int4 &m : rev_mom)
+        for (int r = m.y; r < m.z; r++) {
+            const int mult = (int)rev_md[r];
+            maxmult = std::max(maxmult, mult);
+            rev_flat[r] = make_int2(rev_od[r], (mult & 0xff) | ((r == m.z - 1) ? 0x100 : 0) | (m.x << 16));
+        }
+    AI2B_REQUIRE(maxmult <= 255, AI2B_ERR_UNSUPPORTED, "product multiplier %d > 255", maxmult);
+    for (int t = 0; t < nt; t++)
+        AI2B_REQUIRE(times[4 * t + 2] >= 0, AI2B_ERR_UNSUPPORTED, "negative product multiplier in row %d", t);
     std::vector<int> map(mapping, mapping + ns);
     for (int s = 0; s < ns; s++)
         AI2B_REQUIRE(map[s] >= 0 && map[s] < nm, AI2B_ERR_INVALID, "alpha_moment_mapping[%d] out of range", s);
@@ -262,7 +286,7 @@ extern "C" int ai2b_mtp_program_create(int nm, int nb, const int *basic, int nt,
     size_t o_bd = blob.add(basic_dense), o_db = blob.add(dense_basic), o_e4d = blob.add(e4d), o_g = blob.add(e4g), o_m = blob.add(e4m), o_fd = blob.add(fwd_dst),
            o_fr = blob.add(fwd_ab), o_fmf = blob.add(fwd_mf), o_fmd = blob.add(fwd_md), o_rm = blob.add(rev_mom),
            o_re = blob.add(rev_od), o_rmf = blob.add(rev_mf), o_rmd = blob.add(rev_md), o_map = blob.add(map);
-    size_t o_frow = blob.add(fwd_rows), o_rent = blob.add(rev_ents);
+    size_t o_frow = blob.add(fwd_rows), o_rent = blob.add(rev_ents), o_ff = blob.add(fwd_flat), o_rf = blob.add(rev_flat);
     ai2b_mtp_program *prog = new ai2b_mtp_program;
     prog->blob_bytes = blob.bytes.size();
     prog->d_blob = nullptr;
@@ -292,6 +316,8 @@ extern "C" int ai2b_mtp_program_create(int nm, int nb, const int *basic, int nt,
     P.map = (const int *)(b + o_map);
     P.fwd_rows = (const int2 *)(b + o_frow);
     P.rev_ents = (const int2 *)(b + o_rent);
+    P.fwd_flat = (const int2 *)(b + o_ff);
+    P.rev_flat = (const int2 *)(b + o_rf);
     prog->dev = P;
     *out = prog;
     return AI2B_OK;

@@ -34,6 +34,12 @@ struct MtpProgramDev {
     const double *fwd_mult_d;
     const int2 *fwd_rows;           // [nt] {a | b<<16, multiplier as float bits}: one 8-byte load per row
     const int2 *rev_ents;           // [2 nt] {other | dst<<16, multiplier as float bits}
+    // flat row streams for the lanes-as-atoms kernel: rows of one depth are contiguous, a flag marks the
+    // last row of each destination, so any contiguous share of a depth's rows can be given to a worker
+    const int2 *fwd_flat;           // [nt]   {a | b<<16, mult | last<<8 | dst<<16}
+    const int2 *rev_flat;           // [2 nt] {other | dst<<16, mult | last<<8 | source<<16}
+    int fwd_lev_row[MTP_MAX_LEV + 1];
+    int rev_lev_row[MTP_MAX_LEV + 1];
     const int4 *rev_mom;            // {m, entry_begin, entry_end, -}
     const int *rev_od;              // [2 nt] other | dst<<16
     const float *rev_mult_f;
