@@ -52,8 +52,9 @@ __constant__ double c_C3B[NEP_NLM] = {
 
 __device__ __forceinline__ float gtanh(float x) { return tanhf(x); }
 __device__ __forceinline__ double gtanh(double x) { return tanh(x); }
-__device__ __forceinline__ void gsincos(float x, float *s, float *c) { sincosf(x, s, c); }
-__device__ __forceinline__ void gsincos(double x, double *s, double *c) { sincos(x, s, c); }
+// sin(pi x), cos(pi x): exact argument reduction, no slow path for large arguments
+__device__ __forceinline__ void gsincospi(float x, float *s, float *c) { sincospif(x, s, c); }
+__device__ __forceinline__ void gsincospi(double x, double *s, double *c) { sincospi(x, s, c); }
 
 // f_k = fc (T_k(x)+1)/2 and d f_k / dr, k < CSP (entries >= cs meet zero coefficients)
 template <typename T, int CSP>
@@ -61,7 +62,7 @@ __device__ __forceinline__ void nep_radial(T r, T rc, T (&f)[CSP], T (&df)[CSP])
 {
     const T pi = T(3.14159265358979323846);
     T sn, cn;
-    gsincos(pi * r / rc, &sn, &cn);
+    gsincospi(r / rc, &sn, &cn);
     const T fc = T(0.5) * (T(1) + cn), dfc = T(-0.5) * sn * pi / rc;
     const T s = r / rc - T(1);
     const T x = T(2) * s * s - T(1), xc = T(4) / rc * s;
@@ -82,45 +83,65 @@ __device__ __forceinline__ void nep_radial(T r, T rc, T (&f)[CSP], T (&df)[CSP])
     }
 }
 
-// harmonic polynomials b[l*l-1+m] (l = 1..4) at (x,y,z), r2 = x^2+y^2+z^2, and, if GRAD, their
-// Cartesian gradients (closed forms tabulated in nep_utilities.h:100-383)
+// A gradient component that is identically zero: accumulating it is skipped at compile time.
+struct NepZero {};
+template <typename T> __device__ __forceinline__ void nep_set(T &d, T v) { d = v; }
+template <typename T> __device__ __forceinline__ void nep_set(T &d, NepZero) { d = T(0); }
+template <typename T, int N>
+__device__ __forceinline__ void nep_acc(const T (&e)[N], T v, T (&acc)[N])
+{
+#pragma unroll
+    for (int i = 0; i < N; i++) acc[i] = fma(e[i], v, acc[i]);
+}
+template <typename T, int N>
+__device__ __forceinline__ void nep_acc(const T (&)[N], NepZero, T (&)[N]) {}
+
+// Harmonic polynomials b[l*l-1+m] (l = 1..4) at (x,y,z) and their Cartesian gradients (closed
+// forms tabulated in nep_utilities.h:100-383), as a list X(index, value, d/dx, d/dy, d/dz) over
+// the products defined by NEP_POLY_COMMON.
+#define NEP_POLY_COMMON(x, y, z)                                                                       \
+    const T r2 = x * x + y * y + z * z, x2 = x * x, y2 = y * y, z2 = z * z;                           \
+    const T xy = x * y, xz = x * z, yz = y * z, xmy = x2 - y2;
+#define NEP_Z NepZero{}
+#define NEP_FOR_EACH_LM(X, x, y, z)                                                                    \
+    X(0, z, NEP_Z, NEP_Z, T(1))                                                                        \
+    X(1, x, T(1), NEP_Z, NEP_Z)                                                                        \
+    X(2, y, NEP_Z, T(1), NEP_Z)                                                                        \
+    X(3, T(3) * z2 - r2, T(-2) * x, T(-2) * y, T(4) * z)                                               \
+    X(4, xz, z, NEP_Z, x)                                                                              \
+    X(5, yz, NEP_Z, z, y)                                                                              \
+    X(6, xmy, T(2) * x, T(-2) * y, NEP_Z)                                                              \
+    X(7, T(2) * xy, T(2) * y, T(2) * x, NEP_Z)                                                         \
+    X(8, (T(5) * z2 - T(3) * r2) * z, T(-6) * xz, T(-6) * yz, T(9) * z2 - T(3) * r2)                   \
+    X(9, (T(5) * z2 - r2) * x, T(-2) * x2 + T(5) * z2 - r2, T(-2) * xy, T(8) * xz)                     \
+    X(10, (T(5) * z2 - r2) * y, T(-2) * xy, T(-2) * y2 + T(5) * z2 - r2, T(8) * yz)                    \
+    X(11, xmy * z, T(2) * xz, T(-2) * yz, xmy)                                                         \
+    X(12, T(2) * xy * z, T(2) * yz, T(2) * xz, T(2) * xy)                                              \
+    X(13, (x2 - T(3) * y2) * x, T(3) * xmy, T(-6) * xy, NEP_Z)                                         \
+    X(14, (T(3) * x2 - y2) * y, T(6) * xy, T(3) * xmy, NEP_Z)                                          \
+    X(15, (T(35) * z2 - T(30) * r2) * z2 + T(3) * r2 * r2, T(-60) * x * z2 + T(12) * r2 * x,           \
+      T(-60) * y * z2 + T(12) * r2 * y, T(80) * z2 * z - T(48) * r2 * z)                               \
+    X(16, (T(7) * z2 - T(3) * r2) * xz, T(-6) * x2 * z + T(7) * z2 * z - T(3) * r2 * z, T(-6) * xy * z, \
+      T(15) * x * z2 - T(3) * r2 * x)                                                                  \
+    X(17, (T(7) * z2 - T(3) * r2) * yz, T(-6) * xy * z, T(-6) * y2 * z + T(7) * z2 * z - T(3) * r2 * z, \
+      T(15) * y * z2 - T(3) * r2 * y)                                                                  \
+    X(18, (T(7) * z2 - r2) * xmy, T(-2) * x2 * x + T(2) * x * y2 + T(14) * x * z2 - T(2) * r2 * x,     \
+      T(-2) * x2 * y + T(2) * y2 * y - T(14) * y * z2 + T(2) * r2 * y, T(12) * z * xmy)                \
+    X(19, (T(7) * z2 - r2) * T(2) * xy, T(-4) * x2 * y + T(14) * y * z2 - T(2) * r2 * y,               \
+      T(-4) * x * y2 + T(14) * x * z2 - T(2) * r2 * x, T(24) * xy * z)                                 \
+    X(20, (x2 - T(3) * y2) * xz, T(3) * xmy * z, T(-6) * xy * z, (x2 - T(3) * y2) * x)                 \
+    X(21, (T(3) * x2 - y2) * yz, T(6) * xy * z, T(3) * xmy * z, (T(3) * x2 - y2) * y)                  \
+    X(22, xmy * xmy - T(4) * x2 * y2, T(4) * x2 * x - T(12) * x * y2, T(4) * y2 * y - T(12) * x2 * y, NEP_Z) \
+    X(23, T(4) * xmy * xy, T(12) * x2 * y - T(4) * y2 * y, T(4) * x2 * x - T(12) * x * y2, NEP_Z)
+
 template <typename T, bool GRAD>
 __device__ __forceinline__ void nep_blm(T x, T y, T z, T (&b)[NEP_NLM], T (&g)[GRAD ? NEP_NLM : 1][3])
 {
-    const T r2 = x * x + y * y + z * z, x2 = x * x, y2 = y * y, z2 = z * z;
-    const T xy = x * y, xz = x * z, yz = y * z, xmy = x2 - y2;
-#define NEP_SET(k, val, gx, gy, gz)                                  \
-    b[k] = (val);                                                    \
-    if constexpr (GRAD) { g[k][0] = (gx); g[k][1] = (gy); g[k][2] = (gz); }
-    NEP_SET(0, z, T(0), T(0), T(1))
-    NEP_SET(1, x, T(1), T(0), T(0))
-    NEP_SET(2, y, T(0), T(1), T(0))
-    NEP_SET(3, T(3) * z2 - r2, T(-2) * x, T(-2) * y, T(4) * z)
-    NEP_SET(4, xz, z, T(0), x)
-    NEP_SET(5, yz, T(0), z, y)
-    NEP_SET(6, xmy, T(2) * x, T(-2) * y, T(0))
-    NEP_SET(7, T(2) * xy, T(2) * y, T(2) * x, T(0))
-    NEP_SET(8, (T(5) * z2 - T(3) * r2) * z, T(-6) * xz, T(-6) * yz, T(9) * z2 - T(3) * r2)
-    NEP_SET(9, (T(5) * z2 - r2) * x, T(-2) * x2 + T(5) * z2 - r2, T(-2) * xy, T(8) * xz)
-    NEP_SET(10, (T(5) * z2 - r2) * y, T(-2) * xy, T(-2) * y2 + T(5) * z2 - r2, T(8) * yz)
-    NEP_SET(11, xmy * z, T(2) * xz, T(-2) * yz, xmy)
-    NEP_SET(12, T(2) * xy * z, T(2) * yz, T(2) * xz, T(2) * xy)
-    NEP_SET(13, (x2 - T(3) * y2) * x, T(3) * xmy, T(-6) * xy, T(0))
-    NEP_SET(14, (T(3) * x2 - y2) * y, T(6) * xy, T(3) * xmy, T(0))
-    NEP_SET(15, (T(35) * z2 - T(30) * r2) * z2 + T(3) * r2 * r2, T(-60) * x * z2 + T(12) * r2 * x,
-            T(-60) * y * z2 + T(12) * r2 * y, T(80) * z2 * z - T(48) * r2 * z)
-    NEP_SET(16, (T(7) * z2 - T(3) * r2) * xz, T(-6) * x2 * z + T(7) * z2 * z - T(3) * r2 * z, T(-6) * xy * z,
-            T(15) * x * z2 - T(3) * r2 * x)
-    NEP_SET(17, (T(7) * z2 - T(3) * r2) * yz, T(-6) * xy * z, T(-6) * y2 * z + T(7) * z2 * z - T(3) * r2 * z,
-            T(15) * y * z2 - T(3) * r2 * y)
-    NEP_SET(18, (T(7) * z2 - r2) * xmy, T(-2) * x2 * x + T(2) * x * y2 + T(14) * x * z2 - T(2) * r2 * x,
-            T(-2) * x2 * y + T(2) * y2 * y - T(14) * y * z2 + T(2) * r2 * y, T(12) * z * xmy)
-    NEP_SET(19, (T(7) * z2 - r2) * T(2) * xy, T(-4) * x2 * y + T(14) * y * z2 - T(2) * r2 * y,
-            T(-4) * x * y2 + T(14) * x * z2 - T(2) * r2 * x, T(24) * xy * z)
-    NEP_SET(20, (x2 - T(3) * y2) * xz, T(3) * xmy * z, T(-6) * xy * z, (x2 - T(3) * y2) * x)
-    NEP_SET(21, (T(3) * x2 - y2) * yz, T(6) * xy * z, T(3) * xmy * z, (T(3) * x2 - y2) * y)
-    NEP_SET(22, xmy * xmy - T(4) * x2 * y2, T(4) * x2 * x - T(12) * x * y2, T(4) * y2 * y - T(12) * x2 * y, T(0))
-    NEP_SET(23, T(4) * xmy * xy, T(12) * x2 * y - T(4) * y2 * y, T(4) * x2 * x - T(12) * x * y2, T(0))
+    NEP_POLY_COMMON(x, y, z)
+#define NEP_SET(k, val, gx, gy, gz)                                                       \
+    b[k] = (val);                                                                         \
+    if constexpr (GRAD) { nep_set<T>(g[k][0], gx); nep_set<T>(g[k][1], gy); nep_set<T>(g[k][2], gz); }
+    NEP_FOR_EACH_LM(NEP_SET, x, y, z)
 #undef NEP_SET
 }
 
@@ -471,12 +492,56 @@ __global__ void __launch_bounds__(NEP_WARPS * 32) nep_atom_kernel(const NepArgs<
     }
 }
 
+}  // namespace ai2b
+#include "nep_fast.cuh"
+namespace ai2b {
+
 // ---------------------------------------------------------------------------------------------
 static size_t nep_ws_bytes(int B, int ntypes, int n_r, int n_a, int csp, size_t elem)
 {
     size_t pre = (((size_t)(B > 0 ? B : 0) + 1) * sizeof(int) + 255) & ~size_t(255);
     size_t co = ((size_t)ntypes * ntypes * (n_r + n_a) * csp * elem + 255) & ~size_t(255);
     return pre + co;
+}
+
+static int nep_grid(const void *kern, size_t smem, int B, int npad, long *blocks)
+{
+    int sms = 148, dev = 0, per_sm = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    AI2B_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, NEP_WARPS * 32, smem));
+    if (per_sm < 1) per_sm = 1;
+    *blocks = (long)sms * per_sm;
+    const long need_blocks = ((long)B * npad + NEP_APB - 1) / NEP_APB;
+    if (*blocks > need_blocks) *blocks = need_blocks;
+    return AI2B_OK;
+}
+
+// Specialised kernel for n_radial, n_angular <= NMAX. *done = false if the model's tables or the
+// neighbour width do not fit its shared-memory plan (the general kernel then runs).
+template <typename T, int CSP, int MODE, int NMAX>
+static int launch_nep_fast(const NepArgs<T> &A, const T *coeffs, cudaStream_t st, bool *done)
+{
+    constexpr int MINB = sizeof(T) == 4 ? 4 : 2;
+    auto r4 = [](size_t n) { return (n + 3) & ~size_t(3); };
+    const size_t ntab = (size_t)A.ntypes * A.ntypes * 2 * NMAX * CSP;
+    const size_t smem = (r4(ntab) + (size_t)NEP_APB * nep_fast_atom_elems<NMAX>(A.nd, A.nneu, A.umax, MODE != NEP_DESC)) * sizeof(T) +
+                        (size_t)NEP_APB * A.umax * sizeof(unsigned short) + 16;
+    *done = false;
+    if (smem > 96 * 1024 || A.nd > 96) return AI2B_OK;
+    auto kern = nep_fast_kernel<T, CSP, MODE, NMAX, MINB>;
+    static size_t configured = 0;
+    if (smem > 48 * 1024 && smem > configured) {
+        AI2B_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = smem;
+    }
+    long blocks = 0;
+    int rc = nep_grid((const void *)kern, smem, A.B, A.npad, &blocks);
+    if (rc != AI2B_OK) return rc;
+    kern<<<(unsigned)blocks, NEP_WARPS * 32, smem, st>>>(A, coeffs);
+    AI2B_CUDA(cudaGetLastError());
+    *done = true;
+    return AI2B_OK;
 }
 
 template <typename T, int CSP, int MODE>
@@ -488,7 +553,21 @@ static int launch_nep_csp(NepArgs<T> A, const T *coeffs, void *ws, size_t ws_byt
     T *cpad = reinterpret_cast<T *>(reinterpret_cast<unsigned char *>(ws) + ((((size_t)A.B + 1) * sizeof(int) + 255) & ~size_t(255)));
     A.prefix = prefix;
     A.coeffs_pad = cpad;
-    nep_prefix_kernel<<<1, 32, 0, st>>>(A.binum, A.B, prefix);
+    bool have_prefix = false;
+    if constexpr (CSP == 8) {
+        if (A.n_r <= 8 && A.n_a <= 8) {
+            // the specialised kernel reads the atom offsets only for batches of several structures
+            if (A.B > 1) {
+                nep_prefix_kernel<<<1, 32, 0, st>>>(A.binum, A.B, prefix);
+                have_prefix = true;
+            }
+            bool done = false;
+            int rc = (A.n_r <= 4 && A.n_a <= 4) ? launch_nep_fast<T, CSP, MODE, 4>(A, coeffs, st, &done)
+                                                : launch_nep_fast<T, CSP, MODE, 8>(A, coeffs, st, &done);
+            if (rc != AI2B_OK || done) return rc;
+        }
+    }
+    if (!have_prefix) nep_prefix_kernel<<<1, 32, 0, st>>>(A.binum, A.B, prefix);
     const int rows = A.ntypes * A.ntypes * (A.n_r + A.n_a);
     nep_pad_coeffs_kernel<T><<<(rows * CSP + 255) / 256, 256, 0, st>>>(coeffs, cpad, rows, A.cs, CSP);
     const size_t smem = (size_t)NEP_APB * (nep_atom_elems(A.nd, A.nS, A.nneu) * sizeof(T) + (size_t)A.umax * sizeof(unsigned short)) + 16;

@@ -49,9 +49,11 @@ class Evaluator:
     def compute(self, coords):
         return self.evaluate(self.build_list(coords))
 
-    # kernels of this library launched by one compute() (memsets not counted)
+    # kernels of this library launched by one compute() on a fully periodic cell (memsets not counted):
+    # neighbour build = set-up, count, scan, fill, build; MTP = prefix, coefficient padding, forward,
+    # contraction, force; NEP = prefix, coefficient padding, atom kernel
     def launches_per_step(self):
-        return 8 + 2
+        return 5 + (5 if self.kind == "mtp" else 3)
 
 
 def fma_peak_tflops(is_f64, sms):
@@ -230,7 +232,7 @@ def run_slab_benchmark(w, steps, warmup, dist, sampler):
     roofline = {"kernel": "nep_atom_kernel (+ neighbour build) on this rank's slab", "bound": "fp32", "achieved": achieved, "peak": peak,
                 "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": "FMA-chain microbenchmark in this run (of measured)",
                 "flops_per_atom": fl, "mean_neighbours": mean_nn, "traffic": None, "owned_atoms": dom.nlocal, "ghost_atoms": dom.nghost}
-    return dict(t_dev=t_dev, t_e2e=t_e2e, clocks=clocks, launches=(8 + 3) * steps, h2d=host_owned.numel() * host_owned.element_size(),
+    return dict(t_dev=t_dev, t_e2e=t_e2e, clocks=clocks, launches=(9 + 3) * steps, h2d=host_owned.numel() * host_owned.element_size(),
                 d2h=h_f.numel() * h_f.element_size() + 40, units=len(w["types"]) / world,
                 e2e_path="pinned host positions of the slab -> H2D -> halo exchange (NCCL p2p) -> ai2b_nblist_build_ghost -> ai2b_nep_efv "
                          "-> ghost-force return -> all-reduce(E, virial) -> D2H forces, E, virial",
