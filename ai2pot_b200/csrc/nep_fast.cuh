@@ -14,6 +14,11 @@
 //     mu (a small matrix product) instead of 3 NMAX eight-lane transpose-reductions;
 //   * angular force pass: the harmonic polynomials and their gradients are consumed one lm at a
 //     time against the adjoints of all mu (4 NMAX accumulators), never held as 96 registers;
+//   * the network weights of all types sit in shared memory as zero-padded rows (16-byte loads,
+//     compile-time trip counts);
+//   * energy and virial accumulate per lane over all atoms a group visits and are reduced once
+//     per block at the end of the kernel (or when the structure index changes), so the loop over
+//     atoms has no block-wide barrier;
 //   * structures' atom offsets are read from the workspace only for batches of more than one
 //     structure.
 #pragma once
@@ -52,14 +57,29 @@ __device__ __forceinline__ void store_vec(T *__restrict__ p, const T (&v)[N])
     }
 }
 
+// padded descriptor count: rows of the network's first layer are 16-byte aligned and an odd
+// number of 16-byte chunks long (conflict-free when eight lanes read eight rows)
+template <int NMAX>
+struct NepFastDims {
+    static constexpr int ND = 5 * NMAX;                                   // >= n_r + n_a * l_max
+    static constexpr int NDP = ((ND / 4) & 1) ? ND : ND + 4;
+};
+__host__ __device__ inline int nep_r4(int n) { return (n + 3) & ~3; }
 // shared-memory elements (of T) per atom slot of the specialised kernel
 template <int NMAX>
-__host__ __device__ inline int nep_fast_atom_elems(int nd, int nneu, int umax, bool cache)
+__host__ __device__ inline int nep_fast_atom_elems(int nneu, int umax, bool cache)
 {
-    auto r4 = [](int n) { return (n + 3) & ~3; };
-    const int sea = 2 * NEP_NLM * NMAX + r4(nneu);            // S, ES, act ...
+    const int sea = 2 * NEP_NLM * NMAX + nep_r4(nneu);        // S, ES, act ...
     const int stage = NEP_GROUP * (NMAX + NEP_NLM);           // ... share their space with the staging rows
-    return 2 * r4(nd) + (sea > stage ? sea : stage) + (cache ? umax * NMAX : 0);
+    return 2 * NepFastDims<NMAX>::NDP + (sea > stage ? sea : stage) + (cache ? umax * NMAX : 0);
+}
+// elements (of T) of the block-wide tables: coefficients, then (unless descriptors only) W0, b0, w1
+template <int NMAX, int CSP>
+__host__ __device__ inline int nep_fast_table_elems(int ntypes, int nneu, bool net)
+{
+    int n = nep_r4(ntypes * ntypes * 2 * NMAX * CSP);
+    if (net) n += ntypes * nneu * NepFastDims<NMAX>::NDP + 2 * nep_r4(ntypes * nneu);
+    return n;
 }
 
 template <typename T, int CSP, int MODE, int NMAX, int MINB>
@@ -69,58 +89,113 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_fast_kernel(const Ne
     constexpr int TROW = 2 * NMAX * CSP;   // coefficient rows of one (ti,tj) pair
     constexpr bool CACHE = MODE != NEP_DESC;
     extern __shared__ __align__(16) unsigned char nep_smem[];
+    constexpr int NDP = NepFastDims<NMAX>::NDP;
+    constexpr bool NET = MODE != NEP_DESC;
     __shared__ T blk_acc[10];
     __shared__ int blk_b;
-    __shared__ T iqs[96];
-    __shared__ T fac_s[NEP_NLM];   // (2 - delta_m0) * 2 * C_lm
+    __shared__ T iqs[NDP];           // 1 / q_scaler, zero beyond the descriptor count
+    __shared__ T fac_s[NEP_NLM];     // (2 - delta_m0) * 2 * C_lm
+    __shared__ T c3w_s[NEP_NLM];     // (2 - delta_m0) * C_lm
+    __shared__ unsigned char pm_mu[NDP], pm_l[NDP];   // angular descriptor p -> (mu, l)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int sub = lane & (NEP_GROUP - 1), grp = lane / NEP_GROUP;
     const int slot_in_block = warp * NEP_APW + grp;
     const unsigned gmask_shift = grp * NEP_GROUP;
     const unsigned gmask = 0xffu << gmask_shift;
-    auto r4 = [](int n) { return (n + 3) & ~3; };
-    const int per_atom = nep_fast_atom_elems<NMAX>(A.nd, A.nneu, A.umax, CACHE);
+    const int per_atom = nep_fast_atom_elems<NMAX>(A.nneu, A.umax, CACHE);
     const int ntab = A.ntypes * A.ntypes * TROW;
+    const int nrow = A.ntypes * A.nneu;
     T *ctab_s = reinterpret_cast<T *>(nep_smem);
-    T *q = ctab_s + r4(ntab) + (size_t)slot_in_block * per_atom;
-    T *Eq = q + r4(A.nd);
-    T *S = Eq + r4(A.nd);                  // [NMAX][24]
+    T *W0s = ctab_s + nep_r4(ntab);              // [ntypes * nneu][NDP], zero-padded rows
+    T *B0s = W0s + (NET ? nrow * NDP : 0);
+    T *W1s = B0s + (NET ? nep_r4(nrow) : 0);
+    T *atoms_s = ctab_s + nep_fast_table_elems<NMAX, CSP>(A.ntypes, A.nneu, NET);
+    T *q = atoms_s + (size_t)slot_in_block * per_atom;   // [NDP]
+    T *Eq = q + NDP;                       // [NDP]
+    T *S = Eq + NDP;                       // [NMAX][24]
     T *ES = S + NEP_NLM * NMAX;            // [24][NMAX]
     T *act = ES + NEP_NLM * NMAX;
     T *stage = S;                          // staging rows of the angular sums (before S, ES, act are written)
-    const int sea = 2 * NEP_NLM * NMAX + r4(A.nneu), stg = NEP_GROUP * RS;
+    const int sea = 2 * NEP_NLM * NMAX + nep_r4(A.nneu), stg = NEP_GROUP * RS;
     T *dcache = S + (sea > stg ? sea : stg);   // [umax][NMAX]: g'_n of every neighbour
-    unsigned short *alist = reinterpret_cast<unsigned short *>(ctab_s + r4(ntab) + (size_t)NEP_APB * per_atom) +
-                            (size_t)slot_in_block * A.umax;
+    unsigned short *alist = reinterpret_cast<unsigned short *>(atoms_s + (size_t)NEP_APB * per_atom) + (size_t)slot_in_block * A.umax;
     const int ntot_n = A.n_r + A.n_a;
     const int nlm = A.l_max * A.l_max + 2 * A.l_max;
+    const int nq_a = A.l_max > 0 ? A.n_a * A.l_max : 0;
 
-    // block prologue: zero-padded coefficient table, 1/q_scaler, 3-body factors
-    for (int i = threadIdx.x; i < ntab; i += blockDim.x) {
-        const int k = i % CSP, n = (i / CSP) % (2 * NMAX), pair = i / TROW;
-        T v = T(0);
-        if (k < A.cs) {
-            if (n < NMAX) {
-                if (n < A.n_r) v = coeffs[((size_t)pair * ntot_n + n) * A.cs + k];
-            } else if (n - NMAX < A.n_a) {
-                v = coeffs[((size_t)pair * ntot_n + A.n_r + (n - NMAX)) * A.cs + k];
+    // block prologue: zero-padded tables, 1/q_scaler, 3-body factors, descriptor index map.
+    // fill(n, load, store): every thread first issues up to 8 independent loads, then stores.
+    auto fill = [&](int n, auto load, auto store) {
+        for (int i0 = threadIdx.x; i0 < n; i0 += 8 * blockDim.x) {
+            T v[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int i = i0 + u * blockDim.x;
+                v[u] = i < n ? load(i) : T(0);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int i = i0 + u * blockDim.x;
+                if (i < n) store(i, v[u]);
             }
         }
-        ctab_s[i] = v;
+    };
+    fill(ntab,
+         [&](int i) {
+             const int k = i % CSP, n = (i / CSP) % (2 * NMAX), pair = i / TROW;
+             const int row = n < NMAX ? (n < A.n_r ? n : -1) : (n - NMAX < A.n_a ? A.n_r + n - NMAX : -1);
+             return (k < A.cs && row >= 0) ? coeffs[((size_t)pair * ntot_n + row) * A.cs + k] : T(0);
+         },
+         [&](int i, T v) { ctab_s[i] = v; });
+    if (NET) {
+        fill(nrow * NDP,
+             [&](int i) {
+                 const int row = i / NDP, k = i % NDP;
+                 return k < A.nd ? A.w0[(size_t)row * A.nd + k] : T(0);
+             },
+             [&](int i, T v) { W0s[i] = v; });
+        fill(nrow, [&](int i) { return A.b0[i]; }, [&](int i, T v) { B0s[i] = v; });
+        fill(nrow, [&](int i) { return A.w1[i]; }, [&](int i, T v) { W1s[i] = v; });
+        for (int k = threadIdx.x; k < NDP; k += blockDim.x) iqs[k] = k < A.nd ? T(1) / A.qs[k] : T(0);
     }
     if (threadIdx.x < NEP_NLM) {
         const int lm = threadIdx.x;
         const bool m0 = lm == 0 || lm == 3 || lm == 8 || lm == 15;
+        c3w_s[lm] = (m0 ? T(1) : T(2)) * (T)c_C3B[lm];
         fac_s[lm] = (m0 ? T(1) : T(2)) * T(2) * (T)c_C3B[lm];
     }
-    if (MODE != NEP_DESC)
-        for (int k = threadIdx.x; k < A.nd; k += blockDim.x) iqs[k] = T(1) / A.qs[k];
+    for (int p = threadIdx.x; p < NDP; p += blockDim.x) {
+        const bool in = p < nq_a;
+        pm_mu[p] = (unsigned char)(in ? p / A.l_max : 0);
+        pm_l[p] = (unsigned char)(in ? p % A.l_max + 1 : 0);
+    }
+    // descriptors and their adjoints are read as NDP-long vectors: the padding stays zero
+    for (int i = threadIdx.x; i < NEP_APB * 2 * NDP; i += blockDim.x) atoms_s[(size_t)(i / (2 * NDP)) * per_atom + i % (2 * NDP)] = T(0);
     __syncthreads();
 
     const int ntot = A.B == 1 ? A.binum[0] : A.prefix[A.B];
     const int ngroups = gridDim.x * NEP_APB;
     const int gidx = blockIdx.x * NEP_APB + slot_in_block;
     const int rounds = (ntot + ngroups - 1) / ngroups;
+
+    // energy / virial of the atoms this lane has worked on, all of structure `bcur`
+    T e_acc = T(0), vir[9];
+#pragma unroll
+    for (int k = 0; k < 9; k++) vir[k] = T(0);
+    int bcur = -1;
+    auto flush_group = [&]() {   // called by all lanes of a group together
+        e_acc = group_sum(e_acc, gmask);
+        if (sub == 0) atomicAdd(A.etot + bcur, e_acc);
+        e_acc = T(0);
+        if (MODE == NEP_EFV) {
+#pragma unroll
+            for (int k = 0; k < 9; k++) {
+                const T v = group_sum(vir[k], gmask);
+                if (sub == 0) atomicAdd(A.virial + 9 * bcur + k, v);
+                vir[k] = T(0);
+            }
+        }
+    };
 
     for (int it = 0; it < rounds; it++) {
         const int t = it * ngroups + gidx;
@@ -141,10 +216,9 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_fast_kernel(const Ne
         const T *rc = A.rcs + slot * A.umax * 3;
         const T *ctab = ctab_s + (size_t)ti * A.ntypes * TROW;
 
-        if (MODE != NEP_DESC) {
-            if (threadIdx.x == 0) blk_b = valid ? b : -1;
-            if (threadIdx.x < 10) blk_acc[threadIdx.x] = T(0);
-            __syncthreads();
+        if (NET && valid && b != bcur) {
+            if (bcur >= 0) flush_group();
+            bcur = b;
         }
 
         // ---- 1. radial pass: q_n, cached g'_n, compaction of the angular neighbours ----------------
@@ -152,12 +226,20 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_fast_kernel(const Ne
 #pragma unroll
         for (int n = 0; n < NMAX; n++) qacc[n] = T(0);
         int nang = 0;
+        // the next chunk's positions and indices are requested before this chunk is worked on
+        T xn = 0, yn = 0, zn = 0;
+        int njn = 0;
+        if (sub < nn) { xn = rc[3 * sub]; yn = rc[3 * sub + 1]; zn = rc[3 * sub + 2]; njn = fn[sub]; }
         for (int j0 = 0; j0 < nn; j0 += NEP_GROUP) {
             const int j = j0 + sub;
             bool on = j < nn;
-            T x = 0, y = 0, z = 0;
-            int tj = 0;
-            if (on) { x = rc[3 * j]; y = rc[3 * j + 1]; z = rc[3 * j + 2]; tj = types[fn[j]]; }
+            const T x = xn, y = yn, z = zn;
+            const int tj = on ? types[njn] : 0;
+            {
+                const int jn = j + NEP_GROUP;
+                xn = yn = zn = T(0);
+                if (jn < nn) { xn = rc[3 * jn]; yn = rc[3 * jn + 1]; zn = rc[3 * jn + 2]; njn = fn[jn]; }
+            }
             const T r = gsqrt(x * x + y * y + z * z);
             on = on && r <= A.rc_r && r > T(0);
             T f[CSP], df[CSP];
@@ -180,7 +262,8 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_fast_kernel(const Ne
             if (CACHE && j < A.umax) store_vec<T, NMAX>(dcache + (size_t)j * NMAX, dgv);
             const bool ang = on && r <= A.rc_a && A.l_max > 0;
             const unsigned bal = (__ballot_sync(gmask, ang) >> gmask_shift) & 0xffu;
-            if (ang) alist[nang + __popc(bal & ((1u << sub) - 1u))] = (unsigned short)j;
+            // list entry: neighbour slot (10 bits) | neighbour type (4 bits)
+            if (ang) alist[nang + __popc(bal & ((1u << sub) - 1u))] = (unsigned short)(j | (tj << 10));
             nang += __popc(bal);
         }
 #pragma unroll
@@ -199,11 +282,11 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_fast_kernel(const Ne
             T x = 0, y = 0, z = 0, rinv = 0, r = A.rc_a;
             int tj = 0;
             if (on) {
-                const int j = alist[k0 + sub];
+                const int ent = alist[k0 + sub], j = ent & 1023;
+                tj = ent >> 10;
                 x = rc[3 * j]; y = rc[3 * j + 1]; z = rc[3 * j + 2];
                 r = gsqrt(x * x + y * y + z * z);
                 rinv = T(1) / r;
-                tj = types[fn[j]];
             }
             {
                 T f[CSP], df[CSP], row[RS];
@@ -253,53 +336,65 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_fast_kernel(const Ne
         __syncwarp(gmask);
 
         // ---- 3. angular descriptors, network ------------------------------------------------------------
-        for (int p = sub; p < A.n_a * A.l_max; p += NEP_GROUP) {
-            const int mu = p / A.l_max, l = p % A.l_max + 1;
+        for (int p = sub; p < nq_a; p += NEP_GROUP) {
+            const int mu = pm_mu[p], l = pm_l[p];
+            const T *Srow = S + mu * NEP_NLM + l * l - 1;
+            const T *cw = c3w_s + l * l - 1;
             T acc = T(0);
-            for (int mp = 0; mp < 2 * l + 1; mp++) {
-                const int lm = l * l - 1 + mp;
-                const T s = S[mu * NEP_NLM + lm];
-                acc += (mp == 0 ? T(1) : T(2)) * (T)c_C3B[lm] * s * s;
-            }
+            for (int mp = 0; mp < 2 * l + 1; mp++) acc += cw[mp] * Srow[mp] * Srow[mp];
             q[A.n_r + p] = acc;
         }
         __syncwarp(gmask);
-        if (MODE == NEP_DESC) {
+        if constexpr (MODE == NEP_DESC) {
             if (valid)
                 for (int k = sub; k < A.nd; k += NEP_GROUP) A.desc[slot * A.nd + k] = q[k];
             __syncwarp(gmask);
-            continue;
-        }
-        const T *W0 = A.w0 + (size_t)ti * A.nneu * A.nd, *B0 = A.b0 + (size_t)ti * A.nneu, *W1 = A.w1 + (size_t)ti * A.nneu;
+        } else {
+        // network on the scaled descriptors; rows and vectors are zero-padded to NDP
         for (int k = sub; k < A.nd; k += NEP_GROUP) Eq[k] = q[k] * iqs[k];
         __syncwarp(gmask);
         T es = T(0);
         for (int p = sub; p < A.nneu; p += NEP_GROUP) {
-            const T *wrow = W0 + p * A.nd;
-            T h0 = T(0), h1 = T(0), h2 = T(0), h3 = T(0);
-            int k = 0;
-            for (; k + 3 < A.nd; k += 4) {
-                h0 = fma(wrow[k], Eq[k], h0);
-                h1 = fma(wrow[k + 1], Eq[k + 1], h1);
-                h2 = fma(wrow[k + 2], Eq[k + 2], h2);
-                h3 = fma(wrow[k + 3], Eq[k + 3], h3);
+            const T *wrow = W0s + (size_t)(ti * A.nneu + p) * NDP;
+            T h[4] = {T(0), T(0), T(0), T(0)};
+#pragma unroll
+            for (int c = 0; c < NDP / 4; c++) {
+                T w[4], e[4];
+                load_vec<T, 4>(wrow + 4 * c, w);
+                load_vec<T, 4>(Eq + 4 * c, e);
+#pragma unroll
+                for (int i = 0; i < 4; i++) h[i] = fma(w[i], e[i], h[i]);
             }
-            for (; k < A.nd; k++) h0 = fma(wrow[k], Eq[k], h0);
-            const T th = gtanh((h0 + h1) + (h2 + h3) + B0[p]);
-            es += W1[p] * th;
-            act[p] = W1[p] * (T(1) - th * th);
+            const T th = gtanh((h[0] + h[1]) + (h[2] + h[3]) + B0s[ti * A.nneu + p]);
+            const T w1 = W1s[ti * A.nneu + p];
+            es += w1 * th;
+            act[p] = w1 * (T(1) - th * th);
         }
-        es = group_sum(es, gmask);
+        if (valid) e_acc += es + (sub == 0 ? A.bias[ti] : T(0));
         __syncwarp(gmask);
-        for (int k = sub; k < A.nd; k += NEP_GROUP) {
-            T a0 = T(0), a1 = T(0);
+        for (int c = sub; c < NDP / 4; c += NEP_GROUP) {   // lane c: descriptors 4c .. 4c+3
+            const T *wcol = W0s + (size_t)ti * A.nneu * NDP + 4 * c;
+            T a0[4] = {T(0), T(0), T(0), T(0)}, a1[4] = {T(0), T(0), T(0), T(0)};
             int p = 0;
             for (; p + 1 < A.nneu; p += 2) {
-                a0 = fma(act[p], W0[p * A.nd + k], a0);
-                a1 = fma(act[p + 1], W0[(p + 1) * A.nd + k], a1);
+                T w0[4], w1[4];
+                load_vec<T, 4>(wcol + (size_t)p * NDP, w0);
+                load_vec<T, 4>(wcol + (size_t)(p + 1) * NDP, w1);
+                const T x0 = act[p], x1 = act[p + 1];
+#pragma unroll
+                for (int i = 0; i < 4; i++) { a0[i] = fma(x0, w0[i], a0[i]); a1[i] = fma(x1, w1[i], a1[i]); }
             }
-            if (p < A.nneu) a0 = fma(act[p], W0[p * A.nd + k], a0);
-            Eq[k] = (a0 + a1) * iqs[k];
+            if (p < A.nneu) {
+                T w0[4];
+                load_vec<T, 4>(wcol + (size_t)p * NDP, w0);
+                const T x0 = act[p];
+#pragma unroll
+                for (int i = 0; i < 4; i++) a0[i] = fma(x0, w0[i], a0[i]);
+            }
+            T r[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) r[i] = (a0[i] + a1[i]) * iqs[4 * c + i];
+            store_vec<T, 4>(Eq + 4 * c, r);
         }
         __syncwarp(gmask);
         // adjoints of the sums, layout [lm][NMAX] for 16-byte broadcast loads in the force pass
@@ -320,9 +415,7 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_fast_kernel(const Ne
 
         // ---- 4. force / virial -------------------------------------------------------------------------
         T *frc = A.force + (size_t)b * (A.npad + A.nghost) * 3;
-        T fcx = 0, fcy = 0, fcz = 0, vir[9];
-#pragma unroll
-        for (int k = 0; k < 9; k++) vir[k] = T(0);
+        T fcx = 0, fcy = 0, fcz = 0;
         auto scatter = [&](bool on, int nj, T gx, T gy, T gz, T x, T y, T z) {
             if (!on) return;
             fcx += gx; fcy += gy; fcz += gz;
@@ -335,18 +428,22 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_fast_kernel(const Ne
                 vir[6] -= gz * x; vir[7] -= gz * y; vir[8] -= gz * z;
             }
         };
+        xn = yn = zn = T(0);
+        if (sub < nn) { xn = rc[3 * sub]; yn = rc[3 * sub + 1]; zn = rc[3 * sub + 2]; njn = fn[sub]; }
         for (int j0 = 0; j0 < nn; j0 += NEP_GROUP) {     // radial part from the cached g'_n
             const int j = j0 + sub;
             bool on = j < nn;
-            T x = 0, y = 0, z = 0;
-            int nj = 0;
+            const T x = xn, y = yn, z = zn;
+            const int nj = njn;
+            {
+                const int jn = j + NEP_GROUP;
+                xn = yn = zn = T(0);
+                if (jn < nn) { xn = rc[3 * jn]; yn = rc[3 * jn + 1]; zn = rc[3 * jn + 2]; njn = fn[jn]; }
+            }
             T dgv[NMAX];
 #pragma unroll
             for (int n = 0; n < NMAX; n++) dgv[n] = T(0);
-            if (on) {
-                x = rc[3 * j]; y = rc[3 * j + 1]; z = rc[3 * j + 2]; nj = fn[j];
-                load_vec<T, NMAX>(dcache + (size_t)j * NMAX, dgv);
-            }
+            if (on) load_vec<T, NMAX>(dcache + (size_t)j * NMAX, dgv);
             const T r = gsqrt(x * x + y * y + z * z);
             on = on && r <= A.rc_r && r > T(0);
             T gr = T(0);
@@ -360,12 +457,12 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_fast_kernel(const Ne
             T x = 0, y = 0, z = 0, rinv = 0, r = A.rc_a;
             int nj = 0, tj = 0;
             if (on) {
-                const int j = alist[k0 + sub];
+                const int ent = alist[k0 + sub], j = ent & 1023;
+                tj = ent >> 10;
                 x = rc[3 * j]; y = rc[3 * j + 1]; z = rc[3 * j + 2];
+                nj = fn[j];
                 r = gsqrt(x * x + y * y + z * z);
                 rinv = T(1) / r;
-                nj = fn[j];
-                tj = types[nj];
             }
             const T ux = x * rinv, uy = y * rinv, uz = z * rinv;
             T g[NMAX], dg[NMAX];
@@ -415,19 +512,30 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_fast_kernel(const Ne
             scatter(on, nj, gx, gy, gz, x, y, z);
         }
         fcx = group_sum(fcx, gmask); fcy = group_sum(fcy, gmask); fcz = group_sum(fcz, gmask);
-        if (MODE == NEP_EFV) {
-#pragma unroll
-            for (int k = 0; k < 9; k++) vir[k] = group_sum(vir[k], gmask);
-        }
         if (sub == 0 && valid) {
             atomicAdd(frc + 3 * ci + 0, fcx);
             atomicAdd(frc + 3 * ci + 1, fcy);
             atomicAdd(frc + 3 * ci + 2, fcz);
-            const bool local = b == blk_b;
-            atomicAdd(local ? &blk_acc[0] : A.etot + b, es + A.bias[ti]);
+        }
+        }   // MODE != NEP_DESC
+    }
+
+    // energy / virial: groups whose atoms belong to the structure of the block's first group
+    // combine in shared memory, the others add to the outputs directly
+    if (NET) {
+        if (threadIdx.x == 0) blk_b = bcur;
+        if (threadIdx.x < 10) blk_acc[threadIdx.x] = T(0);
+        __syncthreads();
+        if (bcur >= 0) {
+            const bool local = bcur == blk_b;
+            e_acc = group_sum(e_acc, gmask);
+            if (sub == 0) atomicAdd(local ? &blk_acc[0] : A.etot + bcur, e_acc);
             if (MODE == NEP_EFV) {
 #pragma unroll
-                for (int k = 0; k < 9; k++) atomicAdd(local ? &blk_acc[1 + k] : A.virial + 9 * b + k, vir[k]);
+                for (int k = 0; k < 9; k++) {
+                    const T v = group_sum(vir[k], gmask);
+                    if (sub == 0) atomicAdd(local ? &blk_acc[1 + k] : A.virial + 9 * bcur + k, v);
+                }
             }
         }
         __syncthreads();
@@ -436,7 +544,6 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_fast_kernel(const Ne
             if (threadIdx.x == 0) atomicAdd(A.etot + blk_b, v);
             else if (MODE == NEP_EFV) atomicAdd(A.virial + 9 * blk_b + threadIdx.x - 1, v);
         }
-        __syncwarp();   // blk_b is rewritten by thread 0 at the top of the next round
     }
 }
 

@@ -523,12 +523,13 @@ template <typename T, int CSP, int MODE, int NMAX>
 static int launch_nep_fast(const NepArgs<T> &A, const T *coeffs, cudaStream_t st, bool *done)
 {
     constexpr int MINB = sizeof(T) == 4 ? 4 : 2;
-    auto r4 = [](size_t n) { return (n + 3) & ~size_t(3); };
-    const size_t ntab = (size_t)A.ntypes * A.ntypes * 2 * NMAX * CSP;
-    const size_t smem = (r4(ntab) + (size_t)NEP_APB * nep_fast_atom_elems<NMAX>(A.nd, A.nneu, A.umax, MODE != NEP_DESC)) * sizeof(T) +
-                        (size_t)NEP_APB * A.umax * sizeof(unsigned short) + 16;
+    constexpr bool NET = MODE != NEP_DESC;
     *done = false;
-    if (smem > 96 * 1024 || A.nd > 96) return AI2B_OK;
+    if (A.ntypes > 16 || A.nneu > 256 || A.umax > 1024) return AI2B_OK;
+    const size_t smem = ((size_t)nep_fast_table_elems<NMAX, CSP>(A.ntypes, A.nneu, NET) +
+                         (size_t)NEP_APB * nep_fast_atom_elems<NMAX>(A.nneu, A.umax, NET)) * sizeof(T) +
+                        (size_t)NEP_APB * A.umax * sizeof(unsigned short) + 16;
+    if (smem > 96 * 1024) return AI2B_OK;
     auto kern = nep_fast_kernel<T, CSP, MODE, NMAX, MINB>;
     static size_t configured = 0;
     if (smem > 48 * 1024 && smem > configured) {
