@@ -23,7 +23,7 @@ struct MtpArgs {
 };
 
 // exclusive prefix sum of binum -> prefix[0..B]; one block
-static __global__ void prefix_binum_kernel(const int *__restrict__ binum, int B, int *__restrict__ prefix)
+static __device__ __forceinline__ void prefix_binum_block(const int *__restrict__ binum, int B, int *__restrict__ prefix)
 {
     __shared__ int carry;
     __shared__ int wsum[32];
@@ -59,13 +59,31 @@ static __global__ void prefix_binum_kernel(const int *__restrict__ binum, int B,
     }
 }
 
+// Set-up of one call in a single launch of 256-thread blocks: block 0 writes the structures'
+// atom offsets, blocks 1.. copy the radial coefficients into rows zero-padded to csp entries
+// (no such blocks are launched when the rows already have that length).
 template <typename T>
-__global__ void mtp_pad_coeffs_kernel(const T *__restrict__ c, T *__restrict__ out, int rows, int cs, int csp)
+__global__ void mtp_prep_kernel(const int *__restrict__ binum, int B, int *__restrict__ prefix, const T *__restrict__ c,
+                                T *__restrict__ out, int rows, int cs, int csp)
 {
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (blockIdx.x == 0) {
+        prefix_binum_block(binum, B, prefix);
+        return;
+    }
+    int i = (blockIdx.x - 1) * blockDim.x + threadIdx.x;
     if (i >= rows * csp) return;
     int r = i / csp, k = i % csp;
     out[i] = k < cs ? c[r * cs + k] : T(0);
+}
+
+// Launches the set-up kernel; returns the coefficient table the evaluation kernels should read.
+template <typename T>
+static const T *mtp_prepare(const int *binum, int B, int *prefix, const T *coeffs, T *cpad, int rows, int cs, int csp, cudaStream_t st)
+{
+    // the kernels read coefficient pairs with one vector load
+    const bool pad = cs != csp || (reinterpret_cast<size_t>(coeffs) % (2 * sizeof(T))) != 0;
+    mtp_prep_kernel<T><<<1 + (pad ? (rows * csp + 255) / 256 : 0), 256, 0, st>>>(binum, B, prefix, coeffs, cpad, rows, cs, csp);
+    return pad ? cpad : coeffs;
 }
 
 // structure index of flat atom t: largest b with prefix[b] <= t

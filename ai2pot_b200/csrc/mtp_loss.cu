@@ -543,9 +543,7 @@ static int launch_loss_bwd_v(const ai2b_mtp_program *prog, MtpArgs<T> A, LossArg
     L.Xb = reinterpret_cast<T *>(w + W.xb);
     A.ndp = ndense_pad(P);
     A.nbp = nbasic_pad(P);
-    prefix_binum_kernel<<<1, 256, 0, st>>>(A.binum, A.B, const_cast<int *>(A.prefix));
-    const int rows = A.ntypes * A.ntypes * P.nmus;
-    mtp_pad_coeffs_kernel<T><<<(rows * CSP + 255) / 256, 256, 0, st>>>(A.coeffs, cpad, rows, A.cs, CSP);
+    A.coeffs_pad = mtp_prepare<T>(A.binum, A.B, const_cast<int *>(A.prefix), A.coeffs, cpad, A.ntypes * A.ntypes * P.nmus, A.cs, CSP, st);
     AI2B_CUDA(cudaGetLastError());
     const long atoms_upper = (long)A.B * A.npad;
     const long need = (atoms_upper + MTP_WARPS - 1) / MTP_WARPS;

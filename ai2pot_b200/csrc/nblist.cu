@@ -41,6 +41,7 @@ struct NbParams {
     int nbh[3];          // bins of the periodic axes (host-computed); cap for the others
     double rcut_m;       // rcut with a safety margin, for bin sizing
     double rc2;          // rcut^2 as the reference forms it
+    float rc2_lo, rc2_hi, eps_lo, eps_hi;   // the two thresholds -/+ 2e-6 relative (float builds)
     int n, umax, maxbins;
     int ncentre;         // rows are built for atoms [0, ncentre); the rest are neighbours only (ghosts)
 };
@@ -329,7 +330,16 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
     const unsigned lt_mask = (1u << lane) - 1u;
     int local_max = 0;
 
-    for (int a = blockIdx.x * NB_WARPS + warp; a < P.n; a += nwarps) {
+    // Large systems: every warp takes a contiguous run of the bin-ordered atoms, so consecutive
+    // centres mostly share their bin and the table of neighbouring bins is built once per bin.
+    // Small systems: atoms are dealt round-robin (a run would leave most warps without work).
+    const int gw = blockIdx.x * NB_WARPS + warp;
+    const int per = (P.n + nwarps - 1) / nwarps;
+    const bool runs = per >= 8;
+    int cached_bin = -1;
+    for (int it = 0; it < per; it++) {
+        const int a = runs ? gw * per + it : it * nwarps + gw;
+        if (a >= P.n) break;
         const typename Vec4<T>::type pi = spos[a];
         const int4 si = sinfo[a];
         const int i = si.x;
@@ -340,18 +350,24 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
         int *frow = firstneigh + (size_t)i * P.umax;
         T *rrow = rcs + (size_t)i * P.umax * 3;
 
+        const bool reuse = nnb <= 32 && bin_i == cached_bin;
+        cached_bin = nnb <= 32 ? bin_i : -1;
         for (int base = 0; base < nnb; base += 32) {
             // lanes = neighbouring bins of this group
             const int k = base + lane;
             int start = 0, len = 0, shift = 0;
-            if (k < nnb) {
+            if (!reuse && k < nnb) {
                 int d[3] = {k / (ny * nz) - g.R[0], (k / nz) % ny - g.R[1], k % nz - g.R[2]};
                 int b[3] = {bx + d[0], by + d[1], bz + d[2]}, m[3];
                 bool ok = true;
 #pragma unroll
                 for (int c = 0; c < 3; c++) {
                     if (P.per[c]) {
-                        int q = b[c] >= 0 ? b[c] / g.nb[c] : -((-b[c] + g.nb[c] - 1) / g.nb[c]);
+                        int q;   // floor(b / nb); one period off at most unless the grid is tiny
+                        if (b[c] >= 0 && b[c] < g.nb[c]) q = 0;
+                        else if (b[c] < 0 && b[c] >= -g.nb[c]) q = -1;
+                        else if (b[c] >= g.nb[c] && b[c] < 2 * g.nb[c]) q = 1;
+                        else q = b[c] >= 0 ? b[c] / g.nb[c] : -((-b[c] + g.nb[c] - 1) / g.nb[c]);
                         m[c] = q; b[c] -= q * g.nb[c];
                     } else {
                         m[c] = 0;
@@ -365,16 +381,21 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
                     shift = (m[0] + 512) | ((m[1] + 512) << 10) | ((m[2] + 512) << 20);
                 }
             }
-            int inc = len;
+            int total;
+            if (!reuse) {
+                int inc = len;
 #pragma unroll
-            for (int o = 1; o < 32; o <<= 1) { int n = __shfl_up_sync(FULL_MASK, inc, o); if (lane >= o) inc += n; }
-            const int total = __shfl_sync(FULL_MASK, inc, 31);
-            __syncwarp();
-            s_start[warp][lane] = start;
-            s_pre[warp][lane] = inc - len;
-            s_shift[warp][lane] = shift;
-            if (lane == 31) s_pre[warp][32] = total;
-            __syncwarp();
+                for (int o = 1; o < 32; o <<= 1) { int n = __shfl_up_sync(FULL_MASK, inc, o); if (lane >= o) inc += n; }
+                total = __shfl_sync(FULL_MASK, inc, 31);
+                __syncwarp();
+                s_start[warp][lane] = start;
+                s_pre[warp][lane] = inc - len;
+                s_shift[warp][lane] = shift;
+                if (lane == 31) s_pre[warp][32] = total;
+                __syncwarp();
+            } else {
+                total = s_pre[warp][32];
+            }
 
             // lanes = candidate atoms of the whole group of bins
             for (int c0 = 0; c0 < total; c0 += 32) {
@@ -403,11 +424,23 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
                             iz = add_rn(add_rn(add_rn(pj.z, mul_rn(P.cell[2], f0)), mul_rn(P.cell[5], f1)), mul_rn(P.cell[8], f2));
                         }
                         d0 = sub_rn(ix, pi.x); d1 = sub_rn(iy, pi.y); d2 = sub_rn(iz, pi.z);
-                        // squares accumulate in double for both types (pow(T,int) promotes float), then round to T
-                        const double dd = add_rn(add_rn(mul_rn((double)d0, (double)d0), mul_rn((double)d1, (double)d1)),
-                                                 mul_rn((double)d2, (double)d2));
-                        const double ddT = (double)(T)dd;
-                        hit = (ddT < P.rc2) && (ddT > 1e-3);
+                        // Reference predicate: squares accumulate in double for both types (pow(T,int)
+                        // promotes float), the sum is rounded to T and compared with rc^2 and 1e-3.
+                        // For float a single-precision sum is within a few ulp of that value, so it
+                        // decides every pair outside a 2e-6 relative band around the two thresholds;
+                        // only pairs inside the band take the exact route.
+                        bool decided = false;
+                        if (sizeof(T) == 4) {
+                            const float s = (float)d0 * (float)d0 + (float)d1 * (float)d1 + (float)d2 * (float)d2;
+                            if (s < P.rc2_lo && s > P.eps_hi) { hit = true; decided = true; }
+                            else if (s > P.rc2_hi || s < P.eps_lo) { decided = true; }
+                        }
+                        if (!decided) {
+                            const double dd = add_rn(add_rn(mul_rn((double)d0, (double)d0), mul_rn((double)d1, (double)d1)),
+                                                     mul_rn((double)d2, (double)d2));
+                            const double ddT = (double)(T)dd;
+                            hit = (ddT < P.rc2) && (ddT > 1e-3);
+                        }
                         jidx = sj.x;
                     }
                 }
@@ -541,6 +574,8 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
     P.rcut_m = (double)rcut * 1.0001 + 1e-6;
     P.rc2 = (double)rcut * (double)rcut;
     if (sizeof(T) == 8) { volatile double r2 = (double)rcut * (double)rcut; P.rc2 = r2; }
+    P.rc2_lo = (float)(P.rc2 * (1.0 - 2e-6)); P.rc2_hi = (float)(P.rc2 * (1.0 + 2e-6));
+    P.eps_lo = (float)(1e-3 * (1.0 - 2e-6)); P.eps_hi = (float)(1e-3 * (1.0 + 2e-6));
     P.n = n; P.umax = umax; P.maxbins = maxbins; P.ncentre = ncentre;
     bool any_open = false;
     long prod = 1;
@@ -593,7 +628,14 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
         const int ncount = (int)prod + 1;
         nb_setup_periodic_kernel<T><<<(ncount + 255) / 256, 256, 0, st>>>(P, grid, count, ncount, d_status);
         nb_count_kernel<T><<<nblk, tb, 0, st>>>(P, grid, pos, ainfo, count);
-        nb_scan_small_kernel<<<1, SCAN_BLOCK, 0, st>>>(grid, count, start, cursor);
+        if (ncount <= 16 * SCAN_BLOCK) {
+            nb_scan_small_kernel<<<1, SCAN_BLOCK, 0, st>>>(grid, count, start, cursor);
+        } else {   // large grids: block-parallel scan
+            const int sblk = (ncount + SCAN_BLOCK - 1) / SCAN_BLOCK;
+            nb_scan1_kernel<<<sblk, SCAN_BLOCK, 0, st>>>(grid, count, start, bsum);
+            nb_scan2_kernel<<<1, SCAN_BLOCK, 0, st>>>(grid, bsum);
+            nb_scan3_kernel<<<sblk, SCAN_BLOCK, 0, st>>>(grid, start, bsum, cursor);
+        }
     } else {
         nb_init_kernel<<<1, 32, 0, st>>>(ext, d_status);
         if (any_open) nb_extent_kernel<T><<<(nblk < 1024 ? nblk : 1024), tb, 0, st>>>(P, pos, ext);

@@ -65,11 +65,12 @@ struct NepFastDims {
     static constexpr int NDP = ((ND / 4) & 1) ? ND : ND + 4;
 };
 __host__ __device__ inline int nep_r4(int n) { return (n + 3) & ~3; }
+__host__ __device__ inline int nep_r32(int n) { return (n + 31) & ~31; }   // neurons per type, padded
 // shared-memory elements (of T) per atom slot of the specialised kernel
 template <int NMAX>
 __host__ __device__ inline int nep_fast_atom_elems(int nneu, int umax, bool cache)
 {
-    const int sea = 2 * NEP_NLM * NMAX + nep_r4(nneu);        // S, ES, act ...
+    const int sea = 2 * NEP_NLM * NMAX + nep_r32(nneu);       // S, ES, act ...
     const int stage = NEP_GROUP * (NMAX + NEP_NLM);           // ... share their space with the staging rows
     return 2 * NepFastDims<NMAX>::NDP + (sea > stage ? sea : stage) + (cache ? umax * NMAX : 0);
 }
@@ -78,7 +79,7 @@ template <int NMAX, int CSP>
 __host__ __device__ inline int nep_fast_table_elems(int ntypes, int nneu, bool net)
 {
     int n = nep_r4(ntypes * ntypes * 2 * NMAX * CSP);
-    if (net) n += ntypes * nneu * NepFastDims<NMAX>::NDP + 2 * nep_r4(ntypes * nneu);
+    if (net) n += ntypes * nep_r32(nneu) * (NepFastDims<NMAX>::NDP + 2);
     return n;
 }
 
@@ -104,11 +105,11 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_fast_kernel(const Ne
     const unsigned gmask = 0xffu << gmask_shift;
     const int per_atom = nep_fast_atom_elems<NMAX>(A.nneu, A.umax, CACHE);
     const int ntab = A.ntypes * A.ntypes * TROW;
-    const int nrow = A.ntypes * A.nneu;
+    const int NP = nep_r32(A.nneu), nrow = A.ntypes * NP;   // zero rows pad every type to NP neurons
     T *ctab_s = reinterpret_cast<T *>(nep_smem);
     T *W0s = ctab_s + nep_r4(ntab);              // [ntypes * nneu][NDP], zero-padded rows
     T *B0s = W0s + (NET ? nrow * NDP : 0);
-    T *W1s = B0s + (NET ? nep_r4(nrow) : 0);
+    T *W1s = B0s + (NET ? nrow : 0);
     T *atoms_s = ctab_s + nep_fast_table_elems<NMAX, CSP>(A.ntypes, A.nneu, NET);
     T *q = atoms_s + (size_t)slot_in_block * per_atom;   // [NDP]
     T *Eq = q + NDP;                       // [NDP]
@@ -116,7 +117,7 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_fast_kernel(const Ne
     T *ES = S + NEP_NLM * NMAX;            // [24][NMAX]
     T *act = ES + NEP_NLM * NMAX;
     T *stage = S;                          // staging rows of the angular sums (before S, ES, act are written)
-    const int sea = 2 * NEP_NLM * NMAX + nep_r4(A.nneu), stg = NEP_GROUP * RS;
+    const int sea = 2 * NEP_NLM * NMAX + NP, stg = NEP_GROUP * RS;
     T *dcache = S + (sea > stg ? sea : stg);   // [umax][NMAX]: g'_n of every neighbour
     unsigned short *alist = reinterpret_cast<unsigned short *>(atoms_s + (size_t)NEP_APB * per_atom) + (size_t)slot_in_block * A.umax;
     const int ntot_n = A.n_r + A.n_a;
@@ -124,39 +125,44 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_fast_kernel(const Ne
     const int nq_a = A.l_max > 0 ? A.n_a * A.l_max : 0;
 
     // block prologue: zero-padded tables, 1/q_scaler, 3-body factors, descriptor index map.
-    // fill(n, load, store): every thread first issues up to 8 independent loads, then stores.
-    auto fill = [&](int n, auto load, auto store) {
-        for (int i0 = threadIdx.x; i0 < n; i0 += 8 * blockDim.x) {
-            T v[8];
+    // The tables [coefficients | W0 rows | b0 | w1] are one contiguous run of shared memory; every
+    // thread first issues all of its (independent) global loads, then stores, so the block pays
+    // one memory round trip per 24 * blockDim elements instead of one per element.
+    {
+        T qsv = T(1);
+        if (NET && (int)threadIdx.x < A.nd) qsv = A.qs[threadIdx.x];
+        const int n0 = nep_r4(ntab), n1 = n0 + (NET ? nrow * NDP : 0), n2 = n1 + (NET ? nrow : 0);
+        const int nall = n2 + (NET ? nrow : 0);
+        auto load = [&](int i) -> T {
+            if (i < n0) {
+                if (i >= ntab) return T(0);
+                const int k = i % CSP, n = (i / CSP) % (2 * NMAX), pair = i / TROW;
+                const int row = n < NMAX ? (n < A.n_r ? n : -1) : (n - NMAX < A.n_a ? A.n_r + n - NMAX : -1);
+                return (k < A.cs && row >= 0) ? coeffs[((size_t)pair * ntot_n + row) * A.cs + k] : T(0);
+            }
+            if (i < n1) {
+                const int row = (i - n0) / NDP, k = (i - n0) % NDP, t = row / NP, pn = row % NP;
+                return (k < A.nd && pn < A.nneu) ? A.w0[((size_t)t * A.nneu + pn) * A.nd + k] : T(0);
+            }
+            const int row = i < n2 ? i - n1 : i - n2, t = row / NP, pn = row % NP;
+            if (pn >= A.nneu) return T(0);
+            return i < n2 ? A.b0[t * A.nneu + pn] : A.w1[t * A.nneu + pn];
+        };
+        constexpr int U = 24;
+        for (int i0 = threadIdx.x; i0 < nall; i0 += U * blockDim.x) {
+            T v[U];
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
+            for (int u = 0; u < U; u++) {
                 const int i = i0 + u * blockDim.x;
-                v[u] = i < n ? load(i) : T(0);
+                v[u] = i < nall ? load(i) : T(0);
             }
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
+            for (int u = 0; u < U; u++) {
                 const int i = i0 + u * blockDim.x;
-                if (i < n) store(i, v[u]);
+                if (i < nall) ctab_s[i] = v[u];
             }
         }
-    };
-    fill(ntab,
-         [&](int i) {
-             const int k = i % CSP, n = (i / CSP) % (2 * NMAX), pair = i / TROW;
-             const int row = n < NMAX ? (n < A.n_r ? n : -1) : (n - NMAX < A.n_a ? A.n_r + n - NMAX : -1);
-             return (k < A.cs && row >= 0) ? coeffs[((size_t)pair * ntot_n + row) * A.cs + k] : T(0);
-         },
-         [&](int i, T v) { ctab_s[i] = v; });
-    if (NET) {
-        fill(nrow * NDP,
-             [&](int i) {
-                 const int row = i / NDP, k = i % NDP;
-                 return k < A.nd ? A.w0[(size_t)row * A.nd + k] : T(0);
-             },
-             [&](int i, T v) { W0s[i] = v; });
-        fill(nrow, [&](int i) { return A.b0[i]; }, [&](int i, T v) { B0s[i] = v; });
-        fill(nrow, [&](int i) { return A.w1[i]; }, [&](int i, T v) { W1s[i] = v; });
-        for (int k = threadIdx.x; k < NDP; k += blockDim.x) iqs[k] = k < A.nd ? T(1) / A.qs[k] : T(0);
+        if (NET && threadIdx.x < NDP) iqs[threadIdx.x] = (int)threadIdx.x < A.nd ? T(1) / qsv : T(0);
     }
     if (threadIdx.x < NEP_NLM) {
         const int lm = threadIdx.x;
@@ -354,46 +360,53 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_fast_kernel(const Ne
         for (int k = sub; k < A.nd; k += NEP_GROUP) Eq[k] = q[k] * iqs[k];
         __syncwarp(gmask);
         T es = T(0);
-        for (int p = sub; p < A.nneu; p += NEP_GROUP) {
-            const T *wrow = W0s + (size_t)(ti * A.nneu + p) * NDP;
-            T h[4] = {T(0), T(0), T(0), T(0)};
+        const T *W0t = W0s + (size_t)ti * NP * NDP;
+        for (int p0 = 0; p0 < NP; p0 += 4 * NEP_GROUP) {   // four neurons per lane at a time
+            T h[4][4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) h[i][0] = h[i][1] = h[i][2] = h[i][3] = T(0);
 #pragma unroll
             for (int c = 0; c < NDP / 4; c++) {
-                T w[4], e[4];
-                load_vec<T, 4>(wrow + 4 * c, w);
+                T e[4];
                 load_vec<T, 4>(Eq + 4 * c, e);
 #pragma unroll
-                for (int i = 0; i < 4; i++) h[i] = fma(w[i], e[i], h[i]);
+                for (int i = 0; i < 4; i++) {
+                    T w[4];
+                    load_vec<T, 4>(W0t + (size_t)(p0 + sub + NEP_GROUP * i) * NDP + 4 * c, w);
+#pragma unroll
+                    for (int k = 0; k < 4; k++) h[i][k] = fma(w[k], e[k], h[i][k]);
+                }
             }
-            const T th = gtanh((h[0] + h[1]) + (h[2] + h[3]) + B0s[ti * A.nneu + p]);
-            const T w1 = W1s[ti * A.nneu + p];
-            es += w1 * th;
-            act[p] = w1 * (T(1) - th * th);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int p = p0 + sub + NEP_GROUP * i;
+                const T th = gtanh((h[i][0] + h[i][1]) + (h[i][2] + h[i][3]) + B0s[ti * NP + p]);
+                const T w1 = W1s[ti * NP + p];   // zero for padding neurons
+                es += w1 * th;
+                act[p] = w1 * (T(1) - th * th);
+            }
         }
         if (valid) e_acc += es + (sub == 0 ? A.bias[ti] : T(0));
         __syncwarp(gmask);
         for (int c = sub; c < NDP / 4; c += NEP_GROUP) {   // lane c: descriptors 4c .. 4c+3
-            const T *wcol = W0s + (size_t)ti * A.nneu * NDP + 4 * c;
-            T a0[4] = {T(0), T(0), T(0), T(0)}, a1[4] = {T(0), T(0), T(0), T(0)};
-            int p = 0;
-            for (; p + 1 < A.nneu; p += 2) {
-                T w0[4], w1[4];
-                load_vec<T, 4>(wcol + (size_t)p * NDP, w0);
-                load_vec<T, 4>(wcol + (size_t)(p + 1) * NDP, w1);
-                const T x0 = act[p], x1 = act[p + 1];
+            const T *wcol = W0t + 4 * c;
+            T a[4][4];
 #pragma unroll
-                for (int i = 0; i < 4; i++) { a0[i] = fma(x0, w0[i], a0[i]); a1[i] = fma(x1, w1[i], a1[i]); }
-            }
-            if (p < A.nneu) {
-                T w0[4];
-                load_vec<T, 4>(wcol + (size_t)p * NDP, w0);
-                const T x0 = act[p];
+            for (int i = 0; i < 4; i++) a[i][0] = a[i][1] = a[i][2] = a[i][3] = T(0);
+            for (int p = 0; p < NP; p += 4) {
+                T x[4];
+                load_vec<T, 4>(act + p, x);
 #pragma unroll
-                for (int i = 0; i < 4; i++) a0[i] = fma(x0, w0[i], a0[i]);
+                for (int i = 0; i < 4; i++) {
+                    T w[4];
+                    load_vec<T, 4>(wcol + (size_t)(p + i) * NDP, w);
+#pragma unroll
+                    for (int k = 0; k < 4; k++) a[i][k] = fma(x[i], w[k], a[i][k]);
+                }
             }
             T r[4];
 #pragma unroll
-            for (int i = 0; i < 4; i++) r[i] = (a0[i] + a1[i]) * iqs[4 * c + i];
+            for (int k = 0; k < 4; k++) r[k] = ((a[0][k] + a[1][k]) + (a[2][k] + a[3][k])) * iqs[4 * c + k];
             store_vec<T, 4>(Eq + 4 * c, r);
         }
         __syncwarp(gmask);

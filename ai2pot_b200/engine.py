@@ -50,10 +50,10 @@ class Evaluator:
         return self.evaluate(self.build_list(coords))
 
     # kernels of this library launched by one compute() on a fully periodic cell (memsets not counted):
-    # neighbour build = set-up, count, scan, fill, build; MTP = prefix, coefficient padding, forward,
-    # contraction, force; NEP = prefix, coefficient padding, atom kernel
+    # neighbour build = set-up, count, scan, fill, build; MTP = set-up, forward, contraction, force;
+    # NEP = one kernel (single structure, up to 8 radial / angular functions)
     def launches_per_step(self):
-        return 5 + (5 if self.kind == "mtp" else 3)
+        return 5 + (4 if self.kind == "mtp" else 1)
 
 
 def fma_peak_tflops(is_f64, sms):
@@ -179,7 +179,7 @@ def run_training_benchmark(w, steps, warmup, dist, sampler):
     roofline = {"kernel": "mtp E/F/V + loss-gradient kernels (whole step)", "bound": "fp64", "achieved": achieved, "peak": peak,
                 "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": "FMA-chain microbenchmark in this run (of measured)",
                 "flops_per_atom": fl, "mean_neighbours": mean_nn, "traffic": None}
-    return dict(t_dev=t_dev, t_e2e=t_e2e, clocks=clocks, launches=(5 + 2 + 5) * steps, h2d=0, d2h=hgrad.numel() * 8, units=natoms,
+    return dict(t_dev=t_dev, t_e2e=t_e2e, clocks=clocks, launches=(4 + 2 + 4) * steps, h2d=0, d2h=hgrad.numel() * 8, units=natoms,
                 e2e_path="resident neighbour tensors -> ai2b_mtp_efv -> ai2b_mtp_loss -> ai2b_mtp_loss_backward -> D2H summed gradient",
                 roofline=roofline, parts_ms=None)
 
@@ -232,7 +232,7 @@ def run_slab_benchmark(w, steps, warmup, dist, sampler):
     roofline = {"kernel": "nep_atom_kernel (+ neighbour build) on this rank's slab", "bound": "fp32", "achieved": achieved, "peak": peak,
                 "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": "FMA-chain microbenchmark in this run (of measured)",
                 "flops_per_atom": fl, "mean_neighbours": mean_nn, "traffic": None, "owned_atoms": dom.nlocal, "ghost_atoms": dom.nghost}
-    return dict(t_dev=t_dev, t_e2e=t_e2e, clocks=clocks, launches=(9 + 3) * steps, h2d=host_owned.numel() * host_owned.element_size(),
+    return dict(t_dev=t_dev, t_e2e=t_e2e, clocks=clocks, launches=(9 + 1) * steps, h2d=host_owned.numel() * host_owned.element_size(),
                 d2h=h_f.numel() * h_f.element_size() + 40, units=len(w["types"]) / world,
                 e2e_path="pinned host positions of the slab -> H2D -> halo exchange (NCCL p2p) -> ai2b_nblist_build_ghost -> ai2b_nep_efv "
                          "-> ghost-force return -> all-reduce(E, virial) -> D2H forces, E, virial",
