@@ -104,7 +104,7 @@ struct PairState {
     int nj;
     bool act;
     __device__ __forceinline__ void setup(const MtpProgramDev &P, const MtpArgs<T> &A, const T *rc, const int *fn, const int *types,
-                                          int ti, int nn, int j, int lane, T *fr, T *fdv)
+                                          int ti, int nn, int j, int lane, T *fr, T *fdv, int frs = 32)
     {
         using V2 = typename Vec2<T>::type;
         act = j < nn;
@@ -131,8 +131,8 @@ struct PairState {
                 f = fma(c2.y, q[k + 1], f);
                 if (DERIV) { fd = fma(c2.x, dq[k], fd); fd = fma(c2.y, dq[k + 1], fd); }
             }
-            fr[m * 32 + lane] = act ? f : T(0);
-            if (DERIV) fdv[m * 32 + lane] = act ? fd : T(0);
+            fr[m * frs + lane] = act ? f : T(0);      // frs: row stride of the per-mu arrays
+            if (DERIV) fdv[m * frs + lane] = act ? fd : T(0);
         }
     }
 };

@@ -50,6 +50,197 @@ __global__ void __launch_bounds__(MTP_WARPS * 32, 4) mtp_fwd_kernel(const MtpPro
     }
 }
 
+// ---- kernel A, second form: lanes = neighbours, then lanes = monomials -------------------------------
+// The sums above cost one warp transpose-reduction per moment. Here the lanes first write their
+// neighbour's monomials (all of degree <= KD) to a shared-memory tile mono[neighbour][monomial]
+// and its radial values f_mu to a row fr[neighbour][mu]; then they switch roles: lane l owns the
+// monomials l, l + 32, ... and walks over the neighbours. In canonical order the monomials a mu
+// uses are the first ncan(kmu[mu]) ones, so one monomial load serves every mu, and the f row is a
+// broadcast load. No cross-lane reduction is left. Needs nmus <= NMU and kmu non-increasing.
+//  * The tile holds 16 neighbours: the two half-warps store in turn (the monomials are rebuilt
+//    from the 3 (KD + 1) powers, which is cheaper than a 32-neighbour tile that halves the number
+//    of resident warps).
+//  * The next atom's row (positions, neighbour indices, centre index, count) is requested before
+//    the summation loop of the current atom, and the type look-ups that depend on it are issued
+//    ahead of the radial basis, so little global-memory latency is left exposed.
+// acc[r][m] += sum_jj f[jj][m] * mono[jj][q_r] for the first C_r radial functions of lane-round r
+// (C_0 = NMU); the counts are template parameters so the loop body is branch- and select-free.
+template <typename T, int NMU, int MS, int C1, int C2>
+__device__ __forceinline__ void fwd_accumulate(const T *__restrict__ mono_s, const T *__restrict__ fh, int cnt, const int (&qidx)[3],
+                                               T (&acc)[3][NMU])
+{
+    using V2 = typename Vec2<T>::type;
+#pragma unroll 2
+    for (int jj = 0; jj < cnt; jj++) {
+        const T *mj = mono_s + jj * MS;
+        T f[NMU];
+#pragma unroll
+        for (int m = 0; m < NMU; m += 2) {
+            const V2 v = *reinterpret_cast<const V2 *>(fh + jj * NMU + m);
+            f[m] = v.x; f[m + 1] = v.y;
+        }
+        const T m0 = mj[qidx[0]];
+#pragma unroll
+        for (int m = 0; m < NMU; m++) acc[0][m] = fma(f[m], m0, acc[0][m]);
+        if constexpr (C1 > 0) {
+            const T m1 = mj[qidx[1]];
+#pragma unroll
+            for (int m = 0; m < C1; m++) acc[1][m] = fma(f[m], m1, acc[1][m]);
+        }
+        if constexpr (C2 > 0) {
+            const T m2 = mj[qidx[2]];
+#pragma unroll
+            for (int m = 0; m < C2; m++) acc[2][m] = fma(f[m], m2, acc[2][m]);
+        }
+    }
+}
+
+template <typename T, int KD, int CSP, int NMU>
+__global__ void __launch_bounds__(MTP_WARPS * 32, 4) mtp_fwd_lanes_kernel(const MtpProgramDev P, const MtpArgs<T> A)
+{
+    using V2 = typename Vec2<T>::type;
+    extern __shared__ __align__(32) unsigned char smem_raw[];
+    constexpr int NC = ncan(KD);
+    constexpr int RQ = (NC + 31) / 32;   // monomials per lane
+    constexpr int MS = NC | 1;           // odd row stride: the 16 lanes' stores to one column hit distinct banks
+    constexpr int TJ = 16;               // neighbours per tile
+    static_assert(NMU % 2 == 0, "f rows are read as pairs");
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    T *mono_s = reinterpret_cast<T *>(smem_raw) + (size_t)warp * (TJ * MS + 32 * NMU);
+    T *fr = mono_s + TJ * MS;            // [32 neighbours][NMU]
+    static_assert(RQ == 3 && NMU == 4, "the accumulation loop is specialised for three monomials per lane");
+    int qidx[RQ];
+    int c1 = 0, c2 = 0;                  // radial functions that reach into the 2nd / 3rd group of 32 monomials
+#pragma unroll
+    for (int r = 0; r < RQ; r++) qidx[r] = min(32 * r + lane, NC - 1);
+    for (int m = 0; m < P.nmus; m++) {
+        c1 += ncan(P.kmu[m]) > 32 ? 1 : 0;
+        c2 += ncan(P.kmu[m]) > 64 ? 1 : 0;
+    }
+    const int shape = c1 * 8 + c2;
+    const int ntot = A.prefix[A.B];
+    const int nw = gridDim.x * MTP_WARPS;
+
+    // row of an atom: what the first chunk needs, loaded without waiting for the neighbour count
+    // (rows are padded to umax entries, index -1 marks padding)
+    struct Row { size_t slot; int b, ci, nn, nj; T x, y, z; };
+    auto fetch = [&](int t) {
+        Row w;
+        w.b = find_structure(A.prefix, A.B, t);
+        w.slot = (size_t)w.b * A.npad + (t - A.prefix[w.b]);
+        w.ci = A.bilist[w.slot];
+        w.nn = A.numneigh[w.slot];
+        w.nj = -1; w.x = w.y = w.z = T(0);
+        if (lane < A.umax) {
+            const T *rc = A.rcs + (w.slot * A.umax + lane) * 3;
+            w.x = rc[0]; w.y = rc[1]; w.z = rc[2];
+            w.nj = A.firstneigh[w.slot * A.umax + lane];
+        }
+        return w;
+    };
+    int t = blockIdx.x * MTP_WARPS + warp;
+    Row nx;
+    if (t < ntot) nx = fetch(t);
+    for (; t < ntot; t += nw) {
+        const Row cur = nx;
+        const int nn = min(cur.nn, A.umax);
+        const int *types = A.types + (size_t)cur.b * (A.npad + (A.desc ? 0 : A.nghost));
+        const int ti = types[cur.ci];
+        T acc[RQ][NMU];
+#pragma unroll
+        for (int r = 0; r < RQ; r++)
+#pragma unroll
+            for (int m = 0; m < NMU; m++) acc[r][m] = T(0);
+        for (int j0 = 0; j0 < nn; j0 += 32) {
+            const int j = j0 + lane;
+            T x = cur.x, y = cur.y, z = cur.z;
+            int nj = cur.nj;
+            if (j0 > 0) {
+                x = y = z = T(0); nj = -1;
+                if (j < nn) {
+                    const T *rc = A.rcs + (cur.slot * A.umax + j) * 3;
+                    x = rc[0]; y = rc[1]; z = rc[2];
+                    nj = A.firstneigh[cur.slot * A.umax + j];
+                }
+            }
+            bool act = j < nn && nj >= 0;
+            const int tj = act ? types[nj] : 0;        // in flight during the radial basis
+            const T r = gsqrt(x * x + y * y + z * z);
+            act = act && (r <= A.rmax) && (r > T(0));
+            const T rinv = act ? T(1) / r : T(0);
+            {
+                T q[CSP], dq[CSP], fv[NMU];
+                mtp_radial_basis<T, CSP>(act ? r : A.rmax, A.rmax, A.rmin, A.scaling, q, dq);
+                const T *crow = A.coeffs_pad + (size_t)(ti * A.ntypes + tj) * P.nmus * CSP;
+#pragma unroll
+                for (int m = 0; m < NMU; m++) {
+                    T f = T(0);
+                    if (m < P.nmus) {
+#pragma unroll
+                        for (int k = 0; k < CSP; k += 2) {
+                            const V2 c2 = *reinterpret_cast<const V2 *>(crow + m * CSP + k);
+                            f = fma(c2.x, q[k], f);
+                            f = fma(c2.y, q[k + 1], f);
+                        }
+                    }
+                    fv[m] = act ? f : T(0);
+                }
+#pragma unroll
+                for (int m = 0; m < NMU; m += 2) {
+                    V2 v; v.x = fv[m]; v.y = fv[m + 1];
+                    *reinterpret_cast<V2 *>(fr + lane * NMU + m) = v;
+                }
+            }
+            Powers<T, KD> pw;
+            pw.set(x * rinv, y * rinv, z * rinv);
+            const int left = nn - j0;   // neighbours in this chunk (may exceed 32)
+#pragma unroll 1
+            for (int h = 0; h < 2; h++) {
+                if (h * TJ >= left) break;
+                if ((lane >> 4) == h) {
+                    T *mrow = mono_s + (lane & 15) * MS;
+                    static_for<0, KD + 1>([&](auto dd) {
+                        constexpr int D = decltype(dd)::value;
+                        static_for<0, ndeg(D)>([&](auto qq) {
+                            constexpr int Q = decltype(qq)::value;
+                            mrow[ncan(D - 1) + Q] = mono<T, KD, D, Q>(pw);
+                        });
+                    });
+                }
+                __syncwarp();
+                if (h == 0 && j0 == 0 && t + nw < ntot) nx = fetch(t + nw);   // lands during the loop below
+                const int cnt = min(TJ, left - h * TJ);
+                const T *fh = fr + h * TJ * NMU;
+                switch (shape) {   // kmu is non-increasing, so c2 <= c1
+#define AI2B_ACC(C1, C2) case C1 * 8 + C2: fwd_accumulate<T, NMU, MS, C1, C2>(mono_s, fh, cnt, qidx, acc); break;
+                    AI2B_ACC(0, 0)
+                    AI2B_ACC(1, 0) AI2B_ACC(1, 1)
+                    AI2B_ACC(2, 0) AI2B_ACC(2, 1) AI2B_ACC(2, 2)
+                    AI2B_ACC(3, 0) AI2B_ACC(3, 1) AI2B_ACC(3, 2) AI2B_ACC(3, 3)
+                    AI2B_ACC(4, 0) AI2B_ACC(4, 1) AI2B_ACC(4, 2) AI2B_ACC(4, 3) AI2B_ACC(4, 4)
+#undef AI2B_ACC
+                    default: break;
+                }
+                __syncwarp();
+            }
+        }
+        if (nn <= 0 && t + nw < ntot) nx = fetch(t + nw);
+        T *out = A.Mb + (size_t)t * A.nbp;
+#pragma unroll
+        for (int r = 0; r < RQ; r++) {
+            const int q = 32 * r + lane;
+#pragma unroll
+            for (int m = 0; m < NMU; m++) {
+                if (m < P.nmus && q < ncan(P.kmu[m])) {
+                    const int row = P.dense_basic[P.doff[m] + q];
+                    if (row >= 0) out[row] = acc[r][m];
+                }
+            }
+        }
+        for (int i = P.nb + lane; i < A.nbp; i += 32) out[i] = T(0);
+    }
+}
+
 // ---- kernel B: products and adjoint sweep, lanes = atoms ----------------------------------------
 // TA atoms per tile (32, 16 or 8); with TA < 32 the 32/TA lane groups of a warp work on different
 // rows. Shared memory: M[nm][TA+1] and (unless DESC) E[nm][TA+1], then the row tables.
@@ -398,7 +589,29 @@ static int launch_mtp_v(const ai2b_mtp_program *prog, MtpArgs<T> A, void *ws, cu
 
     const long atoms_upper = (long)A.B * A.npad;
     const long need = (atoms_upper + MTP_WARPS - 1) / MTP_WARPS;
-    {   // A: forward
+    bool fwd_done = false;
+    if constexpr (KD <= 6) {   // A: forward with lanes = monomials in the summation
+        constexpr int NMU = 4;
+        bool ok = P.nmus <= NMU;
+        for (int m = 1; m < P.nmus; m++) ok = ok && P.kmu[m] <= P.kmu[m - 1];
+        if (ok) {
+            const size_t smem = sizeof(T) * (size_t)(16 * (ncan(KD) | 1) + 32 * NMU) * MTP_WARPS;
+            auto kern = mtp_fwd_lanes_kernel<T, KD, CSP, NMU>;
+            static size_t configured = 0;
+            static int per_sm = 0;
+            if (smem > configured || per_sm == 0) {
+                if (int rc = set_smem(kern, smem, &configured)) return rc;
+                AI2B_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, MTP_WARPS * 32, smem));
+                if (per_sm < 1) per_sm = 1;
+            }
+            long blocks = (long)sm_count() * per_sm;
+            if (blocks > need) blocks = need;
+            kern<<<(unsigned)blocks, MTP_WARPS * 32, smem, st>>>(P, A);
+            AI2B_CUDA(cudaGetLastError());
+            fwd_done = true;
+        }
+    }
+    if (!fwd_done) {   // A: forward with warp reductions (levels 18, 20)
         const size_t smem = sizeof(T) * (size_t)(A.ndp + MTP_MAX_MU * 32) * MTP_WARPS;
         auto kern = mtp_fwd_kernel<T, KD, CSP>;
         static size_t configured = 0;
