@@ -106,7 +106,6 @@ struct PairState {
     __device__ __forceinline__ void setup(const MtpProgramDev &P, const MtpArgs<T> &A, const T *rc, const int *fn, const int *types,
                                           int ti, int nn, int j, int lane, T *fr, T *fdv, int frs = 32)
     {
-        using V2 = typename Vec2<T>::type;
         act = j < nn;
         x = y = z = T(0);
         nj = 0;
@@ -114,10 +113,18 @@ struct PairState {
             x = rc[3 * j]; y = rc[3 * j + 1]; z = rc[3 * j + 2];
             nj = fn[j];
         }
+        compute(P, A, types, ti, lane, fr, fdv, frs);
+    }
+    // x, y, z, nj and act (= the slot holds a neighbour) are already set
+    __device__ __forceinline__ void compute(const MtpProgramDev &P, const MtpArgs<T> &A, const int *types, int ti, int lane, T *fr,
+                                            T *fdv, int frs = 32)
+    {
+        using V2 = typename Vec2<T>::type;
+        const int tj_early = act ? types[nj] : 0;   // in flight during the square root
         const T r = gsqrt(x * x + y * y + z * z);
         act = act && (r <= A.rmax) && (r > T(0));
-        int tj = 0;
-        if (act) { tj = types[nj]; rinv = T(1) / r; } else { rinv = T(0); }
+        const int tj = act ? tj_early : 0;
+        rinv = act ? T(1) / r : T(0);
         ux = x * rinv; uy = y * rinv; uz = z * rinv;
         T q[CSP], dq[CSP];
         mtp_radial_basis<T, CSP>(act ? r : A.rmax, A.rmax, A.rmin, A.scaling, q, dq);

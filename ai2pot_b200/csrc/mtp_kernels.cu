@@ -13,6 +13,7 @@
 //
 // Reference semantics: source/descriptor/mtpr/include/mtpBasis.h:400-534, linearMtp.h:190-352.
 #include "mtp_device.cuh"
+#include <cuda_pipeline.h>
 
 namespace ai2b {
 
@@ -118,6 +119,15 @@ __global__ void __launch_bounds__(MTP_WARPS * 32, 4) mtp_fwd_lanes_kernel(const 
         c2 += ncan(P.kmu[m]) > 64 ? 1 : 0;
     }
     const int shape = c1 * 8 + c2;
+    // basic-moment row of (monomial of round r, mu), -1 for none: one table per lane
+    int *orow = reinterpret_cast<int *>(reinterpret_cast<T *>(smem_raw) + (size_t)MTP_WARPS * (TJ * MS + 32 * NMU)) + warp * (RQ * NMU * 32) + lane;
+#pragma unroll
+    for (int r = 0; r < RQ; r++)
+#pragma unroll
+        for (int m = 0; m < NMU; m++) {
+            const int q = 32 * r + lane;
+            orow[(r * NMU + m) * 32] = (m < P.nmus && q < ncan(P.kmu[m])) ? P.dense_basic[P.doff[m] + q] : -1;
+        }
     const int ntot = A.prefix[A.B];
     const int nw = gridDim.x * MTP_WARPS;
 
@@ -227,16 +237,12 @@ __global__ void __launch_bounds__(MTP_WARPS * 32, 4) mtp_fwd_lanes_kernel(const 
         if (nn <= 0 && t + nw < ntot) nx = fetch(t + nw);
         T *out = A.Mb + (size_t)t * A.nbp;
 #pragma unroll
-        for (int r = 0; r < RQ; r++) {
-            const int q = 32 * r + lane;
+        for (int r = 0; r < RQ; r++)
 #pragma unroll
             for (int m = 0; m < NMU; m++) {
-                if (m < P.nmus && q < ncan(P.kmu[m])) {
-                    const int row = P.dense_basic[P.doff[m] + q];
-                    if (row >= 0) out[row] = acc[r][m];
-                }
+                const int row = orow[(r * NMU + m) * 32];
+                if (row >= 0) out[row] = acc[r][m];
             }
-        }
         for (int i = P.nb + lane; i < A.nbp; i += 32) out[i] = T(0);
     }
 }
@@ -423,13 +429,30 @@ __global__ void __launch_bounds__(MTP_CWARPS * 32, 1) mtp_contract_kernel(const 
 template <typename T, int MODE, int KD, int CSP>
 __global__ void __launch_bounds__(MTP_WARPS * 32, 4) mtp_force_kernel(const MtpProgramDev P, const MtpArgs<T> A)
 {
+    using V2 = typename Vec2<T>::type;
     extern __shared__ __align__(32) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    // per warp: E4[4*ndp] Ed[nbp] fr, fd[2 * MU * 32]
-    T *E4 = reinterpret_cast<T *>(smem_raw) + (size_t)warp * (4 * A.ndp + A.nbp + 2 * MTP_MAX_MU * 32);
+    // block: gather table of the coefficient quadruples, s_g[ndp] (basic rows of {value, d/dx, d/dy,
+    // d/dz}; "none" points at a zero slot) and s_m[ndp][4] (their multipliers, already of type T)
+    // per warp: E4[4*ndp] Ed[nbp + 4] fr, fd[2 * MTP_MAX_MU * 32], row buffer
+    int4 *s_g = reinterpret_cast<int4 *>(smem_raw);
+    T *s_m = reinterpret_cast<T *>(smem_raw + sizeof(int4) * A.ndp);
+    T *E4 = s_m + 4 * A.ndp + (size_t)warp * (4 * A.ndp + A.nbp + 4 + 2 * MTP_MAX_MU * 32 + 96 + 36 * sizeof(int) / sizeof(T));
     T *Ed = E4 + 4 * A.ndp;
-    T *fr = Ed + A.nbp;
+    T *fr = Ed + A.nbp + 4;
     T *fdv = fr + MTP_MAX_MU * 32;
+    T *rb_rc = fdv + MTP_MAX_MU * 32;                       // [32][3] positions of the first 32 neighbours
+    int *rb_fn = reinterpret_cast<int *>(rb_rc + 96);       // [32] their indices, then centre index and count
+    for (int c = threadIdx.x; c < P.ndense; c += blockDim.x) {
+        int4 g = P.e4g[c];
+        const int mu = P.e4m[c];
+        g.x = g.x >= 0 ? g.x : A.nbp; g.y = g.y >= 0 ? g.y : A.nbp;
+        g.z = g.z >= 0 ? g.z : A.nbp; g.w = g.w >= 0 ? g.w : A.nbp;
+        s_g[c] = g;
+        s_m[4 * c] = T(1); s_m[4 * c + 1] = T(mu & 255); s_m[4 * c + 2] = T((mu >> 8) & 255); s_m[4 * c + 3] = T((mu >> 16) & 255);
+    }
+    if (lane < 4) Ed[A.nbp + lane] = T(0);
+    __syncthreads();
 
     const int ntot = A.prefix[A.B];
     const int nw = gridDim.x * MTP_WARPS, gw = blockIdx.x * MTP_WARPS + warp;
@@ -450,43 +473,66 @@ __global__ void __launch_bounds__(MTP_WARPS * 32, 4) mtp_force_kernel(const MtpP
         }
     };
 
+    // The row of the next atom (positions and indices of its first 32 neighbours, centre index,
+    // count) and its adjoints are copied into shared memory asynchronously while the current atom
+    // is evaluated: no registers are held, and the copies need not wait for the count because rows
+    // are padded to umax entries.
+    int fb = -1, fb_end = 0, row_b = 0;
+    size_t row_slot = 0;
+    auto request = [&](int t) {
+        if (t >= fb_end || fb < 0) { fb = find_structure(A.prefix, A.B, t); fb_end = A.prefix[fb + 1]; }
+        row_b = fb;
+        row_slot = (size_t)fb * A.npad + (t - A.prefix[fb]);
+        if (lane < A.umax) {
+            const T *src = A.rcs + (row_slot * A.umax + lane) * 3;
+#pragma unroll
+            for (int k = 0; k < 3; k++) __pipeline_memcpy_async(rb_rc + 3 * lane + k, src + k, sizeof(T));
+            __pipeline_memcpy_async(rb_fn + lane, A.firstneigh + row_slot * A.umax + lane, sizeof(int));
+        }
+        if (lane == 0) __pipeline_memcpy_async(rb_fn + 32, A.bilist + row_slot, sizeof(int));
+        if (lane == 1) __pipeline_memcpy_async(rb_fn + 33, A.numneigh + row_slot, sizeof(int));
+        const T *ein = A.Eb + (size_t)t * A.nbp;
+        for (int i = lane; i < A.nbp; i += 32) __pipeline_memcpy_async(Ed + i, ein + i, sizeof(T));
+        __pipeline_commit();
+    };
+    if (t0 < t1) request(t0);
+
     for (int t = t0; t < t1; t++) {
-        if (t >= b_end || cur_b < 0) {
+        __pipeline_wait_prior(0);
+        __syncwarp();
+        if (row_b != cur_b) {
             flush();
-            cur_b = find_structure(A.prefix, A.B, t);
-            b_end = A.prefix[cur_b + 1];
+            cur_b = row_b;
         }
         const int b = cur_b;
-        const size_t slot = (size_t)b * A.npad + (t - A.prefix[b]);
-        const int ci = A.bilist[slot];
-        const int nn = min(A.numneigh[slot], A.umax);
+        const size_t slot = row_slot;
+        const int ci = rb_fn[32];
+        const int nn = min(rb_fn[33], A.umax);
         const int *types = A.types + (size_t)b * (A.npad + A.nghost);
         const int ti = types[ci];
         const int *fn = A.firstneigh + slot * A.umax;
         const T *rc = A.rcs + slot * A.umax * 3;
 
-        // the first chunk of neighbours is set up before the coefficient quadruples are built: its
-        // global loads (neighbour row, types, radial coefficients) overlap the loads of the adjoint row
         PairState<T, CSP, true> ps;
-        ps.setup(P, A, rc, fn, types, ti, nn, lane, lane, fr, fdv);
+        ps.act = lane < nn;
+        ps.x = ps.y = ps.z = T(0); ps.nj = 0;
+        if (ps.act) { ps.x = rb_rc[3 * lane]; ps.y = rb_rc[3 * lane + 1]; ps.z = rb_rc[3 * lane + 2]; ps.nj = rb_fn[lane]; }
+        ps.compute(P, A, types, ti, lane, fr, fdv);
 
-        // adjoints of this atom -> coefficient quadruples {e, (ax+1) e[+x], (ay+1) e[+y], (az+1) e[+z]}
-        const T *ein = A.Eb + (size_t)t * A.nbp;
-        for (int i = lane; i < A.nbp; i += 32) Ed[i] = ein[i];
-        __syncwarp();
+        // adjoints -> coefficient quadruples {e, (ax+1) e[+x], (ay+1) e[+y], (az+1) e[+z]}
         for (int c = lane; c < P.ndense; c += 32) {
-            using V2 = typename Vec2<T>::type;
-            const int4 g = P.e4g[c];
-            const int mu = P.e4m[c];
+            const int4 g = s_g[c];
+            const V2 m01 = *reinterpret_cast<const V2 *>(s_m + 4 * c), m23 = *reinterpret_cast<const V2 *>(s_m + 4 * c + 2);
             V2 lo, hi;
-            lo.x = g.x >= 0 ? Ed[g.x] : T(0);
-            lo.y = g.y >= 0 ? T(mu & 255) * Ed[g.y] : T(0);
-            hi.x = g.z >= 0 ? T((mu >> 8) & 255) * Ed[g.z] : T(0);
-            hi.y = g.w >= 0 ? T((mu >> 16) & 255) * Ed[g.w] : T(0);
+            lo.x = Ed[g.x];
+            lo.y = m01.y * Ed[g.y];
+            hi.x = m23.x * Ed[g.z];
+            hi.y = m23.y * Ed[g.w];
             *reinterpret_cast<V2 *>(E4 + 4 * c) = lo;
             *reinterpret_cast<V2 *>(E4 + 4 * c + 2) = hi;
         }
         __syncwarp();
+        if (t + 1 < t1) request(t + 1);   // lands while this atom is evaluated
 
         T *frc = A.force + (size_t)b * (A.npad + A.nghost) * 3;
         T fcx = T(0), fcy = T(0), fcz = T(0);
@@ -595,7 +641,7 @@ static int launch_mtp_v(const ai2b_mtp_program *prog, MtpArgs<T> A, void *ws, cu
         bool ok = P.nmus <= NMU;
         for (int m = 1; m < P.nmus; m++) ok = ok && P.kmu[m] <= P.kmu[m - 1];
         if (ok) {
-            const size_t smem = sizeof(T) * (size_t)(16 * (ncan(KD) | 1) + 32 * NMU) * MTP_WARPS;
+            const size_t smem = (sizeof(T) * (size_t)(16 * (ncan(KD) | 1) + 32 * NMU) + sizeof(int) * 3 * NMU * 32) * MTP_WARPS;
             auto kern = mtp_fwd_lanes_kernel<T, KD, CSP, NMU>;
             static size_t configured = 0;
             static int per_sm = 0;
@@ -631,7 +677,8 @@ static int launch_mtp_v(const ai2b_mtp_program *prog, MtpArgs<T> A, void *ws, cu
         if (rc) return rc;
     }
     if (MODE != MODE_DESC) {   // C: forces / virial
-        const size_t smem = sizeof(T) * (size_t)(4 * A.ndp + A.nbp + 2 * MTP_MAX_MU * 32) * MTP_WARPS;
+        const size_t smem = sizeof(int4) * A.ndp + sizeof(T) * 4 * A.ndp +
+                            sizeof(T) * (size_t)(4 * A.ndp + A.nbp + 4 + 2 * MTP_MAX_MU * 32 + 96 + 36 * sizeof(int) / sizeof(T)) * MTP_WARPS;
         auto kern = mtp_force_kernel<T, MODE, KD, CSP>;
         static size_t configured = 0;
         static int per_sm = 0;
