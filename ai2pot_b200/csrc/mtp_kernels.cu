@@ -426,22 +426,29 @@ __global__ void __launch_bounds__(MTP_CWARPS * 32, 1) mtp_contract_kernel(const 
 }
 
 // ---- kernel C: force and virial -----------------------------------------------------------------
+// shared-memory elements (of T) per warp: E4[4 ndp] Ed[nbp + 4] fr, fd[2 nmus 32] row buffer [96 + 36 ints]
+template <typename T>
+__host__ __device__ inline size_t force_warp_elems(int ndp, int nbp, int nmus)
+{
+    return (size_t)4 * ndp + nbp + 4 + 2 * nmus * 32 + 96 + 36 * sizeof(int) / sizeof(T);
+}
+
 template <typename T, int MODE, int KD, int CSP>
-__global__ void __launch_bounds__(MTP_WARPS * 32, 4) mtp_force_kernel(const MtpProgramDev P, const MtpArgs<T> A)
+__global__ void __launch_bounds__(MTP_WARPS * 32, 3) mtp_force_kernel(const MtpProgramDev P, const MtpArgs<T> A)
 {
     using V2 = typename Vec2<T>::type;
     extern __shared__ __align__(32) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     // block: gather table of the coefficient quadruples, s_g[ndp] (basic rows of {value, d/dx, d/dy,
     // d/dz}; "none" points at a zero slot) and s_m[ndp][4] (their multipliers, already of type T)
-    // per warp: E4[4*ndp] Ed[nbp + 4] fr, fd[2 * MTP_MAX_MU * 32], row buffer
+    // per warp: see force_warp_elems
     int4 *s_g = reinterpret_cast<int4 *>(smem_raw);
     T *s_m = reinterpret_cast<T *>(smem_raw + sizeof(int4) * A.ndp);
-    T *E4 = s_m + 4 * A.ndp + (size_t)warp * (4 * A.ndp + A.nbp + 4 + 2 * MTP_MAX_MU * 32 + 96 + 36 * sizeof(int) / sizeof(T));
+    T *E4 = s_m + 4 * A.ndp + (size_t)warp * force_warp_elems<T>(A.ndp, A.nbp, P.nmus);
     T *Ed = E4 + 4 * A.ndp;
     T *fr = Ed + A.nbp + 4;
-    T *fdv = fr + MTP_MAX_MU * 32;
-    T *rb_rc = fdv + MTP_MAX_MU * 32;                       // [32][3] positions of the first 32 neighbours
+    T *fdv = fr + P.nmus * 32;
+    T *rb_rc = fdv + P.nmus * 32;                           // [32][3] positions of the first 32 neighbours
     int *rb_fn = reinterpret_cast<int *>(rb_rc + 96);       // [32] their indices, then centre index and count
     for (int c = threadIdx.x; c < P.ndense; c += blockDim.x) {
         int4 g = P.e4g[c];
@@ -678,7 +685,7 @@ static int launch_mtp_v(const ai2b_mtp_program *prog, MtpArgs<T> A, void *ws, cu
     }
     if (MODE != MODE_DESC) {   // C: forces / virial
         const size_t smem = sizeof(int4) * A.ndp + sizeof(T) * 4 * A.ndp +
-                            sizeof(T) * (size_t)(4 * A.ndp + A.nbp + 4 + 2 * MTP_MAX_MU * 32 + 96 + 36 * sizeof(int) / sizeof(T)) * MTP_WARPS;
+                            sizeof(T) * force_warp_elems<T>(A.ndp, A.nbp, P.nmus) * MTP_WARPS;
         auto kern = mtp_force_kernel<T, MODE, KD, CSP>;
         static size_t configured = 0;
         static int per_sm = 0;
