@@ -56,6 +56,11 @@ class ClockSampler:
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thr = threading.Thread(target=self._read, daemon=True)
             self.thr.start()
+            # nvidia-smi takes ~0.1-0.3 s to attach to the driver; wait for its first line so that this
+            # start-up does not run (and perturb kernel launches) inside the timed region
+            t0 = time.time()
+            while not self.rows and time.time() - t0 < 3.0:
+                time.sleep(0.01)
         except Exception:
             self.proc = None
 
