@@ -82,10 +82,24 @@ class SlabDomain:
                                     torch.int32, ())
             self.types[self.nlocal: self.nlocal + self.n_from_left] = tl
             self.types[self.nlocal + self.n_from_left:] = tr
+        # one buffer [owned | ghosts from the left | ghosts from the right]; `owned` is a view of its head
         self.local = torch.empty(self.ntotal, 3, dtype=self.dtype, device=device)
-        # periodic wrap of the end slabs: copies coming "around" the cell are shifted by a0
-        self.shift_from_left = -1.0 if rank == 0 else 0.0
-        self.shift_from_right = 1.0 if rank == nranks - 1 else 0.0
+        self.local[: self.nlocal] = self.owned
+        self.owned = self.local[: self.nlocal]
+        self.ghost_left = self.local[self.nlocal: self.nlocal + self.n_from_left]
+        self.ghost_right = self.local[self.nlocal + self.n_from_left:]
+        # Periodic wrap of the end slabs: copies going "around" the cell are shifted by -/+ a0. The sender
+        # applies it, with the reference's image arithmetic r + a0 * n (source/nblist/include/structure.h:654-682).
+        nl, nr = len(self.send_left), len(self.send_right)
+        self.send_idx = torch.cat([self.send_left, self.send_right])
+        self.send_buf = torch.empty(nl + nr, 3, dtype=self.dtype, device=device)
+        self.back = torch.empty(nl + nr, 3, dtype=self.dtype, device=device)      # ghost forces coming home
+        shift = torch.zeros(nl + nr, 3, dtype=self.dtype, device=device)
+        if nranks > 1 and rank == 0:
+            shift[:nl] = self.a0 * 1.0           # my left neighbour is the last slab: it sees these one cell up
+        if nranks > 1 and rank == nranks - 1:
+            shift[nl:] = self.a0 * -1.0          # my right neighbour is slab 0
+        self.send_shift = shift if (nranks > 1 and (rank == 0 or rank == nranks - 1)) else None
         self.pbc = (nranks == 1, True, True)
 
     # -- plumbing ----------------------------------------------------------------------------------
@@ -98,12 +112,13 @@ class SlabDomain:
         else:
             self.dist.all_gather(out, t)
 
-    def _exchange(self, to_left, to_right, dtype, tail):
+    def _exchange(self, to_left, to_right, dtype, tail, from_left=None, from_right=None):
         """Send `to_left` to the left neighbour and `to_right` to the right one; returns what the
         left and the right neighbours sent here (sizes known from set-up)."""
         d = self.dist
-        from_left = torch.empty((self.n_from_left,) + tail, dtype=dtype, device=self.device)
-        from_right = torch.empty((self.n_from_right,) + tail, dtype=dtype, device=self.device)
+        if from_left is None:
+            from_left = torch.empty((self.n_from_left,) + tail, dtype=dtype, device=self.device)
+            from_right = torch.empty((self.n_from_right,) + tail, dtype=dtype, device=self.device)
         # tag 0: "towards lower x", tag 1: "towards higher x". With two ranks both neighbours are the
         # same peer; the tags (gloo) and the posting order (NCCL, which ignores tags) keep the two
         # messages apart: what the peer sent towards lower x arrives as our right-hand ghosts.
@@ -115,30 +130,30 @@ class SlabDomain:
 
     # -- one evaluation ------------------------------------------------------------------------------
     def halo_exchange(self):
-        """Step 1: self.local = [owned | ghosts from the left | ghosts from the right]."""
-        self.local[: self.nlocal] = self.owned
+        """Step 1: boundary positions (already shifted for the wrap) go straight into the neighbours'
+        ghost rows of `local`: one gather, one add on the end slabs, one grouped send/receive."""
         if self.P > 1:
-            gl, gr = self._exchange(self.owned[self.send_left].contiguous(), self.owned[self.send_right].contiguous(), self.dtype, (3,))
-            # image arithmetic of the reference: r + a0 * n (source/nblist/include/structure.h:654-682)
-            self.local[self.nlocal: self.nlocal + self.n_from_left] = gl + self.a0 * self.shift_from_left if self.shift_from_left else gl
-            self.local[self.nlocal + self.n_from_left:] = gr + self.a0 * self.shift_from_right if self.shift_from_right else gr
+            nl = len(self.send_left)
+            torch.index_select(self.owned, 0, self.send_idx, out=self.send_buf)
+            if self.send_shift is not None:
+                self.send_buf.add_(self.send_shift)
+            self._exchange(self.send_buf[:nl], self.send_buf[nl:], self.dtype, (3,), self.ghost_left, self.ghost_right)
         return self.local
 
     def reduce_ghost_forces(self, force):
-        """Step 4: force is [ntotal,3]; ghost rows go back to the ranks that own those atoms."""
+        """Step 4: force is [ntotal,3]; ghost rows go back to the ranks that own those atoms, which add
+        them with one indexed accumulation."""
         owned = force[: self.nlocal]
         if self.P > 1:
-            gl = force[self.nlocal: self.nlocal + self.n_from_left].contiguous()
-            gr = force[self.nlocal + self.n_from_left:].contiguous()
+            nl = len(self.send_left)
+            gl = force[self.nlocal: self.nlocal + self.n_from_left]
+            gr = force[self.nlocal + self.n_from_left:]
             d = self.dist
-            back_left = torch.empty(len(self.send_left), 3, dtype=self.dtype, device=self.device)     # from the left neighbour
-            back_right = torch.empty(len(self.send_right), 3, dtype=self.dtype, device=self.device)   # from the right neighbour
             ops = [d.P2POp(d.isend, gl, self.left, tag=0), d.P2POp(d.isend, gr, self.right, tag=1),
-                   d.P2POp(d.irecv, back_right, self.right, tag=0), d.P2POp(d.irecv, back_left, self.left, tag=1)]
+                   d.P2POp(d.irecv, self.back[nl:], self.right, tag=0), d.P2POp(d.irecv, self.back[:nl], self.left, tag=1)]
             for r in d.batch_isend_irecv(ops):
                 r.wait()
-            owned.index_add_(0, self.send_left, back_left)
-            owned.index_add_(0, self.send_right, back_right)
+            owned.index_add_(0, self.send_idx, self.back)
         return owned
 
     def evaluate(self, compute):
