@@ -330,15 +330,17 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
     const unsigned lt_mask = (1u << lane) - 1u;
     int local_max = 0;
 
-    // Large systems: every warp takes a contiguous run of the bin-ordered atoms, so consecutive
-    // centres mostly share their bin and the table of neighbouring bins is built once per bin.
-    // Small systems: atoms are dealt round-robin (a run would leave most warps without work).
+    // Large systems: warps take runs of 16 bin-ordered atoms, dealt round-robin, so consecutive centres
+    // mostly share their bin and the table of neighbouring bins is built once per bin, while ghost
+    // regions (atoms that are neighbours only) spread over all warps. Small systems: single atoms are
+    // dealt round-robin (runs would leave most warps without work).
     const int gw = blockIdx.x * NB_WARPS + warp;
-    const int per = (P.n + nwarps - 1) / nwarps;
-    const bool runs = per >= 8;
+    const int RUN = (P.n + nwarps - 1) / nwarps >= 8 ? 16 : 1;
+    const int nruns = (P.n + RUN - 1) / RUN;
     int cached_bin = -1;
-    for (int it = 0; it < per; it++) {
-        const int a = runs ? gw * per + it : it * nwarps + gw;
+    for (int run = gw; run < nruns; run += nwarps)
+    for (int k = 0; k < RUN; k++) {
+        const int a = run * RUN + k;
         if (a >= P.n) break;
         const typename Vec4<T>::type pi = spos[a];
         const int4 si = sinfo[a];
