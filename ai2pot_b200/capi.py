@@ -242,6 +242,20 @@ def nep_efv(model, nb, virial=True, out=None):
     return (e, f, v) if virial else (e, f)
 
 
+def zbl_efv(nb, type_map, rmax, rmin, cks, dks, e, f, v=None):
+    """Adds the ZBL pair correction onto e[B], f[B,Np+nghost,3] and (if given) v[B,9] in place.
+    type_map: int32 atomic numbers [ntypes]; cks, dks: [ntypes*ntypes*4] (device tensors)."""
+    rcs = nb["brcs"]
+    suf, cf = _suf(rcs.dtype)
+    B, npad = nb["bilist"].shape
+    umax = nb["bfirstneigh"].shape[2]
+    _check(getattr(lib(), "ai2b_zbl_efv_" + suf)(
+        _ptr(e), _ptr(f), _ptr(v), C.c_int(B), C.c_int(npad), _ptr(nb["binum"]), _ptr(nb["bilist"]), _ptr(nb["bnumneigh"]),
+        _ptr(nb["bfirstneigh"]), _ptr(rcs), _ptr(nb["btypes"]), C.c_int(int(nb["ntypes"])), _ptr(type_map), C.c_int(umax),
+        C.c_int(int(nb.get("nghost", 0))), cf(rmax), cf(rmin), _ptr(cks), _ptr(dks), _stream()))
+    return e, f, v
+
+
 def nep_descriptors(model, nb):
     rcs = nb["brcs"]
     suf, cf = _suf(rcs.dtype)

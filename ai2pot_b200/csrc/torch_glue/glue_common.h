@@ -46,4 +46,35 @@ inline at::Tensor workspace(size_t bytes, const at::Tensor &like)
     return at::empty({(int64_t)(bytes < 256 ? 256 : bytes)}, like.options().dtype(at::kByte));
 }
 
+// ZBL parameters of an op call (zbl_rmax <= 0: no correction)
+struct ZblArgs {
+    double rmax, rmin;
+    const at::Tensor &cks, &dks;
+};
+
+// adds the ZBL pair correction onto e[B], f[B,Np+nghost,3] and, if defined, v[B,9]
+inline void apply_zbl(const ZblArgs &z, at::Tensor &e, at::Tensor &f, const at::Tensor &v, const at::Tensor &binum,
+                      const at::Tensor &bilist, const at::Tensor &bnumneigh, const at::Tensor &bfirstneigh, const at::Tensor &brcs,
+                      const at::Tensor &btypes, const at::Tensor &type_map, int64_t nghost)
+{
+    if (z.rmax <= 0.0) return;
+    const int B = (int)binum.size(0), npad = (int)bnumneigh.size(1), umax = (int)bfirstneigh.size(2), ntypes = (int)type_map.size(0);
+    TORCH_CHECK(z.cks.numel() >= (int64_t)ntypes * ntypes * 4 && z.dks.numel() >= (int64_t)ntypes * ntypes * 4,
+                "zbl_cks / zbl_dks must hold ntypes * ntypes * 4 values");
+    int rc;
+    if (brcs.scalar_type() == at::kDouble)
+        rc = ai2b_zbl_efv_f64(e.data_ptr<double>(), f.data_ptr<double>(), v.defined() ? v.data_ptr<double>() : nullptr, B, npad,
+                              iptr(binum, "binum"), iptr(bilist, "bilist"), iptr(bnumneigh, "bnumneigh"), iptr(bfirstneigh, "bfirstneigh"),
+                              fptr<double>(brcs, brcs, "brcs"), iptr(btypes, "btypes"), ntypes, iptr(type_map, "type_map"), umax,
+                              (int)nghost, z.rmax, z.rmin, fptr<double>(z.cks, brcs, "zbl_cks"), fptr<double>(z.dks, brcs, "zbl_dks"),
+                              stream());
+    else
+        rc = ai2b_zbl_efv_f32(e.data_ptr<float>(), f.data_ptr<float>(), v.defined() ? v.data_ptr<float>() : nullptr, B, npad,
+                              iptr(binum, "binum"), iptr(bilist, "bilist"), iptr(bnumneigh, "bnumneigh"), iptr(bfirstneigh, "bfirstneigh"),
+                              fptr<float>(brcs, brcs, "brcs"), iptr(btypes, "btypes"), ntypes, iptr(type_map, "type_map"), umax,
+                              (int)nghost, (float)z.rmax, (float)z.rmin, fptr<float>(z.cks, brcs, "zbl_cks"),
+                              fptr<float>(z.dks, brcs, "zbl_dks"), stream());
+    check(rc, "ai2b_zbl_efv");
+}
+
 }  // namespace ai2b_glue

@@ -113,15 +113,19 @@ variable_list efv_dispatch(bool with_virial, int64_t cs, double scaling, const a
                            const at::Tensor &map, int64_t nmus, const at::Tensor &binum, const at::Tensor &bilist,
                            const at::Tensor &bnumneigh, const at::Tensor &bfirstneigh, const at::Tensor &brcs,
                            const at::Tensor &btypes, const at::Tensor &type_map, int64_t nghost, double rmax, double rmin,
-                           const at::Tensor &qs, double zbl_rmax)
+                           const at::Tensor &qs, const ZblArgs &zbl)
 {
-    TORCH_CHECK(zbl_rmax <= 0.0, "the ZBL correction (zbl_rmax > 0) is not part of this build");
-    if (brcs.scalar_type() == at::kDouble)
-        return efv_impl<double>(with_virial, cs, scaling, coeffs, lin, bias, nm, basic, times, map, nmus, binum, bilist, bnumneigh,
-                                bfirstneigh, brcs, btypes, type_map, nghost, rmax, rmin, qs);
-    TORCH_CHECK(brcs.scalar_type() == at::kFloat, "brcs must be float32 or float64");
-    return efv_impl<float>(with_virial, cs, scaling, coeffs, lin, bias, nm, basic, times, map, nmus, binum, bilist, bnumneigh,
-                           bfirstneigh, brcs, btypes, type_map, nghost, rmax, rmin, qs);
+    TORCH_CHECK(brcs.scalar_type() == at::kDouble || brcs.scalar_type() == at::kFloat, "brcs must be float32 or float64");
+    variable_list out = brcs.scalar_type() == at::kDouble
+        ? efv_impl<double>(with_virial, cs, scaling, coeffs, lin, bias, nm, basic, times, map, nmus, binum, bilist, bnumneigh,
+                           bfirstneigh, brcs, btypes, type_map, nghost, rmax, rmin, qs)
+        : efv_impl<float>(with_virial, cs, scaling, coeffs, lin, bias, nm, basic, times, map, nmus, binum, bilist, bnumneigh,
+                          bfirstneigh, brcs, btypes, type_map, nghost, rmax, rmin, qs);
+    // the reference's CUDA op adds the correction before its kernels accumulate (linearMtpOp.cc:2920-2947);
+    // the sum is the same in either order
+    apply_zbl(zbl, out[0], out[1], with_virial ? out[2] : at::Tensor(), binum, bilist, bnumneigh, bfirstneigh, brcs, btypes, type_map,
+              nghost);
+    return out;
 }
 
 variable_list descriptors_dispatch(int64_t cs, double scaling, const at::Tensor &coeffs, int64_t nm, const at::Tensor &basic,
@@ -199,12 +203,11 @@ TORCH_LIBRARY(mtpr, m)
              const at::Tensor &bfirstneigh_tensor, const at::Tensor &brcs_tensor, const at::Tensor &btypes_tensor,
              const at::Tensor &type_map_tensor, int64_t nghost, double rmax, double rmin, const at::Tensor &q_scaler_tensor,
              double zbl_rmax, double zbl_rmin, const at::Tensor &zbl_cks_tensor, const at::Tensor &zbl_dks_tensor) {
-              (void)zbl_rmin; (void)zbl_cks_tensor; (void)zbl_dks_tensor;
               return efv_dispatch(true, chebyshev_size, scaling, coeffs_tensor, linear_coeffs_tensor, type_bias_tensor,
                                   alpha_moments_count, alpha_index_basic_tensor, alpha_index_times_tensor,
                                   alpha_moment_mapping_tensor, nmus, binum_tensor, bilist_tensor, bnumneigh_tensor,
                                   bfirstneigh_tensor, brcs_tensor, btypes_tensor, type_map_tensor, nghost, rmax, rmin,
-                                  q_scaler_tensor, zbl_rmax);
+                                  q_scaler_tensor, ZblArgs{zbl_rmax, zbl_rmin, zbl_cks_tensor, zbl_dks_tensor});
           });
     m.def("linearMtpToEFOp",
           [](int64_t chebyshev_size, double scaling, const at::Tensor &coeffs_tensor, const at::Tensor &linear_coeffs_tensor,
@@ -214,12 +217,11 @@ TORCH_LIBRARY(mtpr, m)
              const at::Tensor &bfirstneigh_tensor, const at::Tensor &brcs_tensor, const at::Tensor &btypes_tensor,
              const at::Tensor &type_map_tensor, int64_t nghost, double rmax, double rmin, const at::Tensor &q_scaler_tensor,
              double zbl_rmax, double zbl_rmin, const at::Tensor &zbl_cks_tensor, const at::Tensor &zbl_dks_tensor) {
-              (void)zbl_rmin; (void)zbl_cks_tensor; (void)zbl_dks_tensor;
               return efv_dispatch(false, chebyshev_size, scaling, coeffs_tensor, linear_coeffs_tensor, type_bias_tensor,
                                   alpha_moments_count, alpha_index_basic_tensor, alpha_index_times_tensor,
                                   alpha_moment_mapping_tensor, nmus, binum_tensor, bilist_tensor, bnumneigh_tensor,
                                   bfirstneigh_tensor, brcs_tensor, btypes_tensor, type_map_tensor, nghost, rmax, rmin,
-                                  q_scaler_tensor, zbl_rmax);
+                                  q_scaler_tensor, ZblArgs{zbl_rmax, zbl_rmin, zbl_cks_tensor, zbl_dks_tensor});
           });
     m.def("linearMtpToDescriptorsOp",
           [](int64_t chebyshev_size, double scaling, const at::Tensor &coeffs_tensor, int64_t alpha_moments_count,

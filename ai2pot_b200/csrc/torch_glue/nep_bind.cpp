@@ -13,9 +13,8 @@ variable_list nep_efv(bool with_virial, int64_t cs, int64_t n_r, int64_t n_a, in
                       const at::Tensor &w0, const at::Tensor &b0, const at::Tensor &w1, const at::Tensor &bias,
                       const at::Tensor &binum, const at::Tensor &bilist, const at::Tensor &bnumneigh, const at::Tensor &bfirstneigh,
                       const at::Tensor &brcs, const at::Tensor &btypes, const at::Tensor &type_map, int64_t nghost, double rc_r,
-                      double rc_a, const at::Tensor &qs, double zbl_rmax)
+                      double rc_a, const at::Tensor &qs, const ZblArgs &zbl)
 {
-    TORCH_CHECK(zbl_rmax <= 0.0, "the ZBL correction (zbl_rmax > 0) is not part of this build");
     require_cuda(brcs, "brcs");
     c10::cuda::CUDAGuard guard(brcs.device());
     const int B = (int)binum.size(0), npad = (int)bnumneigh.size(1), umax = (int)bfirstneigh.size(2), ntypes = (int)type_map.size(0);
@@ -41,6 +40,7 @@ variable_list nep_efv(bool with_virial, int64_t cs, int64_t n_r, int64_t n_a, in
                               fptr<float>(brcs, brcs, "brcs"), iptr(btypes, "btypes"), ntypes, umax, (int)nghost, (float)rc_r, (float)rc_a,
                               fptr<float>(qs, brcs, "q_scaler"), ws.data_ptr(), (size_t)ws.numel(), stream());
     check(rc, "ai2b_nep_efv");
+    apply_zbl(zbl, e, f, v, binum, bilist, bnumneigh, bfirstneigh, brcs, btypes, type_map, nghost);
     if (with_virial) return {e, f, v};
     return {e, f};
 }
@@ -84,16 +84,14 @@ variable_list nep_desc(int64_t cs, int64_t n_r, int64_t n_a, int64_t l_max, cons
 #define NEP_EFV_PASS                                                                                                         \
     chebyshev_size, n_radial_basis, n_angular_basis, l_max, coeffs_tensor, w0_tensor, b0_tensor, w1_tensor, type_bias_tensor, \
         binum_tensor, bilist_tensor, bnumneigh_tensor, bfirstneigh_tensor, brcs_tensor, btypes_tensor, type_map_tensor,      \
-        nghost, rmax_radial, rmax_angular, q_scaler_tensor, zbl_rmax
+        nghost, rmax_radial, rmax_angular, q_scaler_tensor, ZblArgs{zbl_rmax, zbl_rmin, zbl_cks_tensor, zbl_dks_tensor}
 
 TORCH_LIBRARY(nep, m)
 {
     m.def("nepToEFVOp", [](NEP_EFV_ARGS) {
-        (void)zbl_rmin; (void)zbl_cks_tensor; (void)zbl_dks_tensor;
         return nep_efv(true, NEP_EFV_PASS);
     });
     m.def("nepToEFOp", [](NEP_EFV_ARGS) {
-        (void)zbl_rmin; (void)zbl_cks_tensor; (void)zbl_dks_tensor;
         return nep_efv(false, NEP_EFV_PASS);
     });
     m.def("nepToDescriptorsOp",

@@ -235,6 +235,27 @@ int ai2b_nep_efv_static_scratch_f32(float *d_betot, float *d_bforce, float *d_bv
 AI2B_DECL_FVT(f64, double)
 AI2B_DECL_FVT(f32, float)
 
+/* ------------------------------------------------------------------------------------------
+ * ZBL screened-Coulomb pair correction, added onto etot[B], force[B,Np+nghost,3] and (if not NULL)
+ * virial[B,9] of a preceding MTP / NEP evaluation of the same batch. Replaces
+ * correct_zbl_efv_torch_launcher<T> / correct_zbl_ef_torch_launcher<T>
+ * (source/descriptor/correction/gpu/include/zbl_torch_launcher.h, kernels zbl.cuh:423-690) with
+ * the pair functions of source/descriptor/correction/include/zbl.h:276-395. d_type_map[ntypes]
+ * holds the atomic numbers, d_cks / d_dks [ntypes*ntypes*4] the screening coefficients.
+ * The reference's CPU ops differ from its CUDA ops here: GroupZBL::correct_efv adds the energy
+ * only (zbl.h:545-548) and the CPU MTP launcher then zeroes even that; these entry points follow
+ * the CUDA path (energy, force, virial).
+ * ---------------------------------------------------------------------------------------- */
+#define AI2B_DECL_ZBL(SUF, T)                                                                    \
+    int ai2b_zbl_efv_##SUF(T *d_betot, T *d_bforce, T *d_bvirial, int batch_size,                \
+                           int natoms_pad, const int *d_binum, const int *d_bilist,              \
+                           const int *d_bnumneigh, const int *d_bfirstneigh, const T *d_brcs,    \
+                           const int *d_btypes, int ntypes, const int *d_type_map, int umax,     \
+                           int nghost, T zbl_rmax, T zbl_rmin, const T *d_cks, const T *d_dks,   \
+                           void *stream);
+AI2B_DECL_ZBL(f64, double)
+AI2B_DECL_ZBL(f32, float)
+
 /* FMA-pipe microbenchmark used for the roofline denominator (no counterpart in the reference):
  * blocks x 256 threads, 8 independent chains of `iters` fused multiply-adds each. */
 int ai2b_fma_chain(int is_f64, int blocks, int iters, void *d_out, void *stream);

@@ -664,5 +664,50 @@ int NAME2(orc_fvt_virial)(T *virial, int inum, const int *numneigh, const T *rcs
     return 0;
 }
 
+/* ZBL pair correction, complete form (energy, force on the centre atom, virial; accumulates into the
+ * outputs): pair functions of descriptor/correction/include/zbl.h:276-395 applied per directed pair as
+ * in descriptor/correction/gpu/include/zbl.cuh:423-500. Expressions that involve the double constant
+ * K_C_SP or std::pow(T, int) are evaluated in double, as in the reference. */
+int NAME2(orc_zbl_efv)(T *etot, T *force, T *virial, int inum, const int *ilist, const int *numneigh, const int *firstneigh,
+                       const T *rcs, const int *types, int ntypes, const int *type_map, int umax, int nghost, T rmax, T rmin,
+                       const T *cks, const T *dks)
+{
+    const double KC = 14.399645;
+    (void)nghost;
+    for (int ii = 0; ii < inum; ii++) {
+        const int ci = ilist[ii], ti = types[ci];
+        for (int jj = 0; jj < numneigh[ii]; jj++) {
+            const T *v = rcs + ((size_t)ii * umax + jj) * 3;
+            const int tj = types[firstneigh[(size_t)ii * umax + jj]];
+            const T dist = (T)sqrt((double)v[0] * v[0] + (double)v[1] * v[1] + (double)v[2] * v[2]);
+            if (dist > rmax) continue;
+            const int Zi = type_map[ti], Zj = type_map[tj];
+            const T *ck = cks + 4 * (ti * ntypes + tj), *dk = dks + 4 * (ti * ntypes + tj);
+            const T a = (T)(0.46848 / (pow((double)Zi, 0.23) + pow((double)Zj, 0.23)));
+            const T x = dist / a;
+            T phi = 0, dphi = 0;
+            for (int k = 0; k < 4; k++) {
+                phi += ck[k] * (T)exp((double)(-dk[k] * x));
+                dphi += -ck[k] * dk[k] / a * (T)exp((double)(-dk[k] * dist / a));
+            }
+            T sw, dsw;
+            if (dist < rmin) { sw = 1; dsw = 0; }
+            else {
+                const T uu = (dist - rmin) / (rmax - rmin);
+                sw = (T)((double)uu * uu * uu * (-6 * (double)uu * uu + 15 * uu - 10) + 1);
+                dsw = (T)(1 / (rmax - rmin) * (-30 * (double)uu * uu * uu * uu + 60 * (double)uu * uu * uu - 30 * (double)uu * uu));
+            }
+            const T A = (T)(KC * Zi * Zj / dist), dA = (T)(-KC * Zi * Zj / ((double)dist * dist));
+            *etot += (T)(0.5 * (T)(KC * (Zi * Zj) / dist * phi * sw));
+            const T dE = dA * phi * sw + A * dphi * sw + A * phi * dsw;
+            for (int c = 0; c < 3; c++) force[3 * ci + c] += dE * v[c] / dist;
+            if (virial)
+                for (int c = 0; c < 3; c++)
+                    for (int d = 0; d < 3; d++) virial[3 * c + d] += (T)(-0.5 * v[c] * (dE * v[d] / dist));
+        }
+    }
+    return 0;
+}
+
 #undef NB_DECL
 #undef TAB_DECL

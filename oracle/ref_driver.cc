@@ -7,6 +7,7 @@
 //   source/descriptor/mtpr/src/mtpParam.cc
 //   source/descriptor/nep/include/nep_cpu_launcher.h
 //   source/fvt/include/{force_sr,virial_sr}.h
+//   source/descriptor/correction/include/zbl.h
 // The resulting shared object (oracle/_ref/libai2pot_ref.so) is used only by the
 // tests, the smoke check and the CPU-baseline leg of the benchmark, as the checker
 // and the timed CPU baseline; the product never loads it.
@@ -29,6 +30,7 @@
 #include "descriptor/nep/include/nep_cpu_launcher.h"
 #include "fvt/include/force_sr.h"
 #include "fvt/include/virial_sr.h"
+#include "descriptor/correction/include/zbl.h"
 
 namespace {
 
@@ -221,5 +223,54 @@ void ref_fvt_virial_##SUF(T *virial, int inum, int *numneigh, T *rcs, int umax, 
 
 DEF_FVT(double, f64)
 DEF_FVT(float, f32)
+
+// ---- ZBL pair correction: descriptor/correction/include/zbl.h -----------------------------------
+// zbl_efv: the complete correction as the reference's CUDA path applies it
+// (descriptor/correction/gpu/include/zbl.cuh:423-500: energy, force on the centre atom, virial, per
+// directed pair), composed here from the reference's own CPU pair methods
+// (PairZBL::add_atomic_energy_one / add_atomic_force_one / add_virial_one, zbl.h:330-395).
+// zbl_cpu_efv / zbl_cpu_ef: GroupZBL::correct_efv / correct_ef exactly as the CPU ops call them
+// (zbl.h:491-622; correct_efv adds the energy only, correct_ef energy and force).
+#define DEF_ZBL(T, SUF)                                                                              \
+void ref_zbl_efv_##SUF(T *etot, T *force, T *virial, int inum, int *ilist, int *numneigh,            \
+                       int *firstneigh, T *rcs, int *types, int ntypes, int *type_map, int umax,     \
+                       int nghost, T rmax, T rmin, T *cks, T *dks)                                   \
+{                                                                                                    \
+    (void)nghost;                                                                                    \
+    for (int ii = 0; ii < inum; ii++) {                                                              \
+        const int ci = ilist[ii], ti = types[ci];                                                    \
+        for (int jj = 0; jj < numneigh[ii]; jj++) {                                                  \
+            const int tj = types[firstneigh[(size_t)ii * umax + jj]];                                \
+            T vec[3] = {rcs[((size_t)ii * umax + jj) * 3], rcs[((size_t)ii * umax + jj) * 3 + 1],    \
+                        rcs[((size_t)ii * umax + jj) * 3 + 2]};                                      \
+            const T dist = std::sqrt(std::pow(vec[0], 2) + std::pow(vec[1], 2) + std::pow(vec[2], 2)); \
+            if (dist > rmax) continue;                                                               \
+            const int k = ti * ntypes + tj;                                                          \
+            ai2pot::correction::PairZBL<T> pz(type_map[ti], type_map[tj], rmax, rmin, cks + 4 * k, dks + 4 * k); \
+            pz.add_atomic_energy_one(*etot, dist);                                                   \
+            pz.add_atomic_force_one(force + 3 * ci, vec);                                            \
+            if (virial) pz.add_virial_one(virial, vec);                                              \
+        }                                                                                            \
+    }                                                                                                \
+}                                                                                                    \
+void ref_zbl_cpu_efv_##SUF(T *etot, T *force, T *virial, int inum, int *ilist, int *numneigh,        \
+                           int *firstneigh, T *rcs, int *types, int ntypes, int *type_map, int umax, \
+                           int nghost, T rmax, T rmin, T *cks, T *dks)                               \
+{                                                                                                    \
+    ai2pot::correction::GroupZBL<T> g(ntypes, type_map, type_map, rmax, rmin, cks, dks);             \
+    g.correct_efv(*etot, force, virial, inum, ilist, numneigh, firstneigh, (T(*)[3])rcs, types,      \
+                  ntypes, type_map, umax, nghost);                                                   \
+}                                                                                                    \
+void ref_zbl_cpu_ef_##SUF(T *etot, T *force, int inum, int *ilist, int *numneigh, int *firstneigh,   \
+                          T *rcs, int *types, int ntypes, int *type_map, int umax, int nghost,       \
+                          T rmax, T rmin, T *cks, T *dks)                                            \
+{                                                                                                    \
+    ai2pot::correction::GroupZBL<T> g(ntypes, type_map, type_map, rmax, rmin, cks, dks);             \
+    g.correct_ef(*etot, force, inum, ilist, numneigh, firstneigh, (T(*)[3])rcs, types, ntypes,       \
+                 type_map, umax, nghost);                                                            \
+}
+
+DEF_ZBL(double, f64)
+DEF_ZBL(float, f32)
 
 }  // extern "C"

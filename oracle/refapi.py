@@ -207,3 +207,29 @@ class Checker:
         a = [_ci(numneigh), np.ascontiguousarray(rcs), np.ascontiguousarray(dei_drij)]
         f(_p(out), C.c_int(inum), _p(a[0]), _p(a[1]), C.c_int(umax), _p(a[2]))
         return out
+
+    # -- ZBL pair correction (accumulates into copies of e, f, v) ---------------------------
+    def zbl(self, nb1, type_map, rmax, rmin, cks, dks, e=0.0, f=None, v=None, variant="efv"):
+        """One structure: nb1 = dict(ilist, numneigh, firstneigh, rcs, types, nghost). variant "efv" is the
+        complete correction (energy, centre-atom force, virial); "cpu_efv" / "cpu_ef" are the reference's
+        CPU group calls (reference build only)."""
+        rcs = np.ascontiguousarray(nb1["rcs"])
+        dt = rcs.dtype
+        fn, _ = self._fn("zbl_" + variant, dt)
+        inum, umax = nb1["firstneigh"].shape
+        ng = int(nb1.get("nghost", 0))
+        eo = np.array([e], dt)
+        fo = np.zeros((inum + ng, 3), dt) if f is None else np.array(f, dt).reshape(inum + ng, 3).copy()
+        vo = np.zeros(9, dt) if v is None else np.array(v, dt).reshape(9).copy()
+        a = [_ci(nb1["ilist"]), _ci(nb1["numneigh"]), _ci(nb1["firstneigh"]), rcs, _ci(nb1["types"]), _ci(type_map),
+             np.ascontiguousarray(cks, dt), np.ascontiguousarray(dks, dt)]
+        ct = C.c_double if dt == np.float64 else C.c_float
+        ntypes = len(type_map)
+        if variant == "cpu_ef":
+            fn(_p(eo), _p(fo), C.c_int(inum), _p(a[0]), _p(a[1]), _p(a[2]), _p(a[3]), _p(a[4]), C.c_int(ntypes), _p(a[5]),
+               C.c_int(umax), C.c_int(ng), ct(rmax), ct(rmin), _p(a[6]), _p(a[7]))
+        else:
+            fn(_p(eo), _p(fo), _p(vo), C.c_int(inum), _p(a[0]), _p(a[1]), _p(a[2]), _p(a[3]), _p(a[4]), C.c_int(ntypes),
+               _p(a[5]), C.c_int(umax), C.c_int(ng), ct(rmax), ct(rmin), _p(a[6]), _p(a[7]))
+        return eo[0], fo, vo
+

@@ -138,3 +138,30 @@ def test_fvt_vs_reference(orc, ref):
     il = np.arange(len(nn), dtype=np.int32)
     assert util.relerr(orc.fvt_force(il, nn, fn, 0, de), ref.fvt_force(il, nn, fn, 0, de)) < 1e-13
     assert util.relerr(orc.fvt_virial(nn, rc, de), ref.fvt_virial(nn, rc, de)) < 1e-13
+
+
+@pytest.mark.parametrize("dt,tol", [(np.float64, 1e-12), (np.float32, 1e-5)])
+def test_zbl_restatement_against_reference_pair_functions(checkers, dt, tol):
+    """ZBL: the C restatement against the reference's own PairZBL methods; and what the reference's CPU
+    group calls do with them (correct_efv: energy only, zbl.h:545-548; correct_ef: energy and force)."""
+    if "ref" not in checkers:
+        pytest.skip("reference build not available")
+    ref, orc = checkers["ref"], checkers["oracle"]
+    w = util.small_nep_case(n=4, dtype=dt, seed=30, a=2.2)
+    nn, fn, rc, ty, mx = ref.nblist(w["cell"], w["types"], w["coords"], 4.0, 96)
+    n = len(nn)
+    nb1 = dict(ilist=np.arange(n, dtype=np.int32), numneigh=nn, firstneigh=fn, rcs=rc, types=ty, nghost=0)
+    tm = np.array([14, 8, 29], np.int32)
+    rng = np.random.default_rng(3)
+    cks = (np.tile([0.18175, 0.50986, 0.28022, 0.02817], (9, 1)) * rng.uniform(0.9, 1.1, (9, 4))).astype(dt)
+    dks = np.tile([3.1998, 0.94229, 0.4029, 0.20162], (9, 1)).astype(dt)
+    er, fr, vr = ref.zbl(nb1, tm, 2.5, 1.0, cks, dks)
+    eo, fo, vo = orc.zbl(nb1, tm, 2.5, 1.0, cks, dks)
+    assert er > 1.0
+    assert abs(eo - er) <= tol * abs(er) and util.relerr(fo, fr) < tol and util.relerr(vo, vr) < tol
+    assert abs(np.trace(vr.reshape(3, 3))) > 0 and np.allclose(vr.reshape(3, 3), vr.reshape(3, 3).T, rtol=1e-4, atol=1e-6 * abs(vr).max())
+    ec, fc, vc = ref.zbl(nb1, tm, 2.5, 1.0, cks, dks, variant="cpu_efv")
+    assert abs(ec - er) <= 1e-5 * abs(er) and not fc.any() and not vc.any()
+    ee, fe, _ = ref.zbl(nb1, tm, 2.5, 1.0, cks, dks, variant="cpu_ef")
+    assert util.relerr(fe, fr) < tol
+

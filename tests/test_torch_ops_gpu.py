@@ -48,8 +48,9 @@ def test_mtp_ops_g0(checkers):
     d, = fromcc.linearMtpToDescriptorsOp(a[0], a[1], a[2], a[5], a[6], a[7], a[8], a[9], a[10], a[11], a[12], a[13], a[14], a[15], a[16],
                                          a[17], a[18], a[19])
     assert util.relerr(d.cpu().numpy()[0, :8], G["g0_desc_head"]) < 1e-10
-    with pytest.raises(RuntimeError):                  # ZBL is outside this build
-        fromcc.linearMtpToEFVOp(*args[:21], 2.0, 1.0, args[23], args[24])
+    # zbl_rmax > 0 with all-zero screening coefficients adds nothing (the correction itself: test_zbl_gpu.py)
+    e3, f3, v3 = fromcc.linearMtpToEFVOp(*args[:21], 2.0, 1.0, args[23], args[24])
+    assert util.relerr(e3.cpu().numpy(), G["g0_e"]) < 1e-10 and util.relerr(v3.cpu().numpy(), G["g0_v"]) < 1e-10
 
 
 def test_nep_ops(checkers):
