@@ -59,7 +59,8 @@ def build_cuda(force=False, verbose=False):
     return lib
 
 
-GLUE = {"libmtpr_bind.so": ["mtpr_bind.cpp"], "libnep_bind.so": ["nep_bind.cpp"], "libfvt_sr_op_bind.so": ["fvt_sr_op_bind.cpp"]}
+GLUE = {"libmtpr_bind.so": ["mtpr_bind.cpp"], "libnep_bind.so": ["nep_bind.cpp"], "libfvt_sr_op_bind.so": ["fvt_sr_op_bind.cpp"],
+        "libfitutils_bind.so": ["fitutils_bind.cpp"]}
 
 
 def build_glue(force=False, verbose=False):

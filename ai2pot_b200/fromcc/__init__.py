@@ -6,8 +6,8 @@ under the reference's Python names.
     from ai2pot_b200 import fromcc
     fromcc.linearMtpToEFVOp(...), fromcc.nepToEFVOp(...), fromcc.forceSrOp(...), fromcc.nblist.find_info4mlff(...)
 
-Ops outside the per-atom evaluation path (fitutils, deepmd, nnmtp, Gram/cross solver, Schmidt
-orthogonalisation) are not provided here.
+The dataset-statistics ops of the pre-training pass (fitutils) are provided too; ops outside the
+per-atom evaluation path (deepmd, nnmtp, Gram/cross solver, Schmidt orthogonalisation) are not.
 """
 import os
 
@@ -18,7 +18,7 @@ from . import nblist  # noqa: F401  (drop-in for the reference's CPython module 
 _LIBDIR = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "_lib")
 ai2pot_path = os.environ.get("AI2POT_PATH", os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
-for _name in ("libmtpr_bind.so", "libnep_bind.so", "libfvt_sr_op_bind.so"):
+for _name in ("libmtpr_bind.so", "libnep_bind.so", "libfvt_sr_op_bind.so", "libfitutils_bind.so"):
     _p = os.path.join(_LIBDIR, _name)
     if not os.path.exists(_p):
         raise ImportError(f"{_p} is missing: run `python -m ai2pot_b200._build` (there is no CPU fallback)")
@@ -36,6 +36,11 @@ nepToDescriptorsOp = torch.ops.nep.nepToDescriptorsOp
 
 forceSrOp = torch.ops.fvt.ForceSrOp
 virialSrOp = torch.ops.fvt.VirialSrOp
+
+targetStatisticsOp = torch.ops.fitutils.targetStatisticsOp
+allTypeDescriptorsStatisticsOp = torch.ops.fitutils.allTypeDescriptorsStatisticsOp
+eachTypeDescriptorsStatisticsOp = torch.ops.fitutils.eachTypeDescriptorsStatisticsOp
+allTypeDescriptorsMaxminOp = torch.ops.fitutils.allTypeDescriptorsMaxminOp
 
 
 def _optional(ns, name):

@@ -256,6 +256,35 @@ AI2B_DECL_FVT(f32, float)
 AI2B_DECL_ZBL(f64, double)
 AI2B_DECL_ZBL(f32, float)
 
+/* ------------------------------------------------------------------------------------------
+ * Dataset statistics for the descriptor scaler and the target normaliser (the pre-training pass).
+ * desc_stats_all / _each: AllTypeDescriptorsStatistics / EachTypeDescriptorsStatistics
+ * <T>::find_descriptors_statistics (source/descriptor/fitutils/include/descriptorsStatistics.h:
+ * 76-167; CUDA launchers gpu/include/descriptorsStatistics_torch_launcher.h): atom count(s),
+ * mean[ (ntypes,) nd ] and M2 = sum (x - mean)^2 of bdescriptors[B,Np,nd] over the listed atoms
+ * (per centre type btypes[b*Np + bilist[b*Np + i]] for _each). desc_maxmin:
+ * AllTypeDescriptorsMaxmin<T>::find_descriptors_maxmin (:177-205; max starts at FLT_MIN, min at
+ * FLT_MAX as there). target_stats: TargetStatistics<T>::find_ef_statistics
+ * (targetStatistics.h:44-80): d_out3 = {mean, M2 of E_b / n_b over structures, sum of squared
+ * force components}. Sums are accumulated in double (the reference sums sequentially in T).
+ * ---------------------------------------------------------------------------------------- */
+#define AI2B_DECL_STATS(SUF, T)                                                                  \
+    int ai2b_desc_stats_all_##SUF(int *d_natoms, T *d_mean, T *d_m2, int batch_size,             \
+                                  int natoms_pad, int descriptor_dim, const int *d_binum,        \
+                                  const T *d_bdescriptors, void *stream);                        \
+    int ai2b_desc_stats_each_##SUF(int *d_natoms, T *d_mean, T *d_m2, int batch_size,            \
+                                   int natoms_pad, int descriptor_dim, const int *d_binum,       \
+                                   const int *d_bilist, const int *d_btypes, int ntypes,         \
+                                   const T *d_bdescriptors, void *stream);                       \
+    int ai2b_desc_maxmin_##SUF(T *d_max, T *d_min, int batch_size, int natoms_pad,               \
+                               int descriptor_dim, const int *d_binum, const T *d_bdescriptors,  \
+                               void *stream);                                                    \
+    int ai2b_target_stats_##SUF(int *d_natoms, T *d_out3, int batch_size, int natoms_pad,        \
+                                const int *d_binum, const T *d_betot_dft, const T *d_bforce_dft, \
+                                void *stream);
+AI2B_DECL_STATS(f64, double)
+AI2B_DECL_STATS(f32, float)
+
 /* FMA-pipe microbenchmark used for the roofline denominator (no counterpart in the reference):
  * blocks x 256 threads, 8 independent chains of `iters` fused multiply-adds each. */
 int ai2b_fma_chain(int is_f64, int blocks, int iters, void *d_out, void *stream);

@@ -709,5 +709,60 @@ int NAME2(orc_zbl_efv)(T *etot, T *force, T *virial, int inum, const int *ilist,
     return 0;
 }
 
+/* dataset statistics: descriptor/fitutils/include/descriptorsStatistics.h:76-205, targetStatistics.h:44-80
+ * (same two-pass definition; sums in double) */
+int NAME2(orc_desc_stats_each)(int *natoms, T *mean, T *m2, int B, int npad, int nd, const int *binum, const int *bilist,
+                               const int *btypes, int ntypes, const T *bdesc)
+{
+    for (int t = 0; t < ntypes; t++) {
+        for (int k = 0; k < nd; k++) {
+            double s = 0, c = 0, q = 0;
+            for (int b = 0; b < B; b++)
+                for (int ii = 0; ii < binum[b]; ii++)
+                    if (!btypes || btypes[(size_t)b * npad + bilist[(size_t)b * npad + ii]] == t) { s += bdesc[((size_t)b * npad + ii) * nd + k]; c += 1; }
+            T mu = c > 0 ? (T)(s / c) : 0;
+            for (int b = 0; b < B; b++)
+                for (int ii = 0; ii < binum[b]; ii++)
+                    if (!btypes || btypes[(size_t)b * npad + bilist[(size_t)b * npad + ii]] == t) {
+                        double d = (double)(T)(bdesc[((size_t)b * npad + ii) * nd + k] - mu);
+                        q += d * d;
+                    }
+            mean[(size_t)t * nd + k] = mu; m2[(size_t)t * nd + k] = (T)q;
+            if (k == 0) natoms[t] = (int)c;
+        }
+    }
+    return 0;
+}
+int NAME2(orc_desc_stats_all)(int *natoms, T *mean, T *m2, int B, int npad, int nd, const int *binum, const T *bdesc)
+{
+    return NAME2(orc_desc_stats_each)(natoms, mean, m2, B, npad, nd, binum, NULL, NULL, 1, bdesc);
+}
+int NAME2(orc_desc_maxmin)(T *mx, T *mn, int B, int npad, int nd, const int *binum, const T *bdesc)
+{
+    for (int k = 0; k < nd; k++) {
+        T a = (T)1.17549435e-38f, z = (T)3.40282347e+38f;   /* FLT_MIN, FLT_MAX: the reference's starting values */
+        for (int b = 0; b < B; b++)
+            for (int ii = 0; ii < binum[b]; ii++) {
+                T x = bdesc[((size_t)b * npad + ii) * nd + k];
+                a = a > x ? a : x; z = z < x ? z : x;
+            }
+        mx[k] = a; mn[k] = z;
+    }
+    return 0;
+}
+int NAME2(orc_target_stats)(int *natoms, T *out3, int B, int npad, const int *binum, const T *etot, const T *force)
+{
+    double n = 0, es = 0, f2 = 0, q = 0;
+    for (int b = 0; b < B; b++) {
+        n += binum[b]; es += (double)(T)(etot[b] / binum[b]);
+        for (int ii = 0; ii < binum[b]; ii++)
+            for (int a = 0; a < 3; a++) { double f = force[((size_t)b * npad + ii) * 3 + a]; f2 += f * f; }
+    }
+    T mu = (T)(es / B);
+    for (int b = 0; b < B; b++) { double d = (double)(T)(etot[b] / binum[b] - mu); q += d * d; }
+    natoms[0] = (int)n; out3[0] = mu; out3[1] = (T)q; out3[2] = (T)f2;
+    return 0;
+}
+
 #undef NB_DECL
 #undef TAB_DECL

@@ -8,6 +8,7 @@
 //   source/descriptor/nep/include/nep_cpu_launcher.h
 //   source/fvt/include/{force_sr,virial_sr}.h
 //   source/descriptor/correction/include/zbl.h
+//   source/descriptor/fitutils/include/{descriptorsStatistics,targetStatistics}.h
 // The resulting shared object (oracle/_ref/libai2pot_ref.so) is used only by the
 // tests, the smoke check and the CPU-baseline leg of the benchmark, as the checker
 // and the timed CPU baseline; the product never loads it.
@@ -31,6 +32,8 @@
 #include "fvt/include/force_sr.h"
 #include "fvt/include/virial_sr.h"
 #include "descriptor/correction/include/zbl.h"
+#include "descriptor/fitutils/include/descriptorsStatistics.h"
+#include "descriptor/fitutils/include/targetStatistics.h"
 
 namespace {
 
@@ -272,5 +275,29 @@ void ref_zbl_cpu_ef_##SUF(T *etot, T *force, int inum, int *ilist, int *numneigh
 
 DEF_ZBL(double, f64)
 DEF_ZBL(float, f32)
+
+// ---- dataset statistics: descriptor/fitutils/include/descriptorsStatistics.h:76-205, targetStatistics.h:44-80
+#define DEF_STATS(T, SUF)                                                                            \
+void ref_desc_stats_all_##SUF(int *natoms, T *mean, T *m2, int B, int npad, int nd, int *binum, T *bdesc) \
+{                                                                                                    \
+    ai2pot::fitutils::AllTypeDescriptorsStatistics<T>::find_descriptors_statistics(natoms, mean, m2, B, npad, nd, binum, bdesc); \
+}                                                                                                    \
+void ref_desc_stats_each_##SUF(int *natoms, T *mean, T *m2, int B, int npad, int nd, int *binum,     \
+                               int *bilist, int *btypes, int ntypes, T *bdesc)                       \
+{                                                                                                    \
+    ai2pot::fitutils::EachTypeDescriptorsStatistics<T>::find_descriptors_statistics(natoms, mean, m2, B, npad, nd, binum, bilist, \
+                                                                                    btypes, ntypes, bdesc); \
+}                                                                                                    \
+void ref_desc_maxmin_##SUF(T *mx, T *mn, int B, int npad, int nd, int *binum, T *bdesc)              \
+{                                                                                                    \
+    ai2pot::fitutils::AllTypeDescriptorsMaxmin<T>::find_descriptors_maxmin(mx, mn, B, npad, nd, binum, bdesc); \
+}                                                                                                    \
+void ref_target_stats_##SUF(int *natoms, T *out3, int B, int npad, int *binum, T *etot, T *force)    \
+{                                                                                                    \
+    ai2pot::fitutils::TargetStatistics<T>::find_ef_statistics(natoms, out3, out3 + 1, out3 + 2, B, npad, binum, etot, (T(*)[3])force); \
+}
+
+DEF_STATS(double, f64)
+DEF_STATS(float, f32)
 
 }  // extern "C"

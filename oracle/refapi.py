@@ -233,3 +233,38 @@ class Checker:
                _p(a[5]), C.c_int(umax), C.c_int(ng), ct(rmax), ct(rmin), _p(a[6]), _p(a[7]))
         return eo[0], fo, vo
 
+    # -- dataset statistics -------------------------------------------------------------------
+    def desc_stats(self, binum, bdesc, bilist=None, btypes=None, ntypes=1):
+        dt = bdesc.dtype
+        B, npad, nd = bdesc.shape
+        each = btypes is not None
+        n = np.zeros(ntypes if each else 1, np.int32)
+        mean = np.zeros((ntypes, nd) if each else nd, dt); m2 = np.zeros_like(mean)
+        d = np.ascontiguousarray(bdesc); bn = _ci(binum)
+        if each:
+            f, _ = self._fn("desc_stats_each", dt)
+            bl, bt = _ci(bilist), _ci(btypes)
+            f(_p(n), _p(mean), _p(m2), C.c_int(B), C.c_int(npad), C.c_int(nd), _p(bn), _p(bl), _p(bt), C.c_int(ntypes), _p(d))
+        else:
+            f, _ = self._fn("desc_stats_all", dt)
+            f(_p(n), _p(mean), _p(m2), C.c_int(B), C.c_int(npad), C.c_int(nd), _p(bn), _p(d))
+        return n, mean, m2
+
+    def desc_maxmin(self, binum, bdesc):
+        dt = bdesc.dtype
+        B, npad, nd = bdesc.shape
+        mx = np.zeros(nd, dt); mn = np.zeros(nd, dt)
+        f, _ = self._fn("desc_maxmin", dt)
+        d = np.ascontiguousarray(bdesc); bn = _ci(binum)
+        f(_p(mx), _p(mn), C.c_int(B), C.c_int(npad), C.c_int(nd), _p(bn), _p(d))
+        return mx, mn
+
+    def target_stats(self, binum, etot, force):
+        dt = etot.dtype
+        B, npad = force.shape[:2]
+        n = np.zeros(1, np.int32); out = np.zeros(3, dt)
+        f, _ = self._fn("target_stats", dt)
+        e = np.ascontiguousarray(etot); fo = np.ascontiguousarray(force); bn = _ci(binum)
+        f(_p(n), _p(out), C.c_int(B), C.c_int(npad), _p(bn), _p(e), _p(fo))
+        return int(n[0]), out
+

@@ -165,3 +165,20 @@ def test_zbl_restatement_against_reference_pair_functions(checkers, dt, tol):
     ee, fe, _ = ref.zbl(nb1, tm, 2.5, 1.0, cks, dks, variant="cpu_ef")
     assert util.relerr(fe, fr) < tol
 
+
+@pytest.mark.parametrize("dt,tol", [(np.float64, 1e-12), (np.float32, 2e-6)])
+def test_statistics_restatement(checkers, dt, tol):
+    """fitutils statistics: C restatement against the reference templates (descriptorsStatistics.h, targetStatistics.h)."""
+    if "ref" not in checkers:
+        pytest.skip("reference build not available")
+    import test_stats_gpu as tsg
+    ref, orc = checkers["ref"], checkers["oracle"]
+    binum, desc, bilist, btypes, etot, force = tsg._batch(dt)
+    for args in ((binum, desc), (binum, desc, bilist, btypes, 3)):
+        a, b = ref.desc_stats(*args), orc.desc_stats(*args)
+        assert np.array_equal(a[0], b[0]) and util.relerr(b[1], a[1]) < tol and util.relerr(b[2], a[2]) < tol
+    a, b = ref.desc_maxmin(binum, desc), orc.desc_maxmin(binum, desc)
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+    a, b = ref.target_stats(binum, etot, force), orc.target_stats(binum, etot, force)
+    assert a[0] == b[0] and np.all(np.abs(a[1] - b[1]) <= tol * np.abs(a[1]))
+
