@@ -301,3 +301,52 @@ def mtp_loss_backward(prog, model, nb, weights, e_ml, e_dft, f_ml, f_dft, v_ml=N
         _ptr(model["coeffs"]), _ptr(model["linear_coeffs"]), _ptr(model["type_bias"]), *nbargs, cf(model["rmax"]), cf(model["rmin"]),
         _ptr(model["q_scaler"]), _ptr(ws), C.c_size_t(ws.numel()), _stream()))
     return dco, dli, dbi
+
+
+class MdSession:
+    """ctypes wrapper of ai2b_md_session_*: the device-resident input path of an MD host
+    (positions + model types in, forces on local and ghost atoms + energy + six virial components out).
+    `model` holds numpy arrays (see synth.nep_model / synth.mtp_model); for MTP pass the MtpProgram too."""
+
+    def __init__(self, model, umax, prog=None):
+        self.h = C.c_void_p()
+        f32 = lambda a: np.ascontiguousarray(np.asarray(a).ravel(), np.float32)
+        hp = lambda a: a.ctypes.data_as(C.c_void_p)
+        self.kind = model["kind"]
+        if self.kind == "nep":
+            a = [f32(model[k]) for k in ("coeffs", "w0", "b0", "w1", "type_bias", "q_scaler")]
+            _check(lib().ai2b_md_session_create_nep(
+                C.byref(self.h), C.c_int(int(model["chebyshev_size"])), C.c_int(int(model["n_radial"])), C.c_int(int(model["n_angular"])),
+                C.c_int(int(model["l_max"])), C.c_int(int(model["num_neurons"])), C.c_int(int(model["ntypes"])), *[hp(x) for x in a],
+                C.c_float(model["rmax_radial"]), C.c_float(model["rmax_angular"]), C.c_int(int(umax))))
+        else:
+            self.prog = prog
+            a = [f32(model[k]) for k in ("coeffs", "linear_coeffs", "type_bias", "q_scaler")]
+            _check(lib().ai2b_md_session_create_mtp(
+                C.byref(self.h), prog.handle, C.c_int(int(model["chebyshev_size"])), C.c_float(model["scaling"]),
+                C.c_int(int(model["ntypes"])), C.c_int(int(prog.nmus)), C.c_int(int(prog.ns)), *[hp(x) for x in a],
+                C.c_float(model["rmax"]), C.c_float(model["rmin"]), C.c_int(int(umax))))
+
+    def compute(self, nlocal, nghost, x, model_type, want_virial=True):
+        x = np.ascontiguousarray(x, np.float64)
+        t = np.ascontiguousarray(model_type, np.int32)
+        f = np.zeros((nlocal + nghost, 3), np.float64)
+        e = C.c_double(0.0)
+        v = np.zeros(6, np.float64)
+        mx = C.c_int(0)
+        _check(lib().ai2b_md_session_compute(self.h, C.c_int(nlocal), C.c_int(nghost), x.ctypes.data_as(C.c_void_p),
+                                             t.ctypes.data_as(C.c_void_p), C.c_int(int(want_virial)), f.ctypes.data_as(C.c_void_p),
+                                             C.byref(e), v.ctypes.data_as(C.c_void_p), C.byref(mx)))
+        return e.value, f, v, mx.value
+
+    def close(self):
+        if self.h:
+            lib().ai2b_md_session_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+

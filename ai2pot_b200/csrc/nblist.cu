@@ -315,12 +315,14 @@ __global__ void nb_fill_kernel(NbParams<T> P, const T *__restrict__ pos, const i
 constexpr int NB_WARPS = 8;
 
 // pass 3: one warp per centre atom (taken in bin order, so neighbouring warps share bins)
-template <typename T>
+// TO = element type of the rcs rows (T, or float rows from double positions: what an MD host that keeps
+// double coordinates and a single-precision model does on the CPU)
+template <typename T, typename TO>
 __global__ void __launch_bounds__(NB_WARPS * 32)
 nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restrict__ bin_start,
                 const int4 *__restrict__ ainfo, const typename Vec4<T>::type *__restrict__ spos,
                 const int4 *__restrict__ sinfo, int *__restrict__ numneigh, int *__restrict__ firstneigh,
-                T *__restrict__ rcs, int *__restrict__ status)
+                TO *__restrict__ rcs, int *__restrict__ status)
 {
     __shared__ int s_start[NB_WARPS][32], s_pre[NB_WARPS][33], s_shift[NB_WARPS][32];
     const NbGrid g = *gp;
@@ -350,7 +352,7 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
         const int bz = bin_i % g.nb[2], by = (bin_i / g.nb[2]) % g.nb[1], bx = bin_i / (g.nb[2] * g.nb[1]);
         int count = 0;
         int *frow = firstneigh + (size_t)i * P.umax;
-        T *rrow = rcs + (size_t)i * P.umax * 3;
+        TO *rrow = rcs + (size_t)i * P.umax * 3;
 
         const bool reuse = nnb <= 32 && bin_i == cached_bin;
         cached_bin = nnb <= 32 ? bin_i : -1;
@@ -451,7 +453,7 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
                     const int p = count + __popc(bal & lt_mask);
                     if (p < P.umax) {
                         frow[p] = jidx;
-                        rrow[3 * p] = d0; rrow[3 * p + 1] = d1; rrow[3 * p + 2] = d2;
+                        rrow[3 * p] = (TO)d0; rrow[3 * p + 1] = (TO)d1; rrow[3 * p + 2] = (TO)d2;
                     }
                 }
                 count += __popc(bal);
@@ -460,7 +462,7 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
         }
         for (int k = count + lane; k < P.umax; k += 32) {
             frow[k] = -1;
-            rrow[3 * k] = T(0); rrow[3 * k + 1] = T(0); rrow[3 * k + 2] = T(0);
+            rrow[3 * k] = TO(0); rrow[3 * k + 1] = TO(0); rrow[3 * k + 2] = TO(0);
         }
         if (lane == 0) numneigh[i] = min(count, P.umax);
         local_max = max(local_max, count);
@@ -544,9 +546,9 @@ static void plane_distances(const T *cell, T *d)
     }
 }
 
-template <typename T>
+template <typename T, typename TO = T>
 static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, int is_cart, double rcut_in, const int *pbc, int umax,
-                        int *d_numneigh, int *d_firstneigh, T *d_rcs, int *d_status, void *ws, size_t ws_bytes, cudaStream_t st)
+                        int *d_numneigh, int *d_firstneigh, TO *d_rcs, int *d_status, void *ws, size_t ws_bytes, cudaStream_t st)
 {
     AI2B_REQUIRE(h_cell && pbc && d_status, AI2B_ERR_INVALID, "ai2b_nblist_build: NULL argument");
     AI2B_REQUIRE(n >= 0 && umax >= 0 && rcut_in > 0 && ncentre >= 0 && ncentre <= n, AI2B_ERR_INVALID,
@@ -658,7 +660,7 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
     }
     long blocks = ((long)n + NB_WARPS - 1) / NB_WARPS;
     if (blocks > (long)sms * 8) blocks = (long)sms * 8;
-    nb_build_kernel<T><<<(unsigned)blocks, NB_WARPS * 32, 0, st>>>(P, grid, start, ainfo, spos, sinfo, d_numneigh, d_firstneigh, d_rcs, d_status);
+    nb_build_kernel<T, TO><<<(unsigned)blocks, NB_WARPS * 32, 0, st>>>(P, grid, start, ainfo, spos, sinfo, d_numneigh, d_firstneigh, d_rcs, d_status);
     AI2B_CUDA(cudaGetLastError());
     return AI2B_OK;
 }
@@ -730,4 +732,14 @@ extern "C" int ai2b_nblist_build_ghost_f32(int natoms, int ncentres, const float
 {
     return nblist_build<float>(natoms, ncentres, h_cell, d_coords, is_cart, rcut, h_pbc, umax, d_numneigh, d_firstneigh, d_rcs,
                                d_status, d_workspace, workspace_bytes, (cudaStream_t)stream);
+}
+// Double-precision positions, single-precision rows: r_j - r_i is formed in double and rounded once, as
+// PairAI2Pot::construct_mlff_input does on the host (interface/lammps/AI2POT/pair_ai2pot.cpp:232-235).
+extern "C" int ai2b_nblist_build_ghost_f64_rows32(int natoms, int ncentres, const double *h_cell, const double *d_coords, int is_cart,
+                                                  double rcut, const int *h_pbc, int umax, int *d_numneigh, int *d_firstneigh,
+                                                  float *d_rcs, int *d_status, void *d_workspace, size_t workspace_bytes,
+                                                  void *stream)
+{
+    return nblist_build<double, float>(natoms, ncentres, h_cell, d_coords, is_cart, rcut, h_pbc, umax, d_numneigh, d_firstneigh, d_rcs,
+                                       d_status, d_workspace, workspace_bytes, (cudaStream_t)stream);
 }

@@ -285,6 +285,51 @@ AI2B_DECL_ZBL(f32, float)
 AI2B_DECL_STATS(f64, double)
 AI2B_DECL_STATS(f32, float)
 
+/* ------------------------------------------------------------------------------------------
+ * Device-resident input path for a molecular-dynamics host: replaces
+ * PairAI2Pot::construct_mlff_input + the tensor traffic of PairAI2Pot::compute
+ * (interface/lammps/AI2POT/pair_ai2pot.cpp:175-249, 383-471). Unlike the entry points above a
+ * session owns its device and pinned buffers (they grow with the atom counts and are reused, so
+ * a steady-state step allocates nothing) and its own stream, takes HOST arrays in the host
+ * program's layout, and returns when the results are on the host.
+ *   h_x[nlocal+nghost][3]      positions as the host keeps them (double; ghosts carry the
+ *                              periodic images, no cell is needed)
+ *   h_model_type[nlocal+nghost] model type index of every atom (lmp2model_type_map applied)
+ *   h_f[nlocal+nghost][3]      += forces, ghosts included (the host reverse-communicates them)
+ *   h_eng                      += energy (may be NULL);  h_virial6 += xx,yy,zz,xy,xz,yz if
+ *                              want_virial (pair_ai2pot.cpp:461-468)
+ *   h_max_neighbours           largest neighbour count found (may be NULL); more than umax
+ *                              returns AI2B_ERR_OVERFLOW (the reference overruns its rows)
+ * The neighbour rows are built on the device every step from the positions (r_j - r_i in
+ * double, stored as float, as the host loop does), with the model cutoff; pairs the host's list
+ * holds beyond the cutoff (skin) contribute nothing in either case. Models are single precision,
+ * as in pair_ai2pot.cpp. The MTP variant borrows the program handle (keep it alive).
+ * ---------------------------------------------------------------------------------------- */
+typedef struct ai2b_md_session ai2b_md_session;
+int ai2b_md_session_create_nep(ai2b_md_session **out, int chebyshev_size, int n_radial,
+                               int n_angular, int l_max, int num_neurons, int ntypes,
+                               const float *h_coeffs, const float *h_w0, const float *h_b0,
+                               const float *h_w1, const float *h_type_bias,
+                               const float *h_q_scaler, float rmax_radial, float rmax_angular,
+                               int umax);
+int ai2b_md_session_create_mtp(ai2b_md_session **out, const ai2b_mtp_program *prog,
+                               int chebyshev_size, float scaling, int ntypes, int nmus,
+                               int alpha_scalar_moments, const float *h_coeffs,
+                               const float *h_linear_coeffs, const float *h_type_bias,
+                               const float *h_q_scaler, float rmax, float rmin, int umax);
+void ai2b_md_session_destroy(ai2b_md_session *session);
+int ai2b_md_session_compute(ai2b_md_session *session, int nlocal, int nghost, const double *h_x,
+                            const int *h_model_type, int want_virial, double *h_f,
+                            double *h_eng, double *h_virial6, int *h_max_neighbours);
+
+/* Neighbour rows in single precision from double-precision positions (r_j - r_i formed in
+ * double, rounded once: pair_ai2pot.cpp:232-235); otherwise as ai2b_nblist_build_ghost_f64. */
+int ai2b_nblist_build_ghost_f64_rows32(int natoms, int ncentres, const double *h_cell,
+                                       const double *d_coords, int is_cart, double rcut,
+                                       const int *h_pbc, int umax, int *d_numneigh,
+                                       int *d_firstneigh, float *d_rcs, int *d_status,
+                                       void *d_workspace, size_t workspace_bytes, void *stream);
+
 /* FMA-pipe microbenchmark used for the roofline denominator (no counterpart in the reference):
  * blocks x 256 threads, 8 independent chains of `iters` fused multiply-adds each. */
 int ai2b_fma_chain(int is_f64, int blocks, int iters, void *d_out, void *stream);
