@@ -255,37 +255,26 @@ __global__ void __launch_bounds__(MTP_WARPS * 32, 4) mtp_fwd_lanes_kernel(const 
 // no global-memory latency sits between two tiles.
 constexpr int MTP_PREF = 8;   // prefetch registers per thread: basic moments <= 32 * MTP_PREF
 
-// NG independent groups of warps per block (1 or 2): each group owns its M / E arrays and walks over
-// its own tiles, synchronising with a named barrier of its own, so one group's level boundaries
-// are filled by the other group's work; the row tables are shared by the block.
-template <typename T, int TA, int MODE, bool SMEMTAB, int NG>
+template <typename T, int TA, int MODE, bool SMEMTAB>
 __global__ void __launch_bounds__(MTP_CWARPS * 32, 1) mtp_contract_kernel(const MtpProgramDev P, const MtpArgs<T> A)
 {
     extern __shared__ __align__(32) unsigned char smem_raw[];
     constexpr int LD = TA + 1;
     constexpr int G = 32 / TA;
-    constexpr int GW = MTP_CWARPS / NG;          // warps per group
-    constexpr int NWORK = GW * G;
-    constexpr int nthreads = GW * 32;            // threads per group
-    static_assert(MTP_CWARPS % NG == 0, "groups must divide the block");
-    __shared__ T esum_all[NG][NWORK][TA];
-    const int lane = threadIdx.x & 31, bwarp = threadIdx.x >> 5;
-    const int grp = bwarp / GW, warp = bwarp % GW, gtid = threadIdx.x % nthreads;
-    T(*esum)[TA] = esum_all[grp];
-    const size_t arr_elems = (size_t)P.nm * LD * (MODE == MODE_DESC ? 1 : 2);
-    T *M = reinterpret_cast<T *>(smem_raw) + (size_t)grp * arr_elems;
+    constexpr int NWORK = MTP_CWARPS * G;
+    __shared__ T esum[NWORK][TA];
+    T *M = reinterpret_cast<T *>(smem_raw);
     T *E = M + (size_t)P.nm * LD;
-    const size_t arr_bytes = (sizeof(T) * arr_elems * NG + 15) & ~size_t(15);
+    const size_t arr_bytes = (sizeof(T) * (size_t)P.nm * LD * (MODE == MODE_DESC ? 1 : 2) + 15) & ~size_t(15);
     int2 *s_fwd = reinterpret_cast<int2 *>(smem_raw + arr_bytes);
     int2 *s_rev = s_fwd + P.nt;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int a = lane % TA, wid = warp * G + lane / TA;
     const T *Ma = M + a, *Ea = E + a;
     const int ntot = A.prefix[A.B];
     const int ntiles = (ntot + TA - 1) / TA;
-    auto group_sync = [&]() {
-        if (NG == 1) __syncthreads();
-        else asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(nthreads) : "memory");
-    };
+    const int nthreads = MTP_CWARPS * 32;
+    if ((int)blockIdx.x >= ntiles) return;
 
     // row tables, staged once, with the moment indices already scaled to element offsets (index * LD fits 16 bits)
     auto scale = [](int2 r) {
@@ -293,18 +282,17 @@ __global__ void __launch_bounds__(MTP_CWARPS * 32, 1) mtp_contract_kernel(const 
     };
     if (SMEMTAB) {
 #pragma unroll 4
-        for (int i = threadIdx.x; i < P.nt; i += MTP_CWARPS * 32) s_fwd[i] = scale(P.fwd_flat[i]);
+        for (int i = threadIdx.x; i < P.nt; i += nthreads) s_fwd[i] = scale(P.fwd_flat[i]);
         if (MODE != MODE_DESC)
 #pragma unroll 4
-            for (int i = threadIdx.x; i < 2 * P.nt; i += MTP_CWARPS * 32) s_rev[i] = scale(P.rev_flat[i]);
+            for (int i = threadIdx.x; i < 2 * P.nt; i += nthreads) s_rev[i] = scale(P.rev_flat[i]);
     }
-    __syncthreads();
     // large tables (template levels above 16) stay in global memory
     auto frow = [&](int r) { return SMEMTAB ? s_fwd[r] : scale(P.fwd_flat[r]); };
     auto rrow = [&](int r) { return SMEMTAB ? s_rev[r] : scale(P.rev_flat[r]); };
 
     // moment rows of a tile: warp w fetches atom w (and w + nwarps, ..), lanes run over the row
-    const bool can_prefetch = P.nb <= 32 * MTP_PREF && TA <= GW;
+    const bool can_prefetch = P.nb <= 32 * MTP_PREF && TA <= MTP_CWARPS;
     T pre[MTP_PREF];
     auto fetch = [&](int tile) {
 #pragma unroll
@@ -313,16 +301,15 @@ __global__ void __launch_bounds__(MTP_CWARPS * 32, 1) mtp_contract_kernel(const 
             pre[k] = (warp < TA && t < ntot && i < P.nb) ? A.Mb[(size_t)t * A.nbp + i] : T(0);
         }
     };
-    const int tile0 = blockIdx.x * NG + grp, tstride = gridDim.x * NG;
-    if (can_prefetch && tile0 < ntiles) fetch(tile0);
+    if (can_prefetch) fetch(blockIdx.x);
 
-    for (int tile = tile0; tile < ntiles; tile += tstride) {
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
         const int t0 = tile * TA;
-        for (int i = gtid; i < P.nm * LD; i += nthreads) {
+        for (int i = threadIdx.x; i < P.nm * LD; i += nthreads) {
             M[i] = T(0);
             if (MODE != MODE_DESC) E[i] = T(0);
         }
-        group_sync();
+        __syncthreads();
         if (can_prefetch) {
             if (warp < TA) {
 #pragma unroll
@@ -331,14 +318,14 @@ __global__ void __launch_bounds__(MTP_CWARPS * 32, 1) mtp_contract_kernel(const 
                     if (i < P.nb) M[i * LD + warp] = pre[k];
                 }
             }
-            if (tile + tstride < ntiles) fetch(tile + tstride);   // in flight during this tile
+            if (tile + (int)gridDim.x < ntiles) fetch(tile + gridDim.x);   // in flight during this tile
         } else {
-            for (int at = warp; at < TA && t0 + at < ntot; at += GW) {
+            for (int at = warp; at < TA && t0 + at < ntot; at += MTP_CWARPS) {
                 const T *src = A.Mb + (size_t)(t0 + at) * A.nbp;
                 for (int i = lane; i < P.nb; i += 32) M[i * LD + at] = src[i];
             }
         }
-        group_sync();
+        __syncthreads();
 
         // product rows: every depth's rows are one contiguous stream; each worker takes an equal share
         // of it and adds a destination's partial sum when the stream leaves that destination
@@ -356,7 +343,7 @@ __global__ void __launch_bounds__(MTP_CWARPS * 32, 1) mtp_contract_kernel(const 
                     acc = T(0);
                 }
             }
-            group_sync();
+            __syncthreads();
         }
 
         // per-atom bookkeeping (all lanes of a column agree)
@@ -372,7 +359,7 @@ __global__ void __launch_bounds__(MTP_CWARPS * 32, 1) mtp_contract_kernel(const 
         if (MODE == MODE_DESC) {
             if (valid)
                 for (int s = wid; s < P.ns; s += NWORK) A.desc[slot * P.ns + s] = M[P.map[s] * LD + a];
-            group_sync();
+            __syncthreads();
             continue;
         }
 
@@ -386,7 +373,7 @@ __global__ void __launch_bounds__(MTP_CWARPS * 32, 1) mtp_contract_kernel(const 
             E[m * LD + a] = w;
         }
         esum[wid][a] = es;
-        group_sync();
+        __syncthreads();
         if (wid == 0) {
             T e = T(0);
 #pragma unroll
@@ -426,15 +413,15 @@ __global__ void __launch_bounds__(MTP_CWARPS * 32, 1) mtp_contract_kernel(const 
                     acc = T(0);
                 }
             }
-            group_sync();
+            __syncthreads();
         }
 
         // adjoints of the basic moments, back to per-atom rows
-        for (int at = warp; at < TA && t0 + at < ntot; at += GW) {
+        for (int at = warp; at < TA && t0 + at < ntot; at += MTP_CWARPS) {
             T *dstp = A.Eb + (size_t)(t0 + at) * A.nbp;
             for (int i = lane; i < A.nbp; i += 32) dstp[i] = i < P.nb ? E[i * LD + at] : T(0);
         }
-        group_sync();
+        __syncthreads();
     }
 }
 
@@ -598,21 +585,21 @@ __global__ void __launch_bounds__(MTP_WARPS * 32, 3) mtp_force_kernel(const MtpP
 // host side
 // ---------------------------------------------------------------------------------------------
 template <typename T, int MODE>
-static size_t contract_smem(const MtpProgramDev &P, int ta, bool tables, int ng = 1)
+static size_t contract_smem(const MtpProgramDev &P, int ta, bool tables)
 {
-    const size_t arrays = sizeof(T) * (size_t)P.nm * (ta + 1) * (MODE == MODE_DESC ? 1 : 2) * ng;
+    const size_t arrays = sizeof(T) * (size_t)P.nm * (ta + 1) * (MODE == MODE_DESC ? 1 : 2);
     const size_t tab = tables ? sizeof(int2) * (size_t)P.nt * (MODE == MODE_DESC ? 1 : 3) : 0;
     return ((arrays + 15) & ~size_t(15)) + tab + 16;
 }
 
-template <typename T, int TA, int MODE, bool SMEMTAB, int NG>
+template <typename T, int TA, int MODE, bool SMEMTAB>
 static int launch_contract(const MtpProgramDev &P, const MtpArgs<T> &A, long atoms_upper, cudaStream_t st)
 {
-    const size_t smem = contract_smem<T, MODE>(P, TA, SMEMTAB, NG);
-    auto kern = mtp_contract_kernel<T, TA, MODE, SMEMTAB, NG>;
+    const size_t smem = contract_smem<T, MODE>(P, TA, SMEMTAB);
+    auto kern = mtp_contract_kernel<T, TA, MODE, SMEMTAB>;
     static size_t configured = 0;
     if (int rc = set_smem(kern, smem, &configured)) return rc;
-    long tiles = ((atoms_upper + TA - 1) / TA + NG - 1) / NG;
+    long tiles = (atoms_upper + TA - 1) / TA;
     if (tiles > sm_count()) tiles = sm_count();      // persistent: one block per SM walks over the tiles
     kern<<<(unsigned)tiles, MTP_CWARPS * 32, smem, st>>>(P, A);
     AI2B_CUDA(cudaGetLastError());
@@ -624,14 +611,11 @@ static int launch_contract(const MtpProgramDev &P, const MtpArgs<T> &A, long ato
 template <typename T, int MODE>
 static int dispatch_contract(const MtpProgramDev &P, const MtpArgs<T> &A, long atoms_upper, cudaStream_t st)
 {
-    const size_t cap = 216 * 1024;   // dynamic part; the kernel also holds 8 KiB (fp64) of static shared memory
-    // two half-size tiles per block, out of phase with each other, when both fit beside the row tables
-    if ((long)P.nm * 17 <= 65535 && contract_smem<T, MODE>(P, 16, true, 2) <= cap)
-        return launch_contract<T, 16, MODE, true, 2>(P, A, atoms_upper, st);
+    const size_t cap = 222 * 1024;
 #define AI2B_TRY(TA_)                                                                                       \
     if ((long)P.nm * (TA_ + 1) <= 65535) {                                                                  \
-        if (contract_smem<T, MODE>(P, TA_, true) <= cap) return launch_contract<T, TA_, MODE, true, 1>(P, A, atoms_upper, st);   \
-        if (contract_smem<T, MODE>(P, TA_, false) <= cap) return launch_contract<T, TA_, MODE, false, 1>(P, A, atoms_upper, st); \
+        if (contract_smem<T, MODE>(P, TA_, true) <= cap) return launch_contract<T, TA_, MODE, true>(P, A, atoms_upper, st);   \
+        if (contract_smem<T, MODE>(P, TA_, false) <= cap) return launch_contract<T, TA_, MODE, false>(P, A, atoms_upper, st); \
     }
     AI2B_TRY(32) AI2B_TRY(16) AI2B_TRY(8)
 #undef AI2B_TRY
