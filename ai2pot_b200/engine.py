@@ -49,6 +49,31 @@ class Evaluator:
     def compute(self, coords):
         return self.evaluate(self.build_list(coords))
 
+    def capture(self, coords):
+        """Records one compute(coords) (neighbour build + E/F/V, every launch stream-ordered on buffers this
+        object owns) into a CUDA graph; replay() then re-runs it on whatever `coords` holds at that time.
+        Returns False (and leaves the eager path in place) if the capture is refused."""
+        self.graph = None
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self.compute(coords)                      # sizes every buffer before the capture
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.graph_out = self.compute(coords)
+            self.graph = g
+        except Exception:
+            self.graph = None
+            torch.cuda.synchronize()
+        return self.graph is not None
+
+    def replay(self):
+        self.graph.replay()
+        return self.graph_out
+
     # kernels of this library launched by one compute() on a fully periodic cell (memsets not counted):
     # neighbour build = set-up, count, scan, fill, build; MTP = set-up, forward, contraction, force;
     # NEP = one kernel (single structure, up to 8 radial / angular functions)
@@ -258,8 +283,11 @@ def run_single_benchmark(w, steps, warmup, dist, sampler):
     if st[1]:
         raise RuntimeError(f"umax {ev.umax} too small (max {st[0]})")
     mean_nn = float(nb["bnumneigh"].float().mean())
+    # the step is a fixed sequence of launches on fixed buffers: replayed from a CUDA graph when the capture succeeds
+    graphed = ev.capture(coords)
+    step = ev.replay if graphed else (lambda: ev.compute(coords))
     sampler.start()
-    t_dev = _timed(lambda: ev.compute(coords), steps, warmup, flush, barrier)
+    t_dev = _timed(step, steps, warmup, flush, barrier)
     clocks = sampler.stop()
 
     # end to end: host positions in, host E/F/V out, every step
@@ -269,8 +297,12 @@ def run_single_benchmark(w, steps, warmup, dist, sampler):
     dcoords = torch.empty_like(coords)
 
     def e2e_step():
-        dcoords.copy_(host_coords, non_blocking=True)
-        e, f, v = ev.compute(dcoords)
+        if graphed:
+            coords.copy_(host_coords, non_blocking=True)
+            e, f, v = ev.replay()
+        else:
+            dcoords.copy_(host_coords, non_blocking=True)
+            e, f, v = ev.compute(dcoords)
         h_e.copy_(e, non_blocking=True); h_f.copy_(f, non_blocking=True); h_v.copy_(v, non_blocking=True)
     t_e2e = _timed(e2e_step, steps, warmup, flush, barrier)
     h2d = host_coords.numel() * host_coords.element_size()
@@ -315,5 +347,6 @@ def run_single_benchmark(w, steps, warmup, dist, sampler):
                            "peak_source": "MEASURED_PEAKS.json (of measured)" if hbm else "6.65 TB/s (of fallback)",
                            "bytes_per_atom": nb_bytes / n, "ms": 1e3 * t_nb}}
     return dict(t_dev=t_dev, t_e2e=t_e2e, clocks=clocks, launches=ev.launches_per_step() * steps, h2d=h2d, d2h=d2h,
-                e2e_path="pinned host positions -> H2D -> ai2b_nblist_build -> ai2b_*_efv -> D2H E,F,V (C ABI via ctypes)",
+                e2e_path="pinned host positions -> H2D -> ai2b_nblist_build -> ai2b_*_efv -> D2H E,F,V (C ABI via ctypes" +
+                         (", replayed from a CUDA graph)" if graphed else ")"), cuda_graph=graphed,
                 roofline=roofline, parts_ms={"nblist": 1e3 * t_nb, "efv": 1e3 * t_ev})

@@ -223,6 +223,8 @@ def main():
                 "e2e": {"value": total_atoms * args.steps / res["t_e2e"], "unit": "atoms/s",
                         "h2d_bytes_per_step": res["h2d"], "d2h_bytes_per_step": res["d2h"], "path": res["e2e_path"]},
                 "roofline": res["roofline"], "parts_ms": res.get("parts_ms")}
+        if "cuda_graph" in res:
+            config["cuda_graph"] = bool(res["cuda_graph"])
         if world > 1:
             config["parallelism"] = ("replicas only: %d independent copies, no data-path collective" % world) if not strong else \
                 ("structures dealt over %d ranks + one gradient all-reduce" % world if w["kind"] == "train" else "%d x-slabs, halo exchange + ghost-force reduction over NCCL" % world)
