@@ -181,8 +181,30 @@ class LocalCompute:
         self.cell, self.rcut, self.umax, self.ntypes = np.asarray(cell), float(rcut), int(umax), int(model["ntypes"])
         self.status = None
         self._static = None
+        self._graph = None
 
     def __call__(self, local, types, nlocal, pbc):
+        """Neighbour build + E/F/V on the slab. The sequence of launches and every buffer are the same from
+        step to step (the halo exchange writes into `local` in place), so after the first call the whole
+        sequence is replayed from a CUDA graph; a refused capture leaves the eager path in place."""
+        key = (local.data_ptr(), types.data_ptr(), nlocal, local.shape[0], tuple(pbc))
+        if self._graph is not None and self._graph[0] == key:
+            self._graph[1].replay()
+            return self._graph[2]
+        out = self._run(local, types, nlocal, pbc)
+        if self._graph is None or self._graph[0] not in (key, "refused"):
+            try:
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    gout = self._run(local, types, nlocal, pbc)
+                self._graph = (key, g, gout)
+            except Exception:
+                self._graph = ("refused",)
+                torch.cuda.synchronize()
+        return out
+
+    def _run(self, local, types, nlocal, pbc):
         nn, fn, rcs, status = self.builder.build(self.cell, local, self.rcut, self.umax, pbc=pbc, ncentres=nlocal)
         self.status = status
         ntotal = local.shape[0]
