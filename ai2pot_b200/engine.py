@@ -254,7 +254,7 @@ def run_slab_benchmark(w, steps, warmup, dist, sampler):
                   (torch.arange(rcs.shape[1], device=dev)[None] < nn[:, None])).sum(1).float().mean())
     fl = flops_nep(mean_nn, nn_a, m["chebyshev_size"], m["n_radial"], m["n_angular"], m["num_neurons"], m["n_radial"] + m["n_angular"] * m["l_max"])
     achieved = dom.nlocal * fl / t_comp / 1e12
-    roofline = {"kernel": "nep_atom_kernel (+ neighbour build) on this rank's slab", "bound": "fp32", "achieved": achieved, "peak": peak,
+    roofline = {"kernel": "nep_fast_kernel (+ neighbour build) on this rank's slab", "bound": "fp32", "achieved": achieved, "peak": peak,
                 "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": "FMA-chain microbenchmark in this run (of measured)",
                 "flops_per_atom": fl, "mean_neighbours": mean_nn, "traffic": None, "owned_atoms": dom.nlocal, "ghost_atoms": dom.nghost}
     return dict(t_dev=t_dev, t_e2e=t_e2e, clocks=clocks, launches=(9 + 1) * steps, h2d=host_owned.numel() * host_owned.element_size(),
@@ -336,12 +336,13 @@ def run_single_benchmark(w, steps, warmup, dist, sampler):
     hbm = None
     if os.path.exists(MEASURED_PEAKS):
         hbm = json.load(open(MEASURED_PEAKS)).get("hbm_gbs")
-    roofline = {"kernel": "mtp_atom_kernel" if m["kind"] == "mtp" else "nep_atom_kernel", "bound": bound,
+    roofline = {"kernel": "mtp_fwd_lanes + mtp_contract + mtp_force (the three E/F/V kernels of a call)" if m["kind"] == "mtp" else "nep_fast_kernel",
+                "bound": bound,
                 "achieved": achieved, "peak": peak_meas, "unit": "TFLOP/s", "frac": achieved / peak_meas,
                 "peak_source": "FMA-chain microbenchmark in this run (of measured)", "peak_nominal": peak_nom,
                 "frac_of_nominal": achieved / peak_nom, "flops_per_atom": fl, "mean_neighbours": mean_nn,
                 # dram__bytes_read + write of the E/F/V kernels of one call, from the ncu capture summarised under profiles/
-                "traffic": (55.9e6 if m["kind"] == "mtp" else 7.5e6) if n == 13824 else None, "kernel_ms": 1e3 * t_ev,
+                "traffic": (55.0e6 if m["kind"] == "mtp" else 7.5e6) if n == 13824 else None,   # dram bytes of one ncu capture (profiles/) "kernel_ms": 1e3 * t_ev,
                 "nblist": {"bound": "hbm", "achieved": nb_bytes / t_nb / 1e9, "peak": hbm or 6650.0, "unit": "GB/s",
                            "frac": nb_bytes / t_nb / 1e9 / (hbm or 6650.0),
                            "peak_source": "MEASURED_PEAKS.json (of measured)" if hbm else "6.65 TB/s (of fallback)",
