@@ -242,6 +242,25 @@ def nep_efv(model, nb, virial=True, out=None):
     return (e, f, v) if virial else (e, f)
 
 
+def nep_loss_backward(model, nb, weights, e_ml, e_dft, f_ml, f_dft, v_ml=None, v_dft=None):
+    """Per-structure gradients of the NEP loss: (dcoeffs [B,ncoef], dw0 [B,nt*nneu*nd], db0, dw1 [B,nt*nneu], dbias [B,nt])."""
+    rcs = nb["brcs"]
+    suf, cf = _suf(rcs.dtype)
+    B, npad, umax, _ = _nb_args(nb)
+    nt, nneu = int(nb["ntypes"]), int(model["num_neurons"])
+    nd = int(model["n_radial"]) + int(model["n_angular"]) * int(model["l_max"])
+    mk = lambda n: torch.empty(B, n, dtype=rcs.dtype, device=rcs.device)
+    dco, dw0, db0, dw1, dbi = mk(model["coeffs"].numel()), mk(nt * nneu * nd), mk(nt * nneu), mk(nt * nneu), mk(nt)
+    _check(getattr(lib(), "ai2b_nep_loss_backward_" + suf)(
+        _ptr(dco), _ptr(dw0), _ptr(db0), _ptr(dw1), _ptr(dbi), cf(weights[0]), cf(weights[1]), cf(weights[2] if len(weights) > 2 else 0.0),
+        _ptr(e_ml), _ptr(e_dft), _ptr(f_ml), _ptr(f_dft), _ptr(v_ml), _ptr(v_dft), C.c_int(int(model["chebyshev_size"])),
+        C.c_int(int(model["n_radial"])), C.c_int(int(model["n_angular"])), C.c_int(int(model["l_max"])), C.c_int(nneu),
+        _ptr(model["coeffs"]), _ptr(model["w0"]), _ptr(model["b0"]), _ptr(model["w1"]), C.c_int(B), C.c_int(npad), _ptr(nb["binum"]),
+        _ptr(nb["bilist"]), _ptr(nb["bnumneigh"]), _ptr(nb["bfirstneigh"]), _ptr(rcs), _ptr(nb["btypes"]), C.c_int(nt), C.c_int(umax),
+        C.c_int(int(nb.get("nghost", 0))), cf(model["rmax_radial"]), cf(model["rmax_angular"]), _ptr(model["q_scaler"]), _stream()))
+    return dco, dw0, db0, dw1, dbi
+
+
 def zbl_efv(nb, type_map, rmax, rmin, cks, dks, e, f, v=None):
     """Adds the ZBL pair correction onto e[B], f[B,Np+nghost,3] and (if given) v[B,9] in place.
     type_map: int32 atomic numbers [ntypes]; cks, dks: [ntypes*ntypes*4] (device tensors)."""

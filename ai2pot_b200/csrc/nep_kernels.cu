@@ -17,6 +17,7 @@
 #include "common.cuh"
 
 #include <cstring>
+#include <algorithm>
 
 namespace ai2b {
 
@@ -494,6 +495,7 @@ __global__ void __launch_bounds__(NEP_WARPS * 32) nep_atom_kernel(const NepArgs<
 
 }  // namespace ai2b
 #include "nep_fast.cuh"
+#include "nep_loss.cuh"
 namespace ai2b {
 
 // ---------------------------------------------------------------------------------------------
@@ -657,6 +659,28 @@ extern "C" size_t ai2b_nep_workspace_bytes(int batch_size, int ntypes, int n_rad
 
 AI2B_DEF_NEP(f64, double)
 AI2B_DEF_NEP(f32, float)
+
+#define AI2B_DEF_NEP_LOSS(SUF, T)                                                                                   \
+    extern "C" int ai2b_nep_loss_backward_##SUF(                                                                    \
+        T *dco, T *dw0, T *db0, T *dw1, T *dbi, T e_w, T f_w, T v_w, const T *e_ml, const T *e_dft, const T *f_ml,  \
+        const T *f_dft, const T *v_ml, const T *v_dft, int cs, int n_r, int n_a, int l_max, int nneu, const T *coeffs, \
+        const T *w0, const T *b0, const T *w1, int B, int npad, const int *binum, const int *bilist,                \
+        const int *numneigh, const int *firstneigh, const T *rcs, const int *types, int ntypes, int umax, int nghost, \
+        T rc_r, T rc_a, const T *qs, void *stream)                                                                  \
+    {                                                                                                               \
+        AI2B_REQUIRE(dco && dw0 && db0 && dw1 && dbi && e_ml && e_dft && f_ml && f_dft && coeffs && w0 && b0 && w1 && \
+                         qs && binum && bilist && numneigh && firstneigh && rcs && types, AI2B_ERR_INVALID,         \
+                     "ai2b_nep_loss_backward: NULL argument");                                                      \
+        AI2B_REQUIRE((v_ml == nullptr) == (v_dft == nullptr), AI2B_ERR_INVALID,                                     \
+                     "ai2b_nep_loss_backward: pass both virial tensors or neither");                                \
+        NepArgs<T> A{nullptr, nullptr, nullptr, nullptr, nullptr, w0, b0, w1, nullptr, qs, binum, bilist, numneigh, \
+                     firstneigh, types, rcs, nullptr, B, npad, ntypes, umax, nghost, cs, n_r, n_a, l_max, nneu,     \
+                     0, 0, rc_r, rc_a};                                                                             \
+        NepLossArgs<T> L{dco, dw0, db0, dw1, dbi, e_ml, e_dft, f_ml, f_dft, v_ml, v_dft, e_w, f_w, v_w};           \
+        return launch_nep_loss_backward<T>(A, coeffs, L, (cudaStream_t)stream);                                     \
+    }
+AI2B_DEF_NEP_LOSS(f64, double)
+AI2B_DEF_NEP_LOSS(f32, float)
 
 // ---------------------------------------------------------------------------------------------
 // NEP energy/force/virial for callers that must not allocate device memory.

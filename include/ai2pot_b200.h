@@ -235,6 +235,29 @@ int ai2b_nep_efv_static_scratch_f32(float *d_betot, float *d_bforce, float *d_bv
 AI2B_DECL_FVT(f64, double)
 AI2B_DECL_FVT(f32, float)
 
+/* NEP training path: analytic gradient of every structure's loss (same definition as
+ * ai2b_mtp_loss_*, NepLoss<T>::find_loss / find_ef_loss, source/descriptor/nep/include/
+ * nepLoss.h:139-215) w.r.t. coeffs [B, ntypes*ntypes*(n_radial+n_angular)*chebyshev_size],
+ * w0 [B, ntypes*num_neurons*num_descriptors], b0 and w1 [B, ntypes*num_neurons], type_bias
+ * [B, ntypes]. Replaces find_loss_backward_cpu_launcher / find_ef_loss_backward_cpu_launcher
+ * (source/descriptor/nep/include/nepLoss_cpu_launcher.h:69-160, 213-330; CUDA
+ * gpu/include/nepLoss.cuh:1163,1942). The model E/F/V of the same inputs are passed in;
+ * d_bvirial_ml / d_bvirial_dft NULL gives the energy + force variant. Outputs are overwritten;
+ * nghost must be 0. The loss values and RMSEs come from ai2b_mtp_loss_* (same formula). */
+#define AI2B_DECL_NEP_LOSS(SUF, T)                                                               \
+    int ai2b_nep_loss_backward_##SUF(                                                            \
+        T *d_bloss_der2coeffs, T *d_bloss_der2w0, T *d_bloss_der2b0, T *d_bloss_der2w1,          \
+        T *d_bloss_der2type_bias, T e_weight, T f_weight, T v_weight, const T *d_betot_ml,       \
+        const T *d_betot_dft, const T *d_bforce_ml, const T *d_bforce_dft,                       \
+        const T *d_bvirial_ml, const T *d_bvirial_dft, int chebyshev_size, int n_radial_basis,   \
+        int n_angular_basis, int l_max, int num_neurons, const T *d_coeffs, const T *d_w0,       \
+        const T *d_b0, const T *d_w1, int batch_size, int natoms_pad, const int *d_binum,        \
+        const int *d_bilist, const int *d_bnumneigh, const int *d_bfirstneigh, const T *d_brcs,  \
+        const int *d_btypes, int ntypes, int umax, int nghost, T rmax_radial, T rmax_angular,    \
+        const T *d_q_scaler, void *stream);
+AI2B_DECL_NEP_LOSS(f64, double)
+AI2B_DECL_NEP_LOSS(f32, float)
+
 /* ------------------------------------------------------------------------------------------
  * ZBL screened-Coulomb pair correction, added onto etot[B], force[B,Np+nghost,3] and (if not NULL)
  * virial[B,9] of a preceding MTP / NEP evaluation of the same batch. Replaces

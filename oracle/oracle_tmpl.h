@@ -640,6 +640,128 @@ int NAME2(orc_nep_descriptors)(T *bdesc, int cs, int nr, int na, int lmax, const
     return 0;
 }
 
+/* NEP loss gradient w.r.t. coeffs, w0, b0, w1, type_bias, per structure (descriptor/nep/include/nepLoss.h:
+ * find_loss_backward / find_ef_loss_backward; launcher nepLoss_cpu_launcher.h:213-330). Derivation used here:
+ * with lam = 2 e_w/n (E - E*), P_a = 2 f_w/(3n) (F_a - F*_a), Qm = 2 v_w/(9n) (V - V*), the force and virial
+ * terms of the loss are  Phi = sum_ij g_ij . p_ij  with  p_ij = P_i - P_j - Qm r_ij  and g_ij the pair gradient,
+ * so  dL/dtheta = lam dE/dtheta + dPhi/dtheta  and, per atom,  Phi_i = sum_k (dE_i/dq_k) u_k  with
+ * u_k = sum_j dq_k/dr_ij . p_ij  (directional derivative of the descriptors along p). */
+int NAME2(orc_nep_loss_backward)(T *dco, T *dw0, T *db0, T *dw1, T *dbi, T ew, T fw, T vw, const T *e_ml, const T *e_dft,
+                                 const T *f_ml, const T *f_dft, const T *v_ml, const T *v_dft, int cs, int nr, int na, int lmax,
+                                 int nneu, const T *coeffs, const T *w0, const T *b0, const T *w1, const T *bias, NB_DECL, T rcr, T rca, const T *qs)
+{
+    (void)type_map; (void)nghost; (void)bias;
+    NAME(nepdef) m = {cs, nr, na, lmax, ntypes, rcr, rca, coeffs};
+    const int nlm = lmax * lmax + 2 * lmax, nd = nr + na * lmax, nS = na * nlm, nfun = nr + na;
+    const int ncoef = ntypes * ntypes * nfun * cs;
+    T *q = (T *)malloc(sizeof(T) * nd), *S = (T *)malloc(sizeof(T) * (nS + 1)), *u = (T *)malloc(sizeof(T) * nd), *DS = (T *)malloc(sizeof(T) * (nS + 1));
+    T *a = (T *)malloc(sizeof(T) * nd), *be = (T *)malloc(sizeof(T) * nd), *th = (T *)malloc(sizeof(T) * nneu), *sp = (T *)malloc(sizeof(T) * nneu);
+    T *dq = (T *)malloc(sizeof(T) * 3 * (size_t)nr * umax + 8), *dS = (T *)malloc(sizeof(T) * 3 * (size_t)nS * umax + 8);
+    T *p = (T *)malloc(sizeof(T) * 3 * (size_t)umax + 8);
+    T fr[64], dfr[64], fa[64], dfa[64], bl[24], gb[24][3];
+    memset(dco, 0, sizeof(T) * (size_t)B * ncoef); memset(dw0, 0, sizeof(T) * (size_t)B * ntypes * nneu * nd);
+    memset(db0, 0, sizeof(T) * (size_t)B * ntypes * nneu); memset(dw1, 0, sizeof(T) * (size_t)B * ntypes * nneu);
+    memset(dbi, 0, sizeof(T) * (size_t)B * ntypes);
+    for (int b = 0; b < B; b++) {
+        const int n = binum[b];
+        const int *types = btypes + (size_t)b * npad;
+        const T *fm = f_ml + (size_t)b * npad * 3, *fd = f_dft + (size_t)b * npad * 3;
+        const T lam = 2 * ew / n * (e_ml[b] - e_dft[b]), cf = 2 * fw / (3 * n), cv = v_ml ? 2 * vw / (9 * n) : 0;
+        T dV[9] = {0};
+        if (v_ml) for (int k = 0; k < 9; k++) dV[k] = v_ml[9 * b + k] - v_dft[9 * b + k];
+        T *gco = dco + (size_t)b * ncoef;
+        for (int ii = 0; ii < n; ii++) {
+            const size_t slot = (size_t)b * npad + ii;
+            const int ci = bilist[slot], nn = bnumneigh[slot], ti = types[ci];
+            const int *fn = bfirstneigh + slot * umax;
+            const T *rc = brcs + slot * umax * 3;
+            NAME(nep_desc)(&m, ti, nn, fn, rc, types, q, S, dq, dS);
+            for (int j = 0; j < nn; j++)
+                for (int c = 0; c < 3; c++) {
+                    T v = cf * (fm[3 * ci + c] - fd[3 * ci + c]) - cf * (fm[3 * fn[j] + c] - fd[3 * fn[j] + c]);
+                    for (int d = 0; d < 3; d++) v -= cv * dV[3 * c + d] * rc[3 * j + d];
+                    p[3 * j + c] = v;
+                }
+            /* directional derivatives of the sums and of the descriptors */
+            memset(u, 0, sizeof(T) * nd); memset(DS, 0, sizeof(T) * (nS + 1));
+            for (int j = 0; j < nn; j++) {
+                const T *v = rc + 3 * j;
+                T r = (T)sqrt((double)(v[0] * v[0] + v[1] * v[1] + v[2] * v[2]));
+                if (r > rcr) continue;
+                for (int c = 0; c < 3; c++) {
+                    for (int k = 0; k < nr; k++) u[k] += dq[((size_t)k * nn + j) * 3 + c] * p[3 * j + c];
+                    for (int s2 = 0; s2 < nS; s2++) DS[s2] += dS[((size_t)s2 * nn + j) * 3 + c] * p[3 * j + c];
+                }
+            }
+            for (int mu = 0; mu < na; mu++)
+                for (int l = 1; l <= lmax; l++)
+                    for (int mp = 0; mp < 2 * l + 1; mp++) {
+                        int lm = l * l - 1 + mp;
+                        u[nr + mu * lmax + l - 1] += (mp == 0 ? 1 : 2) * 2 * (T)NAME(C3B)[lm] * S[mu * nlm + lm] * DS[mu * nlm + lm];
+                    }
+            /* network: a = dE/dq, s_p = (W0 u~)_p, beta_k = dPhi/dq~_k */
+            const T *W0 = w0 + (size_t)ti * nneu * nd, *B0 = b0 + (size_t)ti * nneu, *W1 = w1 + (size_t)ti * nneu;
+            T *gw0 = dw0 + ((size_t)b * ntypes + ti) * nneu * nd, *gb0 = db0 + ((size_t)b * ntypes + ti) * nneu, *gw1 = dw1 + ((size_t)b * ntypes + ti) * nneu;
+            memset(a, 0, sizeof(T) * nd); memset(be, 0, sizeof(T) * nd);
+            for (int pn = 0; pn < nneu; pn++) {
+                T h = 0, sv = 0;
+                for (int k = 0; k < nd; k++) { h += W0[pn * nd + k] * q[k] / qs[k]; sv += W0[pn * nd + k] * u[k] / qs[k]; }
+                h += B0[pn];
+                th[pn] = (T)tanh((double)h); sp[pn] = sv;
+                const T d1 = 1 - th[pn] * th[pn], d2 = -2 * th[pn] * d1;
+                for (int k = 0; k < nd; k++) { a[k] += W1[pn] * d1 * W0[pn * nd + k] / qs[k]; be[k] += W1[pn] * sv * d2 * W0[pn * nd + k] / qs[k]; }
+                gw1[pn] += lam * th[pn] + d1 * sv;
+                gb0[pn] += lam * W1[pn] * d1 + W1[pn] * sv * d2;
+                for (int k = 0; k < nd; k++)
+                    gw0[pn * nd + k] += (lam * W1[pn] * d1 + W1[pn] * sv * d2) * q[k] / qs[k] + W1[pn] * d1 * u[k] / qs[k];
+            }
+            dbi[(size_t)b * ntypes + ti] += lam;
+            /* coefficients: dL/dc = sum_k (lam a_k + beta_k) dq_k/dc + a_k du_k/dc */
+            for (int j = 0; j < nn; j++) {
+                const T *v = rc + 3 * j;
+                T r = (T)sqrt((double)(v[0] * v[0] + v[1] * v[1] + v[2] * v[2]));
+                if (r > rcr) continue;
+                const int tj = types[fn[j]];
+                const T rinv = 1 / r, vp = (v[0] * p[3 * j] + v[1] * p[3 * j + 1] + v[2] * p[3 * j + 2]) * rinv;
+                NAME(nep_radial)(r, rcr, cs, fr, dfr);
+                NAME(nep_radial)(r, rca, cs, fa, dfa);
+                T *go = gco + (size_t)(ti * ntypes + tj) * nfun * cs;
+                for (int k = 0; k < nr; k++)
+                    for (int xi = 0; xi < cs; xi++) go[k * cs + xi] += (lam * a[k] + be[k]) * fr[xi] + a[k] * dfr[xi] * vp;
+                if (r <= rca && lmax > 0) {
+                    NAME(nep_blm)(v, r, bl, gb);
+                    T rp[5] = {1, r, r * r, r * r * r, r * r * r * r};
+                    for (int mu = 0; mu < na; mu++)
+                        for (int l = 1; l <= lmax; l++) {
+                            const int k = nr + mu * lmax + l - 1;
+                            const T C = 1 / rp[l], pre = -l / (rp[l] * r) * rinv;
+                            for (int mp = 0; mp < 2 * l + 1; mp++) {
+                                const int lm = l * l - 1 + mp, si = mu * nlm + lm;
+                                const T w2c = (mp == 0 ? 1 : 2) * 2 * (T)NAME(C3B)[lm];
+                                const T gp = gb[lm][0] * p[3 * j] + gb[lm][1] * p[3 * j + 1] + gb[lm][2] * p[3 * j + 2];
+                                for (int xi = 0; xi < cs; xi++) {
+                                    const T dSc = fa[xi] * bl[lm] * C;                                   /* dS/dc  */
+                                    const T dDSc = dfa[xi] * vp * bl[lm] * C + fa[xi] * gp * C + fa[xi] * bl[lm] * pre * vp * r;   /* dDS/dc */
+                                    go[(nr + mu) * cs + xi] += (lam * a[k] + be[k]) * w2c * S[si] * dSc + a[k] * w2c * (dSc * DS[si] + S[si] * dDSc);
+                                }
+                            }
+                        }
+                }
+            }
+        }
+    }
+    free(q); free(S); free(u); free(DS); free(a); free(be); free(th); free(sp); free(dq); free(dS); free(p);
+    return 0;
+}
+int NAME2(orc_nep_ef_loss_backward)(T *dco, T *dw0, T *db0, T *dw1, T *dbi, T ew, T fw, const T *e_ml, const T *e_dft, const T *f_ml,
+                                    const T *f_dft, int cs, int nr, int na, int lmax, int nneu, const T *coeffs, const T *w0,
+                                    const T *b0, const T *w1, const T *bias, NB_DECL, T rcr, T rca, const T *qs)
+{
+    return NAME2(orc_nep_loss_backward)(dco, dw0, db0, dw1, dbi, ew, fw, 0, e_ml, e_dft, f_ml, f_dft, NULL, NULL, cs, nr, na, lmax, nneu,
+                                        coeffs, w0, b0, w1, bias, B, npad, binum, bilist, bnumneigh, bfirstneigh, brcs, btypes, ntypes,
+                                        type_map, umax, nghost, rcr, rca, qs);
+}
+
 /* fvt values: fvt/include/force_sr.h:50-81, virial_sr.h:24-51 */
 int NAME2(orc_fvt_force)(T *force, int inum, const int *ilist, const int *numneigh, const int *firstneigh, int nghost, int umax, const T *de)
 {

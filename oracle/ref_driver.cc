@@ -5,7 +5,7 @@
 //   source/nblist/include/{structure,binLinkedList,neighborList}.h
 //   source/descriptor/mtpr/include/{linearMtp_cpu_launcher,linearMtpLoss_cpu_launcher}.h
 //   source/descriptor/mtpr/src/mtpParam.cc
-//   source/descriptor/nep/include/nep_cpu_launcher.h
+//   source/descriptor/nep/include/{nep_cpu_launcher,nepLoss_cpu_launcher}.h
 //   source/fvt/include/{force_sr,virial_sr}.h
 //   source/descriptor/correction/include/zbl.h
 //   source/descriptor/fitutils/include/{descriptorsStatistics,targetStatistics}.h
@@ -29,6 +29,7 @@
 #include "descriptor/mtpr/include/linearMtp_cpu_launcher.h"
 #include "descriptor/mtpr/include/linearMtpLoss_cpu_launcher.h"
 #include "descriptor/nep/include/nep_cpu_launcher.h"
+#include "descriptor/nep/include/nepLoss_cpu_launcher.h"
 #include "fvt/include/force_sr.h"
 #include "fvt/include/virial_sr.h"
 #include "descriptor/correction/include/zbl.h"
@@ -207,6 +208,35 @@ void ref_nep_descriptors_##SUF(T *bdesc, int chebyshev_size, int n_radial, int n
 
 DEF_NEP(double, f64)
 DEF_NEP(float, f32)
+
+// ---- NEP loss gradient: descriptor/nep/include/nepLoss_cpu_launcher.h:69-160,213-330 ------------------
+#define DEF_NEP_LOSS(T, SUF)                                                                 \
+void ref_nep_loss_backward_##SUF(T *dcoeffs, T *dw0, T *db0, T *dw1, T *dbias, T e_w, T f_w, T v_w, \
+                                 T *betot_ml, T *betot_dft, T *bforce_ml, T *bforce_dft,     \
+                                 T *bvirial_ml, T *bvirial_dft, int chebyshev_size, int n_radial, \
+                                 int n_angular, int l_max, int num_neurons, T *coeffs, T *w0, T *b0, \
+                                 T *w1, T *type_bias, NB_ARGS(T), T rmax_radial, T rmax_angular, \
+                                 T *q_scaler)                                                \
+{                                                                                            \
+    ai2pot::nep::find_loss_backward_cpu_launcher<T>(dcoeffs, dw0, db0, dw1, dbias, e_w, f_w, v_w, \
+        betot_ml, betot_dft, (T (*)[3])bforce_ml, (T (*)[3])bforce_dft, bvirial_ml, bvirial_dft, \
+        chebyshev_size, n_radial, n_angular, l_max, num_neurons, coeffs, w0, b0, w1, type_bias, \
+        NB_PASS(T), rmax_radial, rmax_angular, q_scaler);                                    \
+}                                                                                            \
+void ref_nep_ef_loss_backward_##SUF(T *dcoeffs, T *dw0, T *db0, T *dw1, T *dbias, T e_w, T f_w, \
+                                    T *betot_ml, T *betot_dft, T *bforce_ml, T *bforce_dft,  \
+                                    int chebyshev_size, int n_radial, int n_angular, int l_max, \
+                                    int num_neurons, T *coeffs, T *w0, T *b0, T *w1, T *type_bias, \
+                                    NB_ARGS(T), T rmax_radial, T rmax_angular, T *q_scaler)  \
+{                                                                                            \
+    ai2pot::nep::find_ef_loss_backward_cpu_launcher<T>(dcoeffs, dw0, db0, dw1, dbias, e_w, f_w, \
+        betot_ml, betot_dft, (T (*)[3])bforce_ml, (T (*)[3])bforce_dft, chebyshev_size, n_radial, \
+        n_angular, l_max, num_neurons, coeffs, w0, b0, w1, type_bias, NB_PASS(T), rmax_radial, \
+        rmax_angular, q_scaler);                                                             \
+}
+
+DEF_NEP_LOSS(double, f64)
+DEF_NEP_LOSS(float, f32)
 
 // ---- fvt: fvt/include/force_sr.h:50-81, virial_sr.h:24-51 (values only) ---------------
 #define DEF_FVT(T, SUF)                                                                      \

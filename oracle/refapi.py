@@ -177,6 +177,30 @@ class Checker:
           *self._nb(nb, keep), cf(model["rmax_radial"]), cf(model["rmax_angular"]), _p(par[5]))
         return (e, frc, vir) if virial else (e, frc)
 
+    def nep_loss_backward(self, model, nb, w, e_ml, e_dft, f_ml, f_dft, v_ml=None, v_dft=None):
+        """Per-structure gradients [B,num_coeffs], [B,ntypes*neurons*nd], [B,ntypes*neurons] (b0, w1), [B,ntypes]."""
+        dt = nb["brcs"].dtype
+        B, Np = nb["bilist"].shape
+        nt, nneu = nb["ntypes"], model["num_neurons"]
+        nd = model["n_radial"] + model["n_angular"] * model["l_max"]
+        dco = np.zeros((B, model["coeffs"].size), dt); dw0 = np.zeros((B, nt * nneu * nd), dt)
+        db0 = np.zeros((B, nt * nneu), dt); dw1 = np.zeros((B, nt * nneu), dt); dbi = np.zeros((B, nt), dt)
+        keep = []
+        par = [np.ascontiguousarray(model[k], dtype=dt) for k in ("coeffs", "w0", "b0", "w1", "type_bias", "q_scaler")]
+        a = [np.ascontiguousarray(x, dtype=dt) for x in (e_ml, e_dft, f_ml, f_dft)]
+        mdl = (C.c_int(model["chebyshev_size"]), C.c_int(model["n_radial"]), C.c_int(model["n_angular"]), C.c_int(model["l_max"]),
+               C.c_int(nneu), *[_p(x) for x in par[:5]])
+        if v_ml is not None:
+            f, cf = self._fn("nep_loss_backward", dt)
+            v = [np.ascontiguousarray(x, dtype=dt) for x in (v_ml, v_dft)]
+            f(_p(dco), _p(dw0), _p(db0), _p(dw1), _p(dbi), cf(w[0]), cf(w[1]), cf(w[2]), _p(a[0]), _p(a[1]), _p(a[2]), _p(a[3]),
+              _p(v[0]), _p(v[1]), *mdl, *self._nb(nb, keep), cf(model["rmax_radial"]), cf(model["rmax_angular"]), _p(par[5]))
+        else:
+            f, cf = self._fn("nep_ef_loss_backward", dt)
+            f(_p(dco), _p(dw0), _p(db0), _p(dw1), _p(dbi), cf(w[0]), cf(w[1]), _p(a[0]), _p(a[1]), _p(a[2]), _p(a[3]),
+              *mdl, *self._nb(nb, keep), cf(model["rmax_radial"]), cf(model["rmax_angular"]), _p(par[5]))
+        return dco, dw0, db0, dw1, dbi
+
     def nep_descriptors(self, model, nb):
         dt = nb["brcs"].dtype
         f, cf = self._fn("nep_descriptors", dt)
