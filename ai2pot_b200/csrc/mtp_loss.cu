@@ -31,9 +31,10 @@ struct LossArgs {
 };
 
 // ---- loss and squared-error sums ---------------------------------------------------------------
-// one block per structure; se[0..2] accumulate sum dE^2, sum dF^2, sum dV^2, se[3] the atom count
+// one block per structure; se[0..2] accumulate sum dE^2 (of the energy per atom if e_per_atom: the NEP ops'
+// definition, nepLoss_cpu_launcher.h:300-345), sum dF^2, sum dV^2, se[3] the atom count
 template <typename T>
-__global__ void mtp_loss_kernel(T *__restrict__ loss, T *__restrict__ se, int npad, int nghost, const int *__restrict__ binum,
+__global__ void mtp_loss_kernel(T *__restrict__ loss, T *__restrict__ se, int e_per_atom, int npad, int nghost, const int *__restrict__ binum,
                                 const int *__restrict__ bilist, T ew, T fw, T vw, const T *__restrict__ e_ml,
                                 const T *__restrict__ e_dft, const T *__restrict__ f_ml, const T *__restrict__ f_dft,
                                 const T *__restrict__ v_ml, const T *__restrict__ v_dft)
@@ -61,7 +62,7 @@ __global__ void mtp_loss_kernel(T *__restrict__ loss, T *__restrict__ se, int np
         T l = fw / T(3 * n) * f2 + ew / T(n) * de * de;
         if (v_ml) l += vw / T(9 * n) * v2;
         loss[b] = n > 0 ? l : T(0);
-        atomicAdd(se + 0, de * de);
+        atomicAdd(se + 0, e_per_atom ? (n > 0 ? (de / T(n)) * (de / T(n)) : T(0)) : de * de);
         atomicAdd(se + 1, f2);
         atomicAdd(se + 2, v2);
         atomicAdd(se + 3, T(n));
@@ -604,25 +605,42 @@ extern "C" size_t ai2b_mtp_loss_workspace_bytes(const ai2b_mtp_program *prog, in
     return loss_ws_layout(prog->dev, batch_size, natoms_pad, ntypes > 0 ? ntypes : 1, sizeof(double)).total + 256;
 }
 
+template <typename T>
+static int loss_forward(int e_per_atom, T *loss, T *rmse, int B, int npad, int nghost, const int *binum, const int *bilist, T ew, T fw,
+                        T vw, const T *e_ml, const T *e_dft, const T *f_ml, const T *f_dft, const T *v_ml, const T *v_dft, void *ws,
+                        size_t ws_bytes, void *stream)
+{
+    AI2B_REQUIRE(B >= 0 && npad >= 0 && nghost >= 0, AI2B_ERR_INVALID, "loss: negative size");
+    if (B == 0) return AI2B_OK;
+    AI2B_REQUIRE(loss && rmse && binum && bilist && e_ml && e_dft && f_ml && f_dft && (!v_ml == !v_dft), AI2B_ERR_INVALID,
+                 "loss: NULL argument");
+    AI2B_REQUIRE(ws && ws_bytes >= 4 * sizeof(T), AI2B_ERR_WORKSPACE, "loss: workspace too small");
+    cudaStream_t st = (cudaStream_t)stream;
+    T *se = reinterpret_cast<T *>(ws);
+    AI2B_CUDA(cudaMemsetAsync(se, 0, 4 * sizeof(T), st));
+    mtp_loss_kernel<T><<<B, 256, 0, st>>>(loss, se, e_per_atom, npad, nghost, binum, bilist, ew, fw, vw, e_ml, e_dft, f_ml, f_dft, v_ml,
+                                          v_dft);
+    mtp_rmse_kernel<T><<<1, 32, 0, st>>>(rmse, se, B);
+    AI2B_CUDA(cudaGetLastError());
+    return AI2B_OK;
+}
+
 #define AI2B_DEF_LOSS(SUF, T)                                                                                      \
     extern "C" int ai2b_mtp_loss_##SUF(T *loss, T *rmse, int B, int npad, int nghost, const int *binum,            \
                                        const int *bilist, T ew, T fw, T vw, const T *e_ml, const T *e_dft,         \
                                        const T *f_ml, const T *f_dft, const T *v_ml, const T *v_dft, void *ws,     \
                                        size_t ws_bytes, void *stream)                                              \
     {                                                                                                              \
-        AI2B_REQUIRE(B >= 0 && npad >= 0 && nghost >= 0, AI2B_ERR_INVALID, "ai2b_mtp_loss: negative size");         \
-        if (B == 0) return AI2B_OK;                                                                                \
-        AI2B_REQUIRE(loss && rmse && binum && bilist && e_ml && e_dft && f_ml && f_dft && (!v_ml == !v_dft),       \
-                     AI2B_ERR_INVALID, "ai2b_mtp_loss: NULL argument");                                            \
-        AI2B_REQUIRE(ws && ws_bytes >= 4 * sizeof(T), AI2B_ERR_WORKSPACE, "ai2b_mtp_loss: workspace too small");   \
-        cudaStream_t st = (cudaStream_t)stream;                                                                    \
-        T *se = reinterpret_cast<T *>(ws);                                                                         \
-        AI2B_CUDA(cudaMemsetAsync(se, 0, 4 * sizeof(T), st));                                                      \
-        mtp_loss_kernel<T><<<B, 256, 0, st>>>(loss, se, npad, nghost, binum, bilist, ew, fw, vw, e_ml, e_dft,      \
-                                              f_ml, f_dft, v_ml, v_dft);                                           \
-        mtp_rmse_kernel<T><<<1, 32, 0, st>>>(rmse, se, B);                                                         \
-        AI2B_CUDA(cudaGetLastError());                                                                             \
-        return AI2B_OK;                                                                                            \
+        return loss_forward<T>(0, loss, rmse, B, npad, nghost, binum, bilist, ew, fw, vw, e_ml, e_dft, f_ml, f_dft, \
+                               v_ml, v_dft, ws, ws_bytes, stream);                                                 \
+    }                                                                                                              \
+    extern "C" int ai2b_nep_loss_##SUF(T *loss, T *rmse, int B, int npad, int nghost, const int *binum,            \
+                                       const int *bilist, T ew, T fw, T vw, const T *e_ml, const T *e_dft,         \
+                                       const T *f_ml, const T *f_dft, const T *v_ml, const T *v_dft, void *ws,     \
+                                       size_t ws_bytes, void *stream)                                              \
+    {                                                                                                              \
+        return loss_forward<T>(1, loss, rmse, B, npad, nghost, binum, bilist, ew, fw, vw, e_ml, e_dft, f_ml, f_dft, \
+                               v_ml, v_dft, ws, ws_bytes, stream);                                                 \
     }                                                                                                              \
     extern "C" int ai2b_mtp_loss_backward_##SUF(                                                                   \
         const ai2b_mtp_program *prog, T *dcoeffs, T *dlinear, T *dbias, T ew, T fw, T vw, const T *e_ml,           \

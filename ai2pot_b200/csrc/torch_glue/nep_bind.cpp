@@ -86,8 +86,11 @@ variable_list nep_desc(int64_t cs, int64_t n_r, int64_t n_a, int64_t l_max, cons
         binum_tensor, bilist_tensor, bnumneigh_tensor, bfirstneigh_tensor, brcs_tensor, btypes_tensor, type_map_tensor,      \
         nghost, rmax_radial, rmax_angular, q_scaler_tensor, ZblArgs{zbl_rmax, zbl_rmin, zbl_cks_tensor, zbl_dks_tensor}
 
+#include "nep_loss_glue.inc"
+
 TORCH_LIBRARY(nep, m)
 {
+    register_nep_loss_ops(m);
     m.def("nepToEFVOp", [](NEP_EFV_ARGS) {
         return nep_efv(true, NEP_EFV_PASS);
     });

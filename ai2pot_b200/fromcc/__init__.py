@@ -52,3 +52,5 @@ def _optional(ns, name):
 
 linearMtpToLossOp = _optional("mtpr", "linearMtpToLossOp")
 linearMtpToEFLossOp = _optional("mtpr", "linearMtpToEFLossOp")
+nepToLossOp = _optional("nep", "nepToLossOp")
+nepToEFLossOp = _optional("nep", "nepToEFLossOp")

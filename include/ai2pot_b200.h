@@ -243,8 +243,16 @@ AI2B_DECL_FVT(f32, float)
  * (source/descriptor/nep/include/nepLoss_cpu_launcher.h:69-160, 213-330; CUDA
  * gpu/include/nepLoss.cuh:1163,1942). The model E/F/V of the same inputs are passed in;
  * d_bvirial_ml / d_bvirial_dft NULL gives the energy + force variant. Outputs are overwritten;
- * nghost must be 0. The loss values and RMSEs come from ai2b_mtp_loss_* (same formula). */
+ * nghost must be 0. ai2b_nep_loss_*: loss[B] as ai2b_mtp_loss_* (same formula) and rmse[3] with
+ * the NEP ops' energy RMSE, which is per atom: sqrt(mean_b ((E_b - E*_b) / n_b)^2)
+ * (find_efv_rmse_cpu_launcher, nepLoss_cpu_launcher.h:355-411). */
 #define AI2B_DECL_NEP_LOSS(SUF, T)                                                               \
+    int ai2b_nep_loss_##SUF(T *d_bloss, T *d_rmse, int batch_size, int natoms_pad, int nghost,   \
+                            const int *d_binum, const int *d_bilist, T e_weight, T f_weight,     \
+                            T v_weight, const T *d_betot_ml, const T *d_betot_dft,               \
+                            const T *d_bforce_ml, const T *d_bforce_dft, const T *d_bvirial_ml,  \
+                            const T *d_bvirial_dft, void *d_workspace, size_t workspace_bytes,   \
+                            void *stream);                                                       \
     int ai2b_nep_loss_backward_##SUF(                                                            \
         T *d_bloss_der2coeffs, T *d_bloss_der2w0, T *d_bloss_der2b0, T *d_bloss_der2w1,          \
         T *d_bloss_der2type_bias, T e_weight, T f_weight, T v_weight, const T *d_betot_ml,       \

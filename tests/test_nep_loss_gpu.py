@@ -43,3 +43,43 @@ def test_nep_loss_backward(checkers, dt, tol, virial):
     got = capi.nep_loss_backward(md, nbd, wts, t(e), t(E), t(f), t(F), t(v) if virial else None, t(V) if virial else None)
     for name, a, b in zip(("coeffs", "w0", "b0", "w1", "bias"), ref, got):
         assert util.relerr(b.cpu().numpy(), a) < tol, name
+
+
+@pytest.mark.parametrize("virial", [True, False])
+def test_nep_loss_ops_autograd(checkers, virial):
+    """nepToLossOp / nepToEFLossOp: loss values, RMSEs and autograd to coeffs, w0, b0, w1, type_bias."""
+    from ai2pot_b200 import fromcc
+    chk = _chk(checkers)
+    dt = np.float64
+    m, nb, (E, F, V) = _batch(chk, dt)
+    e, f, v = chk.nep_efv(m, nb)
+    wts = (1.0, 2.0, 0.5)
+    ref = chk.nep_loss_backward(m, nb, wts, e, E, f, F, v if virial else None, V if virial else None)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    par = [t(m[k].astype(dt)).requires_grad_(True) for k in ("coeffs", "w0", "b0", "w1", "type_bias")]
+    z = torch.zeros(36, dtype=torch.float64, device="cuda")
+    tail = (m["chebyshev_size"], m["n_radial"], m["n_angular"], m["l_max"], *par, t(nb["binum"]), t(nb["bilist"]), t(nb["bnumneigh"]),
+            t(nb["bfirstneigh"]), t(nb["brcs"]), t(nb["btypes"]), torch.arange(3, dtype=torch.int32, device="cuda"), 0,
+            m["rmax_radial"], m["rmax_angular"], t(m["q_scaler"].astype(dt)), 0.0, 0.0, z, z)
+    if virial:
+        out = fromcc.nepToLossOp(wts[0], wts[1], wts[2], t(E), t(F), t(V), *tail)
+    else:
+        out = fromcc.nepToEFLossOp(wts[0], wts[1], t(E), t(F), *tail)
+    assert len(out) == (4 if virial else 3)
+    loss = out[0]
+    # loss definition (nepLoss.h:139-215) on the checker's E/F/V
+    n = nb["binum"].astype(dt)
+    exp = wts[0] / n * (e - E) ** 2
+    for b in range(len(n)):
+        k = int(n[b])
+        exp[b] += wts[1] / (3 * k) * ((f[b, :k] - F[b, :k]) ** 2).sum()
+        if virial:
+            exp[b] += wts[2] / (9 * k) * ((v[b] - V[b]) ** 2).sum()
+    assert util.relerr(loss.detach().cpu().numpy(), exp) < 1e-10
+    e_rmse = np.sqrt((((e - E) / n) ** 2).mean())
+    assert abs(out[1].item() - e_rmse) < 1e-10 * e_rmse
+    g = torch.tensor([0.5, 1.0, 2.0], dtype=torch.float64, device="cuda")
+    (loss * g).sum().backward()
+    gw = g.cpu().numpy()
+    for p, r, name in zip(par, ref, ("coeffs", "w0", "b0", "w1", "bias")):
+        assert util.relerr(p.grad.cpu().numpy().ravel(), gw @ r) < 1e-10, name
