@@ -39,16 +39,20 @@ __host__ __device__ inline size_t nepl_warp_elems(int nd, int nS, int nneu, int 
     return 4 * (size_t)nd + 4 * (size_t)nS + 3 * (size_t)nneu + ((red + 31) & ~size_t(31)) + 64;
 }
 
-// sum over the warp of `count` per-lane values produced by f(k); result k lands in out[k]
-template <typename T, typename F>
-__device__ __forceinline__ void warp_reduce_many(int count, F f, T *out, int lane, bool add)
+// sum over the warp of `count` <= NMAX per-lane values produced by f(k); result k lands in out[k].
+// NMAX is a compile-time bound so that f sees compile-time indices (its arrays stay in registers).
+template <typename T, int NMAX, typename F>
+__device__ __forceinline__ void warp_reduce_many(int count, F f, T *out, int lane)
 {
-    for (int k0 = 0; k0 < count; k0 += 32) {
-        T v[32];
 #pragma unroll
-        for (int i = 0; i < 32; i++) v[i] = (k0 + i < count) ? f(k0 + i) : T(0);
-        const T r = warp_xreduce<T, 32>(v, lane);
-        if (k0 + lane < count) out[k0 + lane] = add ? out[k0 + lane] + r : r;
+    for (int k0 = 0; k0 < NMAX; k0 += 32) {
+        if (k0 < count) {
+            T v[32];
+#pragma unroll
+            for (int i = 0; i < 32; i++) v[i] = (k0 + i < count) ? f(k0 + i) : T(0);
+            const T r = warp_xreduce<T, 32>(v, lane);
+            if (k0 + lane < count) out[k0 + lane] = r;
+        }
     }
 }
 
@@ -57,6 +61,7 @@ __global__ void __launch_bounds__(NEPL_WARPS * 32) nep_loss_backward_kernel(cons
                                                                               const NepLossArgs<T> L)
 {
     extern __shared__ __align__(16) unsigned char nepl_smem[];
+    __shared__ T iq[96];   // 1 / q_scaler
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int b = blockIdx.y;
     const int nfun = A.n_r + A.n_a, nlm = A.l_max * A.l_max + 2 * A.l_max, nS = A.n_a * nlm, nd = A.nd, nneu = A.nneu;
@@ -72,6 +77,7 @@ __global__ void __launch_bounds__(NEPL_WARPS * 32) nep_loss_backward_kernel(cons
     T *th = yc + nS, *sp = th + nneu, *d2v = sp + nneu;
     T *red = d2v + nneu;
     for (size_t i = threadIdx.x; i < nblk; i += blockDim.x) g_co[i] = T(0);
+    for (int k = threadIdx.x; k < A.nd; k += blockDim.x) iq[k] = T(1) / A.qs[k];
     __syncthreads();
 
     const int n = A.binum[b];
@@ -132,11 +138,11 @@ __global__ void __launch_bounds__(NEPL_WARPS * 32) nep_loss_backward_kernel(cons
             Pair P;
             load_pair(P, rc, fn, ci, nn, j0 + lane);
             const T *crow = ctab + (size_t)P.tj * nfun * A.cs;
-            warp_reduce_many<T>(2 * A.n_r, [&](int k) {
+            warp_reduce_many<T, 32>(2 * A.n_r, [&](int k) {
                 const int nidx = k >> 1;
                 if (!P.on) return T(0);
                 return (k & 1) ? contract(crow + nidx * A.cs, P.dfr) * P.vp : contract(crow + nidx * A.cs, P.fr);
-            }, red, lane, false);
+            }, red, lane);
             __syncwarp();
             if (lane < A.n_r) { q[lane] += red[2 * lane]; u[lane] += red[2 * lane + 1]; }
             __syncwarp();
@@ -146,11 +152,11 @@ __global__ void __launch_bounds__(NEPL_WARPS * 32) nep_loss_backward_kernel(cons
                 for (int mu = 0; mu < A.n_a; mu++) {
                     const T g = P.ang ? contract(crow + (A.n_r + mu) * A.cs, P.fa) : T(0);
                     const T dg = P.ang ? contract(crow + (A.n_r + mu) * A.cs, P.dfa) : T(0);
-                    warp_reduce_many<T>(2 * nlm, [&](int k) {
+                    warp_reduce_many<T, 2 * NEP_NLM>(2 * nlm, [&](int k) {
                         const int lm = k >> 1;
                         if (k & 1) return dg * bl[lm] * P.vp + g * (gb[lm][0] * P.px + gb[lm][1] * P.py + gb[lm][2] * P.pz);
                         return g * bl[lm];
-                    }, red, lane, false);
+                    }, red, lane);
                     __syncwarp();
                     if (lane < nlm) { S[mu * nlm + lane] += red[2 * lane]; DS[mu * nlm + lane] += red[2 * lane + 1]; }
                     __syncwarp();
@@ -174,7 +180,7 @@ __global__ void __launch_bounds__(NEPL_WARPS * 32) nep_loss_backward_kernel(cons
         const T *W0 = A.w0 + (size_t)ti * nneu * nd, *B0 = A.b0 + (size_t)ti * nneu, *W1 = A.w1 + (size_t)ti * nneu;
         for (int pn = lane; pn < nneu; pn += 32) {
             T h = B0[pn], sv = T(0);
-            for (int k = 0; k < nd; k++) { const T w = W0[pn * nd + k] / A.qs[k]; h = fma(w, q[k], h); sv = fma(w, u[k], sv); }
+            for (int k = 0; k < nd; k++) { const T w = W0[pn * nd + k] * iq[k]; h = fma(w, q[k], h); sv = fma(w, u[k], sv); }
             const T t = gtanh(h), d1 = T(1) - t * t, d2 = T(-2) * t * d1;
             th[pn] = W1[pn] * d1;          // weight of W0 in dE/dq
             sp[pn] = W1[pn] * sv * d2;     // weight of W0 in dPhi/dq~
@@ -183,15 +189,15 @@ __global__ void __launch_bounds__(NEPL_WARPS * 32) nep_loss_backward_kernel(cons
             atomicAdd(g_w1 + ti * nneu + pn, lam * t + d1 * sv);
             atomicAdd(g_b0 + ti * nneu + pn, gb0);
             for (int k = 0; k < nd; k++)
-                atomicAdd(g_w0 + ((size_t)ti * nneu + pn) * nd + k, (gb0 * q[k] + W1[pn] * d1 * u[k]) / A.qs[k]);
+                atomicAdd(g_w0 + ((size_t)ti * nneu + pn) * nd + k, (gb0 * q[k] + W1[pn] * d1 * u[k]) * iq[k]);
         }
         if (lane == 0) atomicAdd(g_bi + ti, lam);
         __syncwarp();
         for (int k = lane; k < nd; k += 32) {
             T a0 = T(0), b0v = T(0);
             for (int pn = 0; pn < nneu; pn++) { const T w = W0[pn * nd + k]; a0 = fma(th[pn], w, a0); b0v = fma(sp[pn], w, b0v); }
-            av[k] = a0 / A.qs[k];
-            be[k] = lam * av[k] + b0v / A.qs[k];       // coefficient of dq_k/dc (av: coefficient of du_k/dc)
+            av[k] = a0 * iq[k];
+            be[k] = lam * av[k] + b0v * iq[k];       // coefficient of dq_k/dc (av: coefficient of du_k/dc)
         }
         __syncwarp();
         for (int i = lane; i < nS; i += 32) {
@@ -217,34 +223,30 @@ __global__ void __launch_bounds__(NEPL_WARPS * 32) nep_loss_backward_kernel(cons
                 const int mu = fidx - A.n_r;
                 T X = T(0), Y = T(0), GY = T(0);
                 if (P.ang) {
-                    for (int lm = 0; lm < nlm; lm++) {
-                        const T yv = yc[mu * nlm + lm];
-                        X = fma(xc[mu * nlm + lm], bl[lm], X);
-                        Y = fma(yv, bl[lm], Y);
-                        GY = fma(yv, gb[lm][0] * P.px + gb[lm][1] * P.py + gb[lm][2] * P.pz, GY);
+#pragma unroll
+                    for (int lm = 0; lm < NEP_NLM; lm++) {
+                        if (lm < nlm) {
+                            const T yv = yc[mu * nlm + lm];
+                            X = fma(xc[mu * nlm + lm], bl[lm], X);
+                            Y = fma(yv, bl[lm], Y);
+                            GY = fma(yv, gb[lm][0] * P.px + gb[lm][1] * P.py + gb[lm][2] * P.pz, GY);
+                        }
                     }
                 }
                 wv = X + GY; wd = Y * P.vp;
             };
+            // every lane adds its neighbour's terms to the block accumulator of its (ti, tj) pair
+            // (shared-memory atomics; lanes of the same neighbour type meet on the same addresses)
             for (int fidx = 0; fidx < nfun; fidx++) {
                 T wv, wd;
                 weights(fidx, wv, wd);
-                const bool use = fidx < A.n_r ? P.on : P.ang;
-                const T *f = fidx < A.n_r ? P.fr : P.fa, *df = fidx < A.n_r ? P.dfr : P.dfa;
-                warp_reduce_many<T>(A.ntypes * A.cs, [&](int k) {
-                    const int tj = k / A.cs, xi = k % A.cs;
-                    if (!use || tj != P.tj) return T(0);
-                    T fv = T(0), dv = T(0);
+                const bool rad = fidx < A.n_r;
+                if (rad ? P.on : P.ang) {
+                    T *dst = g_co + (((size_t)ti * A.ntypes + P.tj) * nfun + fidx) * A.cs;
 #pragma unroll
-                    for (int c = 0; c < CSP; c++) if (c == xi) { fv = f[c]; dv = df[c]; }
-                    return wv * fv + wd * dv;
-                }, red, lane, false);
-                __syncwarp();
-                for (int k = lane; k < A.ntypes * A.cs; k += 32) {
-                    const int tj = k / A.cs, xi = k % A.cs;
-                    if (red[k] != T(0)) atomicAdd(g_co + (((size_t)ti * A.ntypes + tj) * nfun + fidx) * A.cs + xi, red[k]);
+                    for (int xi = 0; xi < CSP; xi++)
+                        if (xi < A.cs) atomicAdd(dst + xi, wv * (rad ? P.fr[xi] : P.fa[xi]) + wd * (rad ? P.dfr[xi] : P.dfa[xi]));
                 }
-                __syncwarp();
             }
         }
         __syncwarp();
@@ -293,7 +295,7 @@ static int launch_nep_loss_backward(NepArgs<T> A, const T *coeffs, NepLossArgs<T
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         long bx = ((long)A.npad + NEPL_WARPS - 1) / NEPL_WARPS;
-        const long cap = std::max(1L, (long)sms * 2 / A.B);
+        const long cap = std::max(1L, (long)sms * 8 / A.B);   // enough blocks to fill the GPU; each ends with one flush of its accumulators
         if (bx > cap) bx = cap;
         kern<<<dim3((unsigned)bx, (unsigned)A.B), NEPL_WARPS * 32, smem, st>>>(A, coeffs, L);
         AI2B_CUDA(cudaGetLastError());
