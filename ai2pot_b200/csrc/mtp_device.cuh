@@ -116,11 +116,12 @@ struct PairState {
         compute(P, A, types, ti, lane, fr, fdv, frs);
     }
     // x, y, z, nj and act (= the slot holds a neighbour) are already set
+    // tj_pre >= 0: the neighbour's type has been looked up already
     __device__ __forceinline__ void compute(const MtpProgramDev &P, const MtpArgs<T> &A, const int *types, int ti, int lane, T *fr,
-                                            T *fdv, int frs = 32)
+                                            T *fdv, int frs = 32, int tj_pre = -1)
     {
         using V2 = typename Vec2<T>::type;
-        const int tj_early = act ? types[nj] : 0;   // in flight during the square root
+        const int tj_early = tj_pre >= 0 ? tj_pre : (act ? types[nj] : 0);   // in flight during the square root
         const T r = gsqrt(x * x + y * y + z * z);
         act = act && (r <= A.rmax) && (r > T(0));
         const int tj = act ? tj_early : 0;

@@ -149,13 +149,21 @@ __global__ void __launch_bounds__(MTP_WARPS * 32, 4) mtp_fwd_lanes_kernel(const 
         return w;
     };
     int t = blockIdx.x * MTP_WARPS + warp;
+    // the types of the next atom and of its first 32 neighbours depend on that row: they are looked up
+    // once the row has arrived (after the summation loop), one atom ahead of their use
+    auto row_types = [&](const Row &w, int &ti_out, int &tj_out) {
+        const int *ty = A.types + (size_t)w.b * (A.npad + (A.desc ? 0 : A.nghost));
+        ti_out = ty[w.ci];
+        tj_out = (lane < min(w.nn, A.umax) && w.nj >= 0) ? ty[w.nj] : 0;
+    };
     Row nx;
-    if (t < ntot) nx = fetch(t);
+    int nx_ti = 0, nx_tj = 0;
+    if (t < ntot) { nx = fetch(t); row_types(nx, nx_ti, nx_tj); }
     for (; t < ntot; t += nw) {
         const Row cur = nx;
         const int nn = min(cur.nn, A.umax);
         const int *types = A.types + (size_t)cur.b * (A.npad + (A.desc ? 0 : A.nghost));
-        const int ti = types[cur.ci];
+        const int ti = nx_ti, tj_first = nx_tj;
         T acc[RQ][NMU];
 #pragma unroll
         for (int r = 0; r < RQ; r++)
@@ -174,7 +182,7 @@ __global__ void __launch_bounds__(MTP_WARPS * 32, 4) mtp_fwd_lanes_kernel(const 
                 }
             }
             bool act = j < nn && nj >= 0;
-            const int tj = act ? types[nj] : 0;        // in flight during the radial basis
+            const int tj = j0 == 0 ? tj_first : (act ? types[nj] : 0);
             const T r = gsqrt(x * x + y * y + z * z);
             act = act && (r <= A.rmax) && (r > T(0));
             const T rinv = act ? T(1) / r : T(0);
@@ -235,6 +243,7 @@ __global__ void __launch_bounds__(MTP_WARPS * 32, 4) mtp_fwd_lanes_kernel(const 
             }
         }
         if (nn <= 0 && t + nw < ntot) nx = fetch(t + nw);
+        if (t + nw < ntot) row_types(nx, nx_ti, nx_tj);
         T *out = A.Mb + (size_t)t * A.nbp;
 #pragma unroll
         for (int r = 0; r < RQ; r++)
@@ -502,11 +511,18 @@ __global__ void __launch_bounds__(MTP_WARPS * 32, 3) mtp_force_kernel(const MtpP
         for (int i = lane; i < A.nbp; i += 32) __pipeline_memcpy_async(Ed + i, ein + i, sizeof(T));
         __pipeline_commit();
     };
-    if (t0 < t1) request(t0);
-
-    for (int t = t0; t < t1; t++) {
+    // types of the next atom and of its first 32 neighbours: looked up from the arrived row one atom ahead
+    int nx_ti = 0, nx_tj = 0;
+    auto row_types = [&]() {
         __pipeline_wait_prior(0);
         __syncwarp();
+        const int *ty = A.types + (size_t)row_b * (A.npad + A.nghost);
+        nx_ti = ty[rb_fn[32]];
+        nx_tj = lane < min(rb_fn[33], A.umax) ? ty[rb_fn[lane]] : 0;
+    };
+    if (t0 < t1) { request(t0); row_types(); }
+
+    for (int t = t0; t < t1; t++) {
         if (row_b != cur_b) {
             flush();
             cur_b = row_b;
@@ -516,7 +532,7 @@ __global__ void __launch_bounds__(MTP_WARPS * 32, 3) mtp_force_kernel(const MtpP
         const int ci = rb_fn[32];
         const int nn = min(rb_fn[33], A.umax);
         const int *types = A.types + (size_t)b * (A.npad + A.nghost);
-        const int ti = types[ci];
+        const int ti = nx_ti;
         const int *fn = A.firstneigh + slot * A.umax;
         const T *rc = A.rcs + slot * A.umax * 3;
 
@@ -524,7 +540,7 @@ __global__ void __launch_bounds__(MTP_WARPS * 32, 3) mtp_force_kernel(const MtpP
         ps.act = lane < nn;
         ps.x = ps.y = ps.z = T(0); ps.nj = 0;
         if (ps.act) { ps.x = rb_rc[3 * lane]; ps.y = rb_rc[3 * lane + 1]; ps.z = rb_rc[3 * lane + 2]; ps.nj = rb_fn[lane]; }
-        ps.compute(P, A, types, ti, lane, fr, fdv);
+        ps.compute(P, A, types, ti, lane, fr, fdv, 32, ps.act ? nx_tj : 0);
 
         // adjoints -> coefficient quadruples {e, (ax+1) e[+x], (ay+1) e[+y], (az+1) e[+z]}
         for (int c = lane; c < P.ndense; c += 32) {
@@ -570,6 +586,7 @@ __global__ void __launch_bounds__(MTP_WARPS * 32, 3) mtp_force_kernel(const MtpP
                 }
             }
         }
+        if (t + 1 < t1) row_types();   // the next row has arrived during the evaluation
         fcx = warp_sum(fcx); fcy = warp_sum(fcy); fcz = warp_sum(fcz);
         if (lane == 0) {
             atomicAdd(frc + 3 * ci + 0, fcx);
