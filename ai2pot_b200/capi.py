@@ -303,6 +303,20 @@ def mtp_loss(nb, weights, e_ml, e_dft, f_ml, f_dft, v_ml=None, v_dft=None):
     return loss, rmse
 
 
+def nep_loss(nb, weights, e_ml, e_dft, f_ml, f_dft, v_ml=None, v_dft=None):
+    """As mtp_loss, with the NEP ops' per-atom energy RMSE in rmse[0]."""
+    suf, cf = _suf(e_ml.dtype)
+    B, npad = nb["bilist"].shape
+    loss = torch.empty(B, dtype=e_ml.dtype, device=e_ml.device)
+    rmse = torch.empty(3, dtype=e_ml.dtype, device=e_ml.device)
+    ws = torch.empty(256, dtype=torch.uint8, device=e_ml.device)
+    _check(getattr(lib(), "ai2b_nep_loss_" + suf)(
+        _ptr(loss), _ptr(rmse), C.c_int(B), C.c_int(npad), C.c_int(int(nb.get("nghost", 0))), _ptr(nb["binum"]), _ptr(nb["bilist"]),
+        cf(weights[0]), cf(weights[1]), cf(weights[2]), _ptr(e_ml), _ptr(e_dft), _ptr(f_ml), _ptr(f_dft), _ptr(v_ml), _ptr(v_dft),
+        _ptr(ws), C.c_size_t(ws.numel()), _stream()))
+    return loss, rmse
+
+
 def mtp_loss_backward(prog, model, nb, weights, e_ml, e_dft, f_ml, f_dft, v_ml=None, v_dft=None):
     """Per-structure gradients (dcoeffs [B,ncoef], dlinear [B,ns], dbias [B,ntypes])."""
     rcs = nb["brcs"]

@@ -120,7 +120,59 @@ def _timed(fn, steps, warmup, flush, barrier=None):
     return sum(a.elapsed_time(b) for a, b in evs) * 1e-3
 
 
+def ghost_images(cell, coords, types, rcut):
+    """What an MD host holds for a periodic orthorhombic system: local atoms wrapped into the box plus the
+    periodic images within rcut of it (ghosts), as double positions. Returns x_local, x_ghost, types_ghost, owner."""
+    L = np.diag(np.asarray(cell, np.float64))
+    x = np.mod(np.asarray(coords, np.float64), L)
+    gx, gt, owner = [], [], []
+    for sx in (-1, 0, 1):
+        for sy in (-1, 0, 1):
+            for sz in (-1, 0, 1):
+                if sx == sy == sz == 0:
+                    continue
+                y = x + np.array([sx, sy, sz]) * L
+                keep = np.all((y > -rcut) & (y < L + rcut), axis=1)
+                gx.append(y[keep]); gt.append(np.asarray(types)[keep]); owner.append(np.nonzero(keep)[0])
+    return x, np.concatenate(gx), np.concatenate(gt), np.concatenate(owner)
+
+
+def run_md_benchmark(w, steps, warmup, dist, sampler):
+    """Device-resident MD input path (ai2b_md_session_compute): host positions + types of local and ghost atoms
+    in, host forces / energy / virial out. The call is synchronous and owns its stream, so a step is timed on
+    the host clock around the call; there is no separate device-only number."""
+    import time
+    m = w["model"]
+    x, gx, gt, owner = ghost_images(w["cell"], w["coords"], w["types"], w["rcut"])
+    nlocal, nghost = len(x), len(gx)
+    xa = np.ascontiguousarray(np.concatenate([x, gx])); ta = np.ascontiguousarray(np.concatenate([w["types"], gt]).astype(np.int32))
+    ses = capi.MdSession(m, w["umax"])
+    for _ in range(max(3, warmup)):
+        e, f, v6, mx = ses.compute(nlocal, nghost, xa, ta)
+    if dist is not None:
+        dist.barrier()
+    sampler.start()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        e, f, v6, mx = ses.compute(nlocal, nghost, xa, ta)
+    t = time.perf_counter() - t0
+    clocks = sampler.stop()
+    ses.close()
+    props = torch.cuda.get_device_properties(torch.cuda.current_device())
+    peak = fma_peak_tflops(False, props.multi_processor_count)
+    roofline = {"kernel": "whole ai2b_md_session_compute call (H2D, neighbour build, nep_fast_kernel, D2H, host accumulation)", "bound": "fp32",
+                "achieved": None, "peak": peak, "unit": "TFLOP/s", "frac": None, "traffic": None,
+                "note": "host-timed synchronous call; the kernels are those of the nep workload", "max_neighbours": int(mx),
+                "local_atoms": nlocal, "ghost_atoms": nghost}
+    nall = nlocal + nghost
+    return dict(t_dev=t, t_e2e=t, clocks=clocks, launches=(9 + 1) * steps, h2d=nall * 28, d2h=nall * 12 + 48, units=nlocal,
+                e2e_path="host double positions + types of local and ghost atoms -> ai2b_md_session_compute -> host forces (+=), energy, virial[6]",
+                roofline=roofline, parts_ms=None)
+
+
 def run_benchmark(w, steps, warmup, dist, sampler):
+    if w.get("kind") == "md":
+        return run_md_benchmark(w, steps, warmup, dist, sampler)
     if w.get("kind") == "train":
         return run_training_benchmark(w, steps, warmup, dist, sampler)
     if w.get("kind") == "slab":
@@ -147,11 +199,13 @@ def run_training_benchmark(w, steps, warmup, dist, sampler):
     dataset does at load time) and are resident."""
     rank = dist.get_rank() if dist is not None else 0
     world = dist.get_world_size() if dist is not None else 1
-    dtype = torch.float64
+    model = w["model"]
+    is_nep = model["kind"] == "nep"
+    dtype = torch.float32 if w.get("dtype") == "f32" else torch.float64
+    npdt = np.float32 if dtype == torch.float32 else np.float64
     dev = torch.device("cuda", torch.cuda.current_device())
     structs = w["structs"][rank::world]
-    model = w["model"]
-    prog = capi.MtpProgram(model["tables"])
+    prog = None if is_nep else capi.MtpProgram(model["tables"])
     md = capi.to_device({k: v for k, v in model.items() if k != "tables"}, dev, dtype)
     builder = capi.NeighborBuilder()
     npad = max(len(s_["types"]) for s_ in w["structs"])
@@ -163,7 +217,7 @@ def run_training_benchmark(w, steps, warmup, dist, sampler):
                ntypes=int(model["ntypes"]), nghost=0)
     for b, s_ in enumerate(structs):
         n = len(s_["types"])
-        nn, fn, rcs, st = builder.build(s_["cell"], torch.from_numpy(s_["coords"]).to(dev), w["rcut"], w["umax"])
+        nn, fn, rcs, st = builder.build(s_["cell"].astype(npdt), torch.from_numpy(s_["coords"].astype(npdt)).to(dev), w["rcut"], w["umax"])
         if int(st[1]):
             raise RuntimeError("umax too small for the training batch")
         nbt["binum"][b] = n
@@ -172,18 +226,27 @@ def run_training_benchmark(w, steps, warmup, dist, sampler):
         nbt["btypes"][b, :n] = torch.from_numpy(s_["types"]).to(dev)
     t = w["targets"]
     sel = slice(rank, None, world)
-    E = torch.from_numpy(t["E"][sel]).to(dev); F = torch.from_numpy(np.ascontiguousarray(t["F"][sel, :npad])).to(dev)
-    V = torch.from_numpy(np.ascontiguousarray(t["V"][sel])).to(dev)
+    E = torch.from_numpy(t["E"][sel]).to(dev, dtype); F = torch.from_numpy(np.ascontiguousarray(t["F"][sel, :npad])).to(dev, dtype)
+    V = torch.from_numpy(np.ascontiguousarray(t["V"][sel])).to(dev, dtype)
     natoms = int(nbt["binum"].sum())
     mean_nn = float(nbt["bnumneigh"].sum()) / natoms
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
-    grad = torch.zeros(md["coeffs"].numel() + prog.ns + int(model["ntypes"]) + 1, dtype=dtype, device=dev)
+    if is_nep:
+        ngrad = sum(md[k].numel() for k in ("coeffs", "w0", "b0", "w1")) + int(model["ntypes"]) + 1
+    else:
+        ngrad = md["coeffs"].numel() + prog.ns + int(model["ntypes"]) + 1
+    grad = torch.zeros(ngrad, dtype=dtype, device=dev)
 
     def step():
-        e, f, v = capi.mtp_efv(prog, md, nbt)
-        loss, rmse = capi.mtp_loss(nbt, w["weights"], e, E, f, F, v, V)
-        dco, dli, dbi = capi.mtp_loss_backward(prog, md, nbt, w["weights"], e, E, f, F, v, V)
-        torch.cat([dco.sum(0), dli.sum(0), dbi.sum(0), loss.sum(0, keepdim=True)], out=grad)
+        if is_nep:
+            e, f, v = capi.nep_efv(md, nbt)
+            loss, rmse = capi.nep_loss(nbt, w["weights"], e, E, f, F, v, V)
+            parts = capi.nep_loss_backward(md, nbt, w["weights"], e, E, f, F, v, V)
+        else:
+            e, f, v = capi.mtp_efv(prog, md, nbt)
+            loss, rmse = capi.mtp_loss(nbt, w["weights"], e, E, f, F, v, V)
+            parts = capi.mtp_loss_backward(prog, md, nbt, w["weights"], e, E, f, F, v, V)
+        torch.cat([p_.sum(0) for p_ in parts] + [loss.sum(0, keepdim=True)], out=grad)
         if dist is not None:
             dist.all_reduce(grad)
         return grad
@@ -198,14 +261,26 @@ def run_training_benchmark(w, steps, warmup, dist, sampler):
         hgrad.copy_(grad, non_blocking=True)
     t_e2e = _timed(e2e_step, steps, warmup, flush, barrier)
     props = torch.cuda.get_device_properties(torch.cuda.current_device())
-    peak = fma_peak_tflops(True, props.multi_processor_count)
-    fl = _mtp_flops(model, mean_nn, training=True)
+    peak = fma_peak_tflops(dtype == torch.float64, props.multi_processor_count)
+    if is_nep:
+        from bench import flops_nep
+        rc_all = nbt["brcs"]
+        nn_a = float(((torch.linalg.norm(rc_all, dim=-1) <= model["rmax_angular"]) &
+                      (torch.arange(rc_all.shape[2], device=dev)[None, None] < nbt["bnumneigh"][..., None])).sum()) / natoms
+        # forward + directional-derivative pass + coefficient-gradient pass: three sweeps of the descriptor work
+        fl = 3 * flops_nep(mean_nn, nn_a, model["chebyshev_size"], model["n_radial"], model["n_angular"], model["num_neurons"],
+                           model["n_radial"] + model["n_angular"] * model["l_max"])
+    else:
+        fl = _mtp_flops(model, mean_nn, training=True)
     achieved = natoms * fl / (t_dev / steps) / 1e12
-    roofline = {"kernel": "mtp E/F/V + loss-gradient kernels (whole step)", "bound": "fp64", "achieved": achieved, "peak": peak,
+    roofline = {"kernel": ("nep" if is_nep else "mtp") + " E/F/V + loss-gradient kernels (whole step)", "bound": "fp32" if dtype == torch.float32 else "fp64",
+                "achieved": achieved, "peak": peak,
                 "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": "FMA-chain microbenchmark in this run (of measured)",
                 "flops_per_atom": fl, "mean_neighbours": mean_nn, "traffic": None}
-    return dict(t_dev=t_dev, t_e2e=t_e2e, clocks=clocks, launches=(4 + 2 + 4) * steps, h2d=0, d2h=hgrad.numel() * 8, units=natoms,
-                e2e_path="resident neighbour tensors -> ai2b_mtp_efv -> ai2b_mtp_loss -> ai2b_mtp_loss_backward -> D2H summed gradient",
+    name = "nep" if is_nep else "mtp"
+    return dict(t_dev=t_dev, t_e2e=t_e2e, clocks=clocks, launches=((2 + 2 + 1) if is_nep else (4 + 2 + 4)) * steps, h2d=0,
+                d2h=hgrad.numel() * hgrad.element_size(), units=natoms,
+                e2e_path=f"resident neighbour tensors -> ai2b_{name}_efv -> ai2b_{name}_loss -> ai2b_{name}_loss_backward -> D2H summed gradient",
                 roofline=roofline, parts_ms=None)
 
 

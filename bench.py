@@ -101,6 +101,18 @@ def make_workload(name):
         w["label"] = "configs[3]: MTP level 16 training step, fp64, 64 structures of 64-256 atoms, E/F/V + loss + coefficient gradient"
         w["dtype"] = "f64"
         w["types"] = np.concatenate([s["types"] for s in w["structs"]])
+    elif name == "md":
+        w = synth.g2()
+        w["kind"] = "md"
+        w["label"] = "configs[2] system handed over as an MD host holds it (13,824 local atoms + periodic ghost images, double positions), NEP fp32: one force call"
+        w["dtype"] = "f32"
+    elif name == "nep_train":
+        w = synth.g3(load_tables(16))
+        w["kind"] = "train"
+        w["model"] = synth.nep_model(3, np.random.default_rng(1005), np.float32)
+        w["label"] = "configs[3] structures with an fp32 NEP model: training step, 64 structures of 64-256 atoms, E/F/V + loss + gradient w.r.t. coeffs, w0, b0, w1, bias"
+        w["dtype"] = "f32"
+        w["types"] = np.concatenate([s["types"] for s in w["structs"]])
     elif name.startswith("nep1m"):
         ncell = int(name.split(":")[1]) if ":" in name else 64
         w = synth.g4(ncell=ncell)
@@ -150,13 +162,21 @@ def cpu_reference_train(w, budget_s, threads):
     nb = synth.pad_batch(lists, w["model"]["ntypes"], w["umax"])
     t = w["targets"]
     npad = nb["bilist"].shape[1]
+    is_nep = w["model"]["kind"] == "nep"
+    if is_nep:
+        nb["brcs"] = nb["brcs"].astype(np.float32)
     times = []
     t_start = time.perf_counter()
     while len(times) < 3 and (time.perf_counter() - t_start < budget_s or not times):
         t0 = time.perf_counter()
-        e, f, v = chk.mtp_efv(w["model"], nb)
-        chk.mtp_loss(nb, w["weights"], e, t["E"], f, t["F"][:, :npad], v, t["V"])
-        chk.mtp_loss_backward(w["model"], nb, w["weights"], e, t["E"], f, t["F"][:, :npad], v, t["V"])
+        if is_nep:
+            e, f, v = chk.nep_efv(w["model"], nb)
+            chk.mtp_loss(nb, w["weights"], e, t["E"], f, t["F"][:, :npad], v, t["V"])
+            chk.nep_loss_backward(w["model"], nb, w["weights"], e, t["E"], f, t["F"][:, :npad], v, t["V"])
+        else:
+            e, f, v = chk.mtp_efv(w["model"], nb)
+            chk.mtp_loss(nb, w["weights"], e, t["E"], f, t["F"][:, :npad], v, t["V"])
+            chk.mtp_loss_backward(w["model"], nb, w["weights"], e, t["E"], f, t["F"][:, :npad], v, t["V"])
         times.append(time.perf_counter() - t0)
     return kind, 0.0, min(times), len(times)
 
@@ -177,7 +197,7 @@ def main():
     w = make_workload(args.workload)
     natoms = len(w["types"])
     metric = "atoms/sec for E+F+virial"
-    strong = w.get("kind") in ("train", "slab")           # a fixed batch / system divided over the ranks
+    strong = w.get("kind") in ("train", "slab")           # a fixed batch / system divided over the ranks (md: replicas)
     config = {"workload": w["label"], "atoms_per_gpu": natoms // world if strong else natoms,
               "l2": "256 MiB buffer written between timed steps"}
 
