@@ -55,7 +55,7 @@ def build_cuda(force=False, verbose=False):
             raise RuntimeError(f"nvcc failed on {src}")
     lib = os.path.join(LIBDIR, "libai2pot_b200.so")
     if force or procs or _stale(lib, objs):
-        subprocess.check_call([_nvcc(), "-shared", "-o", lib] + objs + ["-lcudart"])
+        subprocess.check_call([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", lib] + objs + ["-lcudart"])
     return lib
 
 
