@@ -47,6 +47,30 @@ def test_error_reporting_without_gpu():
     assert lib.ai2b_nep_workspace_bytes(C.c_int(4), C.c_int(3), C.c_int(4), C.c_int(4), C.c_int(8), C.c_int(0)) >= 9 * 8 * 8 * 4
 
 
+def test_argument_checks_return_codes_without_gpu():
+    """NULL pointers and bad sizes are refused before any CUDA call, with a message."""
+    lib = capi.lib()
+    null = C.c_void_p(None)
+    one = C.c_int(1)
+    rc = lib.ai2b_zbl_efv_f32(null, null, null, one, one, null, null, null, null, null, null, one, null, one, C.c_int(0),
+                              C.c_float(2.0), C.c_float(1.0), null, null, null)
+    assert rc == -1 and b"NULL" in lib.ai2b_last_error_string()
+    rc = lib.ai2b_md_session_compute(null, one, one, null, null, one, null, null, null, null)
+    assert rc == -1
+    rc = lib.ai2b_desc_maxmin_f64(null, null, one, one, one, null, null, null)
+    assert rc == -1
+    rc = lib.ai2b_target_stats_f32(null, null, one, one, null, null, null, null)
+    assert rc == -1
+    rc = lib.ai2b_nep_loss_backward_f64(null, null, null, null, null, C.c_double(1), C.c_double(1), C.c_double(1), null, null, null,
+                                        null, null, null, one, one, one, one, one, null, null, null, null, one, one, null, null, null,
+                                        null, null, null, one, one, C.c_int(0), C.c_double(6), C.c_double(4), null, null)
+    assert rc == -1 and b"NULL" in lib.ai2b_last_error_string()
+    ses = C.c_void_p()
+    rc = lib.ai2b_md_session_create_nep(C.byref(ses), one, one, one, one, one, one, null, null, null, null, null, null, C.c_float(6),
+                                        C.c_float(4), one)
+    assert rc == -1 and not ses.value
+
+
 @pytest.mark.skipif(not os.path.isdir(REF_TEMPLATES), reason="reference templates not mounted")
 @pytest.mark.parametrize("level", [6, 8, 10, 12, 14, 16, 18, 20, 24, 28])
 def test_almtp_parser_matches_reference(checkers, level):
