@@ -114,3 +114,44 @@ def test_ragged_batch(checkers):
     (e, f, v), *_ = _run(model, nb)
     er, fr, vr = chk.nep_efv(model, nb)
     assert util.relerr(e, er) < 1e-5 and util.relerr(f, fr) < 1e-5 and util.relerr(v, vr) < 1e-5
+
+
+def test_g4_full_size_properties():
+    """configs[4] at full size (1,048,576 atoms, fp32, umax 32) through size-independent properties: the full
+    list holds every pair from both ends (index and displacement sums cancel), no row overflows, net force
+    zero, symmetric virial, and the energy does not move under a rigid translation across the periodic faces."""
+    from ai2pot_b200 import engine
+    w = synth.g4()
+    n = len(w["types"])
+    dt = torch.float32
+    ev = engine.Evaluator(w["model"], w["cell"], w["types"], w["rcut"], w["umax"], dt)
+    coords = torch.from_numpy(np.ascontiguousarray(w["coords"])).to(dt).cuda()
+    nb = ev.build_list(coords)
+    st = ev.status.cpu().numpy()
+    assert st[1] == 0 and 16 <= st[0] <= 32
+    nn, fn, rc = nb["bnumneigh"][0], nb["bfirstneigh"][0], nb["brcs"][0]
+    mask = torch.arange(w["umax"], device="cuda")[None] < nn[:, None]
+    assert bool((fn[~mask] == -1).all())
+    # every pair is listed from both ends, except pairs whose fp32 distance sits on the cutoff (the reference's
+    # single-precision image arithmetic rounds r_j + L - r_i and r_i - L - r_j differently)
+    centre = torch.arange(n, device="cuda", dtype=torch.int64)[:, None].expand(-1, w["umax"])
+    i_, j_ = centre[mask], fn.to(torch.int64)[mask]
+    dist = torch.linalg.norm(rc[mask].double(), dim=-1)
+    key = torch.minimum(i_, j_) * n + torch.maximum(i_, j_)
+    key, order = torch.sort(key)
+    same_next = torch.zeros_like(key, dtype=torch.bool); same_next[:-1] = key[:-1] == key[1:]
+    same_prev = torch.zeros_like(key, dtype=torch.bool); same_prev[1:] = same_next[:-1]
+    single = ~(same_next | same_prev)
+    assert int(single.sum()) < 1e-5 * len(key)
+    assert bool((torch.abs(dist[order][single] - w["rcut"]) < 1e-4).all())
+    pair_sum = (rc.double() * mask[..., None]).sum((0, 1))
+    assert float(pair_sum.abs().max()) < 1e-6 * float(nn.sum())                        # r_ij + r_ji = 0 up to fp32 image rounding
+    e, f, v = [t.clone() for t in ev.evaluate(nb)]
+    fs = float(f.abs().max())
+    assert float(f[0].double().sum(0).abs().max()) < 1e-5 * fs * np.sqrt(n)
+    V = v.double().reshape(3, 3)
+    assert float((V - V.T).abs().max()) < 1e-5 * float(V.abs().max())
+    shift = torch.tensor([1.7, -2.3, 190.0], dtype=dt, device="cuda")                 # wraps about half the atoms in z
+    e2, f2, v2 = ev.compute(coords + shift)
+    assert abs(float(e2) - float(e)) < 2e-5 * abs(float(e))
+    assert float((f2 - f).abs().max()) < 1e-3 * fs                                     # fp32 positions at |x| ~ 400 A move rcs by ~3e-5 A
