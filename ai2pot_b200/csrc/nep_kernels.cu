@@ -496,6 +496,7 @@ __global__ void __launch_bounds__(NEP_WARPS * 32) nep_atom_kernel(const NepArgs<
 }  // namespace ai2b
 #include "nep_fast.cuh"
 #include "nep_loss.cuh"
+#include "nep_loss_fast.cuh"
 namespace ai2b {
 
 // ---------------------------------------------------------------------------------------------

@@ -263,6 +263,10 @@ __global__ void __launch_bounds__(NEPL_WARPS * 32) nep_loss_backward_kernel(cons
     for (int i = threadIdx.x; i < A.ntypes; i += blockDim.x) if (g_bi[i] != T(0)) atomicAdd(L.dbi + (size_t)b * A.ntypes + i, g_bi[i]);
 }
 
+// eight-lanes-per-atom kernel for small models (nep_loss_fast.cuh); *done = false: not applicable
+template <typename T, int NMAX>
+static int launch_nep_loss_fast(const NepArgs<T> &A, const T *coeffs, const NepLossArgs<T> &L, cudaStream_t st, bool *done);
+
 template <typename T>
 static int launch_nep_loss_backward(NepArgs<T> A, const T *coeffs, NepLossArgs<T> L, cudaStream_t st)
 {
@@ -288,6 +292,11 @@ static int launch_nep_loss_backward(NepArgs<T> A, const T *coeffs, NepLossArgs<T
                                      NEPL_WARPS * nepl_warp_elems(A.nd, A.nS, A.nneu, nfun, A.cs, A.ntypes)) + 16;
     AI2B_REQUIRE(smem <= 200 * 1024, AI2B_ERR_UNSUPPORTED, "NEP loss gradient: model needs %zu bytes of shared memory per block", smem);
     AI2B_REQUIRE(A.B <= 65535, AI2B_ERR_UNSUPPORTED, "NEP loss gradient: more than 65535 structures per call");
+    {
+        bool done = false;
+        const int rc = launch_nep_loss_fast<T, 4>(A, coeffs, L, st, &done);
+        if (rc != AI2B_OK || done) return rc;
+    }
     const bool vir = L.v_ml != nullptr;
     auto run = [&](auto kern) -> int {
         AI2B_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

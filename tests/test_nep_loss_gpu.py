@@ -13,9 +13,14 @@ def _chk(checkers):
     return checkers.get("ref") or checkers["oracle"]
 
 
-def _batch(chk, dt, seed=5):
+def _batch(chk, dt, seed=5, shape=None):
     ws = [util.small_nep_case(n=3, dtype=dt, seed=40, a=3.0), util.small_nep_case(n=4, dtype=dt, seed=41, a=2.8),
           util.small_nep_case(n=3, dtype=dt, seed=42, a=3.3)]
+    if shape is not None:   # same structures, another model shape
+        rng = np.random.default_rng(seed + 1)
+        ws[0]["model"] = synth.nep_model(3, rng, dt, **shape)
+        ws[0]["model"]["type_bias"] = rng.normal(0, 0.1, 3).astype(dt)
+        ws[0]["model"]["q_scaler"] = rng.uniform(0.5, 1.5, len(ws[0]["model"]["q_scaler"])).astype(dt)
     lists = []
     for w in ws:
         nn, fn, rc, ty, mx = chk.nblist(w["cell"], w["types"], w["coords"], 6.0, 200)
@@ -41,6 +46,26 @@ def test_nep_loss_backward(checkers, dt, tol, virial):
     nbd = capi.to_device(nb)
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
     got = capi.nep_loss_backward(md, nbd, wts, t(e), t(E), t(f), t(F), t(v) if virial else None, t(V) if virial else None)
+    for name, a, b in zip(("coeffs", "w0", "b0", "w1", "bias"), ref, got):
+        assert util.relerr(b.cpu().numpy(), a) < tol, name
+
+
+# model shapes around the specialised kernel's plan (at most 4 radial / angular functions, basis size <= 8):
+# narrower than the plan, and two that only the general kernel takes
+@pytest.mark.parametrize("shape", [dict(n_radial=3, n_angular=2, chebyshev_size=6, l_max=2, num_neurons=10),
+                                   dict(n_radial=4, n_angular=3, chebyshev_size=5, l_max=3, num_neurons=40),
+                                   dict(n_radial=6, n_angular=4, chebyshev_size=8, l_max=4, num_neurons=30),
+                                   dict(n_radial=4, n_angular=4, chebyshev_size=10, l_max=3, num_neurons=20)])
+@pytest.mark.parametrize("dt,tol", [(np.float64, 1e-10), (np.float32, 5e-5)])
+def test_nep_loss_backward_shapes(checkers, shape, dt, tol):
+    chk = _chk(checkers)
+    m, nb, (E, F, V) = _batch(chk, dt, shape=shape)
+    e, f, v = chk.nep_efv(m, nb)
+    wts = (1.0, 2.0, 0.5)
+    ref = chk.nep_loss_backward(m, nb, wts, e, E, f, F, v, V)
+    md = capi.to_device(m, "cuda", torch.float64 if dt == np.float64 else torch.float32)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    got = capi.nep_loss_backward(md, capi.to_device(nb), wts, t(e), t(E), t(f), t(F), t(v), t(V))
     for name, a, b in zip(("coeffs", "w0", "b0", "w1", "bias"), ref, got):
         assert util.relerr(b.cpu().numpy(), a) < tol, name
 
