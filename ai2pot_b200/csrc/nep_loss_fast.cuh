@@ -8,8 +8,12 @@
 //   2  angular sums S and DS as a staged matrix product (lane s owns lm = 3s..3s+2)
 //   3  descriptors, network with the second-order terms (four neurons per lane, weights in shared
 //      memory), adjoints of q and u, polynomial coefficients x, y per (lm, mu)
-//   4  gradient: radial part from the per-type sums, angular part per compacted neighbour
-// Gradients accumulate per block in shared memory; one structure per blockIdx.y.
+//   4  angular part of the coefficient gradient per compacted neighbour, summed per neighbour type
+// Every atom leaves a small record in shared memory (scaled q and u, the neuron factors, the
+// per-type sums); after each round of sixteen atoms the whole block adds the records into its
+// gradient accumulators, every accumulator element owned by one thread: the first-layer gradient
+// and the radial coefficient gradient are outer products of two record vectors, so no atomics
+// are needed. One structure per blockIdx.y; the block accumulators reach global memory once.
 #pragma once
 
 namespace ai2b {
@@ -32,9 +36,9 @@ __host__ __device__ inline int nepl_fast_atom_elems(int nneu, int ntypes)
 {
     const int NDP = NepFastDims<NMAX>::NDP;
     const int NP = nep_r32(nneu);
-    const int sea = 4 * NEP_NLM * NMAX + 2 * NP;                 // S, DS, xc, yc, th, sp ...
+    const int sea = 2 * NEP_NLM * NMAX + 2 * NP;                 // xc, yc, th, sp ...
     const int stage = NEP_GROUP * NepLossFastDims<NMAX>::RS;      // ... share their space with the staging rows
-    return 4 * NDP + (sea > stage ? sea : stage) + nep_r4(2 * ntypes * 8);
+    return 4 * NDP + (sea > stage ? sea : stage) + nep_r4(2 * ntypes * 8) + ntypes * NMAX * 8 + 2 * NP;
 }
 
 template <typename T, bool VIRIAL, int NMAX, int MINB>
@@ -49,6 +53,7 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_loss_fast_kernel(con
     __shared__ T iqs[NDP];
     __shared__ T c3w_s[NEP_NLM];
     __shared__ unsigned char pm_mu[NDP], pm_l[NDP];
+    __shared__ unsigned tmask[2][16];   // per round parity and type: the block's atom slots of that type
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int sub = lane & (NEP_GROUP - 1), grp = lane / NEP_GROUP;
     const int slot_in_block = warp * NEP_APW + grp;
@@ -78,8 +83,12 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_loss_fast_kernel(con
     T *yc = xc + NEP_NLM * NMAX;                         // [24][NMAX]
     T *th = yc + NEP_NLM * NMAX;                         // [NP] W1 d1     (placed after x, y; S / DS themselves stay in registers)
     T *sp = th + NP;                                     // [NP] W1 s d2
-    const int sea = 4 * NEP_NLM * NMAX + 2 * NP, stg = NEP_GROUP * RS;
+    const int sea = 2 * NEP_NLM * NMAX + 2 * NP, stg = NEP_GROUP * RS;
     T *Fs = S + (sea > stg ? sea : stg);                 // [ntypes][8] sum f_xi, then [ntypes][8] sum f'_xi (r^.p)
+    T *Ga = Fs + nep_r4(2 * A.ntypes * 8);               // [ntypes][NMAX][8] angular coefficient gradient of this atom
+    T *gb0s = Ga + A.ntypes * NMAX * 8;                  // [NP] d/d b0 of this atom
+    T *gw1s = gb0s + NP;                                 // [NP] d/d w1
+    const int off_th = (int)(th - q), off_fs = (int)(Fs - q), off_ga = (int)(Ga - q), off_gb0 = (int)(gb0s - q), off_gw1 = (int)(gw1s - q);
     unsigned short *alist = reinterpret_cast<unsigned short *>(atoms_s + (size_t)NEP_APB * per_atom) + (size_t)slot_in_block * A.umax;
     const int ntot_n = nfun;
 
@@ -123,6 +132,7 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_loss_fast_kernel(con
         pm_mu[p] = (unsigned char)(in ? p / A.l_max : 0);
         pm_l[p] = (unsigned char)(in ? p % A.l_max + 1 : 0);
     }
+    if (threadIdx.x < 32) tmask[threadIdx.x >> 4][threadIdx.x & 15] = 0u;
     for (int i = threadIdx.x; i < NEP_APB * 4 * NDP; i += blockDim.x) atoms_s[(size_t)(i / (4 * NDP)) * per_atom + i % (4 * NDP)] = T(0);
     __syncthreads();
 
@@ -139,277 +149,265 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_loss_fast_kernel(con
     for (int it = 0; it < rounds; it++) {
         const int ii = it * ngroups + blockIdx.x * NEP_APB + slot_in_block;
         const bool valid = ii < n;
-        if (!valid) continue;   // whole groups leave together; the loop has no wider barrier
-        const size_t slot = (size_t)b * A.npad + ii;
-        const int ci = valid ? A.bilist[slot] : 0;
-        const int nn = valid ? min(A.numneigh[slot], A.umax) : 0;
-        const int ti = valid ? types[ci] : 0;
-        const int *fn = A.firstneigh + slot * A.umax;
-        const T *rc = A.rcs + slot * A.umax * 3;
-        const T *ctab = ctab_s + (size_t)ti * A.ntypes * TROW;
-        const T Pi0 = cf * (fm[3 * ci] - fd[3 * ci]), Pi1 = cf * (fm[3 * ci + 1] - fd[3 * ci + 1]), Pi2 = cf * (fm[3 * ci + 2] - fd[3 * ci + 2]);
-        // pair weight p = P_i - P_j - Qm r, its radial part vp = r^ . p and perpendicular part over r
-        auto pair_weight = [&](int nj, T x, T y, T z, T rinv, T &vp, T &px, T &py, T &pz) {
-            const T p0 = Pi0 - cf * (fm[3 * nj] - fd[3 * nj]) - cv * (dV[0] * x + dV[1] * y + dV[2] * z);
-            const T p1 = Pi1 - cf * (fm[3 * nj + 1] - fd[3 * nj + 1]) - cv * (dV[3] * x + dV[4] * y + dV[5] * z);
-            const T p2 = Pi2 - cf * (fm[3 * nj + 2] - fd[3 * nj + 2]) - cv * (dV[6] * x + dV[7] * y + dV[8] * z);
-            const T ux = x * rinv, uy = y * rinv, uz = z * rinv;
-            vp = ux * p0 + uy * p1 + uz * p2;
-            px = (p0 - vp * ux) * rinv; py = (p1 - vp * uy) * rinv; pz = (p2 - vp * uz) * rinv;
-        };
-        for (int i = sub; i < 2 * A.ntypes * 8; i += NEP_GROUP) Fs[i] = T(0);
-        __syncwarp(gmask);
+        if (valid) {
+            const size_t slot = (size_t)b * A.npad + ii;
+            const int ci = A.bilist[slot];
+            const int nn = min(A.numneigh[slot], A.umax);
+            const int ti = types[ci];
+            const int *fn = A.firstneigh + slot * A.umax;
+            const T *rc = A.rcs + slot * A.umax * 3;
+            const T *ctab = ctab_s + (size_t)ti * A.ntypes * TROW;
+            const T Pi0 = cf * (fm[3 * ci] - fd[3 * ci]), Pi1 = cf * (fm[3 * ci + 1] - fd[3 * ci + 1]), Pi2 = cf * (fm[3 * ci + 2] - fd[3 * ci + 2]);
+            // pair weight p = P_i - P_j - Qm r, its radial part vp = r^ . p and perpendicular part over r
+            auto pair_weight = [&](int nj, T x, T y, T z, T rinv, T &vp, T &px, T &py, T &pz) {
+                const T p0 = Pi0 - cf * (fm[3 * nj] - fd[3 * nj]) - cv * (dV[0] * x + dV[1] * y + dV[2] * z);
+                const T p1 = Pi1 - cf * (fm[3 * nj + 1] - fd[3 * nj + 1]) - cv * (dV[3] * x + dV[4] * y + dV[5] * z);
+                const T p2 = Pi2 - cf * (fm[3 * nj + 2] - fd[3 * nj + 2]) - cv * (dV[6] * x + dV[7] * y + dV[8] * z);
+                const T ux = x * rinv, uy = y * rinv, uz = z * rinv;
+                vp = ux * p0 + uy * p1 + uz * p2;
+                px = (p0 - vp * ux) * rinv; py = (p1 - vp * uy) * rinv; pz = (p2 - vp * uz) * rinv;
+            };
+            for (int i = sub; i < 2 * A.ntypes * 8; i += NEP_GROUP) Fs[i] = T(0);
+            for (int i = sub; i < A.ntypes * NMAX * 8; i += NEP_GROUP) Ga[i] = T(0);
+            if (sub == 0) atomicOr(&tmask[it & 1][ti], 1u << slot_in_block);
+            __syncwarp(gmask);
 
-        // ---- 1. radial pass --------------------------------------------------------------------------
-        T qacc[NMAX], uacc[NMAX];
+            // ---- 1. radial pass --------------------------------------------------------------------------
+            T qacc[NMAX], uacc[NMAX];
 #pragma unroll
-        for (int k = 0; k < NMAX; k++) qacc[k] = uacc[k] = T(0);
-        int nang = 0;
-        for (int j0 = 0; j0 < nn; j0 += NEP_GROUP) {
-            const int j = j0 + sub;
-            bool on = j < nn;
-            T x = 0, y = 0, z = 0;
-            int nj = 0;
-            if (on) { x = rc[3 * j]; y = rc[3 * j + 1]; z = rc[3 * j + 2]; nj = fn[j]; }
-            const T r = gsqrt(x * x + y * y + z * z);
-            on = on && r <= A.rc_r && r > T(0);
-            const int tj = on ? types[nj] : 0;
-            const T rinv = on ? T(1) / r : T(0);
-            T vp, px, py, pz;
-            pair_weight(nj, x, y, z, rinv, vp, px, py, pz);
-            T f[CSP], df[CSP];
-            nep_radial<T, CSP>(on ? r : A.rc_r, A.rc_r, f, df);
-            const T *crow = ctab + (size_t)tj * TROW;
-#pragma unroll
-            for (int k = 0; k < NMAX; k++) {
-                T c[CSP];
-                load_vec<T, CSP>(crow + k * CSP, c);
-                T g = T(0), dg = T(0);
-#pragma unroll
-                for (int xi = 0; xi < CSP; xi++) { g = fma(c[xi], f[xi], g); dg = fma(c[xi], df[xi], dg); }
-                if (on) { qacc[k] += g; uacc[k] += dg * vp; }
-            }
-            // per-type sums of f_xi and f'_xi (r^.p): lane xi of the group ends up with entry xi
-            for (int t = 0; t < A.ntypes; t++) {
-                const bool mine = on && tj == t;
-                if (__ballot_sync(gmask, mine) & gmask) {
-                    T v[CSP], w[CSP];
-#pragma unroll
-                    for (int xi = 0; xi < CSP; xi++) { v[xi] = mine ? f[xi] : T(0); w[xi] = mine ? df[xi] * vp : T(0); }
-                    Fs[t * 8 + sub] += group_xreduce8(v, sub, gmask);
-                    Fs[(A.ntypes + t) * 8 + sub] += group_xreduce8(w, sub, gmask);
-                }
-            }
-            const bool ang = on && r <= A.rc_a && A.l_max > 0;
-            const unsigned bal = (__ballot_sync(gmask, ang) >> gmask_shift) & 0xffu;
-            if (ang) alist[nang + __popc(bal & ((1u << sub) - 1u))] = (unsigned short)(j | (tj << 10));
-            nang += __popc(bal);
-        }
-#pragma unroll
-        for (int k = 0; k < NMAX; k++) {
-            const T sq = group_sum(qacc[k], gmask), su = group_sum(uacc[k], gmask);
-            if (sub == (k & (NEP_GROUP - 1)) && k < A.n_r) { q[k] = sq; u[k] = su; }
-        }
-        __syncwarp(gmask);
-
-        // ---- 2. angular sums and their directional derivatives: lane owns lm = 3 sub .. 3 sub + 2 ----------
-        T Sacc[NMAX][3], Dacc[NMAX][3];
-#pragma unroll
-        for (int mu = 0; mu < NMAX; mu++)
-#pragma unroll
-            for (int i = 0; i < 3; i++) Sacc[mu][i] = Dacc[mu][i] = T(0);
-        for (int k0 = 0; k0 < nang; k0 += NEP_GROUP) {
-            const bool on = k0 + sub < nang;
-            {
-                T x = 0, y = 0, z = 0, rinv = 0, r = A.rc_a;
-                int tj = 0, nj = 0;
-                if (on) {
-                    const int ent = alist[k0 + sub], j = ent & 1023;
-                    tj = ent >> 10;
-                    x = rc[3 * j]; y = rc[3 * j + 1]; z = rc[3 * j + 2]; nj = fn[j];
-                    r = gsqrt(x * x + y * y + z * z);
-                    rinv = T(1) / r;
-                }
+            for (int k = 0; k < NMAX; k++) qacc[k] = uacc[k] = T(0);
+            int nang = 0;
+            for (int j0 = 0; j0 < nn; j0 += NEP_GROUP) {
+                const int j = j0 + sub;
+                bool on = j < nn;
+                T x = 0, y = 0, z = 0;
+                int nj = 0;
+                if (on) { x = rc[3 * j]; y = rc[3 * j + 1]; z = rc[3 * j + 2]; nj = fn[j]; }
+                const T r = gsqrt(x * x + y * y + z * z);
+                on = on && r <= A.rc_r && r > T(0);
+                const int tj = on ? types[nj] : 0;
+                const T rinv = on ? T(1) / r : T(0);
                 T vp, px, py, pz;
                 pair_weight(nj, x, y, z, rinv, vp, px, py, pz);
-                T f[CSP], df[CSP], row[RS];
-                nep_radial<T, CSP>(r, A.rc_a, f, df);
-                const T *crow = ctab + (size_t)tj * TROW + NMAX * CSP;
+                T f[CSP], df[CSP];
+                nep_radial<T, CSP>(on ? r : A.rc_r, A.rc_r, f, df);
+                const T *crow = ctab + (size_t)tj * TROW;
 #pragma unroll
-                for (int mu = 0; mu < NMAX; mu++) {
+                for (int k = 0; k < NMAX; k++) {
                     T c[CSP];
-                    load_vec<T, CSP>(crow + mu * CSP, c);
+                    load_vec<T, CSP>(crow + k * CSP, c);
                     T g = T(0), dg = T(0);
 #pragma unroll
                     for (int xi = 0; xi < CSP; xi++) { g = fma(c[xi], f[xi], g); dg = fma(c[xi], df[xi], dg); }
-                    row[mu] = on ? g : T(0);
-                    row[NMAX + mu] = on ? dg * vp : T(0);
+                    if (on) { qacc[k] += g; uacc[k] += dg * vp; }
                 }
-                {
-                    const T x_ = x * rinv, y_ = y * rinv, z_ = z * rinv;
-                    NEP_POLY_COMMON(x_, y_, z_)
-#define NEP_X(k, val, gx, gy, gz)                                                               \
-    row[2 * NMAX + k] = (val);                                                                  \
-    row[2 * NMAX + NEP_NLM + k] = nep_dot3<T>(gx, gy, gz, px, py, pz);
-                    NEP_FOR_EACH_LM(NEP_X, x_, y_, z_)
-#undef NEP_X
-                }
-                store_vec<T, RS>(stage + sub * RS, row);
-            }
-            __syncwarp(gmask);
-            const int cnt = min(NEP_GROUP, nang - k0);
-            for (int jj = 0; jj < cnt; jj++) {
-                const T *rj = stage + jj * RS;
-                T gj[NMAX], gv[NMAX];
-                load_vec<T, NMAX>(rj, gj);
-                load_vec<T, NMAX>(rj + NMAX, gv);
+                // per-type sums of f_xi and f'_xi (r^.p): lane xi of the group ends up with entry xi
+                for (int t = 0; t < A.ntypes; t++) {
+                    const bool mine = on && tj == t;
+                    if (__ballot_sync(gmask, mine) & gmask) {
+                        T v[CSP], w[CSP];
 #pragma unroll
-                for (int i = 0; i < 3; i++) {
-                    const T bv = rj[2 * NMAX + 3 * sub + i], gp = rj[2 * NMAX + NEP_NLM + 3 * sub + i];
-#pragma unroll
-                    for (int mu = 0; mu < NMAX; mu++) {
-                        Sacc[mu][i] = fma(gj[mu], bv, Sacc[mu][i]);
-                        Dacc[mu][i] = fma(gv[mu], bv, fma(gj[mu], gp, Dacc[mu][i]));
+                        for (int xi = 0; xi < CSP; xi++) { v[xi] = mine ? f[xi] : T(0); w[xi] = mine ? df[xi] * vp : T(0); }
+                        Fs[t * 8 + sub] += group_xreduce8(v, sub, gmask);
+                        Fs[(A.ntypes + t) * 8 + sub] += group_xreduce8(w, sub, gmask);
                     }
                 }
+                const bool ang = on && r <= A.rc_a && A.l_max > 0;
+                const unsigned bal = (__ballot_sync(gmask, ang) >> gmask_shift) & 0xffu;
+                if (ang) alist[nang + __popc(bal & ((1u << sub) - 1u))] = (unsigned short)(j | (tj << 10));
+                nang += __popc(bal);
+            }
+#pragma unroll
+            for (int k = 0; k < NMAX; k++) {
+                const T sq = group_sum(qacc[k], gmask), su = group_sum(uacc[k], gmask);
+                if (sub == (k & (NEP_GROUP - 1)) && k < A.n_r) { q[k] = sq; u[k] = su; }
             }
             __syncwarp(gmask);
-        }
-        // descriptors q_{mu,l} and u_{mu,l}: partial sums over this lane's lm, combined per (mu, l) through shared memory
-        // (the staging rows are free now): tq[mu][lm], tu[mu][lm]
-        {
-            T *tq = stage, *tu = stage + NMAX * NEP_NLM;
+
+            // ---- 2. angular sums and their directional derivatives: lane owns lm = 3 sub .. 3 sub + 2 ----------
+            T Sacc[NMAX][3], Dacc[NMAX][3];
 #pragma unroll
             for (int mu = 0; mu < NMAX; mu++)
 #pragma unroll
-                for (int i = 0; i < 3; i++) {
-                    const int lm = 3 * sub + i;
-                    tq[mu * NEP_NLM + lm] = c3w_s[lm] * Sacc[mu][i] * Sacc[mu][i];
-                    tu[mu * NEP_NLM + lm] = T(2) * c3w_s[lm] * Sacc[mu][i] * Dacc[mu][i];
+                for (int i = 0; i < 3; i++) Sacc[mu][i] = Dacc[mu][i] = T(0);
+            for (int k0 = 0; k0 < nang; k0 += NEP_GROUP) {
+                const bool on = k0 + sub < nang;
+                {
+                    T x = 0, y = 0, z = 0, rinv = 0, r = A.rc_a;
+                    int tj = 0, nj = 0;
+                    if (on) {
+                        const int ent = alist[k0 + sub], j = ent & 1023;
+                        tj = ent >> 10;
+                        x = rc[3 * j]; y = rc[3 * j + 1]; z = rc[3 * j + 2]; nj = fn[j];
+                        r = gsqrt(x * x + y * y + z * z);
+                        rinv = T(1) / r;
+                    }
+                    T vp, px, py, pz;
+                    pair_weight(nj, x, y, z, rinv, vp, px, py, pz);
+                    T f[CSP], df[CSP], row[RS];
+                    nep_radial<T, CSP>(r, A.rc_a, f, df);
+                    const T *crow = ctab + (size_t)tj * TROW + NMAX * CSP;
+#pragma unroll
+                    for (int mu = 0; mu < NMAX; mu++) {
+                        T c[CSP];
+                        load_vec<T, CSP>(crow + mu * CSP, c);
+                        T g = T(0), dg = T(0);
+#pragma unroll
+                        for (int xi = 0; xi < CSP; xi++) { g = fma(c[xi], f[xi], g); dg = fma(c[xi], df[xi], dg); }
+                        row[mu] = on ? g : T(0);
+                        row[NMAX + mu] = on ? dg * vp : T(0);
+                    }
+                    {
+                        const T x_ = x * rinv, y_ = y * rinv, z_ = z * rinv;
+                        NEP_POLY_COMMON(x_, y_, z_)
+#define NEP_X(k, val, gx, gy, gz)                                                               \
+    row[2 * NMAX + k] = (val);                                                                  \
+    row[2 * NMAX + NEP_NLM + k] = nep_dot3<T>(gx, gy, gz, px, py, pz);
+                        NEP_FOR_EACH_LM(NEP_X, x_, y_, z_)
+#undef NEP_X
+                    }
+                    store_vec<T, RS>(stage + sub * RS, row);
                 }
-            __syncwarp(gmask);
-            for (int p = sub; p < nq_a; p += NEP_GROUP) {
-                const int mu = pm_mu[p], l = pm_l[p];
-                T aq = T(0), au = T(0);
-                for (int mp = 0; mp < 2 * l + 1; mp++) { aq += tq[mu * NEP_NLM + l * l - 1 + mp]; au += tu[mu * NEP_NLM + l * l - 1 + mp]; }
-                q[A.n_r + p] = aq; u[A.n_r + p] = au;
-            }
-            __syncwarp(gmask);
-        }
-
-        // ---- 3. network with second-order terms --------------------------------------------------------------
-        // scaled copies for the matrix-vector products (q~ = q / qs, u~ = u / qs) go to av / be temporarily
-        for (int k = sub; k < nd; k += NEP_GROUP) { av[k] = q[k] * iqs[k]; be[k] = u[k] * iqs[k]; }
-        __syncwarp(gmask);
-        const T *W0t = W0s + (size_t)ti * NP * NDP;
-        for (int p0 = 0; p0 < NP; p0 += 4 * NEP_GROUP) {
-            T h[4], sv[4];
+                __syncwarp(gmask);
+                const int cnt = min(NEP_GROUP, nang - k0);
+                for (int jj = 0; jj < cnt; jj++) {
+                    const T *rj = stage + jj * RS;
+                    T gj[NMAX], gv[NMAX];
+                    load_vec<T, NMAX>(rj, gj);
+                    load_vec<T, NMAX>(rj + NMAX, gv);
 #pragma unroll
-            for (int i = 0; i < 4; i++) h[i] = sv[i] = T(0);
+                    for (int i = 0; i < 3; i++) {
+                        const T bv = rj[2 * NMAX + 3 * sub + i], gp = rj[2 * NMAX + NEP_NLM + 3 * sub + i];
 #pragma unroll
-            for (int c = 0; c < NDP / 4; c++) {
-                T eq[4], eu[4];
-                load_vec<T, 4>(av + 4 * c, eq);
-                load_vec<T, 4>(be + 4 * c, eu);
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    T w[4];
-                    load_vec<T, 4>(W0t + (size_t)(p0 + sub + NEP_GROUP * i) * NDP + 4 * c, w);
-#pragma unroll
-                    for (int k = 0; k < 4; k++) { h[i] = fma(w[k], eq[k], h[i]); sv[i] = fma(w[k], eu[k], sv[i]); }
+                        for (int mu = 0; mu < NMAX; mu++) {
+                            Sacc[mu][i] = fma(gj[mu], bv, Sacc[mu][i]);
+                            Dacc[mu][i] = fma(gv[mu], bv, fma(gj[mu], gp, Dacc[mu][i]));
+                        }
+                    }
                 }
+                __syncwarp(gmask);
             }
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int pn = p0 + sub + NEP_GROUP * i;
-                const T w1 = W1s[ti * NP + pn];
-                const T t = gtanh(h[i] + B0s[ti * NP + pn]), d1 = T(1) - t * t, d2 = T(-2) * t * d1;
-                th[pn] = w1 * d1;
-                sp[pn] = w1 * sv[i] * d2;
-                if (valid && pn < nneu) {
-                    const T gb0 = lam * w1 * d1 + w1 * sv[i] * d2;
-                    atomicAdd(g_w1 + ti * nneu + pn, lam * t + d1 * sv[i]);
-                    atomicAdd(g_b0 + ti * nneu + pn, gb0);
-                    T *gw = g_w0 + ((size_t)ti * nneu + pn) * nd;
-                    for (int k = 0; k < nd; k++) atomicAdd(gw + k, gb0 * av[k] + w1 * d1 * be[k]);
-                }
-            }
-        }
-        if (valid && sub == 0) atomicAdd(g_bi + ti, lam);
-        __syncwarp(gmask);
-        // adjoints: av = dE/dq, be = coefficient of dq/dc  (overwrite the scaled copies)
-        for (int c = sub; c < NDP / 4; c += NEP_GROUP) {
-            const T *wcol = W0t + 4 * c;
-            T a0[4] = {T(0), T(0), T(0), T(0)}, b0v[4] = {T(0), T(0), T(0), T(0)};
-            for (int pn = 0; pn < NP; pn += 4) {
-                T xt[4], xs[4];
-                load_vec<T, 4>(th + pn, xt);
-                load_vec<T, 4>(sp + pn, xs);
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    T w[4];
-                    load_vec<T, 4>(wcol + (size_t)(pn + i) * NDP, w);
-#pragma unroll
-                    for (int k = 0; k < 4; k++) { a0[k] = fma(xt[i], w[k], a0[k]); b0v[k] = fma(xs[i], w[k], b0v[k]); }
-                }
-            }
-            T ra[4], rb[4];
-#pragma unroll
-            for (int k = 0; k < 4; k++) { ra[k] = a0[k] * iqs[4 * c + k]; rb[k] = lam * ra[k] + b0v[k] * iqs[4 * c + k]; }
-            store_vec<T, 4>(av + 4 * c, ra);
-            store_vec<T, 4>(be + 4 * c, rb);
-        }
-        __syncwarp(gmask);
-        // polynomial coefficients per (lm, mu): x = w2c (be S + av DS), y = w2c av S
-#pragma unroll
-        for (int i = 0; i < 3; i++) {
-            const int lm = 3 * sub + i;
-            const int l = lm >= 15 ? 4 : lm >= 8 ? 3 : lm >= 3 ? 2 : 1;
-            const T w2c = T(2) * c3w_s[lm];
-            T xr[NMAX], yr[NMAX];
-#pragma unroll
-            for (int mu = 0; mu < NMAX; mu++) {
-                const bool in = lm < nlm && mu < A.n_a;
-                const int k = A.n_r + mu * A.l_max + l - 1;
-                const T ak = in ? av[k] : T(0), bk = in ? be[k] : T(0);
-                xr[mu] = w2c * (bk * Sacc[mu][i] + ak * Dacc[mu][i]);
-                yr[mu] = w2c * ak * Sacc[mu][i];
-            }
-            store_vec<T, NMAX>(xc + lm * NMAX, xr);
-            store_vec<T, NMAX>(yc + lm * NMAX, yr);
-        }
-        __syncwarp(gmask);
-
-        // ---- 4. coefficient gradient ----------------------------------------------------------------------------
-        if (valid) {
-            // radial functions: dL/dc[ti,tj,n,xi] += be_n sum_j f_xi + av_n sum_j f'_xi (r^.p), sums per neighbour type
-            for (int i = sub; i < A.ntypes * A.n_r * A.cs; i += NEP_GROUP) {
-                const int xi = i % A.cs, nidx = (i / A.cs) % A.n_r, tj = i / (A.cs * A.n_r);
-                const T v = be[nidx] * Fs[tj * 8 + xi] + av[nidx] * Fs[(A.ntypes + tj) * 8 + xi];
-                if (v != T(0)) atomicAdd(g_co + (((size_t)ti * A.ntypes + tj) * nfun + nidx) * A.cs + xi, v);
-            }
-        }
-        for (int k0 = 0; k0 < nang; k0 += NEP_GROUP) {
-            const bool on = k0 + sub < nang;
-            int tj = 0;
-            T vp = T(0), f[CSP], df[CSP];
-            T X[NMAX], Y[NMAX], GY[NMAX];
-#pragma unroll
-            for (int mu = 0; mu < NMAX; mu++) X[mu] = Y[mu] = GY[mu] = T(0);
+            // descriptors q_{mu,l} and u_{mu,l}: partial sums over this lane's lm, combined per (mu, l) through shared memory
+            // (the staging rows are free now): tq[mu][lm], tu[mu][lm]
             {
-                T x = 0, y = 0, z = 0, rinv = 0, r = A.rc_a;
-                int nj = 0;
-                if (on) {
-                    const int ent = alist[k0 + sub], j = ent & 1023;
-                    tj = ent >> 10;
-                    x = rc[3 * j]; y = rc[3 * j + 1]; z = rc[3 * j + 2]; nj = fn[j];
-                    r = gsqrt(x * x + y * y + z * z);
-                    rinv = T(1) / r;
+                T *tq = stage, *tu = stage + NMAX * NEP_NLM;
+#pragma unroll
+                for (int mu = 0; mu < NMAX; mu++)
+#pragma unroll
+                    for (int i = 0; i < 3; i++) {
+                        const int lm = 3 * sub + i;
+                        tq[mu * NEP_NLM + lm] = c3w_s[lm] * Sacc[mu][i] * Sacc[mu][i];
+                        tu[mu * NEP_NLM + lm] = T(2) * c3w_s[lm] * Sacc[mu][i] * Dacc[mu][i];
+                    }
+                __syncwarp(gmask);
+                for (int p = sub; p < nq_a; p += NEP_GROUP) {
+                    const int mu = pm_mu[p], l = pm_l[p];
+                    T aq = T(0), au = T(0);
+                    for (int mp = 0; mp < 2 * l + 1; mp++) { aq += tq[mu * NEP_NLM + l * l - 1 + mp]; au += tu[mu * NEP_NLM + l * l - 1 + mp]; }
+                    q[A.n_r + p] = aq; u[A.n_r + p] = au;
                 }
-                T px, py, pz;
-                pair_weight(nj, x, y, z, rinv, vp, px, py, pz);
-                const T x_ = x * rinv, y_ = y * rinv, z_ = z * rinv;
-                NEP_POLY_COMMON(x_, y_, z_)
+                __syncwarp(gmask);
+            }
+
+            // ---- 3. network with second-order terms --------------------------------------------------------------
+            // q, u become q / qs, u / qs (what the first layer sees and what its weight gradient needs)
+            for (int k = sub; k < nd; k += NEP_GROUP) { q[k] *= iqs[k]; u[k] *= iqs[k]; }
+            __syncwarp(gmask);
+            const T *W0t = W0s + (size_t)ti * NP * NDP;
+            for (int p0 = 0; p0 < NP; p0 += 4 * NEP_GROUP) {
+                T h[4], sv[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) h[i] = sv[i] = T(0);
+#pragma unroll
+                for (int c = 0; c < NDP / 4; c++) {
+                    T eq[4], eu[4];
+                    load_vec<T, 4>(q + 4 * c, eq);
+                    load_vec<T, 4>(u + 4 * c, eu);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        T w[4];
+                        load_vec<T, 4>(W0t + (size_t)(p0 + sub + NEP_GROUP * i) * NDP + 4 * c, w);
+#pragma unroll
+                        for (int k = 0; k < 4; k++) { h[i] = fma(w[k], eq[k], h[i]); sv[i] = fma(w[k], eu[k], sv[i]); }
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int pn = p0 + sub + NEP_GROUP * i;
+                    const T w1 = W1s[ti * NP + pn];
+                    const T t = gtanh(h[i] + B0s[ti * NP + pn]), d1 = T(1) - t * t, d2 = T(-2) * t * d1;
+                    th[pn] = w1 * d1;                                  // zero for the padding neurons (w1 = 0)
+                    sp[pn] = w1 * sv[i] * d2;
+                    gb0s[pn] = lam * w1 * d1 + w1 * sv[i] * d2;
+                    gw1s[pn] = lam * t + d1 * sv[i];
+                }
+            }
+            __syncwarp(gmask);
+            // adjoints: av = dE/dq, be = coefficient of dq/dc  (overwrite the scaled copies)
+            for (int c = sub; c < NDP / 4; c += NEP_GROUP) {
+                const T *wcol = W0t + 4 * c;
+                T a0[4] = {T(0), T(0), T(0), T(0)}, b0v[4] = {T(0), T(0), T(0), T(0)};
+                for (int pn = 0; pn < NP; pn += 4) {
+                    T xt[4], xs[4];
+                    load_vec<T, 4>(th + pn, xt);
+                    load_vec<T, 4>(sp + pn, xs);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        T w[4];
+                        load_vec<T, 4>(wcol + (size_t)(pn + i) * NDP, w);
+#pragma unroll
+                        for (int k = 0; k < 4; k++) { a0[k] = fma(xt[i], w[k], a0[k]); b0v[k] = fma(xs[i], w[k], b0v[k]); }
+                    }
+                }
+                T ra[4], rb[4];
+#pragma unroll
+                for (int k = 0; k < 4; k++) { ra[k] = a0[k] * iqs[4 * c + k]; rb[k] = lam * ra[k] + b0v[k] * iqs[4 * c + k]; }
+                store_vec<T, 4>(av + 4 * c, ra);
+                store_vec<T, 4>(be + 4 * c, rb);
+            }
+            __syncwarp(gmask);
+            // polynomial coefficients per (lm, mu): x = w2c (be S + av DS), y = w2c av S
+#pragma unroll
+            for (int i = 0; i < 3; i++) {
+                const int lm = 3 * sub + i;
+                const int l = lm >= 15 ? 4 : lm >= 8 ? 3 : lm >= 3 ? 2 : 1;
+                const T w2c = T(2) * c3w_s[lm];
+                T xr[NMAX], yr[NMAX];
+#pragma unroll
+                for (int mu = 0; mu < NMAX; mu++) {
+                    const bool in = lm < nlm && mu < A.n_a;
+                    const int k = A.n_r + mu * A.l_max + l - 1;
+                    const T ak = in ? av[k] : T(0), bk = in ? be[k] : T(0);
+                    xr[mu] = w2c * (bk * Sacc[mu][i] + ak * Dacc[mu][i]);
+                    yr[mu] = w2c * ak * Sacc[mu][i];
+                }
+                store_vec<T, NMAX>(xc + lm * NMAX, xr);
+                store_vec<T, NMAX>(yc + lm * NMAX, yr);
+            }
+            __syncwarp(gmask);
+
+            // ---- 4. coefficient gradient, angular functions (the radial part is an outer product: see the round's end) ----
+            for (int k0 = 0; k0 < nang; k0 += NEP_GROUP) {
+                const bool on = k0 + sub < nang;
+                int tj = 0;
+                T vp = T(0), f[CSP], df[CSP];
+                T X[NMAX], Y[NMAX], GY[NMAX];
+#pragma unroll
+                for (int mu = 0; mu < NMAX; mu++) X[mu] = Y[mu] = GY[mu] = T(0);
+                {
+                    T x = 0, y = 0, z = 0, rinv = 0, r = A.rc_a;
+                    int nj = 0;
+                    if (on) {
+                        const int ent = alist[k0 + sub], j = ent & 1023;
+                        tj = ent >> 10;
+                        x = rc[3 * j]; y = rc[3 * j + 1]; z = rc[3 * j + 2]; nj = fn[j];
+                        r = gsqrt(x * x + y * y + z * z);
+                        rinv = T(1) / r;
+                    }
+                    T px, py, pz;
+                    pair_weight(nj, x, y, z, rinv, vp, px, py, pz);
+                    const T x_ = x * rinv, y_ = y * rinv, z_ = z * rinv;
+                    NEP_POLY_COMMON(x_, y_, z_)
 #define NEP_X(k, val, gx, gy, gz)                                                               \
     {                                                                                           \
         T xe[NMAX], ye[NMAX];                                                                   \
@@ -420,28 +418,74 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_loss_fast_kernel(con
         nep_acc<T, NMAX>(ye, bv, Y);                                                            \
         nep_acc<T, NMAX>(ye, gp, GY);                                                           \
     }
-                NEP_FOR_EACH_LM(NEP_X, x_, y_, z_)
+                    NEP_FOR_EACH_LM(NEP_X, x_, y_, z_)
 #undef NEP_X
-                nep_radial<T, CSP>(r, A.rc_a, f, df);
-            }
-            // sum over the group's neighbours of each type; lane xi adds entry xi to the block accumulator
-            for (int t = 0; t < A.ntypes; t++) {
-                const bool mine = on && tj == t;
-                if (__ballot_sync(gmask, mine) & gmask) {
+                    nep_radial<T, CSP>(r, A.rc_a, f, df);
+                }
+                // sum over the group's neighbours of each type; lane xi adds entry xi to the atom's record
+                for (int t = 0; t < A.ntypes; t++) {
+                    const bool mine = on && tj == t;
+                    if (__ballot_sync(gmask, mine) & gmask) {
 #pragma unroll
-                    for (int mu = 0; mu < NMAX; mu++) {
-                        const T wv = X[mu] + GY[mu], wd = Y[mu] * vp;
-                        T v[CSP];
+                        for (int mu = 0; mu < NMAX; mu++) {
+                            const T wv = X[mu] + GY[mu], wd = Y[mu] * vp;
+                            T v[CSP];
 #pragma unroll
-                        for (int xi = 0; xi < CSP; xi++) v[xi] = mine ? wv * f[xi] + wd * df[xi] : T(0);
-                        const T tot = group_xreduce8(v, sub, gmask);
-                        if (mu < A.n_a && sub < A.cs)
-                            atomicAdd(g_co + (((size_t)ti * A.ntypes + t) * nfun + A.n_r + mu) * A.cs + sub, tot);
+                            for (int xi = 0; xi < CSP; xi++) v[xi] = mine ? wv * f[xi] + wd * df[xi] : T(0);
+                            const T tot = group_xreduce8(v, sub, gmask);
+                            Ga[(t * NMAX + mu) * 8 + sub] += tot;
+                        }
                     }
                 }
             }
+            __syncwarp(gmask);
         }
-        __syncwarp(gmask);
+        // ---- end of the round: the block adds its atoms' records to the accumulators; one owner per element ----
+        __syncthreads();
+        const unsigned *tm = tmask[it & 1];
+        constexpr int NC = NDP / 4;
+        for (int x = threadIdx.x; x < A.ntypes * nneu * NC; x += blockDim.x) {   // first layer: gb0 (x) q + th (x) u
+            const int kc = x % NC, pn = (x / NC) % nneu, t = x / (NC * nneu);
+            T acc[4] = {T(0), T(0), T(0), T(0)};
+            for (unsigned m = tm[t]; m; m &= m - 1) {
+                const T *rec = atoms_s + (size_t)(__ffs(m) - 1) * per_atom;
+                const T gb = rec[off_gb0 + pn], tw = rec[off_th + pn];
+                T eq[4], eu[4];
+                load_vec<T, 4>(rec + 4 * kc, eq);
+                load_vec<T, 4>(rec + NDP + 4 * kc, eu);
+#pragma unroll
+                for (int k = 0; k < 4; k++) acc[k] = fma(gb, eq[k], fma(tw, eu[k], acc[k]));
+            }
+            T *gw = g_w0 + ((size_t)t * nneu + pn) * nd + 4 * kc;
+#pragma unroll
+            for (int k = 0; k < 4; k++) if (4 * kc + k < nd) gw[k] += acc[k];
+        }
+        for (int x = threadIdx.x; x < A.ntypes * nneu; x += blockDim.x) {
+            const int pn = x % nneu, t = x / nneu;
+            T a0 = T(0), a1 = T(0);
+            for (unsigned m = tm[t]; m; m &= m - 1) {
+                const T *rec = atoms_s + (size_t)(__ffs(m) - 1) * per_atom;
+                a0 += rec[off_gb0 + pn]; a1 += rec[off_gw1 + pn];
+            }
+            g_b0[x] += a0; g_w1[x] += a1;
+        }
+        for (int x = threadIdx.x; x < A.ntypes * A.ntypes * nfun * A.cs; x += blockDim.x) {   // coefficients
+            const int xi = x % A.cs, fidx = (x / A.cs) % nfun, tj = (x / (A.cs * nfun)) % A.ntypes, t = x / (A.cs * nfun * A.ntypes);
+            T acc = T(0);
+            if (fidx < A.n_r) {   // radial: be_n sum_j f_xi + av_n sum_j f'_xi (r^.p), sums per neighbour type
+                for (unsigned m = tm[t]; m; m &= m - 1) {
+                    const T *rec = atoms_s + (size_t)(__ffs(m) - 1) * per_atom;
+                    acc = fma(rec[3 * NDP + fidx], rec[off_fs + tj * 8 + xi], fma(rec[2 * NDP + fidx], rec[off_fs + (A.ntypes + tj) * 8 + xi], acc));
+                }
+            } else {
+                for (unsigned m = tm[t]; m; m &= m - 1)
+                    acc += atoms_s[(size_t)(__ffs(m) - 1) * per_atom + off_ga + (tj * NMAX + fidx - A.n_r) * 8 + xi];
+            }
+            g_co[x] += acc;
+        }
+        if ((int)threadIdx.x < A.ntypes) g_bi[threadIdx.x] += lam * T(__popc(tm[threadIdx.x]));
+        if (threadIdx.x < 16) tmask[(it + 1) & 1][threadIdx.x] = 0u;
+        __syncthreads();
     }
     __syncthreads();
     for (size_t i = threadIdx.x; i < nco; i += blockDim.x) if (g_co[i] != T(0)) atomicAdd(L.dco + b * nco + i, g_co[i]);
