@@ -263,6 +263,20 @@ __global__ void __launch_bounds__(NEPL_WARPS * 32) nep_loss_backward_kernel(cons
     for (int i = threadIdx.x; i < A.ntypes; i += blockDim.x) if (g_bi[i] != T(0)) atomicAdd(L.dbi + (size_t)b * A.ntypes + i, g_bi[i]);
 }
 
+// the kernels that add into the per-structure gradients start from zeros
+template <typename T>
+static int nepl_zero_outputs(const NepArgs<T> &A, const NepLossArgs<T> &L, cudaStream_t st)
+{
+    const int nfun = A.n_r + A.n_a;
+    const size_t nco = (size_t)A.ntypes * A.ntypes * nfun * A.cs, nw0 = (size_t)A.ntypes * A.nneu * A.nd, nb0 = (size_t)A.ntypes * A.nneu;
+    AI2B_CUDA(cudaMemsetAsync(L.dco, 0, sizeof(T) * A.B * nco, st));
+    AI2B_CUDA(cudaMemsetAsync(L.dw0, 0, sizeof(T) * A.B * nw0, st));
+    AI2B_CUDA(cudaMemsetAsync(L.db0, 0, sizeof(T) * A.B * nb0, st));
+    AI2B_CUDA(cudaMemsetAsync(L.dw1, 0, sizeof(T) * A.B * nb0, st));
+    AI2B_CUDA(cudaMemsetAsync(L.dbi, 0, sizeof(T) * A.B * A.ntypes, st));
+    return AI2B_OK;
+}
+
 // eight-lanes-per-atom kernel for small models (nep_loss_fast.cuh); *done = false: not applicable
 template <typename T, int NMAX>
 static int launch_nep_loss_fast(const NepArgs<T> &A, const T *coeffs, const NepLossArgs<T> &L, cudaStream_t st, bool *done);
@@ -280,12 +294,7 @@ static int launch_nep_loss_backward(NepArgs<T> A, const T *coeffs, NepLossArgs<T
     const int nfun = A.n_r + A.n_a;
     const size_t nco = (size_t)A.ntypes * A.ntypes * nfun * A.cs, nw0 = (size_t)A.ntypes * A.nneu * A.nd, nb0 = (size_t)A.ntypes * A.nneu;
     if (A.B == 0) return AI2B_OK;
-    AI2B_CUDA(cudaMemsetAsync(L.dco, 0, sizeof(T) * A.B * nco, st));
-    AI2B_CUDA(cudaMemsetAsync(L.dw0, 0, sizeof(T) * A.B * nw0, st));
-    AI2B_CUDA(cudaMemsetAsync(L.db0, 0, sizeof(T) * A.B * nb0, st));
-    AI2B_CUDA(cudaMemsetAsync(L.dw1, 0, sizeof(T) * A.B * nb0, st));
-    AI2B_CUDA(cudaMemsetAsync(L.dbi, 0, sizeof(T) * A.B * A.ntypes, st));
-    if (A.npad == 0) return AI2B_OK;
+    if (A.npad == 0) return nepl_zero_outputs(A, L, st);
     const size_t red_need = std::max<size_t>({(size_t)2 * A.n_r, (size_t)2 * (A.l_max * A.l_max + 2 * A.l_max), (size_t)A.ntypes * A.cs});
     AI2B_REQUIRE(red_need <= (size_t)A.ntypes * nfun * A.cs + 64, AI2B_ERR_UNSUPPORTED, "NEP loss gradient: reduction scratch too small");
     const size_t smem = sizeof(T) * (nepl_block_elems(A.ntypes, nfun, A.cs, A.nneu, A.nd) +
@@ -298,6 +307,10 @@ static int launch_nep_loss_backward(NepArgs<T> A, const T *coeffs, NepLossArgs<T
         if (rc != AI2B_OK || done) return rc;
     }
     const bool vir = L.v_ml != nullptr;
+    {
+        const int rc = nepl_zero_outputs(A, L, st);
+        if (rc != AI2B_OK) return rc;
+    }
     auto run = [&](auto kern) -> int {
         AI2B_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         int sms = 148, dev = 0;

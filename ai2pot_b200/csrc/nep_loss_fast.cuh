@@ -13,8 +13,12 @@
 // per-type sums); after each round of sixteen atoms the whole block adds the records into its
 // gradient accumulators, every accumulator element owned by one thread: the first-layer gradient
 // and the radial coefficient gradient are outer products of two record vectors, so no atomics
-// are needed. One structure per blockIdx.y; the block accumulators reach global memory once.
+// are needed. One structure per blockIdx.y; the block accumulators reach global memory once: when
+// the blocks of a structure form one thread-block cluster (CLUSTER), block r sums slice r of all
+// blocks' accumulators through distributed shared memory and stores it (the outputs need no
+// zeroing and see no atomics); otherwise every block adds its accumulators atomically.
 #pragma once
+#include <cooperative_groups.h>
 
 namespace ai2b {
 
@@ -41,7 +45,7 @@ __host__ __device__ inline int nepl_fast_atom_elems(int nneu, int ntypes)
     return 4 * NDP + (sea > stage ? sea : stage) + nep_r4(2 * ntypes * 8) + ntypes * NMAX * 8 + 2 * NP;
 }
 
-template <typename T, bool VIRIAL, int NMAX, int MINB>
+template <typename T, bool VIRIAL, int NMAX, int MINB, bool CLUSTER>
 __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_loss_fast_kernel(const NepArgs<T> A, const T *__restrict__ coeffs,
                                                                           const NepLossArgs<T> L)
 {
@@ -487,14 +491,33 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_loss_fast_kernel(con
         if (threadIdx.x < 16) tmask[(it + 1) & 1][threadIdx.x] = 0u;
         __syncthreads();
     }
-    __syncthreads();
-    for (size_t i = threadIdx.x; i < nco; i += blockDim.x) if (g_co[i] != T(0)) atomicAdd(L.dco + b * nco + i, g_co[i]);
-    for (size_t i = threadIdx.x; i < nw0; i += blockDim.x) if (g_w0[i] != T(0)) atomicAdd(L.dw0 + b * nw0 + i, g_w0[i]);
-    for (size_t i = threadIdx.x; i < nb0; i += blockDim.x) {
-        if (g_b0[i] != T(0)) atomicAdd(L.db0 + b * nb0 + i, g_b0[i]);
-        if (g_w1[i] != T(0)) atomicAdd(L.dw1 + b * nb0 + i, g_w1[i]);
+    if constexpr (CLUSTER) {
+        namespace cg = cooperative_groups;
+        cg::cluster_group cl = cg::this_cluster();
+        cl.sync();   // every block of the structure has finished its accumulators
+        const unsigned nblk = cl.num_blocks(), rank = cl.block_rank();
+        const size_t per = (nacc + nblk - 1) / nblk, i0 = rank * per, i1 = i0 + per < nacc ? i0 + per : nacc;
+        for (size_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
+            T sum = T(0);
+            for (unsigned c = 0; c < nblk; c++) sum += cl.map_shared_rank(g_co, c)[i];
+            T *dst = i < nco ? L.dco + b * nco + i
+                   : i < nco + nw0 ? L.dw0 + b * nw0 + (i - nco)
+                   : i < nco + nw0 + nb0 ? L.db0 + b * nb0 + (i - nco - nw0)
+                   : i < nco + nw0 + 2 * nb0 ? L.dw1 + b * nb0 + (i - nco - nw0 - nb0)
+                   : L.dbi + (size_t)b * A.ntypes + (i - nco - nw0 - 2 * nb0);
+            *dst = sum;
+        }
+        cl.sync();   // no block leaves while its shared memory is still being read
+    } else {
+        __syncthreads();
+        for (size_t i = threadIdx.x; i < nco; i += blockDim.x) if (g_co[i] != T(0)) atomicAdd(L.dco + b * nco + i, g_co[i]);
+        for (size_t i = threadIdx.x; i < nw0; i += blockDim.x) if (g_w0[i] != T(0)) atomicAdd(L.dw0 + b * nw0 + i, g_w0[i]);
+        for (size_t i = threadIdx.x; i < nb0; i += blockDim.x) {
+            if (g_b0[i] != T(0)) atomicAdd(L.db0 + b * nb0 + i, g_b0[i]);
+            if (g_w1[i] != T(0)) atomicAdd(L.dw1 + b * nb0 + i, g_w1[i]);
+        }
+        for (int i = threadIdx.x; i < A.ntypes; i += blockDim.x) if (g_bi[i] != T(0)) atomicAdd(L.dbi + (size_t)b * A.ntypes + i, g_bi[i]);
     }
-    for (int i = threadIdx.x; i < A.ntypes; i += blockDim.x) if (g_bi[i] != T(0)) atomicAdd(L.dbi + (size_t)b * A.ntypes + i, g_bi[i]);
 }
 
 // *done = false: the model does not fit this kernel's plan (the general kernel then runs)
@@ -513,19 +536,59 @@ static int launch_nep_loss_fast(const NepArgs<T> &A, const T *coeffs, const NepL
     if (smem > 200 * 1024) return AI2B_OK;
     constexpr int MINB = sizeof(T) == 4 ? 3 : 2;
     const bool vir = L.v_ml != nullptr;
+    int sms = 148, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    long bx = ((long)A.npad + NEP_APB - 1) / NEP_APB;
+    const long cap = std::max(1L, (long)sms * std::min<long>(MINB, (long)(227 * 1024 / (smem + 1024))) / A.B);
+    if (bx > cap) bx = cap;
+    const bool cluster = bx <= 8;   // portable cluster size: the blocks of a structure reduce among themselves
+    bool use_cluster = false;
     auto run = [&](auto kern) -> int {
         AI2B_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        int sms = 148, dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        long bx = ((long)A.npad + NEP_APB - 1) / NEP_APB;
-        const long cap = std::max(1L, (long)sms * std::min<long>(MINB, (long)(227 * 1024 / (smem + 1024))) / A.B);
-        if (bx > cap) bx = cap;
-        kern<<<dim3((unsigned)bx, (unsigned)A.B), NEP_WARPS * 32, smem, st>>>(A, coeffs, L);
-        AI2B_CUDA(cudaGetLastError());
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)bx, (unsigned)A.B);
+        cfg.blockDim = dim3(NEP_WARPS * 32);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)bx;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = use_cluster ? 1 : 0;
+        AI2B_CUDA(cudaLaunchKernelEx(&cfg, kern, A, coeffs, L));
         return AI2B_OK;
     };
-    const int rc = vir ? run(nep_loss_fast_kernel<T, true, NMAX, MINB>) : run(nep_loss_fast_kernel<T, false, NMAX, MINB>);
+    // a cluster shape that the device cannot place falls back to the atomic path
+    auto placeable = [&](auto kern) -> bool {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); return false; }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)bx, (unsigned)A.B);
+        cfg.blockDim = dim3(NEP_WARPS * 32);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)bx;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int nclusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&nclusters, kern, &cfg) != cudaSuccess) { cudaGetLastError(); return false; }
+        return nclusters > 0;
+    };
+    use_cluster = cluster && (vir ? placeable(nep_loss_fast_kernel<T, true, NMAX, MINB, true>)
+                                             : placeable(nep_loss_fast_kernel<T, false, NMAX, MINB, true>));
+    int rc;
+    if (use_cluster) {
+        rc = vir ? run(nep_loss_fast_kernel<T, true, NMAX, MINB, true>) : run(nep_loss_fast_kernel<T, false, NMAX, MINB, true>);
+    } else {
+        rc = nepl_zero_outputs(A, L, st);
+        if (rc == AI2B_OK)
+            rc = vir ? run(nep_loss_fast_kernel<T, true, NMAX, MINB, false>) : run(nep_loss_fast_kernel<T, false, NMAX, MINB, false>);
+    }
     if (rc == AI2B_OK) *done = true;
     return rc;
 }

@@ -70,6 +70,28 @@ def test_nep_loss_backward_shapes(checkers, shape, dt, tol):
         assert util.relerr(b.cpu().numpy(), a) < tol, name
 
 
+@pytest.mark.parametrize("dt,tol", [(np.float64, 1e-10), (np.float32, 5e-5)])
+def test_nep_loss_backward_many_blocks_per_structure(checkers, dt, tol):
+    """Structures large enough that their blocks do not form one cluster: the gradients are then
+    summed over the blocks with atomics (216 atoms = 14 blocks of 16 atoms)."""
+    chk = _chk(checkers)
+    ws = [util.small_nep_case(n=6, dtype=dt, seed=50, a=3.0), util.small_nep_case(n=3, dtype=dt, seed=51, a=3.1)]
+    lists = [chk.nblist(w["cell"], w["types"], w["coords"], 6.0, 200)[:4] for w in ws]
+    nb = synth.pad_batch(lists, 3, 200)
+    m = ws[0]["model"]
+    rng = np.random.default_rng(9)
+    B, npad = nb["bilist"].shape
+    E, F, V = rng.normal(size=B).astype(dt), rng.normal(size=(B, npad, 3)).astype(dt), rng.normal(size=(B, 9)).astype(dt)
+    e, f, v = chk.nep_efv(m, nb)
+    wts = (1.0, 2.0, 0.5)
+    ref = chk.nep_loss_backward(m, nb, wts, e, E, f, F, v, V)
+    md = capi.to_device(m, "cuda", torch.float64 if dt == np.float64 else torch.float32)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    got = capi.nep_loss_backward(md, capi.to_device(nb), wts, t(e), t(E), t(f), t(F), t(v), t(V))
+    for name, a, b in zip(("coeffs", "w0", "b0", "w1", "bias"), ref, got):
+        assert util.relerr(b.cpu().numpy(), a) < tol, name
+
+
 @pytest.mark.parametrize("virial", [True, False])
 def test_nep_loss_ops_autograd(checkers, virial):
     """nepToLossOp / nepToEFLossOp: loss values, RMSEs and autograd to coeffs, w0, b0, w1, type_bias."""
