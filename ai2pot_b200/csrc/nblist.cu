@@ -313,6 +313,7 @@ __global__ void nb_fill_kernel(NbParams<T> P, const T *__restrict__ pos, const i
 }
 
 constexpr int NB_WARPS = 8;
+constexpr int NB_CAND = 512;
 
 // pass 3: one warp per centre atom (taken in bin order, so neighbouring warps share bins)
 // TO = element type of the rcs rows (T, or float rows from double positions: what an MD host that keeps
@@ -325,6 +326,10 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
                 TO *__restrict__ rcs, int *__restrict__ status)
 {
     __shared__ int s_start[NB_WARPS][32], s_pre[NB_WARPS][33], s_shift[NB_WARPS][32];
+    // candidate c of the current group of bins -> its atom (bin order) and its bin's slot, filled by the
+    // lanes that own the bins; groups with more than NB_CAND candidates search s_pre instead
+    __shared__ int s_cand[NB_WARPS][NB_CAND];
+    __shared__ unsigned char s_slot[NB_WARPS][NB_CAND];
     const NbGrid g = *gp;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nwarps = gridDim.x * NB_WARPS;
@@ -396,6 +401,10 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
                 s_pre[warp][lane] = inc - len;
                 s_shift[warp][lane] = shift;
                 if (lane == 31) s_pre[warp][32] = total;
+                if (total <= NB_CAND) {
+                    const int pre = inc - len;
+                    for (int q = 0; q < len; q++) { s_cand[warp][pre + q] = start + q; s_slot[warp][pre + q] = (unsigned char)lane; }
+                }
                 __syncwarp();
             } else {
                 total = s_pre[warp][32];
@@ -408,9 +417,16 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
                 int jidx = 0;
                 T d0 = 0, d1 = 0, d2 = 0;
                 if (c < total) {
-                    int lo = 0, hi = 32;    // largest slot with pre[slot] <= c
-                    while (hi - lo > 1) { int mid = (lo + hi) >> 1; if (s_pre[warp][mid] <= c) lo = mid; else hi = mid; }
-                    const int aj = s_start[warp][lo] + (c - s_pre[warp][lo]);
+                    int aj, lo;
+                    if (total <= NB_CAND) {
+                        aj = s_cand[warp][c];
+                        lo = s_slot[warp][c];
+                    } else {
+                        lo = 0;
+                        int hi = 32;    // largest slot with pre[slot] <= c
+                        while (hi - lo > 1) { int mid = (lo + hi) >> 1; if (s_pre[warp][mid] <= c) lo = mid; else hi = mid; }
+                        aj = s_start[warp][lo] + (c - s_pre[warp][lo]);
+                    }
                     const int sh = s_shift[warp][lo];
                     const typename Vec4<T>::type pj = spos[aj];
                     const int4 sj = sinfo[aj];
