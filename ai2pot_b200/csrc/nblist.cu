@@ -22,12 +22,22 @@ namespace ai2b {
 template <typename T> struct Vec4;
 template <> struct Vec4<double> { using type = double4; };
 template <> struct Vec4<float> { using type = float4; };
+// Lattice wraps packed into one word, 10 bits per axis with bias 512: sums and differences of packed
+// words are field-wise sums and differences as long as every true field stays inside +-511. The fourth
+// component of a bin-ordered position carries the atom's packed wrap.
+constexpr int NB_WRAP_MAX = 127;
+constexpr int NB_PACK_ZERO = 512 | (512 << 10) | (512 << 20);
+__host__ __device__ inline int nb_pack3(int a, int b, int c) { return (a + 512) | ((b + 512) << 10) | ((c + 512) << 20); }
+__device__ __forceinline__ float nb_bits_to(float, int v) { return __int_as_float(v); }
+__device__ __forceinline__ double nb_bits_to(double, int v) { return __longlong_as_double((long long)v); }
+__device__ __forceinline__ int nb_bits_of(float v) { return __float_as_int(v); }
+__device__ __forceinline__ int nb_bits_of(double v) { return (int)__double_as_longlong(v); }
 
 struct NbGrid {          // lives in the workspace; written by nb_grid_kernel
     int nb[3];           // bins per fractional axis
     int R[3];            // bins to search on each side
     int total;
-    int pad;
+    int bigwrap;         // set by nb_count_kernel when an atom lies more than NB_WRAP_MAX periods outside the cell
     double lo[3];        // non-periodic axes: lowest fractional coordinate
     double scale[3];     // bin = (s - lo) * scale
 };
@@ -140,6 +150,7 @@ __global__ void nb_grid_kernel(NbParams<T> P, const unsigned long long *__restri
         total *= g->nb[k];
     }
     g->total = (int)total;   // <= maxbins by construction of nbh
+    g->bigwrap = 0;
 }
 
 template <typename T>
@@ -162,7 +173,7 @@ __device__ __forceinline__ void bin_of(const NbParams<T> &P, const NbGrid &g, co
 
 // pass 1: bin index + lattice wrap of every atom, bin populations
 template <typename T>
-__global__ void nb_count_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const T *__restrict__ pos,
+__global__ void nb_count_kernel(NbParams<T> P, NbGrid *gp, const T *__restrict__ pos,
                                 int4 *__restrict__ ainfo, int *__restrict__ bin_count)
 {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -174,6 +185,7 @@ __global__ void nb_count_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, co
     bin_of(P, g, s, b, w);
     int bin = (b[0] * g.nb[1] + b[1]) * g.nb[2] + b[2];
     ainfo[i] = make_int4(bin, w[0], w[1], w[2]);
+    if (abs(w[0]) > NB_WRAP_MAX || abs(w[1]) > NB_WRAP_MAX || abs(w[2]) > NB_WRAP_MAX) gp->bigwrap = 1;
     atomicAdd(bin_count + bin, 1);
 }
 
@@ -261,6 +273,7 @@ __global__ void nb_setup_periodic_kernel(NbParams<T> P, NbGrid *__restrict__ g, 
             total *= P.nbh[k];
         }
         g->total = (int)total;
+        g->bigwrap = 0;
     }
 }
 
@@ -307,7 +320,8 @@ __global__ void nb_fill_kernel(NbParams<T> P, const T *__restrict__ pos, const i
     const int4 a = ainfo[i];
     int k = atomicAdd(cursor + a.x, 1);
     typename Vec4<T>::type p;
-    p.x = pos[3 * i]; p.y = pos[3 * i + 1]; p.z = pos[3 * i + 2]; p.w = T(0);
+    p.x = pos[3 * i]; p.y = pos[3 * i + 1]; p.z = pos[3 * i + 2];
+    p.w = nb_bits_to(T(0), nb_pack3(a.y, a.z, a.w));   // meaningful while no wrap exceeds NB_WRAP_MAX (else unused)
     spos[k] = p;
     sinfo[k] = make_int4(i, a.y, a.z, a.w);
 }
@@ -319,7 +333,7 @@ constexpr int NB_CAND = 512;
 // TO = element type of the rcs rows (T, or float rows from double positions: what an MD host that keeps
 // double coordinates and a single-precision model does on the CPU)
 template <typename T, typename TO>
-__global__ void __launch_bounds__(NB_WARPS * 32)
+__global__ void __launch_bounds__(NB_WARPS * 32, sizeof(T) == 8 ? 3 : 4)
 nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restrict__ bin_start,
                 const int4 *__restrict__ ainfo, const typename Vec4<T>::type *__restrict__ spos,
                 const int4 *__restrict__ sinfo, int *__restrict__ numneigh, int *__restrict__ firstneigh,
@@ -331,6 +345,7 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
     __shared__ int s_cand[NB_WARPS][NB_CAND];
     __shared__ unsigned char s_slot[NB_WARPS][NB_CAND];
     const NbGrid g = *gp;
+    const bool packed = g.bigwrap == 0;   // every wrap fits the packed form
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nwarps = gridDim.x * NB_WARPS;
     const int nx = 2 * g.R[0] + 1, ny = 2 * g.R[1] + 1, nz = 2 * g.R[2] + 1, nnb = nx * ny * nz;
@@ -352,6 +367,7 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
         const typename Vec4<T>::type pi = spos[a];
         const int4 si = sinfo[a];
         const int i = si.x;
+        const int wi = nb_pack3(si.y, si.z, si.w);   // its bias is the one that survives in shift - wrap_j + wrap_i
         if (i >= P.ncentre) continue;
         const int bin_i = ainfo[i].x;
         const int bz = bin_i % g.nb[2], by = (bin_i / g.nb[2]) % g.nb[1], bx = bin_i / (g.nb[2] * g.nb[1]);
@@ -429,20 +445,32 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
                     }
                     const int sh = s_shift[warp][lo];
                     const typename Vec4<T>::type pj = spos[aj];
-                    const int4 sj = sinfo[aj];
-                    const int n0 = (sh & 1023) - 512 - sj.y + si.y;
-                    const int n1 = ((sh >> 10) & 1023) - 512 - sj.z + si.z;
-                    const int n2 = ((sh >> 20) & 1023) - 512 - sj.w + si.w;
-                    if (abs(n0) <= P.e[0] && abs(n1) <= P.e[1] && abs(n2) <= P.e[2]) {
-                        T ix = pj.x, iy = pj.y, iz = pj.z;
-                        // the home image needs no arithmetic: x + a*0 is x bit for bit, except for x = -0.0
-                        // (whose sum with +0 is +0), so exact zeros take the full path
-                        if ((n0 | n1 | n2) != 0 || pj.x == T(0) || pj.y == T(0) || pj.z == T(0)) {
-                            const T f0 = T(n0), f1 = T(n1), f2 = T(n2);
-                            ix = add_rn(add_rn(add_rn(pj.x, mul_rn(P.cell[0], f0)), mul_rn(P.cell[3], f1)), mul_rn(P.cell[6], f2));
-                            iy = add_rn(add_rn(add_rn(pj.y, mul_rn(P.cell[1], f0)), mul_rn(P.cell[4], f1)), mul_rn(P.cell[7], f2));
-                            iz = add_rn(add_rn(add_rn(pj.z, mul_rn(P.cell[2], f0)), mul_rn(P.cell[5], f1)), mul_rn(P.cell[8], f2));
-                        }
+                    T ix = pj.x, iy = pj.y, iz = pj.z;
+                    // periods between the candidate's stored position and the image this bin slot means
+                    int n0 = 0, n1 = 0, n2 = 0;
+                    bool away;       // some period is non-zero
+                    if (packed) {
+                        // bin shift - candidate's wrap + centre's wrap, all three axes in one word
+                        const int nw = sh - nb_bits_of(pj.w) + wi;
+                        away = nw != NB_PACK_ZERO;
+                        if (away) { n0 = (nw & 1023) - 512; n1 = ((nw >> 10) & 1023) - 512; n2 = ((nw >> 20) & 1023) - 512; }
+                    } else {
+                        const int4 sj = sinfo[aj];
+                        n0 = (sh & 1023) - 512 - sj.y + si.y;
+                        n1 = ((sh >> 10) & 1023) - 512 - sj.z + si.z;
+                        n2 = ((sh >> 20) & 1023) - 512 - sj.w + si.w;
+                        away = (n0 | n1 | n2) != 0;
+                    }
+                    const bool covered = !away || (abs(n0) <= P.e[0] && abs(n1) <= P.e[1] && abs(n2) <= P.e[2]);
+                    // the home image needs no arithmetic: x + a*0 is x bit for bit, except for x = -0.0
+                    // (whose sum with +0 is +0), so exact zeros take the full path
+                    if (covered && (away || pj.x == T(0) || pj.y == T(0) || pj.z == T(0))) {
+                        const T f0 = T(n0), f1 = T(n1), f2 = T(n2);
+                        ix = add_rn(add_rn(add_rn(pj.x, mul_rn(P.cell[0], f0)), mul_rn(P.cell[3], f1)), mul_rn(P.cell[6], f2));
+                        iy = add_rn(add_rn(add_rn(pj.y, mul_rn(P.cell[1], f0)), mul_rn(P.cell[4], f1)), mul_rn(P.cell[7], f2));
+                        iz = add_rn(add_rn(add_rn(pj.z, mul_rn(P.cell[2], f0)), mul_rn(P.cell[5], f1)), mul_rn(P.cell[8], f2));
+                    }
+                    if (covered) {
                         d0 = sub_rn(ix, pi.x); d1 = sub_rn(iy, pi.y); d2 = sub_rn(iz, pi.z);
                         // Reference predicate: squares accumulate in double for both types (pow(T,int)
                         // promotes float), the sum is rounded to T and compared with rc^2 and 1e-3.
@@ -461,7 +489,7 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
                             const double ddT = (double)(T)dd;
                             hit = (ddT < P.rc2) && (ddT > 1e-3);
                         }
-                        jidx = sj.x;
+                        if (hit) jidx = sinfo[aj].x;
                     }
                 }
                 const unsigned bal = __ballot_sync(FULL_MASK, hit);
