@@ -429,69 +429,71 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
             // lanes = candidate atoms of the whole group of bins
             for (int c0 = 0; c0 < total; c0 += 32) {
                 const int c = c0 + lane;
+                const bool have = c < total;
                 bool hit = false;
                 int jidx = 0;
                 T d0 = 0, d1 = 0, d2 = 0;
-                if (c < total) {
-                    int aj, lo;
+                int aj = 0, lo = 0;
+                if (have) {
                     if (total <= NB_CAND) {
                         aj = s_cand[warp][c];
                         lo = s_slot[warp][c];
                     } else {
-                        lo = 0;
                         int hi = 32;    // largest slot with pre[slot] <= c
                         while (hi - lo > 1) { int mid = (lo + hi) >> 1; if (s_pre[warp][mid] <= c) lo = mid; else hi = mid; }
                         aj = s_start[warp][lo] + (c - s_pre[warp][lo]);
                     }
-                    const int sh = s_shift[warp][lo];
-                    const typename Vec4<T>::type pj = spos[aj];
-                    T ix = pj.x, iy = pj.y, iz = pj.z;
-                    // periods between the candidate's stored position and the image this bin slot means
-                    int n0 = 0, n1 = 0, n2 = 0;
-                    bool away;       // some period is non-zero
-                    if (packed) {
-                        // bin shift - candidate's wrap + centre's wrap, all three axes in one word
-                        const int nw = sh - nb_bits_of(pj.w) + wi;
-                        away = nw != NB_PACK_ZERO;
-                        if (away) { n0 = (nw & 1023) - 512; n1 = ((nw >> 10) & 1023) - 512; n2 = ((nw >> 20) & 1023) - 512; }
-                    } else {
-                        const int4 sj = sinfo[aj];
-                        n0 = (sh & 1023) - 512 - sj.y + si.y;
-                        n1 = ((sh >> 10) & 1023) - 512 - sj.z + si.z;
-                        n2 = ((sh >> 20) & 1023) - 512 - sj.w + si.w;
-                        away = (n0 | n1 | n2) != 0;
-                    }
-                    const bool covered = !away || (abs(n0) <= P.e[0] && abs(n1) <= P.e[1] && abs(n2) <= P.e[2]);
-                    // the home image needs no arithmetic: x + a*0 is x bit for bit, except for x = -0.0
-                    // (whose sum with +0 is +0), so exact zeros take the full path
-                    if (covered && (away || pj.x == T(0) || pj.y == T(0) || pj.z == T(0))) {
-                        const T f0 = T(n0), f1 = T(n1), f2 = T(n2);
-                        ix = add_rn(add_rn(add_rn(pj.x, mul_rn(P.cell[0], f0)), mul_rn(P.cell[3], f1)), mul_rn(P.cell[6], f2));
-                        iy = add_rn(add_rn(add_rn(pj.y, mul_rn(P.cell[1], f0)), mul_rn(P.cell[4], f1)), mul_rn(P.cell[7], f2));
-                        iz = add_rn(add_rn(add_rn(pj.z, mul_rn(P.cell[2], f0)), mul_rn(P.cell[5], f1)), mul_rn(P.cell[8], f2));
-                    }
-                    if (covered) {
-                        d0 = sub_rn(ix, pi.x); d1 = sub_rn(iy, pi.y); d2 = sub_rn(iz, pi.z);
-                        // Reference predicate: squares accumulate in double for both types (pow(T,int)
-                        // promotes float), the sum is rounded to T and compared with rc^2 and 1e-3.
-                        // For float a single-precision sum is within a few ulp of that value, so it
-                        // decides every pair outside a 2e-6 relative band around the two thresholds;
-                        // only pairs inside the band take the exact route.
-                        bool decided = false;
-                        if (sizeof(T) == 4) {
-                            const float s = (float)d0 * (float)d0 + (float)d1 * (float)d1 + (float)d2 * (float)d2;
-                            if (s < P.rc2_lo && s > P.eps_hi) { hit = true; decided = true; }
-                            else if (s > P.rc2_hi || s < P.eps_lo) { decided = true; }
-                        }
-                        if (!decided) {
-                            const double dd = add_rn(add_rn(mul_rn((double)d0, (double)d0), mul_rn((double)d1, (double)d1)),
-                                                     mul_rn((double)d2, (double)d2));
-                            const double ddT = (double)(T)dd;
-                            hit = (ddT < P.rc2) && (ddT > 1e-3);
-                        }
-                        if (hit) jidx = sinfo[aj].x;
-                    }
                 }
+                const int sh = s_shift[warp][lo];
+                typename Vec4<T>::type pj;
+                pj.x = pj.y = pj.z = pj.w = T(0);
+                if (have) pj = spos[aj];
+                // periods between the candidate's stored position and the image this bin slot means
+                int n0 = 0, n1 = 0, n2 = 0;
+                bool away;       // some period is non-zero
+                if (packed) {
+                    // bin shift - candidate's wrap + centre's wrap, all three axes in one word
+                    const int nw = sh - nb_bits_of(pj.w) + wi;
+                    away = nw != NB_PACK_ZERO;
+                    n0 = (nw & 1023) - 512; n1 = ((nw >> 10) & 1023) - 512; n2 = ((nw >> 20) & 1023) - 512;
+                } else {
+                    int4 sj = make_int4(0, 0, 0, 0);
+                    if (have) sj = sinfo[aj];
+                    n0 = (sh & 1023) - 512 - sj.y + si.y;
+                    n1 = ((sh >> 10) & 1023) - 512 - sj.z + si.z;
+                    n2 = ((sh >> 20) & 1023) - 512 - sj.w + si.w;
+                    away = (n0 | n1 | n2) != 0;
+                }
+                const bool covered = have && (!away || (abs(n0) <= P.e[0] && abs(n1) <= P.e[1] && abs(n2) <= P.e[2]));
+                T ix = pj.x, iy = pj.y, iz = pj.z;
+                // The home image needs no arithmetic: x + a*0 is x bit for bit, except for x = -0.0 (whose
+                // sum with +0 is +0), so exact zeros take the full path.
+                const bool moved = covered && (away || pj.x == T(0) || pj.y == T(0) || pj.z == T(0));
+                if (moved) {
+                    const T f0 = T(n0), f1 = T(n1), f2 = T(n2);
+                    ix = add_rn(add_rn(add_rn(pj.x, mul_rn(P.cell[0], f0)), mul_rn(P.cell[3], f1)), mul_rn(P.cell[6], f2));
+                    iy = add_rn(add_rn(add_rn(pj.y, mul_rn(P.cell[1], f0)), mul_rn(P.cell[4], f1)), mul_rn(P.cell[7], f2));
+                    iz = add_rn(add_rn(add_rn(pj.z, mul_rn(P.cell[2], f0)), mul_rn(P.cell[5], f1)), mul_rn(P.cell[8], f2));
+                }
+                d0 = sub_rn(ix, pi.x); d1 = sub_rn(iy, pi.y); d2 = sub_rn(iz, pi.z);
+                // Reference predicate: squares accumulate in double for both types (pow(T,int) promotes
+                // float), the sum is rounded to T and compared with rc^2 and 1e-3. For float a
+                // single-precision sum is within a few ulp of that value, so it decides every pair outside
+                // a 2e-6 relative band around the two thresholds; only pairs inside the band take the
+                // exact route.
+                bool undecided = covered;
+                if (sizeof(T) == 4) {
+                    const float s = (float)d0 * (float)d0 + (float)d1 * (float)d1 + (float)d2 * (float)d2;
+                    hit = covered && s < P.rc2_lo && s > P.eps_hi;
+                    undecided = covered && !hit && !(s > P.rc2_hi || s < P.eps_lo);
+                }
+                if (undecided) {
+                    const double dd = add_rn(add_rn(mul_rn((double)d0, (double)d0), mul_rn((double)d1, (double)d1)),
+                                             mul_rn((double)d2, (double)d2));
+                    const double ddT = (double)(T)dd;
+                    hit = (ddT < P.rc2) && (ddT > 1e-3);
+                }
+                if (hit) jidx = sinfo[aj].x;
                 const unsigned bal = __ballot_sync(FULL_MASK, hit);
                 if (hit) {
                     const int p = count + __popc(bal & lt_mask);
