@@ -475,7 +475,7 @@ __global__ void __launch_bounds__(MTP_WARPS * 32, 3) mtp_force_kernel(const MtpP
     const int chunk = (ntot + nw - 1) / nw;
     const int t0 = gw * chunk, t1 = min(ntot, t0 + chunk);
 
-    int cur_b = -1, b_end = 0;
+    int cur_b = -1;
     T vir[9];
 #pragma unroll
     for (int k = 0; k < 9; k++) vir[k] = T(0);

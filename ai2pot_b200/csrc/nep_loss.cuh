@@ -292,7 +292,6 @@ static int launch_nep_loss_backward(NepArgs<T> A, const T *coeffs, NepLossArgs<T
     A.nd = A.l_max == 0 ? A.n_r : A.n_r + A.n_a * A.l_max;
     A.nS = A.l_max == 0 ? 0 : A.n_a * (A.l_max * A.l_max + 2 * A.l_max);
     const int nfun = A.n_r + A.n_a;
-    const size_t nco = (size_t)A.ntypes * A.ntypes * nfun * A.cs, nw0 = (size_t)A.ntypes * A.nneu * A.nd, nb0 = (size_t)A.ntypes * A.nneu;
     if (A.B == 0) return AI2B_OK;
     if (A.npad == 0) return nepl_zero_outputs(A, L, st);
     const size_t red_need = std::max<size_t>({(size_t)2 * A.n_r, (size_t)2 * (A.l_max * A.l_max + 2 * A.l_max), (size_t)A.ntypes * A.cs});
