@@ -261,6 +261,26 @@ def nep_loss_backward(model, nb, weights, e_ml, e_dft, f_ml, f_dft, v_ml=None, v
     return dco, dw0, db0, dw1, dbi
 
 
+def weighted_sum_rows(parts, w=None, out=None):
+    """out = concatenation over k of (w @ parts[k].reshape(B, -1)); w None: sums over the first axis.
+    One launch for up to 8 per-structure gradient tensors (ai2b_weighted_sum_rows)."""
+    parts = [p_.contiguous() for p_ in parts]
+    B = parts[0].shape[0]
+    dt, dev = parts[0].dtype, parts[0].device
+    suf, cf = _suf(dt)
+    ns = [p_.numel() // B if B else 0 for p_ in parts]
+    if out is None:
+        out = torch.empty(sum(ns), dtype=dt, device=dev)
+    assert out.numel() == sum(ns) and out.dtype == dt and out.is_contiguous()
+    if sum(ns) == 0:
+        return out
+    ptrs = (C.c_void_p * len(parts))(*[p_.data_ptr() for p_ in parts])
+    n_arr = (C.c_int * len(parts))(*ns)
+    _check(getattr(lib(), "ai2b_weighted_sum_rows_" + suf)(C.c_int(len(parts)), ptrs, n_arr, C.c_int(B),
+                                                          _ptr(w.contiguous()) if w is not None else None, _ptr(out), _stream()))
+    return out
+
+
 def zbl_efv(nb, type_map, rmax, rmin, cks, dks, e, f, v=None):
     """Adds the ZBL pair correction onto e[B], f[B,Np+nghost,3] and (if given) v[B,9] in place.
     type_map: int32 atomic numbers [ntypes]; cks, dks: [ntypes*ntypes*4] (device tensors)."""

@@ -125,6 +125,58 @@ static int desc_stats(int *natoms, T *mean, T *m2, int B, int npad, int nd, cons
     return AI2B_OK;
 }
 
+// out[off_k + i] = sum_b w[b] * part_k[b * n_k + i] for up to WS_MAX_PARTS row-major [B][n_k] arrays in one launch
+constexpr int WS_MAX_PARTS = 8;
+template <typename T>
+struct WsParts {
+    const T *p[WS_MAX_PARTS];
+    int off[WS_MAX_PARTS + 1];   // start of part k in the output; off[nparts] = total
+    int nparts;
+};
+template <typename T>
+__global__ void weighted_sum_rows_kernel(WsParts<T> P, int B, const T *__restrict__ w, T *__restrict__ out)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= P.off[P.nparts]) return;
+    int k = 0;
+#pragma unroll
+    for (int q = 1; q < WS_MAX_PARTS; q++) if (q < P.nparts && i >= P.off[q]) k = q;
+    const int n = P.off[k + 1] - P.off[k];
+    const T *src = P.p[k] + (i - P.off[k]);
+    T acc0 = T(0), acc1 = T(0);   // two chains: B is a few dozen, the loads are independent
+    int b = 0;
+    for (; b + 1 < B; b += 2) {
+        acc0 = fma(w ? w[b] : T(1), src[(size_t)b * n], acc0);
+        acc1 = fma(w ? w[b + 1] : T(1), src[(size_t)(b + 1) * n], acc1);
+    }
+    if (b < B) acc0 = fma(w ? w[b] : T(1), src[(size_t)b * n], acc0);
+    out[i] = acc0 + acc1;
+}
+
+template <typename T>
+static int weighted_sum_rows(int nparts, const T *const *parts, const int *n, int B, const T *w, T *out, cudaStream_t st)
+{
+    AI2B_REQUIRE(nparts >= 1 && nparts <= WS_MAX_PARTS && parts && n && out && B >= 0, AI2B_ERR_INVALID,
+                 "ai2b_weighted_sum_rows: bad argument (1..%d parts)", WS_MAX_PARTS);
+    WsParts<T> P;
+    P.nparts = nparts;
+    P.off[0] = 0;
+    for (int k = 0; k < WS_MAX_PARTS; k++) {
+        P.p[k] = k < nparts ? parts[k] : nullptr;
+        if (k < nparts) {
+            AI2B_REQUIRE(n[k] >= 0 && (n[k] == 0 || parts[k]), AI2B_ERR_INVALID, "ai2b_weighted_sum_rows: part %d is NULL or negative", k);
+            P.off[k + 1] = P.off[k] + n[k];
+        } else {
+            P.off[k + 1] = P.off[k];
+        }
+    }
+    const int total = P.off[nparts];
+    if (total == 0) return AI2B_OK;
+    weighted_sum_rows_kernel<T><<<(total + 127) / 128, 128, 0, st>>>(P, B, w, out);
+    AI2B_CUDA(cudaGetLastError());
+    return AI2B_OK;
+}
+
 }  // namespace ai2b
 
 using namespace ai2b;
@@ -166,3 +218,12 @@ using namespace ai2b;
 
 AI2B_DEF_STATS(f64, double)
 AI2B_DEF_STATS(f32, float)
+
+#define AI2B_DEF_WSUM(SUF, T)                                                                                          \
+    extern "C" int ai2b_weighted_sum_rows_##SUF(int nparts, const T *const *h_parts, const int *h_n, int B,            \
+                                                const T *d_w, T *d_out, void *stream)                                  \
+    {                                                                                                                  \
+        return weighted_sum_rows<T>(nparts, h_parts, h_n, B, d_w, d_out, (cudaStream_t)stream);                        \
+    }
+AI2B_DEF_WSUM(f64, double)
+AI2B_DEF_WSUM(f32, float)

@@ -46,6 +46,30 @@ inline at::Tensor workspace(size_t bytes, const at::Tensor &like)
     return at::empty({(int64_t)(bytes < 256 ? 256 : bytes)}, like.options().dtype(at::kByte));
 }
 
+// g[B] @ parts[k][B, n_k] for every k in one launch (what a training op's backward returns per parameter
+// tensor); results are views into one flat tensor, in the order of `parts`
+inline std::vector<at::Tensor> weighted_sums(const at::Tensor &g, const std::vector<at::Tensor> &parts)
+{
+    const int B = (int)g.numel(), np = (int)parts.size();
+    std::vector<int> n(np);
+    std::vector<const void *> ptr(np);
+    int64_t total = 0;
+    for (int k = 0; k < np; k++) { n[k] = B ? (int)(parts[k].numel() / B) : 0; ptr[k] = parts[k].data_ptr(); total += n[k]; }
+    at::Tensor flat = at::zeros({total}, g.options());
+    if (B > 0 && total > 0) {
+        int rc;
+        if (g.scalar_type() == at::kDouble)
+            rc = ai2b_weighted_sum_rows_f64(np, (const double *const *)ptr.data(), n.data(), B, g.data_ptr<double>(), flat.data_ptr<double>(), stream());
+        else
+            rc = ai2b_weighted_sum_rows_f32(np, (const float *const *)ptr.data(), n.data(), B, g.data_ptr<float>(), flat.data_ptr<float>(), stream());
+        TORCH_CHECK(rc == AI2B_OK, "ai2b_weighted_sum_rows: ", ai2b_last_error_string());
+    }
+    std::vector<at::Tensor> out(np);
+    int64_t off = 0;
+    for (int k = 0; k < np; k++) { out[k] = flat.narrow(0, off, n[k]); off += n[k]; }
+    return out;
+}
+
 // ZBL parameters of an op call (zbl_rmax <= 0: no correction)
 struct ZblArgs {
     double rmax, rmin;

@@ -246,7 +246,7 @@ def run_training_benchmark(w, steps, warmup, dist, sampler):
             e, f, v = capi.mtp_efv(prog, md, nbt)
             loss, rmse = capi.mtp_loss(nbt, w["weights"], e, E, f, F, v, V)
             parts = capi.mtp_loss_backward(prog, md, nbt, w["weights"], e, E, f, F, v, V)
-        torch.cat([p_.sum(0) for p_ in parts] + [loss.sum(0, keepdim=True)], out=grad)
+        capi.weighted_sum_rows(list(parts) + [loss.reshape(-1, 1)], None, out=grad)   # sums over the structures, one launch
 
     # the step's launches are the same every time (resident neighbour tensors, fixed shapes): replay them
     # from a CUDA graph; the all-reduce of the summed gradient stays an eager NCCL call
@@ -303,7 +303,7 @@ def run_training_benchmark(w, steps, warmup, dist, sampler):
                 "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": "FMA-chain microbenchmark in this run (of measured)",
                 "flops_per_atom": fl, "mean_neighbours": mean_nn, "traffic": None}
     name = "nep" if is_nep else "mtp"
-    return dict(t_dev=t_dev, t_e2e=t_e2e, clocks=clocks, launches=((2 + 2 + 1) if is_nep else (4 + 2 + 4)) * steps, h2d=0,
+    return dict(t_dev=t_dev, t_e2e=t_e2e, clocks=clocks, launches=((2 + 2 + 1 + 1) if is_nep else (4 + 2 + 4 + 1)) * steps, h2d=0,
                 d2h=hgrad.numel() * hgrad.element_size(), units=natoms,
                 e2e_path=f"resident neighbour tensors -> ai2b_{name}_efv -> ai2b_{name}_loss -> ai2b_{name}_loss_backward -> D2H summed gradient",
                 roofline=roofline, parts_ms=None, cuda_graph=graph is not None)

@@ -317,6 +317,20 @@ AI2B_DECL_STATS(f64, double)
 AI2B_DECL_STATS(f32, float)
 
 /* ------------------------------------------------------------------------------------------
+ * Reduction of per-structure gradients: d_out[off_k + i] = sum_b d_w[b] * parts[k][b * n[k] + i],
+ * off_k = n[0] + ... + n[k-1], for up to 8 row-major [batch_size][n[k]] device arrays in ONE
+ * launch (d_w NULL: plain sums). This is the `grad_out[B] @ per-structure gradient` product that
+ * the backward of every training op forms once per parameter tensor (source/descriptor/nep/src/
+ * nepOp.cc:2335-2339, 3464-3468; source/descriptor/mtpr/src/linearMtpOp.cc, the *LossOp
+ * backward functions). h_parts / h_n are HOST arrays of nparts device pointers / row lengths.
+ * ---------------------------------------------------------------------------------------- */
+#define AI2B_DECL_WSUM(SUF, T)                                                                   \
+    int ai2b_weighted_sum_rows_##SUF(int nparts, const T *const *h_parts, const int *h_n,        \
+                                     int batch_size, const T *d_w, T *d_out, void *stream);
+AI2B_DECL_WSUM(f64, double)
+AI2B_DECL_WSUM(f32, float)
+
+/* ------------------------------------------------------------------------------------------
  * Device-resident input path for a molecular-dynamics host: replaces
  * PairAI2Pot::construct_mlff_input + the tensor traffic of PairAI2Pot::compute
  * (interface/lammps/AI2POT/pair_ai2pot.cpp:175-249, 383-471). Unlike the entry points above a

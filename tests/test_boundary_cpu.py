@@ -61,6 +61,8 @@ def test_argument_checks_return_codes_without_gpu():
     assert rc == -1
     rc = lib.ai2b_target_stats_f32(null, null, one, one, null, null, null, null)
     assert rc == -1
+    rc = lib.ai2b_weighted_sum_rows_f32(C.c_int(9), null, null, one, null, null, null)
+    assert rc == -1 and b"parts" in lib.ai2b_last_error_string()
     rc = lib.ai2b_nep_loss_backward_f64(null, null, null, null, null, C.c_double(1), C.c_double(1), C.c_double(1), null, null, null,
                                         null, null, null, one, one, one, one, one, null, null, null, null, one, one, null, null, null,
                                         null, null, null, one, one, C.c_int(0), C.c_double(6), C.c_double(4), null, null)

@@ -4,6 +4,7 @@ import pytest
 import torch
 
 import util
+from ai2pot_b200 import capi
 
 pytestmark = pytest.mark.gpu
 
@@ -55,3 +56,21 @@ def test_statistics_ops(checkers, dt, tol):
     assert int(nt) == rnt
     got = np.array([em.item(), em2.item(), f2.item()])
     assert np.all(np.abs(got - rout) <= tol * np.abs(rout))
+
+
+@pytest.mark.parametrize("dt", [torch.float64, torch.float32])
+@pytest.mark.parametrize("weighted", [True, False])
+def test_weighted_sum_rows(dt, weighted):
+    """One launch for `grad_out @ per-structure gradients` of several parameter tensors."""
+    g = torch.Generator(device="cuda").manual_seed(3)
+    B = 37
+    parts = [torch.randn(B, n, dtype=dt, device="cuda", generator=g) for n in (576, 1800, 90, 90, 3, 1)]
+    parts[1] = parts[1].reshape(B, 90, 20)          # any trailing shape
+    w = torch.randn(B, dtype=dt, device="cuda", generator=g) if weighted else None
+    got = capi.weighted_sum_rows(parts, w)
+    ww = w if weighted else torch.ones(B, dtype=dt, device="cuda")
+    exp = torch.cat([(ww.double() @ p_.reshape(B, -1).double()) for p_ in parts])
+    tol = 1e-12 if dt == torch.float64 else 2e-5
+    assert got.dtype == dt and got.shape == exp.shape
+    assert (got.double() - exp).abs().max().item() <= tol * exp.abs().max().item()
+    assert capi.weighted_sum_rows([torch.zeros(0, 5, dtype=dt, device="cuda")]).abs().sum().item() == 0   # empty batch: zeros
