@@ -34,6 +34,8 @@ __device__ __forceinline__ T nep_dot3(GX gx, GY gy, GZ gz, T px, T py, T pz)
 // staging row of the angular sums: g[NMAX] | g' (r^.p) [NMAX] | B_lm[24] | grad B_lm . p_perp / r [24] | pad
 // (15 chunks of 16 bytes for NMAX = 4: eight lanes storing eight rows meet no bank twice)
 template <int NMAX> struct NepLossFastDims { static constexpr int RS = 2 * NMAX + 2 * NEP_NLM + 4; };
+// neighbours staged per step of the angular sums: half a group, which keeps a block's shared memory small enough for four blocks per SM
+constexpr int NEPL_STAGE = 4;
 
 template <int NMAX>
 __host__ __device__ inline int nepl_fast_atom_elems(int nneu, int ntypes)
@@ -41,8 +43,8 @@ __host__ __device__ inline int nepl_fast_atom_elems(int nneu, int ntypes)
     const int NDP = NepFastDims<NMAX>::NDP;
     const int NP = nep_r32(nneu);
     const int sea = 2 * NEP_NLM * NMAX + 2 * NP;                 // xc, yc, th, sp ...
-    const int stage = NEP_GROUP * NepLossFastDims<NMAX>::RS;      // ... share their space with the staging rows
-    return 4 * NDP + (sea > stage ? sea : stage) + nep_r4(2 * ntypes * 8) + ntypes * NMAX * 8 + 2 * NP;
+    const int stage = NEPL_STAGE * NepLossFastDims<NMAX>::RS;     // ... share their space with the staging rows
+    return 4 * NDP + (sea > stage ? sea : stage) + nep_r4(2 * ntypes * 8) + ntypes * NMAX * 8 + NP;
 }
 
 template <typename T, bool VIRIAL, int NMAX, int MINB, bool CLUSTER>
@@ -87,12 +89,11 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_loss_fast_kernel(con
     T *yc = xc + NEP_NLM * NMAX;                         // [24][NMAX]
     T *th = yc + NEP_NLM * NMAX;                         // [NP] W1 d1     (placed after x, y; S / DS themselves stay in registers)
     T *sp = th + NP;                                     // [NP] W1 s d2
-    const int sea = 2 * NEP_NLM * NMAX + 2 * NP, stg = NEP_GROUP * RS;
+    const int sea = 2 * NEP_NLM * NMAX + 2 * NP, stg = NEPL_STAGE * RS;
     T *Fs = S + (sea > stg ? sea : stg);                 // [ntypes][8] sum f_xi, then [ntypes][8] sum f'_xi (r^.p)
     T *Ga = Fs + nep_r4(2 * A.ntypes * 8);               // [ntypes][NMAX][8] angular coefficient gradient of this atom
-    T *gb0s = Ga + A.ntypes * NMAX * 8;                  // [NP] d/d b0 of this atom
-    T *gw1s = gb0s + NP;                                 // [NP] d/d w1
-    const int off_th = (int)(th - q), off_fs = (int)(Fs - q), off_ga = (int)(Ga - q), off_gb0 = (int)(gb0s - q), off_gw1 = (int)(gw1s - q);
+    T *gw1s = Ga + A.ntypes * NMAX * 8;                  // [NP] d/d w1 of this atom (d/d b0 is lam th + sp)
+    const int off_th = (int)(th - q), off_sp = (int)(sp - q), off_fs = (int)(Fs - q), off_ga = (int)(Ga - q), off_gw1 = (int)(gw1s - q);
     unsigned short *alist = reinterpret_cast<unsigned short *>(atoms_s + (size_t)NEP_APB * per_atom) + (size_t)slot_in_block * A.umax;
     const int ntot_n = nfun;
 
@@ -234,9 +235,9 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_loss_fast_kernel(con
             for (int mu = 0; mu < NMAX; mu++)
 #pragma unroll
                 for (int i = 0; i < 3; i++) Sacc[mu][i] = Dacc[mu][i] = T(0);
-            for (int k0 = 0; k0 < nang; k0 += NEP_GROUP) {
-                const bool on = k0 + sub < nang;
-                {
+            for (int k0 = 0; k0 < nang; k0 += NEPL_STAGE) {
+                const bool on = sub < NEPL_STAGE && k0 + sub < nang;
+                if (sub < NEPL_STAGE) {   // the first lanes of the group stage one neighbour each
                     T x = 0, y = 0, z = 0, rinv = 0, r = A.rc_a;
                     int tj = 0, nj = 0;
                     if (on) {
@@ -273,7 +274,7 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_loss_fast_kernel(con
                     store_vec<T, RS>(stage + sub * RS, row);
                 }
                 __syncwarp(gmask);
-                const int cnt = min(NEP_GROUP, nang - k0);
+                const int cnt = min(NEPL_STAGE, nang - k0);
                 for (int jj = 0; jj < cnt; jj++) {
                     const T *rj = stage + jj * RS;
                     T gj[NMAX], gv[NMAX];
@@ -342,7 +343,6 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_loss_fast_kernel(con
                     const T t = gtanh(h[i] + B0s[ti * NP + pn]), d1 = T(1) - t * t, d2 = T(-2) * t * d1;
                     th[pn] = w1 * d1;                                  // zero for the padding neurons (w1 = 0)
                     sp[pn] = w1 * sv[i] * d2;
-                    gb0s[pn] = lam * w1 * d1 + w1 * sv[i] * d2;
                     gw1s[pn] = lam * t + d1 * sv[i];
                 }
             }
@@ -453,7 +453,7 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_loss_fast_kernel(con
             T acc[4] = {T(0), T(0), T(0), T(0)};
             for (unsigned m = tm[t]; m; m &= m - 1) {
                 const T *rec = atoms_s + (size_t)(__ffs(m) - 1) * per_atom;
-                const T gb = rec[off_gb0 + pn], tw = rec[off_th + pn];
+                const T tw = rec[off_th + pn], gb = lam * tw + rec[off_sp + pn];   // d/d b0 of that atom
                 T eq[4], eu[4];
                 load_vec<T, 4>(rec + 4 * kc, eq);
                 load_vec<T, 4>(rec + NDP + 4 * kc, eu);
@@ -469,7 +469,7 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_loss_fast_kernel(con
             T a0 = T(0), a1 = T(0);
             for (unsigned m = tm[t]; m; m &= m - 1) {
                 const T *rec = atoms_s + (size_t)(__ffs(m) - 1) * per_atom;
-                a0 += rec[off_gb0 + pn]; a1 += rec[off_gw1 + pn];
+                a0 += lam * rec[off_th + pn] + rec[off_sp + pn]; a1 += rec[off_gw1 + pn];
             }
             g_b0[x] += a0; g_w1[x] += a1;
         }
@@ -534,7 +534,7 @@ static int launch_nep_loss_fast(const NepArgs<T> &A, const T *coeffs, const NepL
                          (size_t)NEP_APB * nepl_fast_atom_elems<NMAX>(A.nneu, A.ntypes);
     const size_t smem = elems * sizeof(T) + (size_t)NEP_APB * A.umax * sizeof(unsigned short) + 16;
     if (smem > 200 * 1024) return AI2B_OK;
-    constexpr int MINB = sizeof(T) == 4 ? 3 : 2;
+    constexpr int MINB = sizeof(T) == 4 ? 4 : 2;
     const bool vir = L.v_ml != nullptr;
     int sms = 148, dev = 0;
     cudaGetDevice(&dev);
@@ -542,7 +542,10 @@ static int launch_nep_loss_fast(const NepArgs<T> &A, const T *coeffs, const NepL
     long bx = ((long)A.npad + NEP_APB - 1) / NEP_APB;
     const long cap = std::max(1L, (long)sms * std::min<long>(MINB, (long)(227 * 1024 / (smem + 1024))) / A.B);
     if (bx > cap) bx = cap;
-    const bool cluster = bx <= 8;   // portable cluster size: the blocks of a structure reduce among themselves
+    // portable cluster size 8: the blocks of a structure reduce among themselves; up to a third fewer blocks than
+    // the occupancy asks for are traded for that
+    if (bx > 8 && bx <= 12) bx = 8;
+    const bool cluster = bx <= 8;
     bool use_cluster = false;
     auto run = [&](auto kern) -> int {
         AI2B_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
