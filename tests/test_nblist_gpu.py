@@ -63,6 +63,26 @@ def test_triclinic_unwrapped_open_axes(checkers, dt):
         assert np.all(np.diff(d[i, :a[0][i]]) >= 0)
 
 
+@pytest.mark.parametrize("dt", [np.float64, np.float32])
+def test_atoms_many_periods_outside_the_cell(checkers, dt):
+    """Unwrapped trajectories: some atoms sit hundreds of lattice periods away from the cell. Beyond 127 periods
+    the builder leaves its packed-wrap form for full integers; both forms must give the reference algorithm's
+    list. Checked against the plain-C restatement: the reference's own CPU build overruns its bins on such input."""
+    chk = checkers["oracle"]
+    rng = np.random.default_rng(17)
+    cell = np.array([[7.0, 0.3, 0.1], [1.5, 6.5, 0.2], [-0.7, 0.9, 8.0]])
+    frac = rng.random((80, 3))
+    types = rng.integers(0, 2, 80).astype(np.int32)
+    for far in (100, 400):   # within / beyond the packed range
+        k = rng.integers(-far, far + 1, (80, 3))
+        k[::3] = 0           # a third of the atoms stay at home
+        pos = ((frac + k) @ cell).astype(dt)
+        a = _gpu(cell.astype(dt), types, pos, 5.5, 160)
+        b = chk.nblist(cell.astype(dt), types, pos, 5.5, 160)
+        util.assert_nblist_equal(a, b[:3])
+        assert a[0][::3].min() > 0   # (like the reference, only images within the supercell range count: far atoms get none)
+
+
 def test_tiny_cell_many_images(checkers):
     chk = _chk(checkers)
     rng = np.random.default_rng(9)
