@@ -59,6 +59,17 @@ def build_cuda(force=False, verbose=False):
     return lib
 
 
+def build_bench(force=False):
+    """libai2b_fma_peak.so: the FMA-pipe microbenchmark bench.py uses for its roofline denominator (not linked
+    into the product library)."""
+    src = os.path.join(CSRC, "bench", "fma_peak.cu")
+    out = os.path.join(LIBDIR, "libai2b_fma_peak.so")
+    if force or _stale(out, [src]):
+        subprocess.check_call([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-shared", "-Xcompiler",
+                               "-fPIC", "-o", out, src, "-lcudart"])
+    return out
+
+
 GLUE = {"libmtpr_bind.so": ["mtpr_bind.cpp"], "libnep_bind.so": ["nep_bind.cpp"], "libfvt_sr_op_bind.so": ["fvt_sr_op_bind.cpp"],
         "libfitutils_bind.so": ["fitutils_bind.cpp"]}
 
@@ -98,9 +109,17 @@ def build_glue(force=False, verbose=False):
     return outs
 
 
+def install_python_modules():
+    """Python modules the reference's loader expects to find beside the libraries: ``nblist`` (it does
+    ``sys.path.append(lib_dir); import nblist``, ai2pot/fromcc/__init__.py:52-58)."""
+    shutil.copyfile(os.path.join(HERE, "fromcc", "nblist_toplevel.py"), os.path.join(LIBDIR, "nblist.py"))
+
+
 def build(force=False, verbose=False):
     lib = build_cuda(force, verbose)
     build_glue(force, verbose)
+    build_bench(force)
+    install_python_modules()
     return lib
 
 

@@ -166,10 +166,21 @@ class NeighborBuilder:
         self._ws = None
         self._out = None
 
-    def build(self, cell, coords, rcut, umax, is_cart=True, pbc=(True, True, True), ncentres=None):
+    @staticmethod
+    def new_outputs(nc, umax, dtype, dev):
+        return (torch.empty(nc, dtype=torch.int32, device=dev), torch.empty(nc, umax, dtype=torch.int32, device=dev),
+                torch.empty(nc, umax, 3, dtype=dtype, device=dev), torch.zeros(2, dtype=torch.int32, device=dev))
+
+    def build(self, cell, coords, rcut, umax, is_cart=True, pbc=(True, True, True), ncentres=None, cbegin=0, reuse_bins=False,
+              out=None, open_extent=None):
         """cell: host array [3,3]; coords: CUDA tensor [N,3] (float32/float64). With `ncentres`
-        rows are built for the first ncentres atoms only (the rest are ghosts).
-        Returns (numneigh[Nc], firstneigh[Nc,umax], rcs[Nc,umax,3], status[2]) device tensors."""
+        rows are built for the atoms [cbegin, ncentres) only (the rest are candidates only, e.g. ghosts);
+        reuse_bins: this builder's workspace still holds the binning of the same atoms (see
+        ai2b_nblist_build_range_*).
+        open_extent: (lo, hi) fractional bounds of the atoms along a non-periodic first axis, if the caller knows them.
+        out: (numneigh, firstneigh, rcs, status) tensors of the caller to write into (several passes that share
+        one builder keep their own outputs).
+        Returns (numneigh[Nc], firstneigh[Nc,umax], rcs[Nc,umax,3], status[2]) device tensors, Nc = ncentres - cbegin."""
         if not coords.is_cuda:
             raise Ai2bError("coords must be a CUDA tensor")
         suf, _ = _suf(coords.dtype)
@@ -181,20 +192,52 @@ class NeighborBuilder:
         dev = coords.device
         if self._ws is None or self._ws.numel() < need or self._ws.device != dev:
             self._ws = torch.empty(need, dtype=torch.uint8, device=dev)
-        nc = n if ncentres is None else int(ncentres)
-        key = (nc, umax, coords.dtype, dev)
-        if self._out is None or self._out[0] != key:
-            self._out = (key, torch.empty(nc, dtype=torch.int32, device=dev),
-                         torch.empty(nc, umax, dtype=torch.int32, device=dev),
-                         torch.empty(nc, umax, 3, dtype=coords.dtype, device=dev),
-                         torch.zeros(2, dtype=torch.int32, device=dev))
-        _, nn, fn, rcs, status = self._out
+        cend = n if ncentres is None else int(ncentres)
+        nc = cend - int(cbegin)
+        if out is not None:
+            nn, fn, rcs, status = out
+        else:
+            key = (nc, umax, coords.dtype, dev)
+            if self._out is None or self._out[0] != key:
+                self._out = (key,) + self.new_outputs(nc, umax, coords.dtype, dev)
+            _, nn, fn, rcs, status = self._out
         coords = coords.contiguous()
-        _check(getattr(lib(), "ai2b_nblist_build_ghost_" + suf)(
-            C.c_int(n), C.c_int(nc), hcell.ctypes.data_as(C.c_void_p), _ptr(coords), C.c_int(1 if is_cart else 0), C.c_double(rcut),
-            hpbc.ctypes.data_as(C.c_void_p), C.c_int(umax), _ptr(nn), _ptr(fn), _ptr(rcs), _ptr(status), _ptr(self._ws),
-            C.c_size_t(self._ws.numel()), _stream()))
+        ext = None
+        if open_extent is not None and not all(pbc):
+            hext = np.ascontiguousarray([open_extent[0], 0.0, 0.0, open_extent[1], 1.0, 1.0], np.float64)
+            if pbc[0] or not (pbc[1] and pbc[2]):
+                raise Ai2bError("open_extent is taken for a cell that is open along its first axis only")
+            ext = hext.ctypes.data_as(C.c_void_p)
+        _check(getattr(lib(), "ai2b_nblist_build_range_" + suf)(
+            C.c_int(n), C.c_int(int(cbegin)), C.c_int(cend), hcell.ctypes.data_as(C.c_void_p), _ptr(coords), C.c_int(1 if is_cart else 0),
+            C.c_double(rcut), hpbc.ctypes.data_as(C.c_void_p), ext, C.c_int(umax), C.c_int(1 if reuse_bins else 0), _ptr(nn), _ptr(fn),
+            _ptr(rcs), _ptr(status), _ptr(self._ws), C.c_size_t(self._ws.numel()), _stream()))
         return nn, fn, rcs, status
+
+
+def nblist_build_batch(cells, binum, coords, rcut, umax, is_cart=True, pbc=(True, True, True)):
+    """Neighbour tensors of a padded batch in one launch (ai2b_nblist_build_batch_*).
+    cells: host array [B,3,3]; binum: CUDA int32 [B]; coords: CUDA [B,Np,3] (float32/float64).
+    Returns a dict with binum, bilist, bnumneigh, bfirstneigh, brcs, status (device tensors)."""
+    if not coords.is_cuda:
+        raise Ai2bError("coords must be a CUDA tensor")
+    suf, _ = _suf(coords.dtype)
+    B, npad = int(coords.shape[0]), int(coords.shape[1])
+    dev = coords.device
+    npdt = np.float64 if suf == "f64" else np.float32
+    dcells = torch.from_numpy(np.ascontiguousarray(np.asarray(cells, dtype=npdt).reshape(B, 9))).to(dev)
+    hpbc = np.ascontiguousarray([1 if p else 0 for p in pbc], np.int32)
+    binum = binum.to(torch.int32).contiguous()
+    out = dict(binum=binum, bilist=torch.empty(B, npad, dtype=torch.int32, device=dev),
+               bnumneigh=torch.empty(B, npad, dtype=torch.int32, device=dev),
+               bfirstneigh=torch.empty(B, npad, umax, dtype=torch.int32, device=dev),
+               brcs=torch.empty(B, npad, umax, 3, dtype=coords.dtype, device=dev),
+               status=torch.zeros(2, dtype=torch.int32, device=dev))
+    _check(getattr(lib(), "ai2b_nblist_build_batch_" + suf)(
+        C.c_int(B), C.c_int(npad), _ptr(binum), _ptr(dcells), _ptr(coords.contiguous()), C.c_int(1 if is_cart else 0), C.c_double(rcut),
+        hpbc.ctypes.data_as(C.c_void_p), C.c_int(umax), _ptr(out["bilist"]), _ptr(out["bnumneigh"]), _ptr(out["bfirstneigh"]),
+        _ptr(out["brcs"]), _ptr(out["status"]), _stream()))
+    return out
 
 
 def sort_rows_by_distance(numneigh, firstneigh, rcs):
@@ -220,8 +263,10 @@ def _nep_workspace(model, B, dtype, device):
     return ws
 
 
-def nep_efv(model, nb, virial=True, out=None):
-    """NEP energy, forces (and virial) of a batch; `model` / `nb` hold device tensors."""
+def nep_efv(model, nb, virial=True, out=None, accumulate=False, ws=None):
+    """NEP energy, forces (and virial) of a batch; `model` / `nb` hold device tensors. accumulate: add onto
+    `out` (ai2b_nep_efv_accumulate_*) instead of overwriting it. ws: a workspace tensor of the caller (calls
+    that may run concurrently on different streams must not share one)."""
     rcs = nb["brcs"]
     suf, cf = _suf(rcs.dtype)
     B, npad, umax, nbargs = _nb_args(nb)
@@ -232,8 +277,9 @@ def nep_efv(model, nb, virial=True, out=None):
         v = torch.empty(B, 9, dtype=rcs.dtype, device=rcs.device) if virial else None
     else:
         e, f, v = out
-    ws = _nep_workspace(model, B, rcs.dtype, rcs.device)
-    _check(getattr(lib(), "ai2b_nep_efv_" + suf)(
+    if ws is None:
+        ws = _nep_workspace(model, B, rcs.dtype, rcs.device)
+    _check(getattr(lib(), ("ai2b_nep_efv_accumulate_" if accumulate else "ai2b_nep_efv_") + suf)(
         _ptr(e), _ptr(f), _ptr(v), C.c_int(int(model["chebyshev_size"])), C.c_int(int(model["n_radial"])),
         C.c_int(int(model["n_angular"])), C.c_int(int(model["l_max"])), C.c_int(int(model["num_neurons"])),
         _ptr(model["coeffs"]), _ptr(model["w0"]), _ptr(model["b0"]), _ptr(model["w1"]), _ptr(model["type_bias"]),

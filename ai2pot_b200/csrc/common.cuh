@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <cstdarg>
 #include <cstdio>
+#include <mutex>
 #include <type_traits>
 #include "../../include/ai2pot_b200.h"
 
@@ -15,6 +16,7 @@ void set_error(const char *fmt, ...);
     do {                                                                                       \
         cudaError_t e_ = (call);                                                               \
         if (e_ != cudaSuccess) {                                                               \
+            (void)cudaGetLastError(); /* a non-sticky error must not surface at a later launch check */ \
             ::ai2b::set_error("%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, \
                               __LINE__);                                                       \
             return AI2B_ERR_CUDA;                                                              \
@@ -28,6 +30,52 @@ void set_error(const char *fmt, ...);
             return (code);                                                                     \
         }                                                                                      \
     } while (0)
+
+// ---- per-device launch set-up ---------------------------------------------------------------------
+// The opt-in to more than 48 KB of dynamic shared memory (cudaFuncSetAttribute), the occupancy of a
+// kernel and the SM count are properties of one device, so a process that drives several GPUs needs
+// them once per device. One KernelSetup object (function-local static) per kernel instantiation
+// remembers, for every device ordinal, what has been configured; access is serialised by its mutex
+// so that host threads may launch concurrently.
+constexpr int MAX_DEVICES = 64;
+
+struct KernelSetup {
+    std::mutex mu;
+    size_t smem[MAX_DEVICES] = {};       // largest dynamic shared-memory size opted in so far
+    size_t occ_smem[MAX_DEVICES] = {};   // shared-memory size per_sm was computed for (+1, 0 = never)
+    int per_sm[MAX_DEVICES] = {};
+};
+
+// Makes `kern` launchable with `smem` bytes of dynamic shared memory on the current device; if
+// per_sm is given, also returns the number of resident blocks of `threads` threads per SM (>= 1).
+template <typename Kern>
+static int kernel_setup(KernelSetup &ks, Kern kern, size_t smem, int threads = 0, int *per_sm = nullptr)
+{
+    int dev = 0;
+    AI2B_CUDA(cudaGetDevice(&dev));
+    const bool cached = dev >= 0 && dev < MAX_DEVICES;
+    std::lock_guard<std::mutex> guard(ks.mu);
+    if (!cached || smem > ks.smem[dev]) {
+        if (smem > 48 * 1024)
+            AI2B_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (cached) ks.smem[dev] = smem;
+    }
+    if (per_sm) {
+        if (!cached || ks.occ_smem[dev] != smem + 1) {
+            int n = 0;
+            AI2B_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, threads, smem));
+            if (n < 1) n = 1;
+            if (!cached) { *per_sm = n; return AI2B_OK; }
+            ks.per_sm[dev] = n;
+            ks.occ_smem[dev] = smem + 1;
+        }
+        *per_sm = ks.per_sm[dev];
+    }
+    return AI2B_OK;
+}
+
+// SM count of the current device (cached per device ordinal).
+int sm_count();
 
 constexpr unsigned FULL_MASK = 0xffffffffu;
 constexpr int WARP = 32;

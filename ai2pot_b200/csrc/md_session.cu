@@ -63,6 +63,9 @@ void release_step_buffers(ai2b_md_session *s)
     cudaFreeHost(s->h_force);
     s->d_x = nullptr; s->d_types = s->d_numneigh = s->d_firstneigh = s->d_ilist = nullptr;
     s->d_rcs = s->d_force = nullptr; s->d_nbws = s->d_ws = nullptr; s->h_force = nullptr;
+    // nothing is usable until ensure_capacity has run to its end: a growth that failed half-way (out of
+    // memory) must make the next call allocate afresh instead of running on freed or partial buffers
+    s->cap_all = s->cap_local = 0;
 }
 
 int ensure_capacity(ai2b_md_session *s, int nlocal, int nall)

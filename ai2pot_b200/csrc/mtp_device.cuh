@@ -149,18 +149,6 @@ struct PairState {
 // ---------------------------------------------------------------------------------------------
 // host helpers
 // ---------------------------------------------------------------------------------------------
-static int g_sm_count = 0;
-static inline int sm_count()
-{
-    if (!g_sm_count) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (g_sm_count <= 0) g_sm_count = 148;
-    }
-    return g_sm_count;
-}
-
 static inline size_t up256(size_t n) { return (n + 255) & ~size_t(255); }
 static inline int ndense_pad(const MtpProgramDev &P) { return (P.ndense + 3) & ~3; }
 static inline int nbasic_pad(const MtpProgramDev &P) { return (P.nb + 3) & ~3; }
@@ -179,16 +167,5 @@ static inline MtpWs mtp_ws_layout(const MtpProgramDev &P, int B, int npad, int n
     L.total = L.eb + up256(atoms * nbasic_pad(P) * elem);
     return L;
 }
-
-template <typename Kern>
-static int set_smem(Kern kern, size_t smem, size_t *configured)
-{
-    if (smem > *configured) {
-        AI2B_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        *configured = smem;
-    }
-    return AI2B_OK;
-}
-
 
 }  // namespace ai2b

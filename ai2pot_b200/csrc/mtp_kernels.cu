@@ -614,8 +614,8 @@ static int launch_contract(const MtpProgramDev &P, const MtpArgs<T> &A, long ato
 {
     const size_t smem = contract_smem<T, MODE>(P, TA, SMEMTAB);
     auto kern = mtp_contract_kernel<T, TA, MODE, SMEMTAB>;
-    static size_t configured = 0;
-    if (int rc = set_smem(kern, smem, &configured)) return rc;
+    static KernelSetup setup;
+    if (int rc = kernel_setup(setup, kern, smem)) return rc;
     long tiles = (atoms_upper + TA - 1) / TA;
     if (tiles > sm_count()) tiles = sm_count();      // persistent: one block per SM walks over the tiles
     kern<<<(unsigned)tiles, MTP_CWARPS * 32, smem, st>>>(P, A);
@@ -667,13 +667,9 @@ static int launch_mtp_v(const ai2b_mtp_program *prog, MtpArgs<T> A, void *ws, cu
         if (ok) {
             const size_t smem = (sizeof(T) * (size_t)(16 * (ncan(KD) | 1) + 32 * NMU) + sizeof(int) * 3 * NMU * 32) * MTP_WARPS;
             auto kern = mtp_fwd_lanes_kernel<T, KD, CSP, NMU>;
-            static size_t configured = 0;
-            static int per_sm = 0;
-            if (smem > configured || per_sm == 0) {
-                if (int rc = set_smem(kern, smem, &configured)) return rc;
-                AI2B_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, MTP_WARPS * 32, smem));
-                if (per_sm < 1) per_sm = 1;
-            }
+            static KernelSetup setup;
+            int per_sm = 1;
+            if (int rc = kernel_setup(setup, kern, smem, MTP_WARPS * 32, &per_sm)) return rc;
             long blocks = (long)sm_count() * per_sm;
             if (blocks > need) blocks = need;
             kern<<<(unsigned)blocks, MTP_WARPS * 32, smem, st>>>(P, A);
@@ -684,13 +680,9 @@ static int launch_mtp_v(const ai2b_mtp_program *prog, MtpArgs<T> A, void *ws, cu
     if (!fwd_done) {   // A: forward with warp reductions (levels 18, 20)
         const size_t smem = sizeof(T) * (size_t)(A.ndp + MTP_MAX_MU * 32) * MTP_WARPS;
         auto kern = mtp_fwd_kernel<T, KD, CSP>;
-        static size_t configured = 0;
-        static int per_sm = 0;
-        if (smem > configured || per_sm == 0) {
-            if (int rc = set_smem(kern, smem, &configured)) return rc;
-            AI2B_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, MTP_WARPS * 32, smem));
-            if (per_sm < 1) per_sm = 1;
-        }
+        static KernelSetup setup;
+        int per_sm = 1;
+        if (int rc = kernel_setup(setup, kern, smem, MTP_WARPS * 32, &per_sm)) return rc;
         long blocks = (long)sm_count() * per_sm;
         if (blocks > need) blocks = need;
         kern<<<(unsigned)blocks, MTP_WARPS * 32, smem, st>>>(P, A);
@@ -704,13 +696,9 @@ static int launch_mtp_v(const ai2b_mtp_program *prog, MtpArgs<T> A, void *ws, cu
         const size_t smem = sizeof(int4) * A.ndp + sizeof(T) * 4 * A.ndp +
                             sizeof(T) * force_warp_elems<T>(A.ndp, A.nbp, P.nmus) * MTP_WARPS;
         auto kern = mtp_force_kernel<T, MODE, KD, CSP>;
-        static size_t configured = 0;
-        static int per_sm = 0;
-        if (smem > configured || per_sm == 0) {
-            if (int rc = set_smem(kern, smem, &configured)) return rc;
-            AI2B_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, MTP_WARPS * 32, smem));
-            if (per_sm < 1) per_sm = 1;
-        }
+        static KernelSetup setup;
+        int per_sm = 1;
+        if (int rc = kernel_setup(setup, kern, smem, MTP_WARPS * 32, &per_sm)) return rc;
         long blocks = (long)sm_count() * per_sm;
         if (blocks > need) blocks = need;
         kern<<<(unsigned)blocks, MTP_WARPS * 32, smem, st>>>(P, A);

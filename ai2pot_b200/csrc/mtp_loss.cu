@@ -522,8 +522,8 @@ static int launch_loss_contract(const MtpProgramDev &P, const MtpArgs<T> &A, con
 {
     const size_t smem = loss_contract_smem(P, sizeof(T), TA, SMEMTAB);
     auto kern = mtp_loss_contract_kernel<T, TA, SMEMTAB>;
-    static size_t configured = 0;
-    if (int rc = set_smem(kern, smem, &configured)) return rc;
+    static KernelSetup setup;
+    if (int rc = kernel_setup(setup, kern, smem)) return rc;
     kern<<<(unsigned)((atoms_upper + TA - 1) / TA), MTP_CWARPS * 32, smem, st>>>(P, A, L);
     AI2B_CUDA(cudaGetLastError());
     return AI2B_OK;
@@ -551,13 +551,9 @@ static int launch_loss_bwd_v(const ai2b_mtp_program *prog, MtpArgs<T> A, LossArg
     {
         const size_t smem = sizeof(T) * (size_t)(2 * A.ndp + 2 * MTP_MAX_MU * 32) * MTP_WARPS;
         auto kern = mtp_loss_fwd_kernel<T, KD, CSP>;
-        static size_t configured = 0;
-        static int per_sm = 0;
-        if (smem > configured || per_sm == 0) {
-            if (int rc = set_smem(kern, smem, &configured)) return rc;
-            AI2B_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, MTP_WARPS * 32, smem));
-            if (per_sm < 1) per_sm = 1;
-        }
+        static KernelSetup setup;
+        int per_sm = 1;
+        if (int rc = kernel_setup(setup, kern, smem, MTP_WARPS * 32, &per_sm)) return rc;
         long blocks = (long)sm_count() * per_sm;
         if (blocks > need) blocks = need;
         kern<<<(unsigned)blocks, MTP_WARPS * 32, smem, st>>>(P, A, L);
@@ -580,13 +576,9 @@ static int launch_loss_bwd_v(const ai2b_mtp_program *prog, MtpArgs<T> A, LossArg
     {
         const size_t smem = sizeof(T) * (size_t)(5 * A.ndp + 2 * A.nbp + 2 * MTP_MAX_MU * 32) * MTP_WARPS;
         auto kern = mtp_loss_coeff_kernel<T, KD, CSP>;
-        static size_t configured = 0;
-        static int per_sm = 0;
-        if (smem > configured || per_sm == 0) {
-            if (int rc = set_smem(kern, smem, &configured)) return rc;
-            AI2B_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, MTP_WARPS * 32, smem));
-            if (per_sm < 1) per_sm = 1;
-        }
+        static KernelSetup setup;
+        int per_sm = 1;
+        if (int rc = kernel_setup(setup, kern, smem, MTP_WARPS * 32, &per_sm)) return rc;
         long blocks = (long)sm_count() * per_sm;
         if (blocks > need) blocks = need;
         kern<<<(unsigned)blocks, MTP_WARPS * 32, smem, st>>>(P, A, L);

@@ -20,6 +20,20 @@ void set_error(const char *fmt, ...)
     va_end(ap);
 }
 
+int sm_count()
+{
+    static std::mutex mu;
+    static int counts[MAX_DEVICES] = {};
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    const bool cached = dev >= 0 && dev < MAX_DEVICES;
+    std::lock_guard<std::mutex> guard(mu);
+    if (cached && counts[dev] > 0) return counts[dev];
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    if (cached) counts[dev] = n;
+    return n;
+}
+
 }  // namespace ai2b
 
 using namespace ai2b;

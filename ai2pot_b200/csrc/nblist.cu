@@ -53,7 +53,8 @@ struct NbParams {
     double rc2;          // rcut^2 as the reference forms it
     float rc2_lo, rc2_hi, eps_lo, eps_hi;   // the two thresholds -/+ 2e-6 relative (float builds)
     int n, umax, maxbins;
-    int ncentre;         // rows are built for atoms [0, ncentre); the rest are neighbours only (ghosts)
+    int ncentre;         // rows are built for atoms [cbegin, ncentre); the rest are neighbours only (ghosts)
+    int cbegin;          // first centre; its row is row 0 of the outputs
 };
 
 __device__ __forceinline__ double mul_rn(double a, double b) { return __dmul_rn(a, b); }
@@ -257,23 +258,13 @@ __global__ void nb_scan3_kernel(const NbGrid *__restrict__ gp, int *__restrict__
 
 // all axes periodic: grid parameters are known on the host, so one kernel zeroes the bin counters,
 // resets the status words and writes the grid description
-template <typename T>
-__global__ void nb_setup_periodic_kernel(NbParams<T> P, NbGrid *__restrict__ g, int *__restrict__ count, int ncount, int *__restrict__ status)
+__global__ void nb_setup_periodic_kernel(NbGrid host_grid, NbGrid *__restrict__ g, int *__restrict__ count, int ncount, int *__restrict__ status)
 {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < ncount) count[i] = 0;
     if (i == 0) {
         status[0] = 0; status[1] = 0;
-        long total = 1;
-        for (int k = 0; k < 3; k++) {
-            g->nb[k] = P.nbh[k];
-            g->R[k] = (int)ceil(P.rcut_m / (P.dplane[k] / P.nbh[k]));
-            g->lo[k] = 0.0;
-            g->scale[k] = (double)P.nbh[k];
-            total *= P.nbh[k];
-        }
-        g->total = (int)total;
-        g->bigwrap = 0;
+        *g = host_grid;
     }
 }
 
@@ -368,12 +359,12 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
         const int4 si = sinfo[a];
         const int i = si.x;
         const int wi = nb_pack3(si.y, si.z, si.w);   // its bias is the one that survives in shift - wrap_j + wrap_i
-        if (i >= P.ncentre) continue;
+        if (i >= P.ncentre || i < P.cbegin) continue;
         const int bin_i = ainfo[i].x;
         const int bz = bin_i % g.nb[2], by = (bin_i / g.nb[2]) % g.nb[1], bx = bin_i / (g.nb[2] * g.nb[1]);
         int count = 0;
-        int *frow = firstneigh + (size_t)i * P.umax;
-        TO *rrow = rcs + (size_t)i * P.umax * 3;
+        int *frow = firstneigh + (size_t)(i - P.cbegin) * P.umax;
+        TO *rrow = rcs + (size_t)(i - P.cbegin) * P.umax * 3;
 
         const bool reuse = nnb <= 32 && bin_i == cached_bin;
         cached_bin = nnb <= 32 ? bin_i : -1;
@@ -510,7 +501,7 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
             frow[k] = -1;
             rrow[3 * k] = TO(0); rrow[3 * k + 1] = TO(0); rrow[3 * k + 2] = TO(0);
         }
-        if (lane == 0) numneigh[i] = min(count, P.umax);
+        if (lane == 0) numneigh[i - P.cbegin] = min(count, P.umax);
         local_max = max(local_max, count);
     }
     if (lane == 0 && local_max > 0) {
@@ -592,14 +583,18 @@ static void plane_distances(const T *cell, T *d)
     }
 }
 
+// Rows for the centres [cbegin, ncentre) of the n atoms. reuse_bins: the workspace still holds the bins of an
+// earlier call with the same atoms, cell, cutoff and flags, so only the row pass runs (d_status is then
+// accumulated into, not reset).
 template <typename T, typename TO = T>
 static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, int is_cart, double rcut_in, const int *pbc, int umax,
-                        int *d_numneigh, int *d_firstneigh, TO *d_rcs, int *d_status, void *ws, size_t ws_bytes, cudaStream_t st)
+                        int *d_numneigh, int *d_firstneigh, TO *d_rcs, int *d_status, void *ws, size_t ws_bytes, cudaStream_t st,
+                        int cbegin = 0, bool reuse_bins = false, const double *open_ext = nullptr)
 {
     AI2B_REQUIRE(h_cell && pbc && d_status, AI2B_ERR_INVALID, "ai2b_nblist_build: NULL argument");
-    AI2B_REQUIRE(n >= 0 && umax >= 0 && rcut_in > 0 && ncentre >= 0 && ncentre <= n, AI2B_ERR_INVALID,
-                 "ai2b_nblist_build: bad size or cutoff");
-    if (n == 0 || ncentre == 0) return AI2B_OK;
+    AI2B_REQUIRE(n >= 0 && umax >= 0 && rcut_in > 0 && ncentre >= 0 && ncentre <= n && cbegin >= 0 && cbegin <= ncentre,
+                 AI2B_ERR_INVALID, "ai2b_nblist_build: bad size, centre range or cutoff");
+    if (n == 0 || ncentre == cbegin) return AI2B_OK;
     AI2B_REQUIRE(d_coords && d_numneigh && d_firstneigh && d_rcs, AI2B_ERR_INVALID, "ai2b_nblist_build: NULL argument");
     const int maxbins = nb_maxbins(n);
     const NbLayout L = nb_layout<T>(n, maxbins);
@@ -626,7 +621,7 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
     if (sizeof(T) == 8) { volatile double r2 = (double)rcut * (double)rcut; P.rc2 = r2; }
     P.rc2_lo = (float)(P.rc2 * (1.0 - 2e-6)); P.rc2_hi = (float)(P.rc2 * (1.0 + 2e-6));
     P.eps_lo = (float)(1e-3 * (1.0 - 2e-6)); P.eps_hi = (float)(1e-3 * (1.0 + 2e-6));
-    P.n = n; P.umax = umax; P.maxbins = maxbins; P.ncentre = ncentre;
+    P.n = n; P.umax = umax; P.maxbins = maxbins; P.ncentre = ncentre; P.cbegin = cbegin;
     bool any_open = false;
     long prod = 1;
     for (int k = 0; k < 3; k++) {
@@ -657,6 +652,35 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
         int cap = (int)std::floor(std::pow((double)maxbins / (double)prod, 1.0 / nopen));
         for (int k = 0; k < 3; k++) if (!pbc[k]) P.nbh[k] = cap < 1 ? 1 : cap;
     }
+    // The grid is known on the host when every axis is periodic, or when the caller gives the fractional extent
+    // of the atoms along the open axes (atoms outside it are clamped into the edge bins, which keeps every
+    // pair within reach of the +-1 bin search: an extent that is a little off costs time, not pairs).
+    NbGrid hg;
+    memset(&hg, 0, sizeof(hg));
+    const bool host_grid = !any_open || open_ext != nullptr;
+    if (host_grid) {
+        long total = 1;
+        for (int k = 0; k < 3; k++) {
+            if (P.per[k]) {
+                hg.nb[k] = P.nbh[k];
+                hg.R[k] = (int)std::ceil(P.rcut_m / (P.dplane[k] / P.nbh[k]));
+                hg.lo[k] = 0.0;
+                hg.scale[k] = (double)P.nbh[k];
+            } else {
+                const double lo = open_ext[k], hi = open_ext[3 + k];
+                const double span = std::fmax(hi - lo, 1e-12);
+                int nb = (int)std::floor(span * P.dplane[k] / P.rcut_m);
+                nb = nb < 1 ? 1 : (nb > P.nbh[k] ? P.nbh[k] : nb);
+                hg.nb[k] = nb;
+                hg.R[k] = 1;
+                hg.lo[k] = lo;
+                hg.scale[k] = nb / span;
+            }
+            total *= hg.nb[k];
+        }
+        hg.total = (int)total;
+        prod = total;
+    }
 
     unsigned char *w = (unsigned char *)ws;
     NbGrid *grid = (NbGrid *)(w + L.grid);
@@ -670,13 +694,15 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
     const int tb = 256, nblk = (n + tb - 1) / tb;
     const T *pos = d_coords;
     if (!is_cart) {
-        nb_frac2cart_kernel<T><<<nblk, tb, 0, st>>>(P, d_coords, cart);
+        if (!reuse_bins) nb_frac2cart_kernel<T><<<nblk, tb, 0, st>>>(P, d_coords, cart);
         pos = cart;
     }
-    const bool small_grid = !any_open && prod + 1 <= 256 * 1024;
-    if (small_grid) {
+    const bool small_grid = host_grid && prod + 1 <= 256 * 1024;
+    if (reuse_bins) {
+        // bins, bin-ordered positions and (for fractional input) Cartesian positions are in the workspace already
+    } else if (small_grid) {
         const int ncount = (int)prod + 1;
-        nb_setup_periodic_kernel<T><<<(ncount + 255) / 256, 256, 0, st>>>(P, grid, count, ncount, d_status);
+        nb_setup_periodic_kernel<<<(ncount + 255) / 256, 256, 0, st>>>(hg, grid, count, ncount, d_status);
         nb_count_kernel<T><<<nblk, tb, 0, st>>>(P, grid, pos, ainfo, count);
         if (ncount <= 16 * SCAN_BLOCK) {
             nb_scan_small_kernel<<<1, SCAN_BLOCK, 0, st>>>(grid, count, start, cursor);
@@ -697,13 +723,8 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
         nb_scan2_kernel<<<1, SCAN_BLOCK, 0, st>>>(grid, bsum);
         nb_scan3_kernel<<<sblk, SCAN_BLOCK, 0, st>>>(grid, start, bsum, cursor);
     }
-    nb_fill_kernel<T><<<nblk, tb, 0, st>>>(P, pos, ainfo, cursor, spos, sinfo);
-    int sms = 148;
-    {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    }
+    if (!reuse_bins) nb_fill_kernel<T><<<nblk, tb, 0, st>>>(P, pos, ainfo, cursor, spos, sinfo);
+    const int sms = sm_count();
     long blocks = ((long)n + NB_WARPS - 1) / NB_WARPS;
     if (blocks > (long)sms * 8) blocks = (long)sms * 8;
     nb_build_kernel<T, TO><<<(unsigned)blocks, NB_WARPS * 32, 0, st>>>(P, grid, start, ainfo, spos, sinfo, d_numneigh, d_firstneigh, d_rcs, d_status);
@@ -711,9 +732,218 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
     return AI2B_OK;
 }
 
+
+// ---- padded batch of small cells: one launch --------------------------------------------------------
+// A training set holds many small periodic structures (tens to hundreds of atoms); the reference's
+// dataset builds one list per frame and pads every array to the largest structure
+// (ai2pot/data/mlffdataset.py:61-90). For such cells a cell list brings nothing (1-3 bins per axis):
+// every (centre, atom, image) triple of the reference's supercell is tested instead, which is the
+// reference's membership rule by construction. One block per (structure, chunk of centres); the
+// structure's positions are staged through shared memory in tiles; one warp per centre, lanes over
+// the atoms of a tile, the image loops are uniform across the warp.
+constexpr int NBB_WARPS = 8;
+constexpr int NBB_TILE = 1024;      // atoms staged per tile
+constexpr int NBB_CPB = 32;         // centres per block
+
+template <typename T>
+struct NbBatchParams {
+    int B, npad, umax, is_cart, per[3];
+    T rcut;
+    double rc2;
+    float rc2_lo, rc2_hi, eps_lo, eps_hi;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(NBB_WARPS * 32)
+nb_batch_kernel(NbBatchParams<T> P, const int *__restrict__ binum, const T *__restrict__ cells, const T *__restrict__ coords,
+                int *__restrict__ bilist, int *__restrict__ bnumneigh, int *__restrict__ bfirstneigh, T *__restrict__ brcs,
+                int *__restrict__ status)
+{
+    __shared__ T s_pos[NBB_TILE * 3];
+    __shared__ T s_cell[9];
+    __shared__ int s_e[3];
+    const int b = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n = min(max(binum[b], 0), P.npad);
+    const int c_begin = blockIdx.x * NBB_CPB;
+    if (c_begin >= P.npad) return;
+    if (threadIdx.x == 0) {
+        // image range per periodic axis: ceil(rcut / interplanar distance), in type T with the operations of
+        // source/nblist/include/structure.h:818-843 (no contraction)
+        T c[9];
+        for (int k = 0; k < 9; k++) c[k] = s_cell[k] = cells[(size_t)b * 9 + k];
+        for (int k = 0; k < 3; k++) {
+            const T *a = c + 3 * ((k == 0) ? 1 : 0), *bb = c + 3 * ((k == 2) ? 1 : 2);
+            const T nx = sub_rn(mul_rn(a[1], bb[2]), mul_rn(a[2], bb[1])), ny = sub_rn(mul_rn(a[2], bb[0]), mul_rn(a[0], bb[2])),
+                    nz = sub_rn(mul_rn(a[0], bb[1]), mul_rn(a[1], bb[0]));
+            const T len = (T)sqrt((double)add_rn(add_rn(mul_rn(nx, nx), mul_rn(ny, ny)), mul_rn(nz, nz)));
+            const T ux = nx / len, uy = ny / len, uz = nz / len;
+            const T d = (T)fabs((double)add_rn(add_rn(mul_rn(c[3 * k], ux), mul_rn(c[3 * k + 1], uy)), mul_rn(c[3 * k + 2], uz)));
+            int e = 0;
+            if (P.per[k]) {
+                const double q = ceil((double)(P.rcut / d));
+                if (!(q < 500.0)) { e = 0; atomicOr(status + 1, 2); }   // degenerate cell: flagged, no images
+                else e = (int)q;
+            }
+            s_e[k] = e;
+        }
+    }
+    __syncthreads();
+    const int e0 = s_e[0], e1 = s_e[1], e2 = s_e[2];
+    const T *cpos = coords + (size_t)b * P.npad * 3;
+    auto cart = [&](int j, T &x, T &y, T &z) {
+        const T f0 = cpos[3 * j], f1 = cpos[3 * j + 1], f2 = cpos[3 * j + 2];
+        if (P.is_cart) { x = f0; y = f1; z = f2; return; }
+        x = add_rn(add_rn(mul_rn(f0, s_cell[0]), mul_rn(f1, s_cell[3])), mul_rn(f2, s_cell[6]));
+        y = add_rn(add_rn(mul_rn(f0, s_cell[1]), mul_rn(f1, s_cell[4])), mul_rn(f2, s_cell[7]));
+        z = add_rn(add_rn(mul_rn(f0, s_cell[2]), mul_rn(f1, s_cell[5])), mul_rn(f2, s_cell[8]));
+    };
+    const unsigned lt_mask = (1u << lane) - 1u;
+    // each warp owns NBB_CPB / NBB_WARPS centres; all warps walk the tiles together (block-wide staging)
+    constexpr int CPW = NBB_CPB / NBB_WARPS;
+    int cnt[CPW];
+    T cx[CPW], cy[CPW], cz[CPW];
+#pragma unroll
+    for (int q = 0; q < CPW; q++) {
+        cnt[q] = 0;
+        const int i = c_begin + warp * CPW + q;
+        cx[q] = cy[q] = cz[q] = T(0);
+        if (i < n) cart(i, cx[q], cy[q], cz[q]);
+    }
+    for (int t0 = 0; t0 < n; t0 += NBB_TILE) {
+        const int tn = min(NBB_TILE, n - t0);
+        __syncthreads();
+        for (int j = threadIdx.x; j < tn; j += blockDim.x) {
+            T x, y, z;
+            cart(t0 + j, x, y, z);
+            s_pos[3 * j] = x; s_pos[3 * j + 1] = y; s_pos[3 * j + 2] = z;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int q = 0; q < CPW; q++) {
+            const int i = c_begin + warp * CPW + q;
+            if (i >= n) continue;
+            int *frow = bfirstneigh + ((size_t)b * P.npad + i) * P.umax;
+            T *rrow = brcs + ((size_t)b * P.npad + i) * P.umax * 3;
+            int count = cnt[q];
+            for (int n0 = -e0; n0 <= e0; n0++)
+            for (int n1 = -e1; n1 <= e1; n1++)
+            for (int n2 = -e2; n2 <= e2; n2++) {
+                const T f0 = T(n0), f1 = T(n1), f2 = T(n2);
+                // shift of this image, applied in the reference's order ((r + a0 n0) + a1 n1) + a2 n2
+                const T s0x = mul_rn(s_cell[0], f0), s0y = mul_rn(s_cell[1], f0), s0z = mul_rn(s_cell[2], f0);
+                const T s1x = mul_rn(s_cell[3], f1), s1y = mul_rn(s_cell[4], f1), s1z = mul_rn(s_cell[5], f1);
+                const T s2x = mul_rn(s_cell[6], f2), s2y = mul_rn(s_cell[7], f2), s2z = mul_rn(s_cell[8], f2);
+                for (int j0 = 0; j0 < tn; j0 += 32) {
+                    const int j = j0 + lane;
+                    bool hit = false;
+                    T d0 = 0, d1 = 0, d2 = 0;
+                    if (j < tn) {
+                        const T ix = add_rn(add_rn(add_rn(s_pos[3 * j], s0x), s1x), s2x);
+                        const T iy = add_rn(add_rn(add_rn(s_pos[3 * j + 1], s0y), s1y), s2y);
+                        const T iz = add_rn(add_rn(add_rn(s_pos[3 * j + 2], s0z), s1z), s2z);
+                        d0 = sub_rn(ix, cx[q]); d1 = sub_rn(iy, cy[q]); d2 = sub_rn(iz, cz[q]);
+                        bool undecided = true;
+                        if (sizeof(T) == 4) {
+                            const float sq = (float)d0 * (float)d0 + (float)d1 * (float)d1 + (float)d2 * (float)d2;
+                            hit = sq < P.rc2_lo && sq > P.eps_hi;
+                            undecided = !hit && !(sq > P.rc2_hi || sq < P.eps_lo);
+                        }
+                        if (undecided) {
+                            const double dd = add_rn(add_rn(mul_rn((double)d0, (double)d0), mul_rn((double)d1, (double)d1)),
+                                                     mul_rn((double)d2, (double)d2));
+                            const double ddT = (double)(T)dd;
+                            hit = (ddT < P.rc2) && (ddT > 1e-3);
+                        }
+                    }
+                    const unsigned bal = __ballot_sync(FULL_MASK, hit);
+                    if (hit) {
+                        const int p = count + __popc(bal & lt_mask);
+                        if (p < P.umax) {
+                            frow[p] = t0 + j;
+                            rrow[3 * p] = d0; rrow[3 * p + 1] = d1; rrow[3 * p + 2] = d2;
+                        }
+                    }
+                    count += __popc(bal);
+                }
+            }
+            cnt[q] = count;
+        }
+    }
+    // padding, counts, centre list; rows of padded atom slots (i >= n) are all padding
+    int local_max = 0;
+#pragma unroll
+    for (int q = 0; q < CPW; q++) {
+        const int i = c_begin + warp * CPW + q;
+        if (i >= P.npad) continue;
+        const int count = i < n ? cnt[q] : 0;
+        int *frow = bfirstneigh + ((size_t)b * P.npad + i) * P.umax;
+        T *rrow = brcs + ((size_t)b * P.npad + i) * P.umax * 3;
+        for (int k = min(count, P.umax) + lane; k < P.umax; k += 32) {
+            frow[k] = -1;
+            rrow[3 * k] = T(0); rrow[3 * k + 1] = T(0); rrow[3 * k + 2] = T(0);
+        }
+        if (lane == 0) {
+            bnumneigh[(size_t)b * P.npad + i] = min(count, P.umax);
+            bilist[(size_t)b * P.npad + i] = i < n ? i : 0;
+        }
+        local_max = max(local_max, count);
+    }
+    if (lane == 0 && local_max > 0) {
+        atomicMax(status, local_max);
+        if (local_max > P.umax) atomicOr(status + 1, 1);
+    }
+}
+
+template <typename T>
+static int nblist_build_batch(int B, int npad, const int *d_binum, const T *d_cells, const T *d_coords, int is_cart, double rcut_in,
+                              const int *pbc, int umax, int *d_bilist, int *d_bnumneigh, int *d_bfirstneigh, T *d_brcs, int *d_status,
+                              cudaStream_t st)
+{
+    AI2B_REQUIRE(B >= 0 && npad >= 0 && umax >= 0 && rcut_in > 0, AI2B_ERR_INVALID, "ai2b_nblist_build_batch: bad size or cutoff");
+    AI2B_REQUIRE(pbc && d_status, AI2B_ERR_INVALID, "ai2b_nblist_build_batch: NULL argument");
+    AI2B_CUDA(cudaMemsetAsync(d_status, 0, 2 * sizeof(int), st));
+    if (B == 0 || npad == 0) return AI2B_OK;
+    AI2B_REQUIRE(d_binum && d_cells && d_coords && d_bilist && d_bnumneigh && d_bfirstneigh && d_brcs, AI2B_ERR_INVALID,
+                 "ai2b_nblist_build_batch: NULL argument");
+    AI2B_REQUIRE(B <= 65535, AI2B_ERR_UNSUPPORTED, "ai2b_nblist_build_batch: more than 65535 structures in one call");
+    NbBatchParams<T> P;
+    memset(&P, 0, sizeof(P));
+    P.B = B; P.npad = npad; P.umax = umax; P.is_cart = is_cart ? 1 : 0;
+    for (int k = 0; k < 3; k++) P.per[k] = pbc[k] ? 1 : 0;
+    const T rcut = (T)rcut_in;                 // the float build casts rcut first (nblist_bind.cc:133)
+    P.rcut = rcut;
+    P.rc2 = (double)rcut * (double)rcut;
+    if (sizeof(T) == 8) { volatile double r2 = (double)rcut * (double)rcut; P.rc2 = r2; }
+    P.rc2_lo = (float)(P.rc2 * (1.0 - 2e-6)); P.rc2_hi = (float)(P.rc2 * (1.0 + 2e-6));
+    P.eps_lo = (float)(1e-3 * (1.0 - 2e-6)); P.eps_hi = (float)(1e-3 * (1.0 + 2e-6));
+    dim3 grid((unsigned)((npad + NBB_CPB - 1) / NBB_CPB), (unsigned)B);
+    nb_batch_kernel<T><<<grid, NBB_WARPS * 32, 0, st>>>(P, d_binum, d_cells, d_coords, d_bilist, d_bnumneigh, d_bfirstneigh, d_brcs,
+                                                        d_status);
+    AI2B_CUDA(cudaGetLastError());
+    return AI2B_OK;
+}
+
 }  // namespace ai2b
 
 using namespace ai2b;
+
+extern "C" int ai2b_nblist_build_batch_f64(int batch_size, int natoms_pad, const int *d_binum, const double *d_cells,
+                                           const double *d_coords, int is_cart, double rcut, const int *h_pbc, int umax,
+                                           int *d_bilist, int *d_bnumneigh, int *d_bfirstneigh, double *d_brcs, int *d_status,
+                                           void *stream)
+{
+    return nblist_build_batch<double>(batch_size, natoms_pad, d_binum, d_cells, d_coords, is_cart, rcut, h_pbc, umax, d_bilist,
+                                      d_bnumneigh, d_bfirstneigh, d_brcs, d_status, (cudaStream_t)stream);
+}
+extern "C" int ai2b_nblist_build_batch_f32(int batch_size, int natoms_pad, const int *d_binum, const float *d_cells,
+                                           const float *d_coords, int is_cart, double rcut, const int *h_pbc, int umax,
+                                           int *d_bilist, int *d_bnumneigh, int *d_bfirstneigh, float *d_brcs, int *d_status,
+                                           void *stream)
+{
+    return nblist_build_batch<float>(batch_size, natoms_pad, d_binum, d_cells, d_coords, is_cart, rcut, h_pbc, umax, d_bilist,
+                                     d_bnumneigh, d_bfirstneigh, d_brcs, d_status, (cudaStream_t)stream);
+}
 
 extern "C" size_t ai2b_nblist_workspace_bytes(int natoms, int is_f64)
 {
@@ -778,6 +1008,27 @@ extern "C" int ai2b_nblist_build_ghost_f32(int natoms, int ncentres, const float
 {
     return nblist_build<float>(natoms, ncentres, h_cell, d_coords, is_cart, rcut, h_pbc, umax, d_numneigh, d_firstneigh, d_rcs,
                                d_status, d_workspace, workspace_bytes, (cudaStream_t)stream);
+}
+// Rows for the centre range [centre_begin, centre_end) only (row 0 of the outputs = centre_begin), all natoms
+// atoms as candidates; with reuse_bins != 0 the binning left in the workspace by an earlier call on the same
+// atoms is used again (a domain evaluated in several passes bins once per set of candidates).
+extern "C" int ai2b_nblist_build_range_f64(int natoms, int centre_begin, int centre_end, const double *h_cell, const double *d_coords,
+                                           int is_cart, double rcut, const int *h_pbc, const double *h_open_extent, int umax,
+                                           int reuse_bins, int *d_numneigh,
+                                           int *d_firstneigh, double *d_rcs, int *d_status, void *d_workspace, size_t workspace_bytes,
+                                           void *stream)
+{
+    return nblist_build<double>(natoms, centre_end, h_cell, d_coords, is_cart, rcut, h_pbc, umax, d_numneigh, d_firstneigh, d_rcs,
+                                d_status, d_workspace, workspace_bytes, (cudaStream_t)stream, centre_begin, reuse_bins != 0, h_open_extent);
+}
+extern "C" int ai2b_nblist_build_range_f32(int natoms, int centre_begin, int centre_end, const float *h_cell, const float *d_coords,
+                                           int is_cart, double rcut, const int *h_pbc, const double *h_open_extent, int umax,
+                                           int reuse_bins, int *d_numneigh,
+                                           int *d_firstneigh, float *d_rcs, int *d_status, void *d_workspace, size_t workspace_bytes,
+                                           void *stream)
+{
+    return nblist_build<float>(natoms, centre_end, h_cell, d_coords, is_cart, rcut, h_pbc, umax, d_numneigh, d_firstneigh, d_rcs,
+                               d_status, d_workspace, workspace_bytes, (cudaStream_t)stream, centre_begin, reuse_bins != 0, h_open_extent);
 }
 // Double-precision positions, single-precision rows: r_j - r_i is formed in double and rounded once, as
 // PairAI2Pot::construct_mlff_input does on the host (interface/lammps/AI2POT/pair_ai2pot.cpp:232-235).

@@ -534,11 +534,8 @@ static int launch_nep_fast(const NepArgs<T> &A, const T *coeffs, cudaStream_t st
                         (size_t)NEP_APB * A.umax * sizeof(unsigned short) + 16;
     if (smem > 96 * 1024) return AI2B_OK;
     auto kern = nep_fast_kernel<T, CSP, MODE, NMAX, MINB>;
-    static size_t configured = 0;
-    if (smem > 48 * 1024 && smem > configured) {
-        AI2B_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = smem;
-    }
+    static KernelSetup setup;
+    if (int rc = kernel_setup(setup, kern, smem)) return rc;
     long blocks = 0;
     int rc = nep_grid((const void *)kern, smem, A.B, A.npad, &blocks);
     if (rc != AI2B_OK) return rc;
@@ -577,11 +574,8 @@ static int launch_nep_csp(NepArgs<T> A, const T *coeffs, void *ws, size_t ws_byt
     const size_t smem = (size_t)NEP_APB * (nep_atom_elems(A.nd, A.nS, A.nneu) * sizeof(T) + (size_t)A.umax * sizeof(unsigned short)) + 16;
     AI2B_REQUIRE(smem <= 200 * 1024, AI2B_ERR_UNSUPPORTED, "NEP model/umax need %zu bytes of shared memory per block", smem);
     auto kern = nep_atom_kernel<T, CSP, MODE>;
-    static size_t configured = 0;
-    if (smem > 48 * 1024 && smem > configured) {
-        AI2B_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = smem;
-    }
+    static KernelSetup setup;
+    if (int rc = kernel_setup(setup, kern, smem)) return rc;
     int sms = 148, dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -620,17 +614,17 @@ extern "C" size_t ai2b_nep_workspace_bytes(int batch_size, int ntypes, int n_rad
 }
 
 #define AI2B_DEF_NEP(SUF, T)                                                                                    \
-    extern "C" int ai2b_nep_efv_##SUF(T *etot, T *force, T *virial, int cs, int n_r, int n_a, int l_max, int nneu, \
-                                      const T *coeffs, const T *w0, const T *b0, const T *w1, const T *bias,    \
-                                      int B, int npad, const int *binum, const int *bilist, const int *numneigh, \
-                                      const int *firstneigh, const T *rcs, const int *types, int ntypes,        \
-                                      int umax, int nghost, T rc_r, T rc_a, const T *qs, void *ws,              \
-                                      size_t ws_bytes, void *stream)                                            \
+    static int nep_efv_entry_##SUF(bool zero, T *etot, T *force, T *virial, int cs, int n_r, int n_a, int l_max, int nneu, \
+                                   const T *coeffs, const T *w0, const T *b0, const T *w1, const T *bias,       \
+                                   int B, int npad, const int *binum, const int *bilist, const int *numneigh,   \
+                                   const int *firstneigh, const T *rcs, const int *types, int ntypes,           \
+                                   int umax, int nghost, T rc_r, T rc_a, const T *qs, void *ws,                 \
+                                   size_t ws_bytes, void *stream)                                               \
     {                                                                                                           \
         AI2B_REQUIRE(etot && force && coeffs && w0 && b0 && w1 && bias && qs && binum && bilist && numneigh &&  \
                          firstneigh && rcs && types, AI2B_ERR_INVALID, "ai2b_nep_efv: NULL argument");          \
         cudaStream_t st = (cudaStream_t)stream;                                                                 \
-        if (B > 0 && npad >= 0) {                                                                               \
+        if (zero && B > 0 && npad >= 0) {                                                                       \
             AI2B_CUDA(cudaMemsetAsync(etot, 0, sizeof(T) * B, st));                                             \
             AI2B_CUDA(cudaMemsetAsync(force, 0, sizeof(T) * 3 * (size_t)B * (npad + nghost), st));              \
             if (virial) AI2B_CUDA(cudaMemsetAsync(virial, 0, sizeof(T) * 9 * B, st));                           \
@@ -640,6 +634,28 @@ extern "C" size_t ai2b_nep_workspace_bytes(int batch_size, int ntypes, int n_rad
                      0, 0, rc_r, rc_a};                                                                         \
         return virial ? launch_nep<T, NEP_EFV>(A, coeffs, ws, ws_bytes, st)                                     \
                       : launch_nep<T, NEP_EF>(A, coeffs, ws, ws_bytes, st);                                     \
+    }                                                                                                           \
+    extern "C" int ai2b_nep_efv_##SUF(T *etot, T *force, T *virial, int cs, int n_r, int n_a, int l_max, int nneu, \
+                                      const T *coeffs, const T *w0, const T *b0, const T *w1, const T *bias,    \
+                                      int B, int npad, const int *binum, const int *bilist, const int *numneigh, \
+                                      const int *firstneigh, const T *rcs, const int *types, int ntypes,        \
+                                      int umax, int nghost, T rc_r, T rc_a, const T *qs, void *ws,              \
+                                      size_t ws_bytes, void *stream)                                            \
+    {                                                                                                           \
+        return nep_efv_entry_##SUF(true, etot, force, virial, cs, n_r, n_a, l_max, nneu, coeffs, w0, b0, w1, bias, B, npad, \
+                                   binum, bilist, numneigh, firstneigh, rcs, types, ntypes, umax, nghost, rc_r, rc_a, qs, ws, \
+                                   ws_bytes, stream);                                                           \
+    }                                                                                                           \
+    extern "C" int ai2b_nep_efv_accumulate_##SUF(T *etot, T *force, T *virial, int cs, int n_r, int n_a, int l_max, \
+                                                 int nneu, const T *coeffs, const T *w0, const T *b0, const T *w1, \
+                                                 const T *bias, int B, int npad, const int *binum, const int *bilist, \
+                                                 const int *numneigh, const int *firstneigh, const T *rcs,      \
+                                                 const int *types, int ntypes, int umax, int nghost, T rc_r, T rc_a, \
+                                                 const T *qs, void *ws, size_t ws_bytes, void *stream)          \
+    {                                                                                                           \
+        return nep_efv_entry_##SUF(false, etot, force, virial, cs, n_r, n_a, l_max, nneu, coeffs, w0, b0, w1, bias, B, npad, \
+                                   binum, bilist, numneigh, firstneigh, rcs, types, ntypes, umax, nghost, rc_r, rc_a, qs, ws, \
+                                   ws_bytes, stream);                                                           \
     }                                                                                                           \
     extern "C" int ai2b_nep_descriptors_##SUF(T *desc, int cs, int n_r, int n_a, int l_max, const T *coeffs,    \
                                               int B, int npad, const int *binum, const int *bilist,             \

@@ -36,34 +36,51 @@ std::string template_file(int level)
     return template_dir() + name;
 }
 
-// compiled programs are cached by the identity and shape of the alpha tables
-struct ProgKey {
-    const void *basic, *times, *map;
-    int nm, nb, nt, ns, nmus, dev;
-    bool operator<(const ProgKey &o) const
-    {
-        return std::tie(basic, times, map, nm, nb, nt, ns, nmus, dev) <
-               std::tie(o.basic, o.times, o.map, o.nm, o.nb, o.nt, o.ns, o.nmus, o.dev);
-    }
+// Compiled programs are cached per (alpha tables, device). An entry keeps references to the three
+// table tensors it was compiled from: while it is cached their storage cannot be freed, so another
+// model's tables can never appear at the same addresses, and a hit is confirmed by the tensors'
+// version counters (an in-place edit of a table recompiles). The cache holds the most recently used
+// MAX_PROGRAMS entries; an evicted program is destroyed (cudaFree waits for work that still uses it).
+struct ProgEntry {
+    at::Tensor basic, times, map;
+    int64_t vb, vt, vm;
+    int nm, nmus, dev;
+    ai2b_mtp_program *prog;
+    uint64_t used;
 };
-std::map<ProgKey, ai2b_mtp_program *> g_programs;
+constexpr size_t MAX_PROGRAMS = 16;
+std::vector<ProgEntry> g_programs;
+uint64_t g_clock = 0;
 std::mutex g_mutex;
+
+int64_t version_of(const at::Tensor &t) { return t.is_inference() ? 0 : (int64_t)t._version(); }
 
 const ai2b_mtp_program *program_for(int nm, const at::Tensor &basic, const at::Tensor &times, const at::Tensor &map, int nmus,
                                     int dev)
 {
-    ProgKey key{basic.data_ptr(), times.data_ptr(), map.data_ptr(), nm, (int)basic.size(0), (int)times.size(0),
-                (int)map.size(0), nmus, dev};
     std::lock_guard<std::mutex> lock(g_mutex);
-    auto it = g_programs.find(key);
-    if (it != g_programs.end()) return it->second;
+    for (auto &e : g_programs)
+        if (e.basic.data_ptr() == basic.data_ptr() && e.times.data_ptr() == times.data_ptr() && e.map.data_ptr() == map.data_ptr() &&
+            e.basic.sizes() == basic.sizes() && e.times.sizes() == times.sizes() && e.map.sizes() == map.sizes() && e.nm == nm &&
+            e.nmus == nmus && e.dev == dev && e.vb == version_of(basic) && e.vt == version_of(times) && e.vm == version_of(map)) {
+            e.used = ++g_clock;
+            return e.prog;
+        }
     at::Tensor hb = basic.to(at::kCPU, at::kInt).contiguous(), ht = times.to(at::kCPU, at::kInt).contiguous(),
                hm = map.to(at::kCPU, at::kInt).contiguous();
     ai2b_mtp_program *prog = nullptr;
-    check(ai2b_mtp_program_create(nm, key.nb, hb.data_ptr<int>(), key.nt, ht.data_ptr<int>(), key.ns, hm.data_ptr<int>(), nmus,
-                                  &prog),
+    check(ai2b_mtp_program_create(nm, (int)basic.size(0), hb.data_ptr<int>(), (int)times.size(0), ht.data_ptr<int>(), (int)map.size(0),
+                                  hm.data_ptr<int>(), nmus, &prog),
           "ai2b_mtp_program_create");
-    g_programs[key] = prog;
+    if (g_programs.size() >= MAX_PROGRAMS) {
+        size_t old = 0;
+        for (size_t i = 1; i < g_programs.size(); i++)
+            if (g_programs[i].used < g_programs[old].used) old = i;
+        ai2b_mtp_program_destroy(g_programs[old].prog);
+        g_programs.erase(g_programs.begin() + old);
+    }
+    g_programs.push_back(ProgEntry{basic, times, map, version_of(basic), version_of(times), version_of(map), nm, nmus, dev, prog,
+                                   ++g_clock});
     return prog;
 }
 

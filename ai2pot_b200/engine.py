@@ -1,15 +1,9 @@
-"""Host-side driver of the evaluation path: positions -> neighbour list -> E/F/V on one GPU,
-and the measurement loop bench.py uses. Everything on the device goes through the C ABI."""
-import ctypes as C
-import json
-import os
-
+"""Host-side driver of the evaluation path: positions -> neighbour list -> E/F/V on one GPU.
+Everything on the device goes through the C ABI."""
 import numpy as np
 import torch
 
 from . import capi
-
-MEASURED_PEAKS = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
 
 
 class Evaluator:
@@ -79,375 +73,3 @@ class Evaluator:
     # NEP = one kernel (single structure, up to 8 radial / angular functions)
     def launches_per_step(self):
         return 5 + (4 if self.kind == "mtp" else 1)
-
-
-def fma_peak_tflops(is_f64, sms):
-    """Measured FMA-pipe throughput of this GPU (microbenchmark, best of 5)."""
-    blocks, iters = sms * 16, 4096
-    out = torch.empty(blocks * 256, dtype=torch.float64 if is_f64 else torch.float32, device="cuda")
-    best = 0.0
-    for _ in range(6):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        capi._check(capi.lib().ai2b_fma_chain(C.c_int(1 if is_f64 else 0), C.c_int(blocks), C.c_int(iters),
-                                              capi._ptr(out), capi._stream()))
-        e1.record()
-        torch.cuda.synchronize()
-        best = max(best, blocks * 256 * 8 * iters * 2 / (e0.elapsed_time(e1) * 1e-3) / 1e12)
-    return best
-
-
-def _timed(fn, steps, warmup, flush, barrier=None):
-    """Sum of per-step device times (CUDA events on the current stream), L2 flushed between steps."""
-    for _ in range(warmup):
-        flush.zero_()
-        fn()
-    torch.cuda.synchronize()
-    if barrier is not None:
-        barrier()
-        torch.cuda.synchronize()
-    evs = []
-    for _ in range(steps):
-        flush.zero_()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        fn()
-        e1.record()
-        evs.append((e0, e1))
-    torch.cuda.synchronize()
-    if barrier is not None:
-        barrier()
-    return sum(a.elapsed_time(b) for a, b in evs) * 1e-3
-
-
-def ghost_images(cell, coords, types, rcut):
-    """What an MD host holds for a periodic orthorhombic system: local atoms wrapped into the box plus the
-    periodic images within rcut of it (ghosts), as double positions. Returns x_local, x_ghost, types_ghost, owner."""
-    L = np.diag(np.asarray(cell, np.float64))
-    x = np.mod(np.asarray(coords, np.float64), L)
-    gx, gt, owner = [], [], []
-    for sx in (-1, 0, 1):
-        for sy in (-1, 0, 1):
-            for sz in (-1, 0, 1):
-                if sx == sy == sz == 0:
-                    continue
-                y = x + np.array([sx, sy, sz]) * L
-                keep = np.all((y > -rcut) & (y < L + rcut), axis=1)
-                gx.append(y[keep]); gt.append(np.asarray(types)[keep]); owner.append(np.nonzero(keep)[0])
-    return x, np.concatenate(gx), np.concatenate(gt), np.concatenate(owner)
-
-
-def run_md_benchmark(w, steps, warmup, dist, sampler):
-    """Device-resident MD input path (ai2b_md_session_compute): host positions + types of local and ghost atoms
-    in, host forces / energy / virial out. The call is synchronous and owns its stream, so a step is timed on
-    the host clock around the call; there is no separate device-only number."""
-    import time
-    m = w["model"]
-    x, gx, gt, owner = ghost_images(w["cell"], w["coords"], w["types"], w["rcut"])
-    nlocal, nghost = len(x), len(gx)
-    xa = np.ascontiguousarray(np.concatenate([x, gx])); ta = np.ascontiguousarray(np.concatenate([w["types"], gt]).astype(np.int32))
-    ses = capi.MdSession(m, w["umax"])
-    for _ in range(max(3, warmup)):
-        e, f, v6, mx = ses.compute(nlocal, nghost, xa, ta)
-    if dist is not None:
-        dist.barrier()
-    sampler.start()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        e, f, v6, mx = ses.compute(nlocal, nghost, xa, ta)
-    t = time.perf_counter() - t0
-    clocks = sampler.stop()
-    ses.close()
-    props = torch.cuda.get_device_properties(torch.cuda.current_device())
-    peak = fma_peak_tflops(False, props.multi_processor_count)
-    roofline = {"kernel": "whole ai2b_md_session_compute call (H2D, neighbour build, nep_fast_kernel, D2H, host accumulation)", "bound": "fp32",
-                "achieved": None, "peak": peak, "unit": "TFLOP/s", "frac": None, "traffic": None,
-                "note": "host-timed synchronous call; the kernels are those of the nep workload", "max_neighbours": int(mx),
-                "local_atoms": nlocal, "ghost_atoms": nghost}
-    nall = nlocal + nghost
-    return dict(t_dev=t, t_e2e=t, clocks=clocks, launches=(9 + 1) * steps, h2d=nall * 28, d2h=nall * 12 + 48, units=nlocal,
-                e2e_path="host double positions + types of local and ghost atoms -> ai2b_md_session_compute -> host forces (+=), energy, virial[6]",
-                roofline=roofline, parts_ms=None)
-
-
-def run_benchmark(w, steps, warmup, dist, sampler):
-    if w.get("kind") == "md":
-        return run_md_benchmark(w, steps, warmup, dist, sampler)
-    if w.get("kind") == "train":
-        return run_training_benchmark(w, steps, warmup, dist, sampler)
-    if w.get("kind") == "slab":
-        return run_slab_benchmark(w, steps, warmup, dist, sampler)
-    return run_single_benchmark(w, steps, warmup, dist, sampler)
-
-
-def _mtp_flops(m, mean_nn, training=False):
-    from bench import flops_mtp
-    tb = m["tables"]
-    kmax = int(tb["alpha_index_basic"][:, 1:].sum(1).max())
-    nb_, nt_, ns_ = len(tb["alpha_index_basic"]), len(tb["alpha_index_times"]), len(tb["alpha_moment_mapping"])
-    fl = flops_mtp(mean_nn, nb_, nt_, ns_, tb["nmus"], m["chebyshev_size"], kmax)
-    if training:   # F_train = F_MTP + nn (55 n_basic + R) + 18 n_times + 6 n_scalar
-        R = 9 * m["chebyshev_size"] + 20 + 4 * tb["nmus"] * m["chebyshev_size"]
-        fl += mean_nn * (55 * nb_ + R) + 18 * nt_ + 6 * ns_
-    return fl
-
-
-def run_training_benchmark(w, steps, warmup, dist, sampler):
-    """configs[3]: one step = forward E/F/V + loss + analytic gradient w.r.t. the MTP coefficients for
-    this rank's share of the batch (structures dealt round-robin), then one all-reduce of the summed
-    gradient when there is more than one rank. Neighbour tensors are built once (as the reference's
-    dataset does at load time) and are resident."""
-    rank = dist.get_rank() if dist is not None else 0
-    world = dist.get_world_size() if dist is not None else 1
-    model = w["model"]
-    is_nep = model["kind"] == "nep"
-    dtype = torch.float32 if w.get("dtype") == "f32" else torch.float64
-    npdt = np.float32 if dtype == torch.float32 else np.float64
-    dev = torch.device("cuda", torch.cuda.current_device())
-    structs = w["structs"][rank::world]
-    prog = None if is_nep else capi.MtpProgram(model["tables"])
-    md = capi.to_device({k: v for k, v in model.items() if k != "tables"}, dev, dtype)
-    builder = capi.NeighborBuilder()
-    npad = max(len(s_["types"]) for s_ in w["structs"])
-    B = len(structs)
-    nbt = dict(binum=torch.zeros(B, dtype=torch.int32, device=dev), bilist=torch.zeros(B, npad, dtype=torch.int32, device=dev),
-               bnumneigh=torch.zeros(B, npad, dtype=torch.int32, device=dev),
-               bfirstneigh=torch.full((B, npad, w["umax"]), -1, dtype=torch.int32, device=dev),
-               brcs=torch.zeros(B, npad, w["umax"], 3, dtype=dtype, device=dev), btypes=torch.zeros(B, npad, dtype=torch.int32, device=dev),
-               ntypes=int(model["ntypes"]), nghost=0)
-    for b, s_ in enumerate(structs):
-        n = len(s_["types"])
-        nn, fn, rcs, st = builder.build(s_["cell"].astype(npdt), torch.from_numpy(s_["coords"].astype(npdt)).to(dev), w["rcut"], w["umax"])
-        if int(st[1]):
-            raise RuntimeError("umax too small for the training batch")
-        nbt["binum"][b] = n
-        nbt["bilist"][b, :n] = torch.arange(n, dtype=torch.int32, device=dev)
-        nbt["bnumneigh"][b, :n] = nn; nbt["bfirstneigh"][b, :n] = fn; nbt["brcs"][b, :n] = rcs
-        nbt["btypes"][b, :n] = torch.from_numpy(s_["types"]).to(dev)
-    t = w["targets"]
-    sel = slice(rank, None, world)
-    E = torch.from_numpy(t["E"][sel]).to(dev, dtype); F = torch.from_numpy(np.ascontiguousarray(t["F"][sel, :npad])).to(dev, dtype)
-    V = torch.from_numpy(np.ascontiguousarray(t["V"][sel])).to(dev, dtype)
-    natoms = int(nbt["binum"].sum())
-    mean_nn = float(nbt["bnumneigh"].sum()) / natoms
-    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
-    if is_nep:
-        ngrad = sum(md[k].numel() for k in ("coeffs", "w0", "b0", "w1")) + int(model["ntypes"]) + 1
-    else:
-        ngrad = md["coeffs"].numel() + prog.ns + int(model["ntypes"]) + 1
-    grad = torch.zeros(ngrad, dtype=dtype, device=dev)
-
-    def compute():
-        if is_nep:
-            e, f, v = capi.nep_efv(md, nbt)
-            loss, rmse = capi.nep_loss(nbt, w["weights"], e, E, f, F, v, V)
-            parts = capi.nep_loss_backward(md, nbt, w["weights"], e, E, f, F, v, V)
-        else:
-            e, f, v = capi.mtp_efv(prog, md, nbt)
-            loss, rmse = capi.mtp_loss(nbt, w["weights"], e, E, f, F, v, V)
-            parts = capi.mtp_loss_backward(prog, md, nbt, w["weights"], e, E, f, F, v, V)
-        capi.weighted_sum_rows(list(parts) + [loss.reshape(-1, 1)], None, out=grad)   # sums over the structures, one launch
-
-    # the step's launches are the same every time (resident neighbour tensors, fixed shapes): replay them
-    # from a CUDA graph; the all-reduce of the summed gradient stays an eager NCCL call
-    graph = None
-    if os.environ.get("AI2B_NO_GRAPH") != "1":
-        try:
-            side = torch.cuda.Stream()
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                for _ in range(2):
-                    compute()
-            torch.cuda.current_stream().wait_stream(side)
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                compute()
-        except Exception:
-            graph = None
-            torch.cuda.synchronize()
-
-    def step():
-        if graph is not None:
-            graph.replay()
-        else:
-            compute()
-        if dist is not None:
-            dist.all_reduce(grad)
-        return grad
-    barrier = (lambda: dist.barrier()) if dist is not None else None
-    sampler.start()
-    t_dev = _timed(step, steps, warmup, flush, barrier)
-    clocks = sampler.stop()
-    hgrad = torch.empty_like(grad, device="cpu").pin_memory()
-
-    def e2e_step():
-        step()
-        hgrad.copy_(grad, non_blocking=True)
-    t_e2e = _timed(e2e_step, steps, warmup, flush, barrier)
-    props = torch.cuda.get_device_properties(torch.cuda.current_device())
-    peak = fma_peak_tflops(dtype == torch.float64, props.multi_processor_count)
-    if is_nep:
-        from bench import flops_nep
-        rc_all = nbt["brcs"]
-        nn_a = float(((torch.linalg.norm(rc_all, dim=-1) <= model["rmax_angular"]) &
-                      (torch.arange(rc_all.shape[2], device=dev)[None, None] < nbt["bnumneigh"][..., None])).sum()) / natoms
-        # forward + directional-derivative pass + coefficient-gradient pass: three sweeps of the descriptor work
-        fl = 3 * flops_nep(mean_nn, nn_a, model["chebyshev_size"], model["n_radial"], model["n_angular"], model["num_neurons"],
-                           model["n_radial"] + model["n_angular"] * model["l_max"])
-    else:
-        fl = _mtp_flops(model, mean_nn, training=True)
-    achieved = natoms * fl / (t_dev / steps) / 1e12
-    roofline = {"kernel": ("nep" if is_nep else "mtp") + " E/F/V + loss-gradient kernels (whole step)", "bound": "fp32" if dtype == torch.float32 else "fp64",
-                "achieved": achieved, "peak": peak,
-                "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": "FMA-chain microbenchmark in this run (of measured)",
-                "flops_per_atom": fl, "mean_neighbours": mean_nn, "traffic": None}
-    name = "nep" if is_nep else "mtp"
-    return dict(t_dev=t_dev, t_e2e=t_e2e, clocks=clocks, launches=((2 + 2 + 1 + 1) if is_nep else (4 + 2 + 4 + 1)) * steps, h2d=0,
-                d2h=hgrad.numel() * hgrad.element_size(), units=natoms,
-                e2e_path=f"resident neighbour tensors -> ai2b_{name}_efv -> ai2b_{name}_loss -> ai2b_{name}_loss_backward -> D2H summed gradient",
-                roofline=roofline, parts_ms=None, cuda_graph=graph is not None)
-
-
-def run_slab_benchmark(w, steps, warmup, dist, sampler):
-    """configs[4]: x-slab decomposition, halo exchange, ghost-force reduction (ai2pot_b200/slab.py).
-    Strong scaling: the system is fixed, each rank owns 1/N of it."""
-    from . import slab
-    from bench import flops_nep
-    rank = dist.get_rank() if dist is not None else 0
-    world = dist.get_world_size() if dist is not None else 1
-    dtype = torch.float32 if w["dtype"] == "f32" else torch.float64
-    dev = torch.device("cuda", torch.cuda.current_device())
-    dom = slab.SlabDomain(w["cell"], w["coords"], w["types"], w["rcut"], rank, world, dev, dist)
-    compute = slab.LocalCompute(w["model"], w["cell"], w["rcut"], w["umax"], dtype)
-    e, f, v = dom.evaluate(compute)
-    torch.cuda.synchronize()
-    st = compute.status.cpu().numpy()
-    if st[1]:
-        raise RuntimeError(f"umax {w['umax']} too small (max {st[0]})")
-    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
-    barrier = (lambda: dist.barrier()) if dist is not None else None
-    sampler.start()
-    t_dev = _timed(lambda: dom.evaluate(compute), steps, warmup, flush, barrier)
-    clocks = sampler.stop()
-    host_owned = dom.owned.cpu().pin_memory()
-    h_f = torch.empty(dom.nlocal, 3, dtype=dtype).pin_memory()
-    h_ev = torch.empty(10, dtype=dtype).pin_memory()
-
-    def e2e_step():
-        dom.owned.copy_(host_owned, non_blocking=True)
-        e_, f_, v_ = dom.evaluate(compute)
-        h_f.copy_(f_, non_blocking=True)
-        h_ev[:1].copy_(e_.reshape(1), non_blocking=True); h_ev[1:].copy_(v_, non_blocking=True)
-    t_e2e = _timed(e2e_step, steps, warmup, flush, barrier)
-    k = max(3, min(steps, 5))
-    local = dom.halo_exchange()
-    t_halo = _timed(lambda: dom.halo_exchange(), k, 2, flush) / k
-    t_comp = _timed(lambda: compute(local, dom.types, dom.nlocal, dom.pbc), k, 2, flush) / k
-    m = w["model"]
-    props = torch.cuda.get_device_properties(torch.cuda.current_device())
-    peak = fma_peak_tflops(dtype == torch.float64, props.multi_processor_count)
-    nn = compute.builder._out[1]
-    mean_nn = float(nn.float().mean())
-    rcs = compute.builder._out[3]
-    nn_a = float(((torch.linalg.norm(rcs, dim=-1) <= m["rmax_angular"]) &
-                  (torch.arange(rcs.shape[1], device=dev)[None] < nn[:, None])).sum(1).float().mean())
-    fl = flops_nep(mean_nn, nn_a, m["chebyshev_size"], m["n_radial"], m["n_angular"], m["num_neurons"], m["n_radial"] + m["n_angular"] * m["l_max"])
-    achieved = dom.nlocal * fl / t_comp / 1e12
-    roofline = {"kernel": "nep_fast_kernel (+ neighbour build) on this rank's slab", "bound": "fp32", "achieved": achieved, "peak": peak,
-                "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": "FMA-chain microbenchmark in this run (of measured)",
-                "flops_per_atom": fl, "mean_neighbours": mean_nn, "traffic": None, "owned_atoms": dom.nlocal, "ghost_atoms": dom.nghost}
-    return dict(t_dev=t_dev, t_e2e=t_e2e, clocks=clocks, launches=(9 + 1) * steps, h2d=host_owned.numel() * host_owned.element_size(),
-                d2h=h_f.numel() * h_f.element_size() + 40, units=len(w["types"]) / world,
-                e2e_path="pinned host positions of the slab -> H2D -> halo exchange (NCCL p2p) -> ai2b_nblist_build_ghost -> ai2b_nep_efv "
-                         "-> ghost-force return -> all-reduce(E, virial) -> D2H forces, E, virial",
-                roofline=roofline, parts_ms={"halo_exchange": 1e3 * t_halo, "nblist+efv": 1e3 * t_comp})
-
-
-def run_single_benchmark(w, steps, warmup, dist, sampler):
-    from bench import flops_mtp, flops_nep   # formulas live beside the JSON contract
-    dtype = torch.float64 if w["dtype"] == "f64" else torch.float32
-    ev = Evaluator(w["model"], w["cell"], w["types"], w["rcut"], w["umax"], dtype)
-    n = ev.n
-    host_coords = torch.from_numpy(np.ascontiguousarray(w["coords"])).to(dtype).pin_memory()
-    coords = host_coords.cuda()
-    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
-    barrier = (lambda: dist.barrier()) if dist is not None else None
-    props = torch.cuda.get_device_properties(torch.cuda.current_device())
-
-    # device-resident throughput: positions already in HBM
-    nb = ev.build_list(coords)
-    ev.evaluate(nb)
-    torch.cuda.synchronize()
-    st = ev.status.cpu().numpy()
-    if st[1]:
-        raise RuntimeError(f"umax {ev.umax} too small (max {st[0]})")
-    mean_nn = float(nb["bnumneigh"].float().mean())
-    # the step is a fixed sequence of launches on fixed buffers: replayed from a CUDA graph when the capture succeeds
-    graphed = ev.capture(coords)
-    step = ev.replay if graphed else (lambda: ev.compute(coords))
-    sampler.start()
-    t_dev = _timed(step, steps, warmup, flush, barrier)
-    clocks = sampler.stop()
-
-    # end to end: host positions in, host E/F/V out, every step
-    h_e = torch.empty(1, dtype=dtype).pin_memory()
-    h_f = torch.empty(1, n, 3, dtype=dtype).pin_memory()
-    h_v = torch.empty(1, 9, dtype=dtype).pin_memory()
-    dcoords = torch.empty_like(coords)
-
-    def e2e_step():
-        if graphed:
-            coords.copy_(host_coords, non_blocking=True)
-            e, f, v = ev.replay()
-        else:
-            dcoords.copy_(host_coords, non_blocking=True)
-            e, f, v = ev.compute(dcoords)
-        h_e.copy_(e, non_blocking=True); h_f.copy_(f, non_blocking=True); h_v.copy_(v, non_blocking=True)
-    t_e2e = _timed(e2e_step, steps, warmup, flush, barrier)
-    h2d = host_coords.numel() * host_coords.element_size()
-    d2h = sum(t.numel() * t.element_size() for t in (h_e, h_f, h_v))
-
-    # the two parts separately (same timing rules), for the roofline of the dominant kernel
-    k = max(3, min(steps, 10))
-    t_nb = _timed(lambda: ev.build_list(coords), k, 3, flush) / k
-    t_ev = _timed(lambda: ev.evaluate(nb), k, 3, flush) / k
-
-    m = w["model"]
-    if m["kind"] == "mtp":
-        tb = m["tables"]
-        kmax = int(tb["alpha_index_basic"][:, 1:].sum(1).max())
-        fl = flops_mtp(mean_nn, len(tb["alpha_index_basic"]), len(tb["alpha_index_times"]), len(tb["alpha_moment_mapping"]),
-                       tb["nmus"], m["chebyshev_size"], kmax)
-        bound = "fp64"
-    else:
-        nn_a = float((torch.linalg.norm(nb["brcs"][0], dim=-1) <= m["rmax_angular"]).logical_and(
-            torch.arange(ev.umax, device="cuda")[None] < nb["bnumneigh"][0][:, None]).sum(1).float().mean())
-        fl = flops_nep(mean_nn, nn_a, m["chebyshev_size"], m["n_radial"], m["n_angular"], m["num_neurons"],
-                       m["n_radial"] + m["n_angular"] * m["l_max"])
-        bound = "fp32"
-    is64 = dtype == torch.float64
-    peak_meas = fma_peak_tflops(is64, props.multi_processor_count)
-    sm_max = clocks.get("sm_max_mhz") or 1965.0
-    peak_nom = props.multi_processor_count * (64 if is64 else 128) * 2 * sm_max * 1e6 / 1e12
-    achieved = n * fl / t_ev / 1e12
-    sz = 8 if is64 else 4
-    nb_bytes = n * (3 * sz + 4 + ev.umax * (4 + 3 * sz) + 4)
-    hbm = None
-    if os.path.exists(MEASURED_PEAKS):
-        hbm = json.load(open(MEASURED_PEAKS)).get("hbm_gbs")
-    roofline = {"kernel": "mtp_fwd_lanes + mtp_contract + mtp_force (the three E/F/V kernels of a call)" if m["kind"] == "mtp" else "nep_fast_kernel",
-                "bound": bound,
-                "achieved": achieved, "peak": peak_meas, "unit": "TFLOP/s", "frac": achieved / peak_meas,
-                "peak_source": "FMA-chain microbenchmark in this run (of measured)", "peak_nominal": peak_nom,
-                "frac_of_nominal": achieved / peak_nom, "flops_per_atom": fl, "mean_neighbours": mean_nn,
-                # dram__bytes_read + write of the E/F/V kernels of one call, from the ncu capture summarised under profiles/
-                "traffic": (55.0e6 if m["kind"] == "mtp" else 7.5e6) if n == 13824 else None,   # dram bytes of one ncu capture (profiles/) "kernel_ms": 1e3 * t_ev,
-                "nblist": {"bound": "hbm", "achieved": nb_bytes / t_nb / 1e9, "peak": hbm or 6650.0, "unit": "GB/s",
-                           "frac": nb_bytes / t_nb / 1e9 / (hbm or 6650.0),
-                           "peak_source": "MEASURED_PEAKS.json (of measured)" if hbm else "6.65 TB/s (of fallback)",
-                           "bytes_per_atom": nb_bytes / n, "ms": 1e3 * t_nb}}
-    return dict(t_dev=t_dev, t_e2e=t_e2e, clocks=clocks, launches=ev.launches_per_step() * steps, h2d=h2d, d2h=d2h,
-                e2e_path="pinned host positions -> H2D -> ai2b_nblist_build -> ai2b_*_efv -> D2H E,F,V (C ABI via ctypes" +
-                         (", replayed from a CUDA graph)" if graphed else ")"), cuda_graph=graphed,
-                roofline=roofline, parts_ms={"nblist": 1e3 * t_nb, "efv": 1e3 * t_ev})

@@ -43,14 +43,7 @@ eachTypeDescriptorsStatisticsOp = torch.ops.fitutils.eachTypeDescriptorsStatisti
 allTypeDescriptorsMaxminOp = torch.ops.fitutils.allTypeDescriptorsMaxminOp
 
 
-def _optional(ns, name):
-    try:
-        return getattr(getattr(torch.ops, ns), name)
-    except (AttributeError, RuntimeError):
-        return None
-
-
-linearMtpToLossOp = _optional("mtpr", "linearMtpToLossOp")
-linearMtpToEFLossOp = _optional("mtpr", "linearMtpToEFLossOp")
-nepToLossOp = _optional("nep", "nepToLossOp")
-nepToEFLossOp = _optional("nep", "nepToEFLossOp")
+linearMtpToLossOp = torch.ops.mtpr.linearMtpToLossOp
+linearMtpToEFLossOp = torch.ops.mtpr.linearMtpToEFLossOp
+nepToLossOp = torch.ops.nep.nepToLossOp
+nepToEFLossOp = torch.ops.nep.nepToEFLossOp

@@ -177,6 +177,56 @@ int ai2b_nblist_build_ghost_f32(int natoms, int ncentres, const float *h_cell,
                                 float *d_rcs, int *d_status, void *d_workspace,
                                 size_t workspace_bytes, void *stream);
 
+/* As ai2b_nblist_build_ghost_*, for the centre range [centre_begin, centre_end) only: row 0 of
+ * the outputs belongs to atom centre_begin, outputs are sized [centre_end - centre_begin, ...], all
+ * natoms atoms are candidates. A domain that is evaluated in several passes (interior centres while
+ * the halo is in flight, boundary centres after it: the role LAMMPS' communication plays around
+ * interface/lammps/AI2POT/pair_ai2pot.cpp:175-249) calls this once per pass. reuse_bins != 0: the
+ * workspace still holds the binning of an earlier call with the same atoms, cell, cutoff and flags,
+ * so only the row pass runs and d_status is accumulated into instead of being reset.
+ * h_open_extent (may be NULL): fractional coordinates {lo0, lo1, lo2, hi0, hi1, hi2} that bound the
+ * atoms along the non-periodic axes (entries of periodic axes are ignored). With it the bin grid is
+ * sized on the host and the build needs no reduction over the positions; atoms outside the bounds
+ * are still handled correctly (they share the edge bins). */
+int ai2b_nblist_build_range_f64(int natoms, int centre_begin, int centre_end,
+                                const double *h_cell, const double *d_coords, int is_cart,
+                                double rcut, const int *h_pbc, const double *h_open_extent,
+                                int umax, int reuse_bins,
+                                int *d_numneigh, int *d_firstneigh, double *d_rcs,
+                                int *d_status, void *d_workspace, size_t workspace_bytes,
+                                void *stream);
+int ai2b_nblist_build_range_f32(int natoms, int centre_begin, int centre_end,
+                                const float *h_cell, const float *d_coords, int is_cart,
+                                double rcut, const int *h_pbc, const double *h_open_extent,
+                                int umax, int reuse_bins,
+                                int *d_numneigh, int *d_firstneigh, float *d_rcs, int *d_status,
+                                void *d_workspace, size_t workspace_bytes, void *stream);
+
+/* Neighbour lists of a padded batch of small periodic structures in ONE launch: what the
+ * reference's dataset does frame by frame on the host before padding every array to the largest
+ * structure (ai2pot/data/mlffdataset.py:61-90, each frame through
+ * source/nblist/bind/nblist_bind.cc:35-207). Same membership rule, image arithmetic and row
+ * contents as ai2b_nblist_build_*; every (centre, atom, image) triple of the reference's supercell
+ * is tested, so it is meant for cells of up to a few thousand atoms.
+ *   d_binum[B]            atoms of each structure (<= natoms_pad)
+ *   d_cells[B][9]         lattice vectors of each structure, rows = a0, a1, a2 (device)
+ *   d_coords[B][Np][3]    positions (Cartesian, or fractional if !is_cart); padded slots unused
+ *   h_pbc[3]              periodic flags, shared by the batch
+ * Outputs, fully written (padding included): d_bilist[B][Np] (0..n-1, pad 0), d_bnumneigh[B][Np],
+ * d_bfirstneigh[B][Np][umax] (pad -1), d_brcs[B][Np][umax][3] (pad 0); d_status[0] = largest
+ * neighbour count, d_status[1] bit 0 = a row was truncated to umax, bit 1 = a cell more than 500
+ * times thinner than the cutoff was skipped. No workspace. */
+int ai2b_nblist_build_batch_f64(int batch_size, int natoms_pad, const int *d_binum,
+                                const double *d_cells, const double *d_coords, int is_cart,
+                                double rcut, const int *h_pbc, int umax, int *d_bilist,
+                                int *d_bnumneigh, int *d_bfirstneigh, double *d_brcs,
+                                int *d_status, void *stream);
+int ai2b_nblist_build_batch_f32(int batch_size, int natoms_pad, const int *d_binum,
+                                const float *d_cells, const float *d_coords, int is_cart,
+                                double rcut, const int *h_pbc, int umax, int *d_bilist,
+                                int *d_bnumneigh, int *d_bfirstneigh, float *d_brcs,
+                                int *d_status, void *stream);
+
 /* Orders every row by distance, in place (the reference's sort=true argument,
  * source/nblist/include/neighborList.h:290-335). Ties keep their build order. */
 int ai2b_nblist_sort_rows_f64(int natoms, int umax, const int *d_numneigh, int *d_firstneigh,
@@ -375,10 +425,6 @@ int ai2b_nblist_build_ghost_f64_rows32(int natoms, int ncentres, const double *h
                                        int *d_firstneigh, float *d_rcs, int *d_status,
                                        void *d_workspace, size_t workspace_bytes, void *stream);
 
-/* FMA-pipe microbenchmark used for the roofline denominator (no counterpart in the reference):
- * blocks x 256 threads, 8 independent chains of `iters` fused multiply-adds each. */
-int ai2b_fma_chain(int is_f64, int blocks, int iters, void *d_out, void *stream);
-
 /* ------------------------------------------------------------------------------------------
  * NEP (3-body terms, l_max <= 4, chebyshev_size <= 16)
  * ---------------------------------------------------------------------------------------- */
@@ -394,6 +440,18 @@ size_t ai2b_nep_workspace_bytes(int batch_size, int ntypes, int n_radial, int n_
  * overwritten. d_bvirial may be NULL: energy + force only (find_ef, nep_cpu_launcher.h:116-184). */
 #define AI2B_DECL_NEP(SUF, T)                                                                    \
     int ai2b_nep_efv_##SUF(T *d_betot, T *d_bforce, T *d_bvirial, int chebyshev_size,            \
+                           int n_radial, int n_angular, int l_max, int num_neurons,              \
+                           const T *d_coeffs, const T *d_w0, const T *d_b0, const T *d_w1,       \
+                           const T *d_type_bias, int batch_size, int natoms_pad,                 \
+                           const int *d_binum, const int *d_bilist, const int *d_bnumneigh,      \
+                           const int *d_bfirstneigh, const T *d_brcs, const int *d_btypes,       \
+                           int ntypes, int umax, int nghost, T rmax_radial, T rmax_angular,      \
+                           const T *d_q_scaler, void *d_workspace, size_t workspace_bytes,       \
+                           void *stream);                                                        \
+    /* same, ADDING onto d_betot, d_bforce, d_bvirial instead of overwriting them: what the     \
+     * reference's own launchers do (they never zero their outputs, nep.h:320-529). Lets a      \
+     * caller evaluate one system in several passes over disjoint sets of centres. */           \
+    int ai2b_nep_efv_accumulate_##SUF(T *d_betot, T *d_bforce, T *d_bvirial, int chebyshev_size, \
                            int n_radial, int n_angular, int l_max, int num_neurons,              \
                            const T *d_coeffs, const T *d_w0, const T *d_b0, const T *d_w1,       \
                            const T *d_type_bias, int batch_size, int natoms_pad,                 \

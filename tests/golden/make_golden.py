@@ -4,7 +4,7 @@ Everything here is produced by the REFERENCE's own CPU code (oracle/_ref, compil
 reference tree by oracle/Makefile) on the seeded inputs defined in tests/util.py, with one
 OpenMP thread so the sums are reproducible. The 12-atom MoS2 cell is read from the text of the
 reference's own neighbour-list unit test (source/nblist/tests/test_neighborList.cc:30-93).
-Run where the reference is mounted:  OMP_NUM_THREADS=1 python tests/golden/make_golden.py
+Run where the reference is mounted:  REF_ROOT=<reference tree> OMP_NUM_THREADS=1 python tests/golden/make_golden.py
 """
 import os, re, sys
 os.environ.setdefault("OMP_NUM_THREADS", "1")
@@ -16,7 +16,7 @@ from oracle.refapi import Checker
 from ai2pot_b200 import synth
 import util
 
-root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+root = sys.argv[1] if len(sys.argv) > 1 else os.environ["REF_ROOT"]
 ref = Checker("ref")
 out = {}
 

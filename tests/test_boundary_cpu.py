@@ -13,7 +13,7 @@ import util
 from ai2pot_b200 import capi
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF_TEMPLATES = "/root/reference/source/descriptor/mtpr/MTP_templates"
+REF_TEMPLATES = os.path.join(util.REF_ROOT, "source", "descriptor", "mtpr", "MTP_templates")
 
 
 def _declared():
@@ -92,7 +92,7 @@ def test_almtp_parser_matches_reference(checkers, level):
 
 def test_torch_ops_registered(monkeypatch):
     if os.path.isdir(REF_TEMPLATES):
-        monkeypatch.setenv("AI2POT_PATH", "/root/reference")
+        monkeypatch.setenv("AI2POT_PATH", util.REF_ROOT)
     from ai2pot_b200 import fromcc
     for name in ("mtpParamOp", "linearMtpToEFVOp", "linearMtpToEFOp", "linearMtpToDescriptorsOp", "nepToEFVOp", "nepToEFOp",
                  "nepToDescriptorsOp", "forceSrOp", "virialSrOp"):
@@ -113,3 +113,28 @@ def test_torch_ops_registered(monkeypatch):
     with pytest.raises(RuntimeError):
         fromcc.nepToEFVOp(8, 4, 4, 4, z, z, z, z, z, zi, zi.view(1, 1), zi.view(1, 1), zi.view(1, 1, 1), torch.zeros(1, 1, 1, 3), zi.view(1, 1),
                           zi, 0, 6.0, 4.0, z, 0.0, 0.0, z, z)
+
+
+def test_toplevel_nblist_module_resolves():
+    """`sys.path.append(lib_dir); import nblist`, as the reference's loader does (ai2pot/fromcc/__init__.py:52-58), finds
+    the module the build step installs next to the libraries (no compute call here)."""
+    import subprocess
+    import sys
+    code = ("import sys; sys.path.append(sys.argv[1]); import nblist; "
+            "assert callable(nblist.find_info4mlff) and nblist.__file__.startswith(sys.argv[1])")
+    env = dict(os.environ)
+    env.pop("PYTHONPATH", None)
+    r = subprocess.run([sys.executable, "-c", code, os.path.join(ROOT, "ai2pot_b200", "_lib")], cwd="/", env=env, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-1500:]
+
+
+def test_predict_efv_modules_script_and_save(tmp_path):
+    """The modules of the TorchScript route (what pair_style ai2pot loads) script and serialise against this build's
+    op schemas; running them needs a GPU (tests/test_boundary_tail_gpu.py)."""
+    from ai2pot_b200 import fromcc  # noqa: F401
+    import test_boundary_tail_gpu as tail
+    for module in (tail.ScriptedNep(util.small_nep_case(3, np.float32)["model"]), tail.ScriptedMtp(util.small_mtp_case(10, 3, np.float64)["model"])):
+        path = str(tmp_path / "m.pt")
+        torch.jit.save(torch.jit.script(module), path)
+        back = torch.jit.load(path)
+        assert hasattr(back, "predict_efv")

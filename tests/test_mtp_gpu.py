@@ -62,6 +62,19 @@ def test_g1_slice_vs_checker(checkers):
     assert util.relerr(e, er) < 1e-10 and util.relerr(f, fr) < 1e-10 and util.relerr(v, vr) < 1e-10
 
 
+def test_g1_full_size_vs_checker(checkers):
+    """configs[1] itself: level 16, fp64, 13,824 atoms, rcut 6 - energy, forces and virial against the CPU code at
+    rel 1e-10 (neighbour list from the CPU code; the CUDA list is compared bit for bit in test_nblist_gpu.py)."""
+    w = synth.g1(util.tables(16))
+    chk = _chk(checkers)
+    nb = util.nblist_batch(chk, w)
+    (e, f, v), *_ = _run(w, nb)
+    er, fr, vr = chk.mtp_efv(w["model"], nb)
+    errs = dict(energy=util.relerr(e, er), force=util.relerr(f, fr), virial=util.relerr(v, vr))
+    print("configs[1] full size, CUDA vs CPU code:", errs)
+    assert max(errs.values()) < 1e-10, errs
+
+
 def test_many_neighbours_and_ragged_batch(checkers):
     """> 32 neighbours per atom (two lane chunks), padded batch with an empty structure and ghosts."""
     chk = _chk(checkers)

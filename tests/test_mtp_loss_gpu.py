@@ -70,6 +70,54 @@ def test_level16_batch_vs_checker(checkers, virial):
         assert util.relerr(a.cpu().numpy(), b) < 1e-10, name
 
 
+def test_g3_full_batch_vs_checker(checkers):
+    """configs[3] itself: 64 structures of 64-256 atoms, level 16, fp64. The padded neighbour tensors are built on the
+    device in one launch (ai2b_nblist_build_batch) and must equal the CPU code's lists bit for bit; then E/F/V,
+    loss[64], the three RMSEs and all three per-structure gradients against the CPU code at rel 1e-10."""
+    chk = _chk(checkers)
+    g = synth.g3(util.tables(16))
+    structs = g["structs"]
+    B = len(structs)
+    npad = max(len(s["types"]) for s in structs)
+    lists = []
+    for s in structs:
+        nn, fn, rc, ty, mx = chk.nblist(s["cell"], s["types"], s["coords"], g["rcut"], g["umax"])
+        lists.append((nn, fn, rc, ty))
+    nb = synth.pad_batch(lists, 3, g["umax"])
+    coords = np.zeros((B, npad, 3)); binum = np.zeros(B, np.int32)
+    for b, s in enumerate(structs):
+        binum[b] = len(s["types"]); coords[b, :binum[b]] = s["coords"]
+    cells = np.stack([s["cell"] for s in structs])
+    nbd = capi.nblist_build_batch(cells, torch.from_numpy(binum).cuda(), torch.from_numpy(coords).cuda(), g["rcut"], g["umax"])
+    st = nbd["status"].cpu().numpy()
+    assert st[1] == 0 and st[0] == max(int(l[0].max()) for l in lists)
+    assert np.array_equal(nbd["bilist"].cpu().numpy(), nb["bilist"])
+    for b in range(B):
+        n = binum[b]
+        util.assert_nblist_equal((nbd["bnumneigh"][b, :n].cpu().numpy(), nbd["bfirstneigh"][b, :n].cpu().numpy(), nbd["brcs"][b, :n].cpu().numpy()),
+                                 (lists[b][0], lists[b][1], lists[b][2]))
+        assert int(nbd["bnumneigh"][b, n:].abs().sum()) == 0 and bool((nbd["bfirstneigh"][b, n:] == -1).all())
+    nbd.update(btypes=torch.from_numpy(nb["btypes"]).cuda(), ntypes=3, nghost=0)
+    prog, md, _, (E, F, V) = _dev(g, nb)
+    e, f, v = capi.mtp_efv(prog, md, nbd)
+    er, fr, vr = chk.mtp_efv(g["model"], nb)
+    assert util.relerr(e.cpu().numpy(), er) < 1e-10 and util.relerr(f.cpu().numpy(), fr) < 1e-10 and util.relerr(v.cpu().numpy(), vr) < 1e-10
+    t = g["targets"]
+    loss, rmse = capi.mtp_loss(nbd, g["weights"], e, E, f, F, v, V)
+    got = capi.mtp_loss_backward(prog, md, nbd, g["weights"], e, E, f, F, v, V)
+    lr = chk.mtp_loss(nb, g["weights"], er, t["E"], fr, t["F"][:, :npad], vr, t["V"])
+    ref = chk.mtp_loss_backward(g["model"], nb, g["weights"], er, t["E"], fr, t["F"][:, :npad], vr, t["V"])
+    errs = dict(loss=util.relerr(loss.cpu().numpy(), lr))
+    for a, r, name in zip(got, ref, ("dcoeffs", "dlinear", "dbias")):
+        errs[name] = util.relerr(a.cpu().numpy(), r)
+    mask = (np.arange(npad)[None] < binum[:, None])[..., None]
+    exp = [np.sqrt(((er - t["E"]) ** 2).sum() / B), np.sqrt((((fr - t["F"][:, :npad]) ** 2) * mask).sum() / (3 * binum.sum())),
+           np.sqrt(((vr - t["V"]) ** 2).sum() / (9 * B))]
+    errs["rmse"] = util.relerr(rmse.cpu().numpy(), np.array(exp))
+    print("configs[3] full batch, CUDA vs CPU code:", errs)
+    assert max(errs.values()) < 1e-10, errs
+
+
 def test_loss_op_autograd(checkers):
     """torch.ops.mtpr.linearMtpToLossOp: outputs and autograd gradients of mean(loss)."""
     from ai2pot_b200 import fromcc

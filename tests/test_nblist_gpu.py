@@ -135,3 +135,75 @@ def test_empty_structure():
     nb = capi.NeighborBuilder()
     nn, fn, rc, st = nb.build(np.eye(3) * 5, torch.zeros(0, 3, dtype=torch.float64, device="cuda"), 3.0, 8)
     assert nn.numel() == 0
+
+
+@pytest.mark.parametrize("dt", [np.float64, np.float32])
+def test_centre_ranges_bin_reuse_and_host_extent(checkers, dt):
+    """ai2b_nblist_build_range_*: rows for a range of centres equal the same rows of the full list; a second range
+    built from the bins the first call left in the workspace is identical; a host-given extent along an open
+    first axis (even a wrong one: atoms outside it share the edge bins) changes nothing."""
+    chk = _chk(checkers)
+    rng = np.random.default_rng(8)
+    cell, pos = synth.cubic_lattice(8, 2.9, 0.12, rng, dt)
+    n = len(pos)
+    types = np.zeros(n, np.int32)
+    tdt = torch.float64 if dt == np.float64 else torch.float32
+    dpos = torch.from_numpy(pos).cuda()
+    for pbc in ((True, True, True), (False, True, True)):
+        ref = chk.nblist(cell, types, pos, 5.0, 64, pbc=[int(p) for p in pbc])
+        b = capi.NeighborBuilder()
+        c0, c1, c2 = 37, 300, n
+        o1 = capi.NeighborBuilder.new_outputs(c1 - c0, 64, tdt, dpos.device)
+        o2 = capi.NeighborBuilder.new_outputs(c2 - c1, 64, tdt, dpos.device)
+        b.build(cell, dpos, 5.0, 64, pbc=pbc, ncentres=c1, cbegin=c0, out=o1)
+        b.build(cell, dpos, 5.0, 64, pbc=pbc, ncentres=c2, cbegin=c1, reuse_bins=True, out=o2)
+        for (nn, fn, rc, st), (lo, hi) in ((o1, (c0, c1)), (o2, (c1, c2))):
+            assert int(st[1]) == 0
+            util.assert_nblist_equal((nn.cpu().numpy(), fn.cpu().numpy(), rc.cpu().numpy()), (ref[0][lo:hi], ref[1][lo:hi], ref[2][lo:hi]))
+        if not pbc[0]:
+            frac = pos[:, 0].astype(np.float64) / float(cell[0, 0])
+            for ext in ((frac.min(), frac.max()), (0.2, 0.7)):
+                o3 = capi.NeighborBuilder.new_outputs(n, 64, tdt, dpos.device)
+                capi.NeighborBuilder().build(cell, dpos, 5.0, 64, pbc=pbc, out=o3, open_extent=ext)
+                util.assert_nblist_equal((o3[0].cpu().numpy(), o3[1].cpu().numpy(), o3[2].cpu().numpy()), ref[:3])
+
+
+@pytest.mark.parametrize("dt", [np.float64, np.float32])
+def test_batched_build_ragged_triclinic_fractional(checkers, dt):
+    """ai2b_nblist_build_batch_*: a ragged batch (one empty structure, one cell thinner than the cutoff, triclinic cells,
+    fractional input, an open axis) against the CPU code structure by structure; truncation to umax is flagged."""
+    chk = _chk(checkers)
+    rng = np.random.default_rng(21)
+    tdt = torch.float64 if dt == np.float64 else torch.float32
+    cells, fracs, ns = [], [], [40, 0, 9, 75, 130]
+    for k, n in enumerate(ns):
+        L = (3.4 if k == 2 else 9.0) + k
+        cell = (np.eye(3) * L + rng.normal(0, 0.4, (3, 3))).astype(dt)
+        cells.append(cell)
+        fracs.append((rng.random((n, 3)) * 1.6 - 0.3).astype(dt))          # some atoms outside the cell
+    npad = max(ns)
+    B = len(ns)
+    coords = np.zeros((B, npad, 3), dt)
+    for b in range(B):
+        coords[b, :ns[b]] = fracs[b]
+    for pbc in ((True, True, True), (True, False, True)):
+        out = capi.nblist_build_batch(np.stack(cells), torch.tensor(ns, dtype=torch.int32).cuda(), torch.from_numpy(coords).cuda(), 4.5, 200,
+                                      is_cart=False, pbc=pbc)
+        st = out["status"].cpu().numpy()
+        assert st[1] == 0
+        mxs = [0]
+        for b in range(B):
+            n = ns[b]
+            if n == 0:
+                assert int(out["bnumneigh"][b].abs().sum()) == 0
+                continue
+            nn, fn, rc, ty, mx = chk.nblist(cells[b], np.zeros(n, np.int32), fracs[b], 4.5, 200, is_cart=False, pbc=[int(p) for p in pbc])
+            mxs.append(mx)
+            util.assert_nblist_equal((out["bnumneigh"][b, :n].cpu().numpy(), out["bfirstneigh"][b, :n].cpu().numpy(),
+                                      out["brcs"][b, :n].cpu().numpy()), (nn, fn, rc))
+            assert bool((out["bfirstneigh"][b, n:] == -1).all()) and float(out["brcs"][b, n:].abs().sum()) == 0.0
+        assert st[0] == max(mxs)
+    small = capi.nblist_build_batch(np.stack(cells), torch.tensor(ns, dtype=torch.int32).cuda(), torch.from_numpy(coords).cuda(), 4.5, 8,
+                                    is_cart=False)
+    st = small["status"].cpu().numpy()
+    assert st[1] & 1 and st[0] > 8 and int(small["bnumneigh"].max()) == 8

@@ -62,22 +62,53 @@ def test_g2_full_size_fp64(checkers):
 def test_g2_full_size_fp32(checkers):
     """The benchmark configuration itself (fp32). Sums over 4e5 pairs in fp32 carry the CPU
     code's own rounding (its energy moves by 4e-7 between two OpenMP runs, its virial by more), so
-    the check is two-sided: the CUDA result is within 1e-5 of the same model evaluated in fp64 on
-    the same fp32 neighbour list, and within 1e-5 + (the fp32 CPU code's own distance from that
-    fp64 value) of the fp32 CPU result."""
+    the check is the two-sided one of util.fp32_parity (tol 1e-5), with the three distances recorded."""
     chk = _chk(checkers)
     w, model = _g2(np.float32)
     nn, fn, rc, ty, mx = chk.nblist(w["cell"], w["types"], w["coords"], w["rcut"], w["umax"])
     nb = synth.batch_from_nblist(nn, fn, rc, ty, 3)
     (e, f, v), *_ = _run(model, nb)
     r32 = chk.nep_efv(model, nb)
-    nb64 = dict(nb, brcs=nb["brcs"].astype(np.float64))
-    model64 = {k: (v_.astype(np.float64) if isinstance(v_, np.ndarray) else v_) for k, v_ in model.items()}
-    r64 = chk.nep_efv(model64, nb64)
+    r64 = chk.nep_efv(util.to64(model), dict(nb, brcs=nb["brcs"].astype(np.float64)))
     for a, a32, a64, name in zip((e, f, v), r32, r64, ("energy", "force", "virial")):
-        own = util.relerr(a32, a64)
-        assert util.relerr(a, a64) < 1e-5, (name, util.relerr(a, a64))
-        assert util.relerr(a, a32) < 1e-5 + own, (name, util.relerr(a, a32), own)
+        util.fp32_parity("configs[2] NEP fp32, 13,824 atoms", name, a, a32, a64)
+
+
+def _g4_case(chk, ncell):
+    """configs[4] lattice with ncell^3 cells: CUDA neighbour list (bit-exact against the CPU code) and NEP E/F/V."""
+    from ai2pot_b200 import engine
+    w = synth.g4(ncell=ncell)
+    n = len(w["types"])
+    ev = engine.Evaluator(w["model"], w["cell"], w["types"], w["rcut"], w["umax"], torch.float32)
+    coords = torch.from_numpy(np.ascontiguousarray(w["coords"])).cuda()
+    nbd = ev.build_list(coords)
+    st = ev.status.cpu().numpy()
+    assert st[1] == 0
+    nn, fn, rc, ty, mx = chk.nblist(w["cell"], w["types"], w["coords"], w["rcut"], w["umax"])
+    assert mx == st[0]
+    util.assert_nblist_equal((nbd["bnumneigh"][0].cpu().numpy(), nbd["bfirstneigh"][0].cpu().numpy(), nbd["brcs"][0].cpu().numpy()),
+                             (nn, fn, rc))
+    e, f, v = [t.cpu().numpy() for t in ev.evaluate(nbd)]
+    nb = synth.batch_from_nblist(nn, fn, rc, ty, 3)
+    r32 = chk.nep_efv(w["model"], nb)
+    r64 = chk.nep_efv(util.to64(w["model"]), dict(nb, brcs=rc[None].astype(np.float64)))
+    for a, a32, a64, name in zip((e, f, v), r32, r64, ("energy", "force", "virial")):
+        util.fp32_parity(f"configs[4] NEP fp32, {n:,} atoms", name, a, a32, a64)
+
+
+def test_g4_one_rank_share(checkers):
+    """A 32^3-cell system of the configs[4] lattice (131,072 atoms: what one of eight ranks owns): neighbour list
+    bit-exact and E/F/V against the CPU code."""
+    _g4_case(_chk(checkers), 32)
+
+
+def test_g4_full_size_vs_checker(checkers):
+    """configs[4] itself, 1,048,576 atoms, against the CPU code (neighbour list bit-exact, E/F/V two-sided fp32
+    statement). Needs ~8 GB of host memory and about a minute of host time; skipped on smaller hosts."""
+    import psutil
+    if psutil.virtual_memory().available < 24e9:
+        pytest.skip("needs 24 GB of free host memory for the CPU code's neighbour list")
+    _g4_case(_chk(checkers), 64)
 
 
 @pytest.mark.parametrize("cfg", [dict(n_radial=6, n_angular=3, l_max=2, chebyshev_size=5, num_neurons=17),

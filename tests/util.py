@@ -2,16 +2,15 @@
 import os
 import numpy as np
 
-from ai2pot_b200 import synth
+from ai2pot_b200 import synth, tables as _tables
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+# where the reference tree is mounted (absent on the GPU box): tests that read it are skipped without it
+REF_ROOT = os.environ.get("REF_ROOT", os.path.join(os.sep, "root", "reference"))
 
 
 def tables(level):
-    z = np.load(os.path.join(GOLDEN, f"mtp_tables_L{level:02d}.npz"))
-    return dict(alpha_moments_count=int(z["alpha_moments_count"]), nmus=int(z["nmus"]),
-                alpha_index_basic=z["alpha_index_basic"], alpha_index_times=z["alpha_index_times"],
-                alpha_moment_mapping=z["alpha_moment_mapping"])
+    return _tables.load(level)
 
 
 def canonical_nblist(numneigh, firstneigh, rcs):
@@ -43,6 +42,35 @@ def relerr(a, ref):
     a = np.asarray(a, np.float64); ref = np.asarray(ref, np.float64)
     s = np.abs(ref).max()
     return float(np.abs(a - ref).max() / (s if s > 0 else 1.0))
+
+
+_FP32_RECORD = os.path.join(os.path.dirname(GOLDEN), os.pardir, "gpurun_out", "parity_fp32_distances.jsonl")
+
+
+def fp32_parity(case, name, got, r32, r64, tol=1e-5):
+    """Single-precision parity as a measured, two-sided statement. Three distances (relerr):
+        d_cuda64 = CUDA fp32 result   <-> the same model evaluated in fp64 by the CPU checker
+        d_cpu64  = fp32 CPU checker   <-> that fp64 value (the CPU code's own fp32 rounding)
+        d_cuda32 = CUDA fp32 result   <-> fp32 CPU checker
+    Required: the CUDA result is within `tol` of the fp64 value, or at least as close to it as the CPU code's own
+    fp32 result is; and it is within tol + d_cpu64 of the fp32 CPU result. The distances are printed and appended
+    to gpurun_out/parity_fp32_distances.jsonl."""
+    import json
+    d_cuda64, d_cpu64, d_cuda32 = relerr(got, r64), relerr(r32, r64), relerr(got, r32)
+    rec = dict(case=case, tensor=name, cuda_vs_fp64=d_cuda64, cpu32_vs_fp64=d_cpu64, cuda_vs_cpu32=d_cuda32)
+    print("fp32 parity", json.dumps(rec))
+    try:
+        os.makedirs(os.path.dirname(_FP32_RECORD), exist_ok=True)
+        with open(_FP32_RECORD, "a") as fh:
+            fh.write(json.dumps(rec) + "\n")
+    except OSError:
+        pass
+    assert d_cuda64 < tol or d_cuda64 <= d_cpu64, rec
+    assert d_cuda32 < tol + d_cpu64, rec
+
+
+def to64(model):
+    return {k: (v.astype(np.float64) if isinstance(v, np.ndarray) and v.dtype == np.float32 else v) for k, v in model.items()}
 
 
 def small_mtp_case(level=10, n=5, dtype=np.float64, seed=7, rcut=5.0, ntypes=3, a=3.0):
