@@ -434,6 +434,245 @@ __global__ void __launch_bounds__(MTP_CWARPS * 32, 1) mtp_contract_kernel(const 
     }
 }
 
+
+// ---- kernel B, segment form: lanes = atoms, one worker (warp) owns a moment ------------------------
+// The flat-stream kernel above spends ~30 instructions around the two FP64 instructions of a product row
+// (offset unpacking, multiplier conversion, flag test, shared-memory atomic flush). Here the tables are
+// compiled into segments (mtp_program.cuh): a header {moment, row count, multiplier} followed by rows of
+// two element offsets, every moment owned by one warp, so a row is one 8-byte broadcast load, two address
+// adds, two operand loads and one FMA, and a moment is finished with a plain store. Tiles of 32 atoms;
+// the per-atom rows of the workspace are transposed into [moment][atom] on the way in and out (row
+// stride 33 keeps those transposing accesses spread over the banks), the next tile's rows travelling in
+// registers while the current tile is processed.
+// Shared memory: M[nm][33], E[nm][33] (not for descriptors), headers, rows, seeds, worker tables.
+template <typename T>
+struct SegSmem {
+    T *M, *E, *seed, *wsc;     // wsc[s] = lin[s] / q[s]; seed[m] = sum of wsc over the scalars mapped to moment m
+    int4 *hdr;
+    int2 *row;
+    int *wseg, *wrow;
+};
+template <typename T, int MODE>
+__host__ __device__ inline size_t seg_smem_layout(const MtpProgramDev &P, unsigned char *base, SegSmem<T> *out)
+{
+    size_t o = 0;
+    auto take = [&](size_t bytes) { size_t r = o; o += (bytes + 15) & ~size_t(15); return r; };
+    const size_t oM = take(sizeof(T) * (size_t)P.nm * MTP_SEG_LD);
+    // the adjoint array also holds the per-worker partial site energies before the adjoint phases: at least one row per worker
+    const size_t oE = MODE == MODE_DESC ? oM : take(sizeof(T) * (size_t)(P.nm > MTP_SEG_WORKERS ? P.nm : MTP_SEG_WORKERS) * MTP_SEG_LD);
+    const size_t oh = take(sizeof(int4) * (size_t)P.nseg);
+    const size_t orow = take(sizeof(int2) * (size_t)P.nseg_rows);
+    const size_t os = take(sizeof(T) * (size_t)P.nm);
+    const size_t osc = take(sizeof(T) * (size_t)P.ns);
+    const size_t ow = take(sizeof(int) * (size_t)(2 * P.nlev) * (MTP_SEG_WORKERS + 1));
+    const size_t owr = take(sizeof(int) * (size_t)(2 * P.nlev) * MTP_SEG_WORKERS);
+    if (out) {
+        out->M = reinterpret_cast<T *>(base + oM); out->E = reinterpret_cast<T *>(base + oE);
+        out->hdr = reinterpret_cast<int4 *>(base + oh); out->row = reinterpret_cast<int2 *>(base + orow);
+        out->seed = reinterpret_cast<T *>(base + os); out->wsc = reinterpret_cast<T *>(base + osc);
+        out->wseg = reinterpret_cast<int *>(base + ow); out->wrow = reinterpret_cast<int *>(base + owr);
+    }
+    return o;
+}
+
+// Shared-memory accesses of the row loop, by 32-bit shared-window address (explicit ld.shared / st.shared: the
+// loop is bound by instruction issue and shared-memory bandwidth, so it must not fall back to generic addressing).
+__device__ __forceinline__ int2 lds_int2(unsigned a)
+{
+    int2 v;
+    asm volatile("ld.shared.v2.s32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ int4 lds_int4(unsigned a)
+{
+    int4 v;
+    asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ double lds_val(unsigned a, double)
+{
+    double v;
+    asm volatile("ld.shared.f64 %0, [%1];" : "=d"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ float lds_val(unsigned a, float)
+{
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void sts_val(unsigned a, double v) { asm volatile("st.shared.f64 [%0], %1;" ::"r"(a), "d"(v) : "memory"); }
+__device__ __forceinline__ void sts_val(unsigned a, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory"); }
+
+// one phase for one worker. xl, yl = shared addresses of this lane's column of the arrays a row's first / second
+// offset refers to, dl = of the destination array; hdr, row, seed = shared addresses of the tables
+template <typename T, bool SEEDED>
+__device__ __forceinline__ void seg_phase(int h, int hend, unsigned hdr, unsigned rp, unsigned seed, unsigned xl, unsigned yl, unsigned dl)
+{
+    T dsum = T(0);
+    for (; h < hend; h++) {
+        const int4 hd = lds_int4(hdr + 16u * (unsigned)h);
+        const int n = hd.y & 0x3fffffff;
+        T acc0 = T(0), acc1 = T(0);
+        const unsigned rend = rp + 8u * (unsigned)n;
+#pragma unroll 1
+        for (; rp + 8u < rend; rp += 16u) {
+            const int2 r0 = lds_int2(rp), r1 = lds_int2(rp + 8u);
+            const T x0 = lds_val(xl + (unsigned)r0.x * (unsigned)sizeof(T), T()), y0 = lds_val(yl + (unsigned)r0.y * (unsigned)sizeof(T), T());
+            const T x1 = lds_val(xl + (unsigned)r1.x * (unsigned)sizeof(T), T()), y1 = lds_val(yl + (unsigned)r1.y * (unsigned)sizeof(T), T());
+            acc0 = fma(x0, y0, acc0);
+            acc1 = fma(x1, y1, acc1);
+        }
+        if (rp < rend) {
+            const int2 r0 = lds_int2(rp);
+            acc0 = fma(lds_val(xl + (unsigned)r0.x * (unsigned)sizeof(T), T()), lds_val(yl + (unsigned)r0.y * (unsigned)sizeof(T), T()), acc0);
+            rp += 8u;
+        }
+        const T mult = (T)__hiloint2double(hd.w, hd.z);
+        const T acc = acc0 + acc1;
+        dsum = (hd.y & (1 << 30)) ? mult * acc : fma(mult, acc, dsum);
+        if (hd.y < 0) {                                  // bit 31: last segment of the moment
+            T out = dsum;
+            if (SEEDED) out += lds_val(seed + (unsigned)(hd.x / MTP_SEG_LD) * (unsigned)sizeof(T), T());
+            sts_val(dl + (unsigned)hd.x * (unsigned)sizeof(T), out);
+        }
+    }
+}
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(MTP_SEG_WORKERS * 32, 1) mtp_contract_seg_kernel(const MtpProgramDev P, const MtpArgs<T> A)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int NT = MTP_SEG_WORKERS * 32;
+    SegSmem<T> S;
+    seg_smem_layout<T, MODE>(P, smem_raw, &S);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int ntot = A.prefix[A.B];
+    const int ntiles = (ntot + MTP_TILE - 1) / MTP_TILE;
+    if ((int)blockIdx.x >= ntiles) return;
+
+    // tables, staged once per block
+    for (int i = threadIdx.x; i < P.nseg; i += NT) S.hdr[i] = P.seg_hdr[i];
+    for (int i = threadIdx.x; i < P.nseg_rows; i += NT) S.row[i] = P.seg_row[i];
+    for (int i = threadIdx.x; i < 2 * P.nlev * (MTP_SEG_WORKERS + 1); i += NT) S.wseg[i] = P.seg_wseg[i];
+    for (int i = threadIdx.x; i < 2 * P.nlev * MTP_SEG_WORKERS; i += NT) S.wrow[i] = P.seg_wrow[i];
+    if (MODE != MODE_DESC) {
+        for (int i = threadIdx.x; i < P.nm; i += NT) S.seed[i] = T(0);
+        __syncthreads();
+        // adjoint seeds lin[s] / q[s] (linearMtp.h:292-295); a moment may serve several scalars
+        for (int s = threadIdx.x; s < P.ns; s += NT) {
+            const T w = A.lin[s] / A.qs[s];
+            S.wsc[s] = w;
+            atomicAdd(S.seed + P.map[s], w);
+        }
+    }
+
+    // basic-moment rows of a tile: warp w fetches atom w, lanes run over the row; fetched one tile ahead
+    const bool can_prefetch = P.nb <= 32 * MTP_PREF;
+    T pre[MTP_PREF];
+    auto fetch = [&](int tile) {
+#pragma unroll
+        for (int k = 0; k < MTP_PREF; k++) {
+            const int i = lane + 32 * k, t = tile * MTP_TILE + warp;
+            pre[k] = (t < ntot && i < P.nb) ? A.Mb[(size_t)t * A.nbp + i] : T(0);
+        }
+    };
+    if (can_prefetch) fetch(blockIdx.x);
+    // shared-window addresses of this lane's columns and of the tables
+    const unsigned ml = (unsigned)__cvta_generic_to_shared(S.M + lane), el = (unsigned)__cvta_generic_to_shared(S.E + lane);
+    const unsigned a_hdr = (unsigned)__cvta_generic_to_shared(S.hdr), a_row = (unsigned)__cvta_generic_to_shared(S.row),
+                   a_seed = (unsigned)__cvta_generic_to_shared(S.seed);
+    auto run_phase = [&](int p, auto seeded, unsigned xl, unsigned yl, unsigned dl) {
+        const int h = S.wseg[p * (MTP_SEG_WORKERS + 1) + warp], hend = S.wseg[p * (MTP_SEG_WORKERS + 1) + warp + 1];
+        seg_phase<T, decltype(seeded)::value>(h, hend, a_hdr, a_row + 8u * (unsigned)S.wrow[p * MTP_SEG_WORKERS + warp], a_seed, xl, yl, dl);
+    };
+
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        __syncthreads();     // tables staged / the previous tile's adjoints written and its moments no longer read
+        if (can_prefetch) {
+#pragma unroll
+            for (int k = 0; k < MTP_PREF; k++) {
+                const int i = lane + 32 * k;
+                if (i < P.nb) S.M[i * MTP_SEG_LD + warp] = pre[k];
+            }
+            if (tile + (int)gridDim.x < ntiles) fetch(tile + gridDim.x);   // in flight during this tile
+        } else {
+            const int t = tile * MTP_TILE + warp;
+            const T *src = A.Mb + (size_t)t * A.nbp;
+            for (int i = lane; i < P.nb; i += 32) S.M[i * MTP_SEG_LD + warp] = t < ntot ? src[i] : T(0);
+        }
+        __syncthreads();
+
+        for (int p = 0; p < P.nlev; p++) {
+            run_phase(p, std::false_type{}, ml, ml, ml);
+            __syncthreads();
+        }
+
+        // per-atom bookkeeping (lane = atom of the tile)
+        const int t = tile * MTP_TILE + lane;
+        const bool valid = t < ntot;
+        int b = 0;
+        size_t slot = 0;
+        if (valid) {
+            b = find_structure(A.prefix, A.B, t);
+            slot = (size_t)b * A.npad + (t - A.prefix[b]);
+        }
+        if (MODE == MODE_DESC) {
+            if (valid)
+                for (int s = warp; s < P.ns; s += MTP_SEG_WORKERS) A.desc[slot * P.ns + s] = S.M[P.map[s] * MTP_SEG_LD + lane];
+            continue;
+        }
+
+        // site energies (linearMtp.h:281-289): partial sums per warp in the (still unused) adjoint array
+        T es = T(0);
+        for (int s = warp; s < P.ns; s += MTP_SEG_WORKERS) es = fma(S.wsc[s], S.M[P.map[s] * MTP_SEG_LD + lane], es);
+        S.E[warp * MTP_SEG_LD + lane] = es;
+        __syncthreads();
+        if (warp == 0) {
+            T e = T(0);
+#pragma unroll 8
+            for (int k = 0; k < MTP_SEG_WORKERS; k++) e += S.E[k * MTP_SEG_LD + lane];
+            if (valid) {
+                const int *types = A.types + (size_t)b * (A.npad + A.nghost);
+                e += A.bias[types[A.bilist[slot]]];
+            } else {
+                e = T(0);
+            }
+            // one atomic per structure present in these 32 atoms
+            const int key = valid ? b : -1;
+            T tot = T(0);
+            int leader = MTP_TILE;
+            for (int k = 0; k < MTP_TILE; k++) {
+                const T ek = __shfl_sync(FULL_MASK, e, k);
+                const int bk = __shfl_sync(FULL_MASK, key, k);
+                if (bk == key) { tot += ek; leader = min(leader, k); }
+            }
+            if (valid && lane == leader) atomicAdd(A.etot + b, tot);
+        }
+        __syncthreads();
+        // moments whose adjoint is only their seed
+        for (int i = warp; i < P.nseg_init; i += MTP_SEG_WORKERS) {
+            const int m = P.seg_init[i];
+            S.E[m * MTP_SEG_LD + lane] = S.seed[m];
+        }
+        __syncthreads();
+
+        // adjoints, deepest sources first: E[src] = seed + sum mult E[dst] M[other]
+        for (int p = P.nlev; p < 2 * P.nlev; p++) {
+            run_phase(p, std::true_type{}, el, ml, el);
+            __syncthreads();
+        }
+        // adjoints of the basic moments, back to per-atom rows (warp w writes atom w)
+        {
+            const int t = tile * MTP_TILE + warp;
+            if (t < ntot) {
+                T *dstp = A.Eb + (size_t)t * A.nbp;
+                for (int i = lane; i < A.nbp; i += 32) dstp[i] = i < P.nb ? S.E[i * MTP_SEG_LD + warp] : T(0);
+            }
+        }
+    }
+}
+
 // ---- kernel C: force and virial -----------------------------------------------------------------
 // shared-memory elements (of T) per warp: E4[4 ndp] Ed[nbp + 4] fr, fd[2 nmus 32] row buffer [96 + 36 ints]
 template <typename T>
@@ -629,6 +868,19 @@ template <typename T, int MODE>
 static int dispatch_contract(const MtpProgramDev &P, const MtpArgs<T> &A, long atoms_upper, cudaStream_t st)
 {
     const size_t cap = 222 * 1024;
+    {   // segment form: whole tables and a tile of 32 atoms in shared memory
+        const size_t smem = seg_smem_layout<T, MODE>(P, nullptr, nullptr);
+        if (smem <= 226 * 1024 && P.nseg > 0) {
+            auto kern = mtp_contract_seg_kernel<T, MODE>;
+            static KernelSetup setup;
+            if (int rc = kernel_setup(setup, kern, smem)) return rc;
+            long tiles = (atoms_upper + MTP_TILE - 1) / MTP_TILE;
+            if (tiles > sm_count()) tiles = sm_count();      // persistent: one block per SM walks over the tiles
+            kern<<<(unsigned)tiles, MTP_SEG_WORKERS * 32, smem, st>>>(P, A);
+            AI2B_CUDA(cudaGetLastError());
+            return AI2B_OK;
+        }
+    }
 #define AI2B_TRY(TA_)                                                                                       \
     if ((long)P.nm * (TA_ + 1) <= 65535) {                                                                  \
         if (contract_smem<T, MODE>(P, TA_, true) <= cap) return launch_contract<T, TA_, MODE, true>(P, A, atoms_upper, st);   \

@@ -296,7 +296,89 @@ extern "C" int ai2b_mtp_program_create(int nm, int nb, const int *basic, int nt,
     for (int s = 0; s < ns; s++)
         AI2B_REQUIRE(map[s] >= 0 && map[s] < nm, AI2B_ERR_INVALID, "alpha_moment_mapping[%d] out of range", s);
 
+    // segment streams (see mtp_program.cuh)
+    std::vector<int4> seg_hdr;
+    std::vector<int2> seg_row;
+    std::vector<int> seg_wseg, seg_wrow, seg_init;
+    {
+        std::vector<char> is_source(nm, 0), is_mapped(nm, 0);
+        for (int t = 0; t < nt; t++) { is_source[times[4 * t]] = 1; is_source[times[4 * t + 1]] = 1; }
+        for (int s = 0; s < ns; s++) is_mapped[mapping[s]] = 1;
+        // moments whose adjoint is just their seed: scalars that are no operand of any product, and basic
+        // moments nothing uses (seed 0); every other adjoint that is read is written by a gather phase
+        for (int m = 0; m < nm; m++)
+            if (!is_source[m] && (is_mapped[m] || m < nb)) seg_init.push_back(m);
+        struct Row { int x, y, mult; };
+        auto emit_phase = [&](const std::vector<std::pair<int, std::vector<Row>>> &moments) {
+            // longest processing time first over the workers; cost = rows + one per segment
+            std::vector<size_t> order(moments.size());
+            for (size_t i = 0; i < order.size(); i++) order[i] = i;
+            std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) { return moments[a].second.size() > moments[b].second.size(); });
+            std::vector<std::vector<size_t>> mine(MTP_SEG_WORKERS);
+            std::vector<long> load(MTP_SEG_WORKERS, 0);
+            for (size_t i : order) {
+                int w = (int)(std::min_element(load.begin(), load.end()) - load.begin());
+                mine[w].push_back(i);
+                load[w] += (long)moments[i].second.size() + 2;
+            }
+            for (int w = 0; w < MTP_SEG_WORKERS; w++) {
+                seg_wseg.push_back((int)seg_hdr.size());
+                seg_wrow.push_back((int)seg_row.size());
+                for (size_t i : mine[w]) {
+                    std::vector<Row> rows = moments[i].second;
+                    std::stable_sort(rows.begin(), rows.end(), [](const Row &a, const Row &b) { return a.mult < b.mult; });
+                    size_t r = 0;
+                    bool first = true;
+                    while (r < rows.size()) {
+                        size_t e = r;
+                        while (e < rows.size() && rows[e].mult == rows[r].mult) e++;
+                        const double mult = (double)rows[r].mult;
+                        long long bits;
+                        memcpy(&bits, &mult, 8);
+                        unsigned flags = (unsigned)(e - r) | (first ? 1u << 30 : 0u) | (e == rows.size() ? 1u << 31 : 0u);
+                        seg_hdr.push_back(make_int4(moments[i].first * MTP_SEG_LD, (int)flags, (int)(bits & 0xffffffffll), (int)(bits >> 32)));
+                        for (size_t k = r; k < e; k++) seg_row.push_back(make_int2(rows[k].x * MTP_SEG_LD, rows[k].y * MTP_SEG_LD));
+                        first = false;
+                        r = e;
+                    }
+                }
+            }
+            seg_wseg.push_back((int)seg_hdr.size());
+        };
+        for (int lev = 1; lev <= P.nlev; lev++) {
+            std::vector<std::pair<int, std::vector<Row>>> moments;
+            for (int m = 0; m < nm; m++)
+                if (depth[m] == lev && !rows_of[m].empty()) {
+                    std::vector<Row> rows;
+                    for (int t : rows_of[m]) rows.push_back(Row{times[4 * t], times[4 * t + 1], times[4 * t + 2]});
+                    moments.emplace_back(m, rows);
+                }
+            emit_phase(moments);
+        }
+        for (int k = 0; k < P.nlev; k++) {
+            const int lev = P.nlev - 1 - k;
+            std::vector<std::pair<int, std::vector<Row>>> moments;
+            for (int m = 0; m < nm; m++)
+                if (depth[m] == lev && !occ_of[m].empty()) {
+                    std::vector<Row> rows;
+                    for (int o : occ_of[m]) {
+                        const int t = o >> 1;
+                        const int other = (o & 1) ? times[4 * t] : times[4 * t + 1];
+                        rows.push_back(Row{times[4 * t + 3], other, times[4 * t + 2]});
+                    }
+                    moments.emplace_back(m, rows);
+                }
+            emit_phase(moments);
+        }
+        for (const int4 &h : seg_hdr)
+            AI2B_REQUIRE((h.y & 0x3fffffff) < (1 << 24), AI2B_ERR_UNSUPPORTED, "a product segment has too many rows");
+    }
+    P.nseg = (int)seg_hdr.size();
+    P.nseg_rows = (int)seg_row.size();
+    P.nseg_init = (int)seg_init.size();
+
     Blob blob;
+    size_t o_sh = blob.add(seg_hdr), o_sr = blob.add(seg_row), o_sws = blob.add(seg_wseg), o_swr = blob.add(seg_wrow), o_si = blob.add(seg_init);
     size_t o_bd = blob.add(basic_dense), o_db = blob.add(dense_basic), o_e4d = blob.add(e4d), o_g = blob.add(e4g), o_m = blob.add(e4m), o_fd = blob.add(fwd_dst),
            o_fr = blob.add(fwd_ab), o_fmf = blob.add(fwd_mf), o_fmd = blob.add(fwd_md), o_rm = blob.add(rev_mom),
            o_re = blob.add(rev_od), o_rmf = blob.add(rev_mf), o_rmd = blob.add(rev_md), o_map = blob.add(map);
@@ -332,6 +414,11 @@ extern "C" int ai2b_mtp_program_create(int nm, int nb, const int *basic, int nt,
     P.rev_ents = (const int2 *)(b + o_rent);
     P.fwd_flat = (const int2 *)(b + o_ff);
     P.rev_flat = (const int2 *)(b + o_rf);
+    P.seg_hdr = (const int4 *)(b + o_sh);
+    P.seg_row = (const int2 *)(b + o_sr);
+    P.seg_wseg = (const int *)(b + o_sws);
+    P.seg_wrow = (const int *)(b + o_swr);
+    P.seg_init = (const int *)(b + o_si);
     prog->dev = P;
     *out = prog;
     return AI2B_OK;

@@ -45,7 +45,23 @@ struct MtpProgramDev {
     const float *rev_mult_f;
     const double *rev_mult_d;
     const int *map;                 // [ns] alpha_moment_mapping
+    // Segment streams of the lanes-as-atoms contraction (tiles of MTP_TILE atoms, MTP_SEG_WORKERS workers):
+    // the rows that feed one moment with one multiplier form a segment {header, rows}. Phase p < nlev is
+    // product depth p + 1 (rows {a, b}: M[dst] = sum mult * M[a] * M[b]); phase nlev + k gathers the adjoints
+    // of the source moments of depth nlev - 1 - k (rows {dst, other}: E[src] = seed + sum mult * E[dst] * M[other]).
+    // Every moment's segments belong to ONE worker and are consecutive, so there are no atomics; the
+    // moments of a phase are dealt to the workers by decreasing row count (longest processing time first).
+    // All moment references are element offsets m * MTP_SEG_LD.
+    const int4 *seg_hdr;            // [nseg] {moment offset, nrows | first << 30 | last << 31, multiplier (double) lo, hi}
+    const int2 *seg_row;            // [2 nt rows of the adjoint phases + nt of the product phases]
+    const int *seg_wseg;            // [2 nlev][MTP_SEG_WORKERS + 1] first header of worker w in phase p
+    const int *seg_wrow;            // [2 nlev][MTP_SEG_WORKERS] first row of worker w in phase p
+    const int *seg_init;            // [nseg_init] moments whose adjoint is only their seed (no product reads them)
+    int nseg, nseg_rows, nseg_init;
 };
+constexpr int MTP_SEG_WORKERS = 32;
+constexpr int MTP_TILE = 32;        // atoms per tile of the contraction
+constexpr int MTP_SEG_LD = 33;      // row stride of its [moment][atom] arrays
 
 template <typename T> __device__ __forceinline__ const T *fwd_mult(const MtpProgramDev &P);
 template <> __device__ __forceinline__ const float *fwd_mult<float>(const MtpProgramDev &P) { return P.fwd_mult_f; }

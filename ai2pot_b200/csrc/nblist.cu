@@ -8,10 +8,14 @@
 // padding -1 / 0. The order inside a row is not part of the contract.
 //
 // Here: atoms are binned once by their fractional coordinates wrapped into the cell (bins at
-// least rcut thick), each centre atom is handled by one warp that walks the neighbouring bins
-// with lanes over candidate atoms, applies the reference's predicate with the reference's
-// operation order (no FMA contraction), and compacts hits with a warp ballot. The padded row
-// is written once, by the same warp.
+// least rcut / 2 thick, so a centre looks at 5 x 5 x 5 bins: 125 candidates at one atom per bin
+// where bins of a full cutoff give 216), each centre atom is handled by one warp that walks the
+// neighbouring bins with lanes over candidate atoms, applies the reference's predicate with the
+// reference's operation order (no FMA contraction), and compacts hits with a warp ballot. Bins
+// that follow one another along the third axis are contiguous in bin order, so the 5 bins of a
+// column are ONE range of atoms: the warp's table holds 25 ranges (plus the wrapped remainders
+// for centres next to a periodic face) instead of 125 bins. The padded row is written once, by
+// the same warp.
 #include "common.cuh"
 
 #include <cmath>
@@ -26,6 +30,7 @@ template <> struct Vec4<float> { using type = float4; };
 // words are field-wise sums and differences as long as every true field stays inside +-511. The fourth
 // component of a bin-ordered position carries the atom's packed wrap.
 constexpr int NB_WRAP_MAX = 127;
+constexpr int NB_SUB = 2;            // bins per cutoff length along each axis
 constexpr int NB_PACK_ZERO = 512 | (512 << 10) | (512 << 20);
 __host__ __device__ inline int nb_pack3(int a, int b, int c) { return (a + 512) | ((b + 512) << 10) | ((c + 512) << 20); }
 __device__ __forceinline__ float nb_bits_to(float, int v) { return __int_as_float(v); }
@@ -37,6 +42,7 @@ struct NbGrid {          // lives in the workspace; written by nb_grid_kernel
     int nb[3];           // bins per fractional axis
     int R[3];            // bins to search on each side
     int total;
+    int zmerge;          // the bins of a column along the third axis are taken as one range (needs nb[2] >= 2 R[2] + 1 if periodic)
     int bigwrap;         // set by nb_count_kernel when an atom lies more than NB_WRAP_MAX periods outside the cell
     double lo[3];        // non-periodic axes: lowest fractional coordinate
     double scale[3];     // bin = (s - lo) * scale
@@ -141,16 +147,17 @@ __global__ void nb_grid_kernel(NbParams<T> P, const unsigned long long *__restri
         } else {
             double lo = dec_double(ext[k]), hi = dec_double(ext[3 + k]);
             double span = fmax(hi - lo, 1e-12);
-            int nb = (int)floor(span * P.dplane[k] / P.rcut_m);
+            int nb = (int)floor(span * P.dplane[k] * NB_SUB / P.rcut_m);
             nb = max(1, min(nb, P.nbh[k]));
             g->nb[k] = nb;
-            g->R[k] = 1;
+            g->R[k] = NB_SUB;
             g->lo[k] = lo;
             g->scale[k] = nb / span;
         }
         total *= g->nb[k];
     }
     g->total = (int)total;   // <= maxbins by construction of nbh
+    g->zmerge = (!P.per[2] || g->nb[2] >= 2 * g->R[2] + 1) ? 1 : 0;
     g->bigwrap = 0;
 }
 
@@ -268,8 +275,11 @@ __global__ void nb_setup_periodic_kernel(NbGrid host_grid, NbGrid *__restrict__ 
     }
 }
 
-// exclusive scan by one block (grids of up to a few hundred thousand bins): bin_start and cursor
-__global__ void nb_scan_small_kernel(const NbGrid *__restrict__ gp, const int *__restrict__ in, int *__restrict__ out, int *__restrict__ cursor)
+// exclusive scan by one block (grids of up to 64 K bins): bin_start and cursor. Every thread takes SCAN_ITEMS
+// consecutive counters, so 16 K counters go through one round of the block-wide scan.
+constexpr int SCAN_ITEMS = 16;
+__global__ void __launch_bounds__(SCAN_BLOCK) nb_scan_small_kernel(const NbGrid *__restrict__ gp, const int *__restrict__ in, int *__restrict__ out,
+                                                                  int *__restrict__ cursor)
 {
     __shared__ int ws[32];
     __shared__ int carry;
@@ -277,10 +287,16 @@ __global__ void nb_scan_small_kernel(const NbGrid *__restrict__ gp, const int *_
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (threadIdx.x == 0) carry = 0;
     __syncthreads();
-    for (int base = 0; base <= total; base += SCAN_BLOCK) {
-        const int i = base + threadIdx.x;
-        const int v = i < total ? in[i] : 0;
-        int inc = v;
+    for (int base = 0; base <= total; base += SCAN_BLOCK * SCAN_ITEMS) {
+        const int i0 = base + threadIdx.x * SCAN_ITEMS;
+        int v[SCAN_ITEMS];
+        int sum = 0;
+#pragma unroll
+        for (int k = 0; k < SCAN_ITEMS; k++) {
+            v[k] = i0 + k < total ? in[i0 + k] : 0;
+            sum += v[k];
+        }
+        int inc = sum;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) { int n = __shfl_up_sync(FULL_MASK, inc, o); if (lane >= o) inc += n; }
         if (lane == 31) ws[warp] = inc;
@@ -292,11 +308,15 @@ __global__ void nb_scan_small_kernel(const NbGrid *__restrict__ gp, const int *_
             ws[lane] = w;
         }
         __syncthreads();
-        const int excl = carry + inc - v + (warp > 0 ? ws[warp - 1] : 0);
-        if (i <= total) out[i] = excl;
-        if (i < total) cursor[i] = excl;
+        int excl = carry + inc - sum + (warp > 0 ? ws[warp - 1] : 0);
+#pragma unroll
+        for (int k = 0; k < SCAN_ITEMS; k++) {
+            if (i0 + k <= total) out[i0 + k] = excl;
+            if (i0 + k < total) cursor[i0 + k] = excl;
+            excl += v[k];
+        }
         __syncthreads();
-        if (threadIdx.x == SCAN_BLOCK - 1) carry = excl + v;
+        if (threadIdx.x == SCAN_BLOCK - 1) carry = excl;
         __syncthreads();
     }
 }
@@ -324,7 +344,7 @@ constexpr int NB_CAND = 512;
 // TO = element type of the rcs rows (T, or float rows from double positions: what an MD host that keeps
 // double coordinates and a single-precision model does on the CPU)
 template <typename T, typename TO>
-__global__ void __launch_bounds__(NB_WARPS * 32, sizeof(T) == 8 ? 3 : 4)
+__global__ void __launch_bounds__(NB_WARPS * 32, 4)
 nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restrict__ bin_start,
                 const int4 *__restrict__ ainfo, const typename Vec4<T>::type *__restrict__ spos,
                 const int4 *__restrict__ sinfo, int *__restrict__ numneigh, int *__restrict__ firstneigh,
@@ -339,16 +359,18 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
     const bool packed = g.bigwrap == 0;   // every wrap fits the packed form
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nwarps = gridDim.x * NB_WARPS;
-    const int nx = 2 * g.R[0] + 1, ny = 2 * g.R[1] + 1, nz = 2 * g.R[2] + 1, nnb = nx * ny * nz;
+    const int nx = 2 * g.R[0] + 1, ny = 2 * g.R[1] + 1, nz = 2 * g.R[2] + 1;
+    const bool zmerge = g.zmerge != 0;
+    const int nnb_full = zmerge ? nx * ny : nx * ny * nz;   // table entries of a centre away from the third axis' faces
     const unsigned lt_mask = (1u << lane) - 1u;
     int local_max = 0;
 
-    // Large systems: warps take runs of 16 bin-ordered atoms, dealt round-robin, so consecutive centres
-    // mostly share their bin and the table of neighbouring bins is built once per bin, while ghost
-    // regions (atoms that are neighbours only) spread over all warps. Small systems: single atoms are
-    // dealt round-robin (runs would leave most warps without work).
+    // Large systems: warps take runs of up to 16 bin-ordered atoms, dealt round-robin, so consecutive centres
+    // touch the same bins and candidates, while ghost regions (atoms that are neighbours only) spread over
+    // all warps. Small systems: single atoms are dealt round-robin (runs would leave most warps without work).
     const int gw = blockIdx.x * NB_WARPS + warp;
-    const int RUN = (P.n + nwarps - 1) / nwarps >= 8 ? 16 : 1;
+    const int per_warp = (P.n + nwarps - 1) / nwarps;
+    const int RUN = min(16, max(1, per_warp / 4));    // at least four runs per warp, so that the last round of runs is short
     const int nruns = (P.n + RUN - 1) / RUN;
     int cached_bin = -1;
     for (int run = gw; run < nruns; run += nwarps)
@@ -366,15 +388,22 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
         int *frow = firstneigh + (size_t)(i - P.cbegin) * P.umax;
         TO *rrow = rcs + (size_t)(i - P.cbegin) * P.umax * 3;
 
+        // With merged columns a centre within R bins of a periodic face of the third axis has, per column, a second
+        // range: the part of its 2R+1 bins that lies across the face (entries nnb_full .. 2 nnb_full - 1).
+        const bool zsplit = zmerge && P.per[2] && (bz - g.R[2] < 0 || bz + g.R[2] >= g.nb[2]);
+        const int nnb = zsplit ? 2 * nnb_full : nnb_full;
         const bool reuse = nnb <= 32 && bin_i == cached_bin;
         cached_bin = nnb <= 32 ? bin_i : -1;
         for (int base = 0; base < nnb; base += 32) {
-            // lanes = neighbouring bins of this group
+            // lanes = table entries (neighbouring bins, or columns of bins) of this group
             const int k = base + lane;
             int start = 0, len = 0, shift = 0;
             if (!reuse && k < nnb) {
-                int d[3] = {k / (ny * nz) - g.R[0], (k / nz) % ny - g.R[1], k % nz - g.R[2]};
-                int b[3] = {bx + d[0], by + d[1], bz + d[2]}, m[3];
+                const int kk = zmerge ? (k >= nnb_full ? k - nnb_full : k) : k;
+                int d[3], b[3], m[3];
+                if (zmerge) { d[0] = kk / ny - g.R[0]; d[1] = kk % ny - g.R[1]; d[2] = 0; }
+                else { d[0] = kk / (ny * nz) - g.R[0]; d[1] = (kk / nz) % ny - g.R[1]; d[2] = kk % nz - g.R[2]; }
+                b[0] = bx + d[0]; b[1] = by + d[1]; b[2] = bz + d[2];
                 bool ok = true;
 #pragma unroll
                 for (int c = 0; c < 3; c++) {
@@ -390,10 +419,23 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
                         ok = ok && b[c] >= 0 && b[c] < g.nb[c];
                     }
                 }
+                int zlo = b[2], zhi = b[2];          // bins of the third axis this entry covers (inside the grid)
+                if (zmerge) {
+                    zlo = bz - g.R[2]; zhi = bz + g.R[2];
+                    if (k < nnb_full) {              // the part inside the cell
+                        zlo = max(zlo, 0); zhi = min(zhi, g.nb[2] - 1);
+                        m[2] = 0;
+                        ok = ok && zlo <= zhi;
+                    } else if (zlo < 0) {            // the part below the face: bins nb + zlo .. nb - 1 of the image one period down
+                        zlo += g.nb[2]; zhi = g.nb[2] - 1; m[2] = -1;
+                    } else {                         // the part above the face
+                        zhi -= g.nb[2]; zlo = 0; m[2] = 1;
+                    }
+                }
                 if (ok) {
-                    int bin = (b[0] * g.nb[1] + b[1]) * g.nb[2] + b[2];
-                    start = bin_start[bin];
-                    len = bin_start[bin + 1] - start;
+                    const int col = (b[0] * g.nb[1] + b[1]) * g.nb[2];
+                    start = bin_start[col + zlo];
+                    len = bin_start[col + zhi + 1] - start;
                     shift = (m[0] + 512) | ((m[1] + 512) << 10) | ((m[2] + 512) << 20);
                 }
             }
@@ -630,7 +672,7 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
         P.e[k] = pbc[k] ? (int)std::ceil((double)(rcut / dT[k])) : 0;
         AI2B_REQUIRE(P.e[k] < 500, AI2B_ERR_UNSUPPORTED, "cell far smaller than the cutoff (%d images on axis %d)", P.e[k], k);
         if (pbc[k]) {
-            int nb = (int)std::floor(P.dplane[k] / P.rcut_m);
+            int nb = (int)std::floor(P.dplane[k] * NB_SUB / P.rcut_m);
             P.nbh[k] = nb < 1 ? 1 : nb;
         } else {
             any_open = true;
@@ -654,7 +696,7 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
     }
     // The grid is known on the host when every axis is periodic, or when the caller gives the fractional extent
     // of the atoms along the open axes (atoms outside it are clamped into the edge bins, which keeps every
-    // pair within reach of the +-1 bin search: an extent that is a little off costs time, not pairs).
+    // pair within reach of the bin search: an extent that is a little off costs time, not pairs).
     NbGrid hg;
     memset(&hg, 0, sizeof(hg));
     const bool host_grid = !any_open || open_ext != nullptr;
@@ -669,16 +711,17 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
             } else {
                 const double lo = open_ext[k], hi = open_ext[3 + k];
                 const double span = std::fmax(hi - lo, 1e-12);
-                int nb = (int)std::floor(span * P.dplane[k] / P.rcut_m);
+                int nb = (int)std::floor(span * P.dplane[k] * NB_SUB / P.rcut_m);
                 nb = nb < 1 ? 1 : (nb > P.nbh[k] ? P.nbh[k] : nb);
                 hg.nb[k] = nb;
-                hg.R[k] = 1;
+                hg.R[k] = NB_SUB;
                 hg.lo[k] = lo;
                 hg.scale[k] = nb / span;
             }
             total *= hg.nb[k];
         }
         hg.total = (int)total;
+        hg.zmerge = (!P.per[2] || hg.nb[2] >= 2 * hg.R[2] + 1) ? 1 : 0;
         prod = total;
     }
 
@@ -697,14 +740,14 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
         if (!reuse_bins) nb_frac2cart_kernel<T><<<nblk, tb, 0, st>>>(P, d_coords, cart);
         pos = cart;
     }
-    const bool small_grid = host_grid && prod + 1 <= 256 * 1024;
+    const bool small_grid = host_grid;
     if (reuse_bins) {
         // bins, bin-ordered positions and (for fractional input) Cartesian positions are in the workspace already
     } else if (small_grid) {
         const int ncount = (int)prod + 1;
         nb_setup_periodic_kernel<<<(ncount + 255) / 256, 256, 0, st>>>(hg, grid, count, ncount, d_status);
         nb_count_kernel<T><<<nblk, tb, 0, st>>>(P, grid, pos, ainfo, count);
-        if (ncount <= 16 * SCAN_BLOCK) {
+        if (ncount <= 64 * SCAN_BLOCK) {
             nb_scan_small_kernel<<<1, SCAN_BLOCK, 0, st>>>(grid, count, start, cursor);
         } else {   // large grids: block-parallel scan
             const int sblk = (ncount + SCAN_BLOCK - 1) / SCAN_BLOCK;
