@@ -402,6 +402,69 @@ def mtp_loss_backward(prog, model, nb, weights, e_ml, e_dft, f_ml, f_dft, v_ml=N
     return dco, dli, dbi
 
 
+AI2B_ERR_TIMEOUT = -6
+
+
+def peer_push_rows(src, src_index, dst_index, nrows, shift3, peer_dst, peer_flag, flag_value, counter):
+    """ai2b_peer_push_rows_*: peer_dst[dst_index[k]] = src[src_index[k]] + shift3 for k < nrows, then the flag
+    (an int32 element of the neighbour's flag tensor) is set to flag_value. All tensors are CUDA tensors; peer_dst
+    and peer_flag alias the neighbour's memory."""
+    suf, _ = _suf(src.dtype)
+    npdt = np.float64 if suf == "f64" else np.float32
+    sh = None
+    if shift3 is not None:
+        hs = np.ascontiguousarray(shift3, npdt)
+        sh = hs.ctypes.data_as(C.c_void_p)
+    _check(getattr(lib(), "ai2b_peer_push_rows_" + suf)(
+        _ptr(src), _ptr(src_index), _ptr(dst_index), C.c_int(int(nrows)), sh, C.c_void_p(peer_dst.data_ptr()),
+        C.c_void_p(peer_flag.data_ptr()), C.c_int(int(flag_value)), _ptr(counter), _stream()))
+
+
+def peer_exchange(left, right, flag_value, my_flag_l, my_flag_r, status, counter, max_polls=20_000_000):
+    """ai2b_peer_exchange_*: both pushes of an exchange and the wait for the neighbours' pushes in one launch.
+    left / right: dict(src, src_idx, dst_idx, n, shift, dst, flag) as for peer_push_rows."""
+    suf, _ = _suf(left["src"].dtype)
+    npdt = np.float64 if suf == "f64" else np.float32
+    keep = []
+
+    def side(p):
+        sh = None
+        if p.get("shift") is not None:
+            hs = np.ascontiguousarray(p["shift"], npdt)
+            keep.append(hs)
+            sh = hs.ctypes.data_as(C.c_void_p)
+        return (_ptr(p["src"]), _ptr(p.get("src_idx")), _ptr(p.get("dst_idx")), C.c_int(int(p["n"])), sh,
+                C.c_void_p(p["dst"].data_ptr()), C.c_void_p(p["flag"].data_ptr()))
+    _check(getattr(lib(), "ai2b_peer_exchange_" + suf)(*side(left), *side(right), C.c_int(int(flag_value)), _ptr(my_flag_l), _ptr(my_flag_r),
+                                                       C.c_longlong(int(max_polls)), _ptr(status), _ptr(counter), _stream()))
+
+
+def peer_return_reduce(left, right, flag_value, my_flag_l, my_flag_r, back, back_index, force, partial, peer_tables, peer_table_flags,
+                       my_table, my_table_flags, reduced, rank, nranks, status, counter, max_polls=20_000_000):
+    """ai2b_peer_return_reduce_*: ghost-force rows to both neighbours, partial sums to every rank, then the received
+    rows added onto `force` and the partials of all ranks summed into `reduced`, in one launch. left / right:
+    dict(src, n, dst, flag) or None; peer_tables / peer_table_flags: int64 CUDA tensors of device addresses."""
+    suf, _ = _suf(force.dtype)
+
+    def side(p):
+        if p is None or p["n"] == 0:
+            return (None, C.c_int(0), None, None if p is None else C.c_void_p(p["flag"].data_ptr()))
+        return (_ptr(p["src"]), C.c_int(int(p["n"])), C.c_void_p(p["dst"].data_ptr()), C.c_void_p(p["flag"].data_ptr()))
+    nback = 0 if back_index is None else int(back_index.numel())
+    nvalues = int(partial.numel())
+    _check(getattr(lib(), "ai2b_peer_return_reduce_" + suf)(
+        *side(left), *side(right), C.c_int(int(flag_value)), _ptr(my_flag_l), _ptr(my_flag_r), _ptr(back) if nback else None,
+        _ptr(back_index) if nback else None, C.c_int(nback), _ptr(force), _ptr(partial), _ptr(peer_tables), _ptr(peer_table_flags),
+        _ptr(my_table), _ptr(my_table_flags), _ptr(reduced), C.c_int(int(rank)), C.c_int(int(nranks)), C.c_int(nvalues),
+        C.c_longlong(int(max_polls)), _ptr(status), _ptr(counter), _stream()))
+
+
+def peer_wait(flag, value, status, max_polls=5_000_000):
+    """ai2b_peer_wait: the current stream waits until flag[0] >= value, for at most max_polls polls of 200 ns;
+    a wait that gives up stores 1 to status[0]."""
+    _check(lib().ai2b_peer_wait(_ptr(flag), C.c_int(int(value)), C.c_longlong(int(max_polls)), _ptr(status), _stream()))
+
+
 class MdSession:
     """ctypes wrapper of ai2b_md_session_*: the device-resident input path of an MD host
     (positions + model types in, forces on local and ghost atoms + energy + six virial components out).

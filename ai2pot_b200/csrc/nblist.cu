@@ -43,6 +43,7 @@ struct NbGrid {          // lives in the workspace; written by nb_grid_kernel
     int R[3];            // bins to search on each side
     int total;
     int zmerge;          // the bins of a column along the third axis are taken as one range (needs nb[2] >= 2 R[2] + 1 if periodic)
+    float pre_lo, pre_hi;   // single-precision pre-test on positions wrapped into the cell: 1e-3 and rcut^2 widened by its rounding error
     int bigwrap;         // set by nb_count_kernel when an atom lies more than NB_WRAP_MAX periods outside the cell
     double lo[3];        // non-periodic axes: lowest fractional coordinate
     double scale[3];     // bin = (s - lo) * scale
@@ -132,6 +133,29 @@ __global__ void nb_init_kernel(unsigned long long *ext, int *status)
     if (threadIdx.x < 2) status[threadIdx.x] = 0;
 }
 
+// Bounds of the single-precision pre-test. It works on float copies of the positions wrapped into the cell plus
+// the float image shift of the candidate's bin; with coordinates bounded by reach = sum_k (max|s_k| + 2) |a_k| every
+// difference carries at most ~6 ulp(reach), so d^2 near the cutoff is off by less than 64 eps reach rcut.
+template <typename T>
+__host__ __device__ inline void nb_pretest_bounds(const NbParams<T> &P, const double *lo, const double *scale_or_hi, bool have_hi, NbGrid *g)
+{
+    double reach = 0.0;
+    for (int k = 0; k < 3; k++) {
+        const double len = sqrt((double)P.cell[3 * k] * (double)P.cell[3 * k] + (double)P.cell[3 * k + 1] * (double)P.cell[3 * k + 1] +
+                                (double)P.cell[3 * k + 2] * (double)P.cell[3 * k + 2]);
+        double smax = 1.0;
+        if (!P.per[k]) {
+            const double hi = have_hi ? scale_or_hi[k] : lo[k] + g->nb[k] / g->scale[k];
+            smax = fmax(fabs(lo[k]), fabs(hi));
+        }
+        reach += (smax + 2.0) * len;
+    }
+    const double rc = sqrt(P.rc2);
+    const double err = 64.0 * 6e-8 * reach * rc + 1e-6 * P.rc2;
+    g->pre_hi = (float)((P.rc2 + err) * (1.0 + 1e-6));
+    g->pre_lo = (float)((1e-3 - err) * (1.0 - 1e-6));
+}
+
 template <typename T>
 __global__ void nb_grid_kernel(NbParams<T> P, const unsigned long long *__restrict__ ext, NbGrid *__restrict__ g)
 {
@@ -159,6 +183,7 @@ __global__ void nb_grid_kernel(NbParams<T> P, const unsigned long long *__restri
     g->total = (int)total;   // <= maxbins by construction of nbh
     g->zmerge = (!P.per[2] || g->nb[2] >= 2 * g->R[2] + 1) ? 1 : 0;
     g->bigwrap = 0;
+    nb_pretest_bounds(P, g->lo, nullptr, false, g);
 }
 
 template <typename T>
@@ -275,56 +300,54 @@ __global__ void nb_setup_periodic_kernel(NbGrid host_grid, NbGrid *__restrict__ 
     }
 }
 
-// exclusive scan by one block (grids of up to 64 K bins): bin_start and cursor. Every thread takes SCAN_ITEMS
-// consecutive counters, so 16 K counters go through one round of the block-wide scan.
+// exclusive scan by one block (grids of up to 64 K bins): bin_start and cursor. The counters of SCAN_ITEMS rounds
+// of the block-wide scan are loaded together (coalesced, all loads in flight at once) and the results stored
+// together, so the rounds themselves run out of registers.
 constexpr int SCAN_ITEMS = 16;
 __global__ void __launch_bounds__(SCAN_BLOCK) nb_scan_small_kernel(const NbGrid *__restrict__ gp, const int *__restrict__ in, int *__restrict__ out,
                                                                   int *__restrict__ cursor)
 {
-    __shared__ int ws[32];
-    __shared__ int carry;
+    __shared__ int ws[2][32];
     const int total = gp->total;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (threadIdx.x == 0) carry = 0;
-    __syncthreads();
+    int carry = 0;      // every thread keeps the running total
     for (int base = 0; base <= total; base += SCAN_BLOCK * SCAN_ITEMS) {
-        const int i0 = base + threadIdx.x * SCAN_ITEMS;
         int v[SCAN_ITEMS];
-        int sum = 0;
 #pragma unroll
         for (int k = 0; k < SCAN_ITEMS; k++) {
-            v[k] = i0 + k < total ? in[i0 + k] : 0;
-            sum += v[k];
+            const int i = base + k * SCAN_BLOCK + threadIdx.x;
+            v[k] = i < total ? in[i] : 0;
         }
-        int inc = sum;
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) { int n = __shfl_up_sync(FULL_MASK, inc, o); if (lane >= o) inc += n; }
-        if (lane == 31) ws[warp] = inc;
-        __syncthreads();
-        if (warp == 0) {
-            int w = ws[lane];
+        for (int k = 0; k < SCAN_ITEMS; k++) {
+            int inc = v[k];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { int n = __shfl_up_sync(FULL_MASK, inc, o); if (lane >= o) inc += n; }
+            if (lane == 31) ws[k & 1][warp] = inc;
+            __syncthreads();
+            int w = ws[k & 1][lane];                 // every warp scans the 32 warp totals itself
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) { int n = __shfl_up_sync(FULL_MASK, w, o); if (lane >= o) w += n; }
-            ws[lane] = w;
+            const int before = __shfl_sync(FULL_MASK, w, max(warp - 1, 0));
+            const int all = __shfl_sync(FULL_MASK, w, 31);
+            const int excl = carry + inc - v[k] + (warp > 0 ? before : 0);
+            v[k] = excl;
+            carry += all;
         }
-        __syncthreads();
-        int excl = carry + inc - sum + (warp > 0 ? ws[warp - 1] : 0);
 #pragma unroll
         for (int k = 0; k < SCAN_ITEMS; k++) {
-            if (i0 + k <= total) out[i0 + k] = excl;
-            if (i0 + k < total) cursor[i0 + k] = excl;
-            excl += v[k];
+            const int i = base + k * SCAN_BLOCK + threadIdx.x;
+            if (i <= total) out[i] = v[k];
+            if (i < total) cursor[i] = v[k];
         }
-        __syncthreads();
-        if (threadIdx.x == SCAN_BLOCK - 1) carry = excl;
-        __syncthreads();
     }
 }
 
 // pass 2: atoms into bin order: position (type T) + {original index, wrap}
 template <typename T>
 __global__ void nb_fill_kernel(NbParams<T> P, const T *__restrict__ pos, const int4 *__restrict__ ainfo,
-                               int *__restrict__ cursor, typename Vec4<T>::type *__restrict__ spos, int4 *__restrict__ sinfo)
+                               int *__restrict__ cursor, typename Vec4<T>::type *__restrict__ spos, int4 *__restrict__ sinfo,
+                               float4 *__restrict__ sposw)
 {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= P.n) return;
@@ -335,6 +358,14 @@ __global__ void nb_fill_kernel(NbParams<T> P, const T *__restrict__ pos, const i
     p.w = nb_bits_to(T(0), nb_pack3(a.y, a.z, a.w));   // meaningful while no wrap exceeds NB_WRAP_MAX (else unused)
     spos[k] = p;
     sinfo[k] = make_int4(i, a.y, a.z, a.w);
+    // single-precision copy of the position brought into the cell, for the pre-test
+    const double w0 = a.y, w1 = a.z, w2 = a.w;
+    float4 q;
+    q.x = (float)((double)p.x - (w0 * (double)P.cell[0] + w1 * (double)P.cell[3] + w2 * (double)P.cell[6]));
+    q.y = (float)((double)p.y - (w0 * (double)P.cell[1] + w1 * (double)P.cell[4] + w2 * (double)P.cell[7]));
+    q.z = (float)((double)p.z - (w0 * (double)P.cell[2] + w1 * (double)P.cell[5] + w2 * (double)P.cell[8]));
+    q.w = 0.f;
+    sposw[k] = q;
 }
 
 constexpr int NB_WARPS = 8;
@@ -347,10 +378,11 @@ template <typename T, typename TO>
 __global__ void __launch_bounds__(NB_WARPS * 32, 4)
 nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restrict__ bin_start,
                 const int4 *__restrict__ ainfo, const typename Vec4<T>::type *__restrict__ spos,
-                const int4 *__restrict__ sinfo, int *__restrict__ numneigh, int *__restrict__ firstneigh,
-                TO *__restrict__ rcs, int *__restrict__ status)
+                const int4 *__restrict__ sinfo, const float4 *__restrict__ sposw, int *__restrict__ numneigh,
+                int *__restrict__ firstneigh, TO *__restrict__ rcs, int *__restrict__ status)
 {
     __shared__ int s_start[NB_WARPS][32], s_pre[NB_WARPS][33], s_shift[NB_WARPS][32];
+    __shared__ float4 s_sv[NB_WARPS][32];      // image shift of a table entry as a single-precision vector
     // candidate c of the current group of bins -> its atom (bin order) and its bin's slot, filled by the
     // lanes that own the bins; groups with more than NB_CAND candidates search s_pre instead
     __shared__ int s_cand[NB_WARPS][NB_CAND];
@@ -372,12 +404,12 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
     const int per_warp = (P.n + nwarps - 1) / nwarps;
     const int RUN = min(16, max(1, per_warp / 4));    // at least four runs per warp, so that the last round of runs is short
     const int nruns = (P.n + RUN - 1) / RUN;
-    int cached_bin = -1;
     for (int run = gw; run < nruns; run += nwarps)
     for (int k = 0; k < RUN; k++) {
         const int a = run * RUN + k;
         if (a >= P.n) break;
         const typename Vec4<T>::type pi = spos[a];
+        const float4 piw = sposw[a];
         const int4 si = sinfo[a];
         const int i = si.x;
         const int wi = nb_pack3(si.y, si.z, si.w);   // its bias is the one that survives in shift - wrap_j + wrap_i
@@ -392,12 +424,14 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
         // range: the part of its 2R+1 bins that lies across the face (entries nnb_full .. 2 nnb_full - 1).
         const bool zsplit = zmerge && P.per[2] && (bz - g.R[2] < 0 || bz + g.R[2] >= g.nb[2]);
         const int nnb = zsplit ? 2 * nnb_full : nnb_full;
-        const bool reuse = nnb <= 32 && bin_i == cached_bin;
-        cached_bin = nnb <= 32 ? bin_i : -1;
+        // (the candidate table of a centre is consumed by the pre-test's in-place compaction, so it is rebuilt
+        // for every centre; with bins of half a cutoff two consecutive centres rarely share a bin anyway)
+        constexpr bool reuse = false;
         for (int base = 0; base < nnb; base += 32) {
             // lanes = table entries (neighbouring bins, or columns of bins) of this group
             const int k = base + lane;
             int start = 0, len = 0, shift = 0;
+            float4 sv = make_float4(0.f, 0.f, 0.f, 0.f);
             if (!reuse && k < nnb) {
                 const int kk = zmerge ? (k >= nnb_full ? k - nnb_full : k) : k;
                 int d[3], b[3], m[3];
@@ -437,6 +471,10 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
                     start = bin_start[col + zlo];
                     len = bin_start[col + zhi + 1] - start;
                     shift = (m[0] + 512) | ((m[1] + 512) << 10) | ((m[2] + 512) << 20);
+                    const float f0 = (float)m[0], f1 = (float)m[1], f2 = (float)m[2];
+                    sv.x = f0 * (float)P.cell[0] + f1 * (float)P.cell[3] + f2 * (float)P.cell[6];
+                    sv.y = f0 * (float)P.cell[1] + f1 * (float)P.cell[4] + f2 * (float)P.cell[7];
+                    sv.z = f0 * (float)P.cell[2] + f1 * (float)P.cell[5] + f2 * (float)P.cell[8];
                 }
             }
             int total;
@@ -449,6 +487,7 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
                 s_start[warp][lane] = start;
                 s_pre[warp][lane] = inc - len;
                 s_shift[warp][lane] = shift;
+                s_sv[warp][lane] = sv;
                 if (lane == 31) s_pre[warp][32] = total;
                 if (total <= NB_CAND) {
                     const int pre = inc - len;
@@ -459,10 +498,41 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
                 total = s_pre[warp][32];
             }
 
-            // lanes = candidate atoms of the whole group of bins
-            for (int c0 = 0; c0 < total; c0 += 32) {
+            // Pre-test, lanes = candidate atoms of the whole group: single-precision distance between the positions
+            // wrapped into the cell, shifted by the entry's image vector. Candidates that are certainly outside the
+            // cutoff shell drop out here without any of the image bookkeeping; the survivors are compacted in place.
+            int nsurv = total;
+            if (total <= NB_CAND) {
+                nsurv = 0;
+                for (int c0 = 0; c0 < total; c0 += 32) {
+                    const int c = c0 + lane;
+                    bool pass = false;
+                    int aj = 0, lo = 0;
+                    if (c < total) {
+                        aj = s_cand[warp][c];
+                        lo = s_slot[warp][c];
+                        const float4 pw = sposw[aj];
+                        const float4 v = s_sv[warp][lo];
+                        const float dx = (pw.x + v.x) - piw.x, dy = (pw.y + v.y) - piw.y, dz = (pw.z + v.z) - piw.z;
+                        const float sq = dx * dx + dy * dy + dz * dz;
+                        pass = sq < g.pre_hi && sq > g.pre_lo;
+                    }
+                    const unsigned bal = __ballot_sync(FULL_MASK, pass);
+                    __syncwarp();
+                    if (pass) {
+                        const int p = nsurv + __popc(bal & lt_mask);
+                        s_cand[warp][p] = aj;
+                        s_slot[warp][p] = (unsigned char)lo;
+                    }
+                    nsurv += __popc(bal);
+                }
+                __syncwarp();
+            }
+
+            // exact test, lanes = surviving candidates
+            for (int c0 = 0; c0 < nsurv; c0 += 32) {
                 const int c = c0 + lane;
-                const bool have = c < total;
+                const bool have = c < nsurv;
                 bool hit = false;
                 int jidx = 0;
                 T d0 = 0, d1 = 0, d2 = 0;
@@ -587,7 +657,7 @@ __global__ void nb_sort_rows_kernel(int n, int umax, const int *__restrict__ num
 
 // ---------------------------------------------------------------------------------------------
 struct NbLayout {
-    size_t grid, ext, status_unused, cart, ainfo, count, start, cursor, bsum, spos, sinfo, total;
+    size_t grid, ext, status_unused, cart, ainfo, count, start, cursor, bsum, spos, sinfo, sposw, total;
 };
 template <typename T>
 static NbLayout nb_layout(int n, int maxbins)
@@ -606,6 +676,7 @@ static NbLayout nb_layout(int n, int maxbins)
     L.bsum = take(sizeof(int) * ((size_t)maxbins / SCAN_BLOCK + 2));
     L.spos = take(sizeof(typename Vec4<T>::type) * (size_t)n);
     L.sinfo = take(sizeof(int4) * (size_t)n);
+    L.sposw = take(sizeof(float4) * (size_t)n);
     L.total = o;
     return L;
 }
@@ -722,6 +793,7 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
         }
         hg.total = (int)total;
         hg.zmerge = (!P.per[2] || hg.nb[2] >= 2 * hg.R[2] + 1) ? 1 : 0;
+        nb_pretest_bounds(P, hg.lo, nullptr, false, &hg);
         prod = total;
     }
 
@@ -733,6 +805,7 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
     int *count = (int *)(w + L.count), *start = (int *)(w + L.start), *cursor = (int *)(w + L.cursor), *bsum = (int *)(w + L.bsum);
     auto *spos = (typename Vec4<T>::type *)(w + L.spos);
     int4 *sinfo = (int4 *)(w + L.sinfo);
+    float4 *sposw = (float4 *)(w + L.sposw);
 
     const int tb = 256, nblk = (n + tb - 1) / tb;
     const T *pos = d_coords;
@@ -766,11 +839,11 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
         nb_scan2_kernel<<<1, SCAN_BLOCK, 0, st>>>(grid, bsum);
         nb_scan3_kernel<<<sblk, SCAN_BLOCK, 0, st>>>(grid, start, bsum, cursor);
     }
-    if (!reuse_bins) nb_fill_kernel<T><<<nblk, tb, 0, st>>>(P, pos, ainfo, cursor, spos, sinfo);
+    if (!reuse_bins) nb_fill_kernel<T><<<nblk, tb, 0, st>>>(P, pos, ainfo, cursor, spos, sinfo, sposw);
     const int sms = sm_count();
     long blocks = ((long)n + NB_WARPS - 1) / NB_WARPS;
     if (blocks > (long)sms * 8) blocks = (long)sms * 8;
-    nb_build_kernel<T, TO><<<(unsigned)blocks, NB_WARPS * 32, 0, st>>>(P, grid, start, ainfo, spos, sinfo, d_numneigh, d_firstneigh, d_rcs, d_status);
+    nb_build_kernel<T, TO><<<(unsigned)blocks, NB_WARPS * 32, 0, st>>>(P, grid, start, ainfo, spos, sinfo, sposw, d_numneigh, d_firstneigh, d_rcs, d_status);
     AI2B_CUDA(cudaGetLastError());
     return AI2B_OK;
 }

@@ -24,7 +24,11 @@ Three schedules of a step (`SlabStep`):
              owned atom is computed locally and step 3 disappears
 
 `torch.distributed` (NCCL on GPUs, gloo in the CPU tests) carries the messages; message sizes are
-fixed at set-up, so a step makes no host synchronisation. The per-pass compute is injected
+fixed at set-up, so a step makes no host synchronisation. With `transport="peer"` the two neighbour
+exchanges of a step are this library's own kernels instead: the boundary rows are gathered, shifted and
+stored straight into the neighbour GPU's arrays over NVLink (`ai2b_peer_push_rows_*`, arrays in
+`torch.distributed._symmetric_memory`), a flag follows the data, and the receiving stream is held by a
+bounded wait (`ai2b_peer_wait`); only the all-reduce of energy and virial stays with NCCL. The per-pass compute is injected
 (`CudaPasses` on a GPU), so the partition / exchange / schedule logic is tested on CPU ranks.
 
 Positions of the owned atoms may be updated in place between steps (`SlabDomain.owned`), as an MD
@@ -47,11 +51,15 @@ def partition(cell, coords, nranks):
 
 
 class SlabDomain:
-    def __init__(self, cell, coords, types, rcut, rank, nranks, device, dist=None, halo_margin=1e-6, skin=0.0, halo_cutoffs=1):
+    def __init__(self, cell, coords, types, rcut, rank, nranks, device, dist=None, halo_margin=1e-6, skin=0.0, halo_cutoffs=1,
+                 transport="nccl"):
         """cell [3,3], coords [N,3], types [N] describe the WHOLE system (host arrays, identical on
         every rank); each rank keeps only its slab. halo_cutoffs = 2 builds the wide halo of the
         owner-computes schedule."""
         self.rank, self.P, self.dist, self.device = rank, nranks, dist, device
+        if transport not in ("nccl", "peer"):
+            raise ValueError("transport must be 'nccl' or 'peer'")
+        self.transport = transport if nranks > 1 else "nccl"
         self.cell = np.asarray(cell)
         self.rcut, self.skin, self.halo_cutoffs = float(rcut), float(skin), int(halo_cutoffs)
         self.dtype = torch.float64 if np.asarray(coords).dtype == np.float64 else torch.float32
@@ -109,7 +117,11 @@ class SlabDomain:
         self.n_inner_ghost = self.recv_counts[0] + self.recv_counts[1]       # ghosts within one cutoff of a face
         self.ntotal = self.nlocal + self.nghost
         # one buffer [owned | ghost L0 | ghost R0 | ghost L1 | ghost R1]; `owned` is a view of its head
-        self.local = torch.empty(self.ntotal, 3, dtype=self.dtype, device=device)
+        if self.transport == "peer":
+            self._peer_setup_begin([len(s) for s in sends])
+            self.local = self._sym_local[: self.ntotal * 3].view(self.ntotal, 3)
+        else:
+            self.local = torch.empty(self.ntotal, 3, dtype=self.dtype, device=device)
         self.local[: self.nlocal] = owned
         self.owned = self.local[: self.nlocal]
         self.owned_at_setup = self.owned.clone()
@@ -129,7 +141,8 @@ class SlabDomain:
         self.send_views = [self.send_buf[s] for s in self.send_slices]
         # ghost forces coming home (one-cutoff halo only): rows line up with send lists 0 and 1
         nback = len(sends[0]) + len(sends[1])
-        self.back = torch.empty(nback, 3, dtype=self.dtype, device=device)
+        self.back = self._sym_back[: nback * 3].view(nback, 3) if self.transport == "peer" else \
+            torch.empty(nback, 3, dtype=self.dtype, device=device)
         self.back_idx = self.send_idx[:nback]
         shift = torch.zeros(nsend, 3, dtype=self.dtype, device=device)
         if nranks > 1 and rank == 0:                        # my left neighbour is the last slab: it sees these one cell up
@@ -145,6 +158,8 @@ class SlabDomain:
         lo = rank / nranks - (halo + skin) / d0
         hi = (rank + 1) / nranks + (halo + skin) / d0
         self.open_extent = None if nranks == 1 else (lo, hi)
+        if self.transport == "peer":
+            self._peer_setup_finish()
         if nranks > 1:
             tys = [self.owned_types[s].contiguous() for s in self.send_lists]
             got = self._exchange(tys, [torch.empty(c, dtype=torch.int32, device=device) for c in self.recv_counts])
@@ -185,10 +200,120 @@ class SlabDomain:
                 r.wait()
         return recv
 
+    # -- peer transport: symmetric arrays, row maps, flags -------------------------------------------------
+    def _peer_setup_begin(self, nsend):
+        """Symmetric-memory arrays (same size on every rank) for the positions and the returning ghost forces, and the
+        geometry of every rank (owned count, ghost counts, send counts) so that a rank knows where its rows land."""
+        import torch.distributed._symmetric_memory as symm
+        d = self.dist
+        mine = torch.tensor([self.nlocal] + self.recv_counts + list(nsend), dtype=torch.int64)
+        allg = [torch.zeros(9, dtype=torch.int64) for _ in range(self.P)]
+        self._all_gather_cpu(allg, mine)
+        self._geom = [[int(v) for v in g] for g in allg]           # per rank: nlocal, recv[4], nsend[4]
+        max_total = max(g[0] + sum(g[1:5]) for g in self._geom)
+        max_back = max(g[5] + g[6] for g in self._geom)
+        self._sym_local = symm.empty(max(max_total, 1) * 3, dtype=self.dtype, device=self.device)
+        self._sym_back = symm.empty(max(max_back, 1) * 3, dtype=self.dtype, device=self.device)
+        # flags: [0..3] halo from left / right, forces from left / right; [8 + P h + q] partial sums of rank q have arrived
+        # (h = step parity: tables and their flags are double-buffered, so a rank that is a step ahead never writes
+        # into a table another rank is still summing)
+        self._sym_flags = symm.empty(8 + 2 * self.P, dtype=torch.int32, device=self.device)
+        self._sym_flags.zero_()
+        self._sym_table = symm.empty(2 * self.P * 16, dtype=self.dtype, device=self.device)     # [parity][rank][16] partial energy / virial
+        self._sym_table.zero_()
+        group = d.group.WORLD
+        self._h_local = symm.rendezvous(self._sym_local, group)
+        self._h_back = symm.rendezvous(self._sym_back, group)
+        self._h_flags = symm.rendezvous(self._sym_flags, group)
+        self._h_table = symm.rendezvous(self._sym_table, group)
+        self._max_total, self._max_back = max_total, max_back
+
+    def _peer_setup_finish(self):
+        """Row maps of the pushes. Ghost rows of a rank are laid out [from-left 0 | from-right 0 | from-left 1 | from-right 1]
+        after its owned rows; what goes to the LEFT neighbour lands in its from-RIGHT rows and vice versa. Returning
+        forces land in the owner's `back` rows, which follow its send lists 0 (to-left) and 1 (to-right)."""
+        dev, i32 = self.device, torch.int32
+        gl, gr = self._geom[self.left], self._geom[self.right]
+
+        def ghost_off(g, k):            # first row of ghost slice k on a rank with geometry g
+            return g[0] + sum(g[1:1 + k])
+        peer_local = {p: self._h_local.get_buffer(p, (self._max_total * 3,), self.dtype) for p in {self.left, self.right}}
+        peer_back = {p: self._h_back.get_buffer(p, (self._max_back * 3,), self.dtype) for p in {self.left, self.right}}
+        peer_flags = {p: self._h_flags.get_buffer(p, (8 + 2 * self.P,), torch.int32) for p in {self.left, self.right}}
+        # every rank's table and table flags, for the all-to-all of the partial energy / virial
+        P = self.P
+        self._all_tables = [self._sym_table if q == self.rank else self._h_table.get_buffer(q, (2 * P * 16,), self.dtype) for q in range(P)]
+        self._all_flags = [self._sym_flags if q == self.rank else self._h_flags.get_buffer(q, (8 + 2 * P,), torch.int32) for q in range(P)]
+        self._table_ptrs = [torch.tensor([t[h * P * 16:].data_ptr() for t in self._all_tables], dtype=torch.int64, device=dev) for h in (0, 1)]
+        self._table_flag_ptrs = [torch.tensor([f[8 + h * P:].data_ptr() for f in self._all_flags], dtype=torch.int64, device=dev) for h in (0, 1)]
+        self._back_idx32 = None
+        # halo pushes: source rows = my send lists, destination rows in the neighbour's position array
+        src_l = torch.cat([self.send_lists[0], self.send_lists[2]]).to(i32)
+        dst_l = torch.cat([torch.arange(len(self.send_lists[0]), device=dev) + ghost_off(gl, 1),
+                           torch.arange(len(self.send_lists[2]), device=dev) + ghost_off(gl, 3)]).to(i32)
+        src_r = torch.cat([self.send_lists[1], self.send_lists[3]]).to(i32)
+        dst_r = torch.cat([torch.arange(len(self.send_lists[1]), device=dev) + ghost_off(gr, 0),
+                           torch.arange(len(self.send_lists[3]), device=dev) + ghost_off(gr, 2)]).to(i32)
+        assert len(self.send_lists[0]) == gl[2] and len(self.send_lists[1]) == gr[1] and len(self.send_lists[2]) == gl[4] and \
+            len(self.send_lists[3]) == gr[3], "neighbour ghost counts do not match the send lists"
+        a0 = self.cell[0].astype(np.float64)
+        self._push = dict(
+            halo_left=dict(src_idx=src_l.contiguous(), dst_idx=dst_l.contiguous(), shift=(a0 if self.rank == 0 else None),
+                           dst=peer_local[self.left], flag=peer_flags[self.left][1:2]),       # arrives as its from-right data
+            halo_right=dict(src_idx=src_r.contiguous(), dst_idx=dst_r.contiguous(), shift=(-a0 if self.rank == self.P - 1 else None),
+                            dst=peer_local[self.right], flag=peer_flags[self.right][0:1]),
+            # ghost forces: my from-left ghost rows are the left neighbour's send list 1 -> its back rows after its list 0
+            force_left=dict(src0=ghost_off(self._geom[self.rank], 0), n=self.recv_counts[0], dst0=gl[5], dst=peer_back[self.left],
+                            flag=peer_flags[self.left][3:4]),
+            force_right=dict(src0=ghost_off(self._geom[self.rank], 1), n=self.recv_counts[1], dst0=0, dst=peer_back[self.right],
+                             flag=peer_flags[self.right][2:3]))
+        assert self.recv_counts[0] == gl[6] and self.recv_counts[1] == gr[5]
+        self._counter = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.peer_status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._epoch = 0
+        self.dist.barrier()
+
+    def _peer_halo_exchange(self):
+        from . import capi
+        self._epoch += 1
+        pl, pr = self._push["halo_left"], self._push["halo_right"]
+        capi.peer_exchange(dict(src=self.owned, src_idx=pl["src_idx"], dst_idx=pl["dst_idx"], n=len(pl["src_idx"]), shift=pl["shift"],
+                                dst=pl["dst"], flag=pl["flag"]),
+                           dict(src=self.owned, src_idx=pr["src_idx"], dst_idx=pr["dst_idx"], n=len(pr["src_idx"]), shift=pr["shift"],
+                                dst=pr["dst"], flag=pr["flag"]),
+                           self._epoch, self._sym_flags[0:1], self._sym_flags[1:2], self.peer_status, self._counter[0:1])
+
+    def _peer_return_ghost_forces(self, force):
+        from . import capi
+        pl, pr = self._push["force_left"], self._push["force_right"]
+        capi.peer_exchange(dict(src=force[pl["src0"]: pl["src0"] + pl["n"]], n=pl["n"], dst=pl["dst"][pl["dst0"] * 3:], flag=pl["flag"]),
+                           dict(src=force[pr["src0"]: pr["src0"] + pr["n"]], n=pr["n"], dst=pr["dst"][pr["dst0"] * 3:], flag=pr["flag"]),
+                           self._epoch, self._sym_flags[2:3], self._sym_flags[3:4], self.peer_status, self._counter[1:2])
+
+    def peer_finish(self, force, partial, reduced, with_forces=True):
+        """The closing exchange of a step in one launch (peer transport): ghost-force rows to the neighbours, partial
+        energy / virial to every rank, received rows added onto the owned atoms, partials summed in rank order."""
+        from . import capi
+        pl, pr = self._push["force_left"], self._push["force_right"]
+        if self._back_idx32 is None:
+            self._back_idx32 = self.back_idx.to(torch.int32).contiguous()
+        left = right = None
+        if with_forces:
+            left = dict(src=force[pl["src0"]: pl["src0"] + pl["n"]], n=pl["n"], dst=pl["dst"][pl["dst0"] * 3:], flag=pl["flag"])
+            right = dict(src=force[pr["src0"]: pr["src0"] + pr["n"]], n=pr["n"], dst=pr["dst"][pr["dst0"] * 3:], flag=pr["flag"])
+        h, P = self._epoch & 1, self.P
+        capi.peer_return_reduce(left, right, self._epoch, self._sym_flags[2:3], self._sym_flags[3:4], self.back if with_forces else None,
+                                self._back_idx32 if with_forces else None, force, partial, self._table_ptrs[h], self._table_flag_ptrs[h],
+                                self._sym_table[h * P * 16:], self._sym_flags[8 + h * P:], reduced, self.rank, P, self.peer_status,
+                                self._counter[1:2])
+
     # -- the communication steps ---------------------------------------------------------------------
     def halo_exchange(self):
         """Boundary positions (already shifted for the wrap) go straight into the neighbours'
         ghost rows of `local`: one gather, one add on the end slabs, one grouped send/receive."""
+        if self.transport == "peer":
+            self._peer_halo_exchange()
+            return self.local
         if self.P > 1:
             torch.index_select(self.owned, 0, self.send_idx, out=self.send_buf)
             if self.send_shift is not None:
@@ -199,6 +324,9 @@ class SlabDomain:
     def return_ghost_forces(self, force):
         """force is [ntotal,3]; the rows of the one-cutoff ghosts go back to the ranks that own those atoms
         (into `back`, rows in send-list order)."""
+        if self.transport == "peer":
+            self._peer_return_ghost_forces(force)
+            return
         if self.P > 1:
             nl = len(self.send_lists[0])
             z = force[:0]
@@ -315,6 +443,7 @@ class SlabStep:
         self.flat = torch.zeros(16 + 3 * dom.ntotal, dtype=dt, device=dom.device)
         self.ev = self.flat[:10]
         self.acc = (self.flat[:1], self.flat[16:].view(dom.ntotal, 3), self.flat[1:10])
+        self.ev_reduced = torch.zeros(10, dtype=dt, device=dom.device)     # energy / virial summed over the ranks (peer transport)
         # forces-only passes of the owner-computes schedule put their energy / virial here (discarded)
         self.scratch_ev = torch.zeros(16, dtype=dt, device=dom.device)
         # interior centres are split: the tail runs while the ghost forces travel back
@@ -395,6 +524,9 @@ class SlabStep:
         d = self.dom
         d.halo_exchange()
         self._seg("all")
+        if d.transport == "peer":       # force return, accumulation and the reduction of E / virial in one launch
+            d.peer_finish(self.acc[1], self.ev, self.ev_reduced)
+            return self.ev_reduced[0], self.acc[1][: d.nlocal], self.ev_reduced[1:]
         d.return_ghost_forces(self.acc[1])
         owned_f = d.add_returned_forces(self.acc[1])
         d.dist.all_reduce(self.ev)
@@ -437,6 +569,9 @@ class SlabStep:
         self._seg("head")
         self._wait(halo)
         self._seg("rest")
+        if d.transport == "peer":
+            d.peer_finish(self.acc[1], self.ev, self.ev_reduced, with_forces=False)
+            return self.ev_reduced[0], self.acc[1][: d.nlocal], self.ev_reduced[1:]
         d.dist.all_reduce(self.ev)
         return self.ev[0], self.acc[1][: d.nlocal], self.ev[1:]
 
@@ -447,6 +582,9 @@ class SlabStep:
             s = st.cpu().numpy()
             if s[1]:
                 raise RuntimeError(f"umax too small (largest neighbour count {int(s[0])})")
+        if self.dom.transport == "peer" and int(self.dom.peer_status[0]):
+            from .capi import Ai2bError, AI2B_ERR_TIMEOUT
+            raise Ai2bError(f"ai2pot_b200 error {AI2B_ERR_TIMEOUT}: a neighbour's halo or ghost-force rows did not arrive within the wait limit")
         moved = float(self.dom.max_displacement())
         if moved > 0.5 * self.dom.skin + 1e-6:
             raise RuntimeError(f"an atom moved {moved:.3g} since the domain was set up (skin {self.dom.skin}): build a new SlabDomain")

@@ -358,8 +358,12 @@ def run_slab_benchmark(w, steps, warmup, dist, sampler):
     world = dist.get_world_size() if dist is not None else 1
     dtype = torch.float32 if w["dtype"] == "f32" else torch.float64
     dev = torch.device("cuda", torch.cuda.current_device())
-    dom = slab.SlabDomain(w["cell"], w["coords"], w["types"], w["rcut"], rank, world, dev, dist)
-    step_obj = slab.SlabStep(dom, w["model"], w["umax"], dtype, schedule=os.environ.get("AI2B_SLAB_SCHEDULE", "overlap"))
+    schedule = os.environ.get("AI2B_SLAB_SCHEDULE", "overlap")
+    transport = os.environ.get("AI2B_SLAB_TRANSPORT", "nccl")
+    dom = slab.SlabDomain(w["cell"], w["coords"], w["types"], w["rcut"], rank, world, dev, dist,
+                          halo_cutoffs=2 if (schedule == "owner" and world > 1) else 1, transport=transport)
+    step_obj = slab.SlabStep(dom, w["model"], w["umax"], dtype, schedule=schedule,
+                             tail_fraction=float(os.environ.get("AI2B_SLAB_TAIL", "0.25")))
     e, f, v = step_obj.evaluate()
     torch.cuda.synchronize()
     step_obj.check_status()
@@ -400,7 +404,7 @@ def run_slab_benchmark(w, steps, warmup, dist, sampler):
                 d2h=h_f.numel() * h_f.element_size() + 10 * elem, units=len(w["types"]) / world,
                 e2e_path="pinned host positions of the slab -> H2D -> halo exchange (NCCL p2p) -> ai2b_nblist_build_ghost -> ai2b_nep_efv "
                          "-> ghost-force return -> all-reduce(E, virial) -> D2H forces, E, virial",
-                roofline=roofline, parts_ms=parts, host_ms_per_call=1e3 * t_host, schedule=step_obj.schedule)
+                roofline=roofline, parts_ms=parts, host_ms_per_call=1e3 * t_host, schedule=step_obj.schedule + "/" + dom.transport)
 
 
 def run_single_benchmark(w, steps, warmup, dist, sampler):

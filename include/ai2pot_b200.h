@@ -471,6 +471,70 @@ size_t ai2b_nep_workspace_bytes(int batch_size, int ntypes, int n_radial, int n_
 AI2B_DECL_NEP(f64, double)
 AI2B_DECL_NEP(f32, float)
 
+/* ------------------------------------------------------------------------------------------
+ * Halo exchange between neighbouring spatial domains by direct stores into the neighbour GPU's
+ * memory (NVLink peer access). It does the job MPI does for the reference when LAMMPS runs the
+ * pair style on several ranks: ghost positions before the evaluation, ghost forces back after it
+ * (interface/lammps/AI2POT/pair_ai2pot.cpp:177-205, 452-455).
+ *   ai2b_peer_push_rows_*  d_peer_dst[d_dst_index[k]][0..2] = d_src[d_src_index[k]][0..2] + h_shift3
+ *                          for k < nrows (either index may be NULL = k; h_shift3 NULL = no shift),
+ *                          then *d_peer_flag = flag_value with a system-scope release once every
+ *                          row is written. d_peer_dst and d_peer_flag are addresses in the
+ *                          NEIGHBOUR's memory as mapped into this process (peer access must be
+ *                          enabled by whoever mapped them); d_counter is one zero-initialised
+ *                          word of THIS device, private to the pushes of one stream.
+ *   ai2b_peer_wait         holds the stream until *d_flag >= value (system-scope acquire polls).
+ *                          Bounded: after max_polls polls (200 ns apart) it stores 1 to *d_status
+ *                          and lets the stream go on, so nothing hangs; the host reads d_status
+ *                          when it next synchronises and treats 1 as AI2B_ERR_TIMEOUT.
+ *   ai2b_peer_exchange_*   both directions of an exchange in one launch: the two pushes (arguments
+ *                          *_l to the lower neighbour, *_r to the upper one), both neighbours'
+ *                          flags raised, then the bounded wait for this rank's two flags
+ *                          (d_my_flag_l: raised by the lower neighbour, d_my_flag_r: by the upper).
+ *   ai2b_peer_return_reduce_*  the closing exchange of a step in one launch: contiguous
+ *                          ghost-force rows to the two neighbours' d_back arrays; this rank's
+ *                          partial sums d_partial[nvalues] (energy, virial) written into row `rank`
+ *                          of every rank's table ([nranks][16] values, d_peer_tables[q] = rank q's
+ *                          table as mapped here, own entry = own table) with a flag per source
+ *                          rank; after the bounded waits, d_force[d_back_index[k]] += d_back[k]
+ *                          for the rows the neighbours pushed here, and d_reduced[nvalues] = sum
+ *                          over the ranks' partials in rank order (identical on every rank).
+ *                          nranks = 0 skips the reduction, nback = nrows = 0 the force part.
+ * Use increasing flag values (a step counter): a flag is never reset.
+ * ---------------------------------------------------------------------------------------- */
+int ai2b_peer_push_rows_f32(const float *d_src, const int *d_src_index, const int *d_dst_index,
+                            int nrows, const float *h_shift3, float *d_peer_dst,
+                            int *d_peer_flag, int flag_value, unsigned *d_counter, void *stream);
+int ai2b_peer_push_rows_f64(const double *d_src, const int *d_src_index, const int *d_dst_index,
+                            int nrows, const double *h_shift3, double *d_peer_dst,
+                            int *d_peer_flag, int flag_value, unsigned *d_counter, void *stream);
+int ai2b_peer_wait(const int *d_flag, int value, long long max_polls, int *d_status,
+                   void *stream);
+#define AI2B_DECL_PEER_EXCHANGE(SUF, T)                                                          \
+    int ai2b_peer_exchange_##SUF(const T *d_src_l, const int *d_src_index_l,                     \
+                                 const int *d_dst_index_l, int nrows_l, const T *h_shift3_l,     \
+                                 T *d_peer_dst_l, int *d_peer_flag_l, const T *d_src_r,          \
+                                 const int *d_src_index_r, const int *d_dst_index_r,             \
+                                 int nrows_r, const T *h_shift3_r, T *d_peer_dst_r,              \
+                                 int *d_peer_flag_r, int flag_value, const int *d_my_flag_l,     \
+                                 const int *d_my_flag_r, long long max_polls, int *d_status,     \
+                                 unsigned *d_counter, void *stream);
+AI2B_DECL_PEER_EXCHANGE(f64, double)
+AI2B_DECL_PEER_EXCHANGE(f32, float)
+#define AI2B_DECL_PEER_RETURN(SUF, T)                                                            \
+    int ai2b_peer_return_reduce_##SUF(const T *d_src_l, int nrows_l, T *d_peer_dst_l,            \
+                                      int *d_peer_flag_l, const T *d_src_r, int nrows_r,         \
+                                      T *d_peer_dst_r, int *d_peer_flag_r, int flag_value,       \
+                                      const int *d_my_flag_l, const int *d_my_flag_r,            \
+                                      const T *d_back, const int *d_back_index, int nback,       \
+                                      T *d_force, const T *d_partial, T *const *d_peer_tables,   \
+                                      int *const *d_peer_table_flags, const T *d_my_table,       \
+                                      const int *d_my_table_flags, T *d_reduced, int rank,       \
+                                      int nranks, int nvalues, long long max_polls,              \
+                                      int *d_status, unsigned *d_counter, void *stream);
+AI2B_DECL_PEER_RETURN(f64, double)
+AI2B_DECL_PEER_RETURN(f32, float)
+
 #ifdef __cplusplus
 }
 #endif
