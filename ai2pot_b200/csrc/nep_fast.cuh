@@ -133,6 +133,13 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_fast_kernel(const Ne
         if (NET && (int)threadIdx.x < A.nd) qsv = A.qs[threadIdx.x];
         const int n0 = nep_r4(ntab), n1 = n0 + (NET ? nrow * NDP : 0), n2 = n1 + (NET ? nrow : 0);
         const int nall = n2 + (NET ? nrow : 0);
+        // neurons per type are padded to a multiple of 32: a power of two for the usual sizes, so the row -> (type,
+        // neuron) split is a shift instead of an integer division per staged element
+        const int np_shift = (NP & (NP - 1)) == 0 ? __ffs(NP) - 1 : -1;
+        auto split = [&](int row, int &t, int &pn) {
+            if (np_shift >= 0) { t = row >> np_shift; pn = row & (NP - 1); }
+            else { t = row / NP; pn = row % NP; }
+        };
         auto load = [&](int i) -> T {
             if (i < n0) {
                 if (i >= ntab) return T(0);
@@ -141,10 +148,14 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_fast_kernel(const Ne
                 return (k < A.cs && row >= 0) ? coeffs[((size_t)pair * ntot_n + row) * A.cs + k] : T(0);
             }
             if (i < n1) {
-                const int row = (i - n0) / NDP, k = (i - n0) % NDP, t = row / NP, pn = row % NP;
+                const int row = (i - n0) / NDP, k = (i - n0) % NDP;
+                int t, pn;
+                split(row, t, pn);
                 return (k < A.nd && pn < A.nneu) ? A.w0[((size_t)t * A.nneu + pn) * A.nd + k] : T(0);
             }
-            const int row = i < n2 ? i - n1 : i - n2, t = row / NP, pn = row % NP;
+            const int row = i < n2 ? i - n1 : i - n2;
+            int t, pn;
+            split(row, t, pn);
             if (pn >= A.nneu) return T(0);
             return i < n2 ? A.b0[t * A.nneu + pn] : A.w1[t * A.nneu + pn];
         };

@@ -428,7 +428,7 @@ class SlabStep:
     with the same run_pass)."""
     SCHEDULES = ("serial", "overlap", "owner")
 
-    def __init__(self, dom, model=None, umax=None, dtype=None, schedule="overlap", passes=None, tail_fraction=0.25, graphs=True):
+    def __init__(self, dom, model=None, umax=None, dtype=None, schedule="serial", passes=None, tail_fraction=0.25, graphs=True):
         if schedule not in self.SCHEDULES:
             raise ValueError(f"schedule must be one of {self.SCHEDULES}")
         if schedule == "owner" and dom.P > 1 and dom.halo_cutoffs < 2:

@@ -169,7 +169,7 @@ def config_of(w, world, strong):
     if world > 1:
         config["parallelism"] = ("replicas only: %d independent copies, no data-path collective" % world) if not strong else \
             ("structures dealt over %d ranks + one gradient all-reduce" % world if w["kind"] == "train"
-             else "%d x-slabs, halo exchange + ghost-force reduction over NCCL" % world)
+             else "%d x-slabs with 6 A halos: halo exchange, ghost-force return, reduction of E and virial" % world)
     return config
 
 
@@ -200,6 +200,11 @@ def gpu_line(w, args, world, dist, local):
             "cuda_graph": bool(res["cuda_graph"]) if "cuda_graph" in res else None}
     if "schedule" in res:
         line["schedule"] = res["schedule"]
+        if world > 1:     # how the exchanges of a step travel (kept out of `config`, which both arms share)
+            line["transport"] = ("peer stores over NVLink by this library's kernels (NCCL for set-up only)" if res["schedule"].endswith("/peer")
+                                 else "NCCL send/recv + all-reduce")
+        if res.get("note"):
+            line["note"] = res["note"]
     return line
 
 
@@ -240,6 +245,8 @@ def main():
         print(json.dumps(line))
         return
 
+    # the peer-store exchange maps the neighbours' arrays with plain peer access; NVLink multicast objects are not used
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
     import torch
     torch.cuda.set_device(local)
     dist = None
