@@ -347,12 +347,17 @@ __global__ void __launch_bounds__(SCAN_BLOCK) nb_scan_small_kernel(const NbGrid 
 template <typename T>
 __global__ void nb_fill_kernel(NbParams<T> P, const T *__restrict__ pos, const int4 *__restrict__ ainfo,
                                int *__restrict__ cursor, typename Vec4<T>::type *__restrict__ spos, int4 *__restrict__ sinfo,
-                               float4 *__restrict__ sposw)
+                               float4 *__restrict__ sposw, int4 *__restrict__ sbin, const NbGrid *__restrict__ gp)
 {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= P.n) return;
     const int4 a = ainfo[i];
     int k = atomicAdd(cursor + a.x, 1);
+    {   // bin coordinates of the atom, so that the row pass needs no integer division per centre
+        const int nb2 = gp->nb[2], nb1 = gp->nb[1];
+        const int t = a.x / nb2;
+        sbin[k] = make_int4(t / nb1, t % nb1, a.x % nb2, a.x);
+    }
     typename Vec4<T>::type p;
     p.x = pos[3 * i]; p.y = pos[3 * i + 1]; p.z = pos[3 * i + 2];
     p.w = nb_bits_to(T(0), nb_pack3(a.y, a.z, a.w));   // meaningful while no wrap exceeds NB_WRAP_MAX (else unused)
@@ -378,7 +383,7 @@ template <typename T, typename TO>
 __global__ void __launch_bounds__(NB_WARPS * 32, 4)
 nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restrict__ bin_start,
                 const int4 *__restrict__ ainfo, const typename Vec4<T>::type *__restrict__ spos,
-                const int4 *__restrict__ sinfo, const float4 *__restrict__ sposw, int *__restrict__ numneigh,
+                const int4 *__restrict__ sinfo, const float4 *__restrict__ sposw, const int4 *__restrict__ sbin, int *__restrict__ numneigh,
                 int *__restrict__ firstneigh, TO *__restrict__ rcs, int *__restrict__ status)
 {
     __shared__ int s_start[NB_WARPS][32], s_pre[NB_WARPS][33], s_shift[NB_WARPS][32];
@@ -396,6 +401,19 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
     const int nnb_full = zmerge ? nx * ny : nx * ny * nz;   // table entries of a centre away from the third axis' faces
     const unsigned lt_mask = (1u << lane) - 1u;
     int local_max = 0;
+    // merged columns: the (d0, d1) offsets of the table entries this lane builds (entry lane, entry lane + 32) never change
+    int ent_d0[2] = {0, 0}, ent_d1[2] = {0, 0};
+    const bool ent_fast = zmerge && nnb_full <= 64;
+    if (ent_fast) {
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            int kk = lane + 32 * u;
+            if (kk >= nnb_full) kk -= nnb_full;          // second half of a split table: the same columns again
+            if (kk >= nnb_full) kk = 0;
+            ent_d0[u] = kk / ny - g.R[0];
+            ent_d1[u] = kk % ny - g.R[1];
+        }
+    }
 
     // Large systems: warps take runs of up to 16 bin-ordered atoms, dealt round-robin, so consecutive centres
     // touch the same bins and candidates, while ghost regions (atoms that are neighbours only) spread over
@@ -414,8 +432,8 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
         const int i = si.x;
         const int wi = nb_pack3(si.y, si.z, si.w);   // its bias is the one that survives in shift - wrap_j + wrap_i
         if (i >= P.ncentre || i < P.cbegin) continue;
-        const int bin_i = ainfo[i].x;
-        const int bz = bin_i % g.nb[2], by = (bin_i / g.nb[2]) % g.nb[1], bx = bin_i / (g.nb[2] * g.nb[1]);
+        const int4 cb = sbin[a];
+        const int bx = cb.x, by = cb.y, bz = cb.z;
         int count = 0;
         int *frow = firstneigh + (size_t)(i - P.cbegin) * P.umax;
         TO *rrow = rcs + (size_t)(i - P.cbegin) * P.umax * 3;
@@ -435,7 +453,9 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
             if (!reuse && k < nnb) {
                 const int kk = zmerge ? (k >= nnb_full ? k - nnb_full : k) : k;
                 int d[3], b[3], m[3];
-                if (zmerge) { d[0] = kk / ny - g.R[0]; d[1] = kk % ny - g.R[1]; d[2] = 0; }
+                if (ent_fast && base == 0) { d[0] = ent_d0[0]; d[1] = ent_d1[0]; d[2] = 0; }
+                else if (ent_fast && base == 32) { d[0] = ent_d0[1]; d[1] = ent_d1[1]; d[2] = 0; }
+                else if (zmerge) { d[0] = kk / ny - g.R[0]; d[1] = kk % ny - g.R[1]; d[2] = 0; }
                 else { d[0] = kk / (ny * nz) - g.R[0]; d[1] = (kk / nz) % ny - g.R[1]; d[2] = kk % nz - g.R[2]; }
                 b[0] = bx + d[0]; b[1] = by + d[1]; b[2] = bz + d[2];
                 bool ok = true;
@@ -471,7 +491,9 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
                     start = bin_start[col + zlo];
                     len = bin_start[col + zhi + 1] - start;
                     shift = (m[0] + 512) | ((m[1] + 512) << 10) | ((m[2] + 512) << 20);
-                    const float f0 = (float)m[0], f1 = (float)m[1], f2 = (float)m[2];
+                    // image counts are -1, 0 or 1 unless the grid is tiny: selects instead of int -> float conversions
+                    auto tof = [](int v) { return v == 0 ? 0.f : v == 1 ? 1.f : v == -1 ? -1.f : (float)v; };
+                    const float f0 = tof(m[0]), f1 = tof(m[1]), f2 = tof(m[2]);
                     sv.x = f0 * (float)P.cell[0] + f1 * (float)P.cell[3] + f2 * (float)P.cell[6];
                     sv.y = f0 * (float)P.cell[1] + f1 * (float)P.cell[4] + f2 * (float)P.cell[7];
                     sv.z = f0 * (float)P.cell[2] + f1 * (float)P.cell[5] + f2 * (float)P.cell[8];
@@ -657,7 +679,7 @@ __global__ void nb_sort_rows_kernel(int n, int umax, const int *__restrict__ num
 
 // ---------------------------------------------------------------------------------------------
 struct NbLayout {
-    size_t grid, ext, status_unused, cart, ainfo, count, start, cursor, bsum, spos, sinfo, sposw, total;
+    size_t grid, ext, status_unused, cart, ainfo, count, start, cursor, bsum, spos, sinfo, sposw, sbin, total;
 };
 template <typename T>
 static NbLayout nb_layout(int n, int maxbins)
@@ -677,6 +699,7 @@ static NbLayout nb_layout(int n, int maxbins)
     L.spos = take(sizeof(typename Vec4<T>::type) * (size_t)n);
     L.sinfo = take(sizeof(int4) * (size_t)n);
     L.sposw = take(sizeof(float4) * (size_t)n);
+    L.sbin = take(sizeof(int4) * (size_t)n);
     L.total = o;
     return L;
 }
@@ -806,6 +829,7 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
     auto *spos = (typename Vec4<T>::type *)(w + L.spos);
     int4 *sinfo = (int4 *)(w + L.sinfo);
     float4 *sposw = (float4 *)(w + L.sposw);
+    int4 *sbin = (int4 *)(w + L.sbin);
 
     const int tb = 256, nblk = (n + tb - 1) / tb;
     const T *pos = d_coords;
@@ -839,11 +863,11 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
         nb_scan2_kernel<<<1, SCAN_BLOCK, 0, st>>>(grid, bsum);
         nb_scan3_kernel<<<sblk, SCAN_BLOCK, 0, st>>>(grid, start, bsum, cursor);
     }
-    if (!reuse_bins) nb_fill_kernel<T><<<nblk, tb, 0, st>>>(P, pos, ainfo, cursor, spos, sinfo, sposw);
+    if (!reuse_bins) nb_fill_kernel<T><<<nblk, tb, 0, st>>>(P, pos, ainfo, cursor, spos, sinfo, sposw, sbin, grid);
     const int sms = sm_count();
     long blocks = ((long)n + NB_WARPS - 1) / NB_WARPS;
     if (blocks > (long)sms * 8) blocks = (long)sms * 8;
-    nb_build_kernel<T, TO><<<(unsigned)blocks, NB_WARPS * 32, 0, st>>>(P, grid, start, ainfo, spos, sinfo, sposw, d_numneigh, d_firstneigh, d_rcs, d_status);
+    nb_build_kernel<T, TO><<<(unsigned)blocks, NB_WARPS * 32, 0, st>>>(P, grid, start, ainfo, spos, sinfo, sposw, sbin, d_numneigh, d_firstneigh, d_rcs, d_status);
     AI2B_CUDA(cudaGetLastError());
     return AI2B_OK;
 }
