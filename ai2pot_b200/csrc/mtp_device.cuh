@@ -17,10 +17,17 @@ struct MtpArgs {
     const int *binum, *bilist, *numneigh, *firstneigh, *types;
     const T *rcs;
     const int *prefix;     // [B+1] exclusive prefix sum of binum (workspace)
-    T *Mb, *Eb;            // [atoms][nbp] basic moments / their adjoints, in alpha_index_basic order (workspace)
+    T *Mb, *Eb;            // basic moments / their adjoints, in alpha_index_basic order (workspace):
+                           // [atoms][nbp], or [tile][nbp][32 atoms] when `tiled` is set
     int B, npad, ntypes, umax, nghost, cs, ndp, nbp;
     T scaling, rmax, rmin;
+    int tiled = 0;
 };
+
+// Lanes-as-atoms forward / force kernels (mtp_atoms.cu): available for the tables they are compiled for.
+bool mtp_atoms_supported(const MtpProgramDev &P, int ntypes, int cs, size_t elem);
+template <typename T> int mtp_fwd_atoms(const MtpProgramDev &P, const MtpArgs<T> &A, cudaStream_t st);
+template <typename T, int MODE> int mtp_force_atoms(const MtpProgramDev &P, const MtpArgs<T> &A, cudaStream_t st);
 
 // exclusive prefix sum of binum -> prefix[0..B]; one block
 static __device__ __forceinline__ void prefix_binum_block(const int *__restrict__ binum, int B, int *__restrict__ prefix)
@@ -159,7 +166,8 @@ struct MtpWs {
 static inline MtpWs mtp_ws_layout(const MtpProgramDev &P, int B, int npad, int ntypes, size_t elem)
 {
     MtpWs L;
-    const size_t atoms = (size_t)(B > 0 ? B : 0) * (npad > 0 ? npad : 0);
+    // rounded up to whole tiles of 32 atoms (the tiled layout of the basic moments)
+    const size_t atoms = ((size_t)(B > 0 ? B : 0) * (npad > 0 ? npad : 0) + 31) & ~size_t(31);
     L.prefix = 0;
     L.cpad = up256(((size_t)(B > 0 ? B : 0) + 1) * sizeof(int));
     L.mb = L.cpad + up256((size_t)ntypes * ntypes * P.nmus * 16 * elem);

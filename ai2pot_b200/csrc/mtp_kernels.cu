@@ -570,11 +570,17 @@ __global__ void __launch_bounds__(MTP_SEG_WORKERS * 32, 1) mtp_contract_seg_kern
     // basic-moment rows of a tile: warp w fetches atom w, lanes run over the row; fetched one tile ahead
     const bool can_prefetch = P.nb <= 32 * MTP_PREF;
     T pre[MTP_PREF];
+    // (tiled workspace: warp w fetches the rows w, w + 32, ... of the tile, lanes run over its atoms)
     auto fetch = [&](int tile) {
 #pragma unroll
         for (int k = 0; k < MTP_PREF; k++) {
-            const int i = lane + 32 * k, t = tile * MTP_TILE + warp;
-            pre[k] = (t < ntot && i < P.nb) ? A.Mb[(size_t)t * A.nbp + i] : T(0);
+            if (A.tiled) {
+                const int i = warp + 32 * k;
+                pre[k] = i < P.nb ? A.Mb[((size_t)tile * A.nbp + i) * MTP_TILE + lane] : T(0);
+            } else {
+                const int i = lane + 32 * k, t = tile * MTP_TILE + warp;
+                pre[k] = (t < ntot && i < P.nb) ? A.Mb[(size_t)t * A.nbp + i] : T(0);
+            }
         }
     };
     if (can_prefetch) fetch(blockIdx.x);
@@ -592,10 +598,13 @@ __global__ void __launch_bounds__(MTP_SEG_WORKERS * 32, 1) mtp_contract_seg_kern
         if (can_prefetch) {
 #pragma unroll
             for (int k = 0; k < MTP_PREF; k++) {
-                const int i = lane + 32 * k;
-                if (i < P.nb) S.M[i * MTP_SEG_LD + warp] = pre[k];
+                const int i = (A.tiled ? warp : lane) + 32 * k;
+                if (i < P.nb) S.M[i * MTP_SEG_LD + (A.tiled ? lane : warp)] = pre[k];
             }
             if (tile + (int)gridDim.x < ntiles) fetch(tile + gridDim.x);   // in flight during this tile
+        } else if (A.tiled) {
+            const T *src = A.Mb + (size_t)tile * A.nbp * MTP_TILE + lane;
+            for (int i = warp; i < P.nb; i += MTP_SEG_WORKERS) S.M[i * MTP_SEG_LD + lane] = src[(size_t)i * MTP_TILE];
         } else {
             const int t = tile * MTP_TILE + warp;
             const T *src = A.Mb + (size_t)t * A.nbp;
@@ -662,8 +671,11 @@ __global__ void __launch_bounds__(MTP_SEG_WORKERS * 32, 1) mtp_contract_seg_kern
             run_phase(p, std::true_type{}, el, ml, el);
             __syncthreads();
         }
-        // adjoints of the basic moments, back to per-atom rows (warp w writes atom w)
-        {
+        // adjoints of the basic moments: whole rows of the tile, or back to per-atom rows (warp w writes atom w)
+        if (A.tiled) {
+            T *dstp = A.Eb + (size_t)tile * A.nbp * MTP_TILE + lane;
+            for (int i = warp; i < P.nb; i += MTP_SEG_WORKERS) dstp[(size_t)i * MTP_TILE] = S.E[i * MTP_SEG_LD + lane];
+        } else {
             const int t = tile * MTP_TILE + warp;
             if (t < ntot) {
                 T *dstp = A.Eb + (size_t)t * A.nbp;
@@ -912,7 +924,17 @@ static int launch_mtp_v(const ai2b_mtp_program *prog, MtpArgs<T> A, void *ws, cu
     const long atoms_upper = (long)A.B * A.npad;
     const long need = (atoms_upper + MTP_WARPS - 1) / MTP_WARPS;
     bool fwd_done = false;
-    if constexpr (KD <= 6) {   // A: forward with lanes = monomials in the summation
+    // lanes-as-atoms forward and force kernels around the segment contraction, where all three apply
+    bool atoms_path = false;
+    if constexpr (KD <= 6 && CSP == 8)
+        atoms_path = mtp_atoms_supported(P, A.ntypes, A.cs, sizeof(T)) && P.nseg > 0 &&
+                     seg_smem_layout<T, MODE>(P, nullptr, nullptr) <= 226 * 1024;
+    if (atoms_path) {
+        A.tiled = 1;
+        if (int rc = mtp_fwd_atoms<T>(P, A, st)) return rc;
+        fwd_done = true;
+    }
+    if constexpr (KD <= 6) if (!fwd_done) {   // A: forward with lanes = monomials in the summation
         constexpr int NMU = 4;
         bool ok = P.nmus <= NMU;
         for (int m = 1; m < P.nmus; m++) ok = ok && P.kmu[m] <= P.kmu[m - 1];
@@ -943,6 +965,9 @@ static int launch_mtp_v(const ai2b_mtp_program *prog, MtpArgs<T> A, void *ws, cu
     {   // B: products / adjoints with lanes = atoms; tile size by shared-memory footprint
         int rc = dispatch_contract<T, MODE>(P, A, atoms_upper, st);
         if (rc) return rc;
+    }
+    if constexpr (MODE != MODE_DESC) {
+        if (atoms_path) return mtp_force_atoms<T, MODE>(P, A, st);
     }
     if (MODE != MODE_DESC) {   // C: forces / virial
         const size_t smem = sizeof(int4) * A.ndp + sizeof(T) * 4 * A.ndp +
