@@ -7,7 +7,7 @@
 // sum or a polynomial value never leaves the registers of its thread:
 //  * forward: the four warps of the block share the tile; each owns the monomial degrees of one group
 //    (groups balanced by accumulator count) and keeps those moments of its atom in registers while it
-//    walks over the atom's neighbours. The radial functions and unit vectors of 32 neighbour slots at a
+//    walks over the atom's neighbours. The radial functions and unit vectors of 16 neighbour slots at a
 //    time are computed once (each warp a quarter of them) and handed over through shared memory.
 //  * force: each warp takes every fourth neighbour slot. The adjoints of the tile's basic moments sit in
 //    shared memory as [dense moment][atom], so a coefficient is one conflict-free load at a compile-time
@@ -19,11 +19,12 @@
 // (non-increasing, at most four functions); other tables take the warp-per-atom kernels.
 #include <cuda_pipeline.h>
 #include "mtp_device.cuh"
+#include "tile_rows.cuh"
 
 namespace ai2b {
 
 constexpr int AT_WARPS = 4;       // warps per block; a block works on one tile of MTP_TILE atoms at a time
-constexpr int AT_CH = 32;         // neighbour slots staged per round of the forward kernel
+constexpr int AT_CH = 16;         // neighbour slots staged per round of the forward kernel
 constexpr size_t AT_CF_BYTES = 16 * 1024;   // largest radial-coefficient table kept in shared memory
 
 template <int K0, int K1, int K2, int K3>
@@ -103,6 +104,21 @@ struct PairEval {
         }
     }
     __device__ __forceinline__ void lookup(const int *types_b) { tj = act ? types_b[nj] : 0; }
+    // slot j of this lane's atom: from the staged rows, or from global memory beyond them
+    __device__ __forceinline__ void fetch(const MtpArgs<T> &A, const TileRows<T> &tr, const int *types_b, size_t row, int lane, int j, int nn)
+    {
+        if (j < TR_SLOTS) {
+            act = j < nn;
+            const T *p = tr.pos + lane * TR_RS + 3 * j;
+            const int w = tr.idx[lane * TR_IS + j];
+            x = act ? p[0] : T(0); y = act ? p[1] : T(0); z = act ? p[2] : T(0);
+            nj = w & TR_INDEX_MASK;
+            tj = w >> TR_TYPE_SHIFT;
+        } else {
+            load(A, row, j, nn);
+            lookup(types_b);
+        }
+    }
     template <bool DERIV>
     __device__ __forceinline__ void compute(const MtpArgs<T> &A, const T *cf, int ti)
     {
@@ -179,6 +195,8 @@ __global__ void __launch_bounds__(AT_WARPS * 32, 3) mtp_fwd_atoms_kernel(const M
     constexpr int KD = SIG::KD;
     T *cf = reinterpret_cast<T *>(smem_raw);
     T *st = cf + A.ntypes * A.ntypes * cf_stride<SIG, CSP>();
+    TileRows<T> tr;
+    tr.bind(reinterpret_cast<unsigned char *>(st + (size_t)AT_CH * NV * 32));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     stage_coefficients<T, SIG, CSP>(A, cf);
     const int ntot = A.prefix[A.B];
@@ -190,6 +208,10 @@ __global__ void __launch_bounds__(AT_WARPS * 32, 3) mtp_fwd_atoms_kernel(const M
         const int nmax = warp_max_int(at.nn);      // the same in every warp of the block
         const size_t row = at.slot * A.umax;
         T *out = A.Mb + (size_t)tile * A.nbp * MTP_TILE + lane;
+        __syncthreads();     // the previous tile's rows are no longer read
+        if (warp == 0) tr.describe(lane, row, (size_t)(at.types_b - A.types), at.nn);
+        __syncthreads();
+        tr.template stage<AT_WARPS * 32>(A.rcs, A.firstneigh, A.types, A.umax);
 
         auto body = [&](auto gg) {
             constexpr int G = decltype(gg)::value;
@@ -199,24 +221,14 @@ __global__ void __launch_bounds__(AT_WARPS * 32, 3) mtp_fwd_atoms_kernel(const M
             for (int i = 0; i < (NACC > 0 ? NACC : 1); i++) acc[i] = T(0);
             for (int j0 = 0; j0 < nmax; j0 += AT_CH) {
                 const int cnt = min(AT_CH, nmax - j0);
-                __syncthreads();     // coefficients staged / the previous round's slots consumed
-                {   // this warp's slots of the round: all loads first, then the arithmetic
-                    constexpr int NS = AT_CH / AT_WARPS;
-                    PairEval<T, SIG, CSP> pe[NS];
-#pragma unroll
-                    for (int k = 0; k < NS; k++) pe[k].load(A, row, j0 + warp + AT_WARPS * k, at.nn);
-#pragma unroll
-                    for (int k = 0; k < NS; k++) pe[k].lookup(at.types_b);
-#pragma unroll
-                    for (int k = 0; k < NS; k++) {
-                        const int jj = warp + AT_WARPS * k;
-                        if (jj < cnt) {
-                            pe[k].template compute<false>(A, cf, at.ti);
-                            T *s = st + (size_t)jj * NV * 32 + lane;
-                            s[0] = pe[k].ux; s[32] = pe[k].uy; s[64] = pe[k].uz;
-                            static_for<0, SIG::NMUS>([&](auto mm) { s[(3 + decltype(mm)::value) * 32] = pe[k].f[decltype(mm)::value]; });
-                        }
-                    }
+                __syncthreads();     // rows and coefficients staged / the previous round's slots consumed
+                for (int jj = warp; jj < cnt; jj += AT_WARPS) {   // this warp's slots of the round
+                    PairEval<T, SIG, CSP> pe;
+                    pe.fetch(A, tr, at.types_b, row, lane, j0 + jj, at.nn);
+                    pe.template compute<false>(A, cf, at.ti);
+                    T *s = st + (size_t)jj * NV * 32 + lane;
+                    s[0] = pe.ux; s[32] = pe.uy; s[64] = pe.uz;
+                    static_for<0, SIG::NMUS>([&](auto mm) { s[(3 + decltype(mm)::value) * 32] = pe.f[decltype(mm)::value]; });
                 }
                 __syncthreads();
                 if constexpr (NACC > 0) {
@@ -277,13 +289,21 @@ __global__ void __launch_bounds__(AT_WARPS * 32, 3) mtp_force_atoms_kernel(const
     constexpr int KD = SIG::KD;
     T *cf = reinterpret_cast<T *>(smem_raw);
     T *Es = cf + A.ntypes * A.ntypes * cf_stride<SIG, CSP>();
+    TileRows<T> tr;
+    tr.bind(reinterpret_cast<unsigned char *>(Es + (size_t)SIG::NDENSE * 32));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     stage_coefficients<T, SIG, CSP>(A, cf);
     const int ntot = A.prefix[A.B];
     const int ntiles = (ntot + MTP_TILE - 1) / MTP_TILE;
 
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-        __syncthreads();     // the previous tile's adjoints are no longer read
+        TileAtom<T> at;
+        at.set(A, tile * MTP_TILE + lane, ntot);
+        const int nmax = warp_max_int(at.nn);
+        const size_t row = at.slot * A.umax;
+        T *frc = A.force + (size_t)at.b * (A.npad + A.nghost) * 3;
+        __syncthreads();     // the previous tile's adjoints and rows are no longer read
+        if (warp == 0) tr.describe(lane, row, (size_t)(at.types_b - A.types), at.nn);
         {
             const T *ein = A.Eb + (size_t)tile * A.nbp * MTP_TILE + lane;
             for (int d = warp; d < SIG::NDENSE; d += AT_WARPS) {
@@ -291,11 +311,8 @@ __global__ void __launch_bounds__(AT_WARPS * 32, 3) mtp_force_atoms_kernel(const
                 Es[d * 32 + lane] = r >= 0 ? ein[(size_t)r * MTP_TILE] : T(0);
             }
         }
-        TileAtom<T> at;
-        at.set(A, tile * MTP_TILE + lane, ntot);
-        const int nmax = warp_max_int(at.nn);
-        const size_t row = at.slot * A.umax;
-        T *frc = A.force + (size_t)at.b * (A.npad + A.nghost) * 3;
+        __syncthreads();
+        tr.template stage<AT_WARPS * 32>(A.rcs, A.firstneigh, A.types, A.umax);
         __syncthreads();
 
         T fcx = T(0), fcy = T(0), fcz = T(0);
@@ -303,15 +320,9 @@ __global__ void __launch_bounds__(AT_WARPS * 32, 3) mtp_force_atoms_kernel(const
 #pragma unroll
         for (int k = 0; k < 9; k++) vir[k] = T(0);
         const T *el = Es + lane;
-        // the next slot's position, index and type are fetched while the current one is evaluated
-        // (the type look-up, which needs the fetched index, is issued after the evaluation)
-        PairEval<T, SIG, CSP> nx;
-        nx.load(A, row, warp, at.nn);
-        nx.lookup(at.types_b);
         for (int j = warp; j < nmax; j += AT_WARPS) {
             PairEval<T, SIG, CSP> pe;
-            pe.x = nx.x; pe.y = nx.y; pe.z = nx.z; pe.nj = nx.nj; pe.tj = nx.tj; pe.act = nx.act;
-            nx.load(A, row, j + AT_WARPS, at.nn);
+            pe.fetch(A, tr, at.types_b, row, lane, j, at.nn);
             pe.template compute<true>(A, cf, at.ti);
             // powers of the unit vector and their derivatives k u^(k-1)
             T X[KD + 1], Y[KD + 1], Z[KD + 1], dX[KD + 1], dY[KD + 1], dZ[KD + 1];
@@ -370,7 +381,6 @@ __global__ void __launch_bounds__(AT_WARPS * 32, 3) mtp_force_atoms_kernel(const
                     vir[6] -= gz * pe.x; vir[7] -= gz * pe.y; vir[8] -= gz * pe.z;
                 }
             }
-            nx.lookup(at.types_b);
         }
         if (at.valid && warp < at.nn) {      // this warp saw at least one slot of the atom
             atomicAdd(frc + 3 * at.ci + 0, fcx);
@@ -419,9 +429,10 @@ using Sig10 = KSig<3, 1, 0, -1>;
 
 constexpr int AT_CSP = 8;
 
-bool mtp_atoms_supported(const MtpProgramDev &P, int ntypes, int cs, size_t elem)
+bool mtp_atoms_supported(const MtpProgramDev &P, int ntypes, int cs, size_t elem, long atom_ids)
 {
     if (cs > AT_CSP || P.nmus > 4) return false;
+    if (ntypes > 32 || atom_ids > TR_INDEX_MASK) return false;   // index | type << 26 in the staged rows
     if ((size_t)ntypes * ntypes * (P.nmus * AT_CSP + 2) * elem > AT_CF_BYTES) return false;
 #define AI2B_SIG_YES(S) return true;
     AI2B_FOR_SIG(P, AI2B_SIG_YES)
@@ -433,7 +444,7 @@ template <typename T, typename SIG>
 static int launch_fwd_atoms(const MtpProgramDev &P, const MtpArgs<T> &A, cudaStream_t st)
 {
     const size_t ncf = (size_t)A.ntypes * A.ntypes * cf_stride<SIG, AT_CSP>();
-    const size_t smem = sizeof(T) * (ncf + (size_t)AT_CH * (3 + SIG::NMUS) * 32);
+    const size_t smem = sizeof(T) * (ncf + (size_t)AT_CH * (3 + SIG::NMUS) * 32) + tile_rows_bytes<T>();
     auto kern = mtp_fwd_atoms_kernel<T, SIG, AT_CSP>;
     static KernelSetup setup;
     int per_sm = 1;
@@ -450,7 +461,7 @@ template <typename T, int MODE, typename SIG>
 static int launch_force_atoms(const MtpProgramDev &P, const MtpArgs<T> &A, cudaStream_t st)
 {
     const size_t ncf = (size_t)A.ntypes * A.ntypes * cf_stride<SIG, AT_CSP>();
-    const size_t smem = sizeof(T) * (ncf + (size_t)SIG::NDENSE * 32);
+    const size_t smem = sizeof(T) * (ncf + (size_t)SIG::NDENSE * 32) + tile_rows_bytes<T>();
     auto kern = mtp_force_atoms_kernel<T, MODE, SIG, AT_CSP>;
     static KernelSetup setup;
     int per_sm = 1;

@@ -25,7 +25,7 @@ struct MtpArgs {
 };
 
 // Lanes-as-atoms forward / force kernels (mtp_atoms.cu): available for the tables they are compiled for.
-bool mtp_atoms_supported(const MtpProgramDev &P, int ntypes, int cs, size_t elem);
+bool mtp_atoms_supported(const MtpProgramDev &P, int ntypes, int cs, size_t elem, long atom_ids);
 template <typename T> int mtp_fwd_atoms(const MtpProgramDev &P, const MtpArgs<T> &A, cudaStream_t st);
 template <typename T, int MODE> int mtp_force_atoms(const MtpProgramDev &P, const MtpArgs<T> &A, cudaStream_t st);
 

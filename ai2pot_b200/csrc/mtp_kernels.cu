@@ -927,7 +927,7 @@ static int launch_mtp_v(const ai2b_mtp_program *prog, MtpArgs<T> A, void *ws, cu
     // lanes-as-atoms forward and force kernels around the segment contraction, where all three apply
     bool atoms_path = false;
     if constexpr (KD <= 6 && CSP == 8)
-        atoms_path = mtp_atoms_supported(P, A.ntypes, A.cs, sizeof(T)) && P.nseg > 0 &&
+        atoms_path = mtp_atoms_supported(P, A.ntypes, A.cs, sizeof(T), (long)A.npad + A.nghost) && P.nseg > 0 &&
                      seg_smem_layout<T, MODE>(P, nullptr, nullptr) <= 226 * 1024;
     if (atoms_path) {
         A.tiled = 1;

@@ -207,3 +207,43 @@ def test_batched_build_ragged_triclinic_fractional(checkers, dt):
                                     is_cart=False)
     st = small["status"].cpu().numpy()
     assert st[1] & 1 and st[0] > 8 and int(small["bnumneigh"].max()) == 8
+
+
+@pytest.mark.parametrize("dt", [np.float64, np.float32])
+def test_lanes_as_centres_kernel_on_small_cases(checkers, dt, monkeypatch):
+    """Systems of 400,000 atoms and more take the kernel whose lanes are centre atoms (the full-size configs[4]
+    test runs it). AI2B_NBL_MIN_ATOMS = 0 sends every build with merged columns through it: triclinic cell with
+    atoms outside it, open axes, fractional input, a centre range with bin reuse, truncated rows."""
+    monkeypatch.setenv("AI2B_NBL_MIN_ATOMS", "0")
+    chk = _chk(checkers)
+    rng = np.random.default_rng(15)
+    cell = np.array([[17.0, 0.3, 0.1], [1.5, 16.5, 0.2], [-0.7, 0.9, 18.0]]).astype(dt)
+    frac = rng.random((400, 3))
+    pos = (frac @ cell.astype(np.float64) + rng.normal(0, 6.0, (400, 3))).astype(dt)
+    types = rng.integers(0, 2, 400).astype(np.int32)
+    for pbc in ((1, 1, 1), (1, 0, 1), (0, 0, 0), (0, 1, 0), (1, 1, 0)):
+        a = _gpu(cell, types, pos, 5.5, 160, pbc=pbc)
+        b = chk.nblist(cell, types, pos, 5.5, 160, pbc=pbc)
+        util.assert_nblist_equal(a, b[:3])
+    a = _gpu(cell, types, frac.astype(dt), 5.5, 160, is_cart=False)
+    b = chk.nblist(cell, types, frac.astype(dt), 5.5, 160, is_cart=False)
+    util.assert_nblist_equal(a, b[:3])
+    # the benchmark structure, a centre range and bin reuse
+    w = synth.g1(util.tables(16))
+    p1 = w["coords"].astype(dt); c1 = w["cell"].astype(dt)
+    ref = chk.nblist(c1, w["types"], p1, 6.0, 64)
+    util.assert_nblist_equal(_gpu(c1, w["types"], p1, 6.0, 64), ref[:3])
+    tdt = torch.float64 if dt == np.float64 else torch.float32
+    dpos = torch.from_numpy(p1).cuda()
+    nb = capi.NeighborBuilder()
+    lo, mid, hi = 1000, 5000, 9000
+    o1 = capi.NeighborBuilder.new_outputs(mid - lo, 64, tdt, dpos.device)
+    o2 = capi.NeighborBuilder.new_outputs(hi - mid, 64, tdt, dpos.device)
+    nb.build(c1, dpos, 6.0, 64, ncentres=mid, cbegin=lo, out=o1)
+    nb.build(c1, dpos, 6.0, 64, ncentres=hi, cbegin=mid, reuse_bins=True, out=o2)
+    for (nn, fn, rc, st), (x0, x1) in ((o1, (lo, mid)), (o2, (mid, hi))):
+        util.assert_nblist_equal((nn.cpu().numpy(), fn.cpu().numpy(), rc.cpu().numpy()), (ref[0][x0:x1], ref[1][x0:x1], ref[2][x0:x1]))
+    # truncated rows are flagged, the counts are the true ones
+    nn, fn, rc, st = capi.NeighborBuilder().build(c1, dpos, 6.0, 8)
+    st = st.cpu().numpy()
+    assert st[1] == 1 and st[0] == ref[0].max() and nn.max().item() == 8
