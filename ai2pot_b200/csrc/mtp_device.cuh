@@ -22,6 +22,7 @@ struct MtpArgs {
     int B, npad, ntypes, umax, nghost, cs, ndp, nbp;
     T scaling, rmax, rmin;
     int tiled = 0;
+    int zero_outputs = 0;   // etot, force and virial are zeroed by the set-up launch
 };
 
 // Lanes-as-atoms forward / force kernels (mtp_atoms.cu): available for the tables they are compiled for.
@@ -66,30 +67,50 @@ static __device__ __forceinline__ void prefix_binum_block(const int *__restrict_
     }
 }
 
+// Outputs the set-up launch zeroes (instead of one memset per array ahead of it).
+template <typename T>
+struct MtpZero {
+    T *p[3] = {nullptr, nullptr, nullptr};
+    size_t n[3] = {0, 0, 0};
+};
+
 // Set-up of one call in a single launch of 256-thread blocks: block 0 writes the structures'
-// atom offsets, blocks 1.. copy the radial coefficients into rows zero-padded to csp entries
-// (no such blocks are launched when the rows already have that length).
+// atom offsets, the next blocks copy the radial coefficients into rows zero-padded to csp entries
+// (no such blocks are launched when the rows already have that length), the rest zero the outputs.
 template <typename T>
 __global__ void mtp_prep_kernel(const int *__restrict__ binum, int B, int *__restrict__ prefix, const T *__restrict__ c,
-                                T *__restrict__ out, int rows, int cs, int csp)
+                                T *__restrict__ out, int rows, int cs, int csp, int pad_blocks, MtpZero<T> Z)
 {
     if (blockIdx.x == 0) {
         prefix_binum_block(binum, B, prefix);
         return;
     }
-    int i = (blockIdx.x - 1) * blockDim.x + threadIdx.x;
-    if (i >= rows * csp) return;
-    int r = i / csp, k = i % csp;
-    out[i] = k < cs ? c[r * cs + k] : T(0);
+    if ((int)blockIdx.x <= pad_blocks) {
+        int i = (blockIdx.x - 1) * blockDim.x + threadIdx.x;
+        if (i >= rows * csp) return;
+        int r = i / csp, k = i % csp;
+        out[i] = k < cs ? c[r * cs + k] : T(0);
+        return;
+    }
+    const size_t nz = gridDim.x - 1 - pad_blocks;
+    const size_t i0 = (size_t)(blockIdx.x - 1 - pad_blocks) * blockDim.x + threadIdx.x;
+#pragma unroll
+    for (int a = 0; a < 3; a++)
+        for (size_t i = i0; i < Z.n[a]; i += nz * blockDim.x) Z.p[a][i] = T(0);
 }
 
 // Launches the set-up kernel; returns the coefficient table the evaluation kernels should read.
 template <typename T>
-static const T *mtp_prepare(const int *binum, int B, int *prefix, const T *coeffs, T *cpad, int rows, int cs, int csp, cudaStream_t st)
+static const T *mtp_prepare(const int *binum, int B, int *prefix, const T *coeffs, T *cpad, int rows, int cs, int csp, cudaStream_t st,
+                            const MtpZero<T> &Z = MtpZero<T>())
 {
     // the kernels read coefficient pairs with one vector load
     const bool pad = cs != csp || (reinterpret_cast<size_t>(coeffs) % (2 * sizeof(T))) != 0;
-    mtp_prep_kernel<T><<<1 + (pad ? (rows * csp + 255) / 256 : 0), 256, 0, st>>>(binum, B, prefix, coeffs, cpad, rows, cs, csp);
+    const int pad_blocks = pad ? (rows * csp + 255) / 256 : 0;
+    const size_t nzero = Z.n[0] + Z.n[1] + Z.n[2];
+    size_t zb = (nzero + 4 * 256 - 1) / (4 * 256);      // four elements per thread
+    if (zb > 4096) zb = 4096;
+    mtp_prep_kernel<T><<<1 + pad_blocks + (unsigned)zb, 256, 0, st>>>(binum, B, prefix, coeffs, cpad, rows, cs, csp, pad_blocks, Z);
     return pad ? cpad : coeffs;
 }
 

@@ -918,7 +918,13 @@ static int launch_mtp_v(const ai2b_mtp_program *prog, MtpArgs<T> A, void *ws, cu
     A.Eb = reinterpret_cast<T *>(w + L.eb);
     A.ndp = ndense_pad(P);
     A.nbp = nbasic_pad(P);
-    A.coeffs_pad = mtp_prepare<T>(A.binum, A.B, prefix, A.coeffs, cpad, A.ntypes * A.ntypes * P.nmus, A.cs, CSP, st);
+    MtpZero<T> Z;
+    if (A.zero_outputs) {
+        Z.p[0] = A.etot; Z.n[0] = (size_t)A.B;
+        Z.p[1] = A.force; Z.n[1] = 3 * (size_t)A.B * (A.npad + A.nghost);
+        if (A.virial) { Z.p[2] = A.virial; Z.n[2] = 9 * (size_t)A.B; }
+    }
+    A.coeffs_pad = mtp_prepare<T>(A.binum, A.B, prefix, A.coeffs, cpad, A.ntypes * A.ntypes * P.nmus, A.cs, CSP, st, Z);
     AI2B_CUDA(cudaGetLastError());
 
     const long atoms_upper = (long)A.B * A.npad;
@@ -1019,7 +1025,7 @@ extern "C" size_t ai2b_mtp_workspace_bytes(const ai2b_mtp_program *prog, int bat
         AI2B_REQUIRE(prog && etot && force && coeffs && lin && bias && qs && binum && bilist && numneigh &&    \
                          firstneigh && rcs && types, AI2B_ERR_INVALID, "ai2b_mtp_efv: NULL argument");         \
         cudaStream_t st = (cudaStream_t)stream;                                                                \
-        if (B > 0 && npad >= 0) {                                                                              \
+        if (B > 0 && npad == 0) {   /* no atoms: the kernels are not launched */                               \
             AI2B_CUDA(cudaMemsetAsync(etot, 0, sizeof(T) * B, st));                                            \
             AI2B_CUDA(cudaMemsetAsync(force, 0, sizeof(T) * 3 * (size_t)B * (npad + nghost), st));             \
             if (virial) AI2B_CUDA(cudaMemsetAsync(virial, 0, sizeof(T) * 9 * B, st));                          \
@@ -1027,6 +1033,7 @@ extern "C" size_t ai2b_mtp_workspace_bytes(const ai2b_mtp_program *prog, int bat
         MtpArgs<T> A{etot, force, virial, nullptr, coeffs, lin, bias, qs, nullptr, binum, bilist, numneigh,    \
                      firstneigh, types, rcs, nullptr, nullptr, nullptr, B, npad, ntypes, umax, nghost, cs, 0, 0, \
                      scaling, rmax, rmin};                                                                     \
+        A.zero_outputs = 1;                                                                                    \
         return virial ? launch_mtp<T, MODE_EFV>(prog, A, ws, ws_bytes, st)                                     \
                       : launch_mtp<T, MODE_EF>(prog, A, ws, ws_bytes, st);                                     \
     }                                                                                                          \

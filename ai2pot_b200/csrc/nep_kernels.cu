@@ -184,6 +184,27 @@ __global__ void nep_pad_coeffs_kernel(const T *__restrict__ c, T *__restrict__ o
     out[i] = k < cs ? c[r * cs + k] : T(0);
 }
 
+// zeroes up to three output arrays in one launch (instead of one memset per array)
+template <typename T>
+__global__ void nep_zero_kernel(T *__restrict__ a, size_t na, T *__restrict__ b, size_t nb, T *__restrict__ c, size_t nc)
+{
+    const size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x, step = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = i0; i < na; i += step) a[i] = T(0);
+    for (size_t i = i0; i < nb; i += step) b[i] = T(0);
+    for (size_t i = i0; i < nc; i += step) c[i] = T(0);
+}
+template <typename T>
+static int nep_zero_outputs(T *etot, size_t ne, T *force, size_t nf, T *virial, size_t nv, cudaStream_t st)
+{
+    const size_t n = ne + nf + nv;
+    if (n == 0) return AI2B_OK;
+    size_t blocks = (n + 4 * 256 - 1) / (4 * 256);
+    if (blocks > 4096) blocks = 4096;
+    nep_zero_kernel<T><<<(unsigned)blocks, 256, 0, st>>>(etot, ne, force, nf, virial, virial ? nv : 0);
+    AI2B_CUDA(cudaGetLastError());
+    return AI2B_OK;
+}
+
 __global__ void nep_prefix_kernel(const int *__restrict__ binum, int B, int *__restrict__ prefix)
 {
     // B is small (structures per batch): one thread is enough
@@ -625,9 +646,8 @@ extern "C" size_t ai2b_nep_workspace_bytes(int batch_size, int ntypes, int n_rad
                          firstneigh && rcs && types, AI2B_ERR_INVALID, "ai2b_nep_efv: NULL argument");          \
         cudaStream_t st = (cudaStream_t)stream;                                                                 \
         if (zero && B > 0 && npad >= 0) {                                                                       \
-            AI2B_CUDA(cudaMemsetAsync(etot, 0, sizeof(T) * B, st));                                             \
-            AI2B_CUDA(cudaMemsetAsync(force, 0, sizeof(T) * 3 * (size_t)B * (npad + nghost), st));              \
-            if (virial) AI2B_CUDA(cudaMemsetAsync(virial, 0, sizeof(T) * 9 * B, st));                           \
+            if (int rc = nep_zero_outputs<T>(etot, (size_t)B, force, 3 * (size_t)B * (npad + nghost), virial,   \
+                                             virial ? 9 * (size_t)B : 0, st)) return rc;                        \
         }                                                                                                       \
         NepArgs<T> A{etot, force, virial, nullptr, nullptr, w0, b0, w1, bias, qs, binum, bilist, numneigh,      \
                      firstneigh, types, rcs, nullptr, B, npad, ntypes, umax, nghost, cs, n_r, n_a, l_max, nneu, \
@@ -753,9 +773,8 @@ extern "C" int ai2b_nep_efv_static_scratch_f32(float *etot, float *force, float 
     }
     cudaStream_t st = (cudaStream_t)stream;
     if (B > 0 && npad >= 0) {
-        AI2B_CUDA(cudaMemsetAsync(etot, 0, sizeof(float) * B, st));
-        AI2B_CUDA(cudaMemsetAsync(force, 0, sizeof(float) * 3 * (size_t)B * (npad + nghost), st));
-        if (virial) AI2B_CUDA(cudaMemsetAsync(virial, 0, sizeof(float) * 9 * B, st));
+        if (int rc = nep_zero_outputs<float>(etot, (size_t)B, force, 3 * (size_t)B * (npad + nghost), virial,
+                                             virial ? 9 * (size_t)B : 0, st)) return rc;
     }
     NepArgs<float> A{etot, force, virial, nullptr, nullptr, w0, b0, w1, bias, qs, binum, bilist, numneigh,
                      firstneigh, types, rcs, nullptr, B, npad, ntypes, umax, nghost, cs, n_r, n_a, l_max, nneu,
