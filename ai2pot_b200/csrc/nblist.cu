@@ -819,7 +819,6 @@ nb_build_lanes_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *_
     }
 }
 
-
 // optional pass 4: order each row by distance (the reference's sort=true, neighborList.h:290-335:
 // std::sort on sqrt(dx^2+dy^2+dz^2)). Stable rank sort, one warp per row; ties keep build order.
 template <typename T>
@@ -1044,7 +1043,7 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
     // search window (known on the host: open axes always search NB_SUB bins)
     const int R2 = P.per[2] ? (int)std::ceil(P.rcut_m / (P.dplane[2] / P.nbh[2])) : NB_SUB;
     const bool zmerge = !P.per[2] || P.nbh[2] >= 2 * R2 + 1;
-    // Lanes = centres for large systems: a third of the instructions per atom, but every lane walks through memory
+    // Lanes = centres for large systems: far fewer instructions per atom, but every lane walks through memory
     // on its own, which only pays once there are enough warps per SM to hide that latency (measured: 5 % faster
     // at 1,048,576 atoms, 2-3 times slower at 13,824).
     int min_atoms = NBL_MIN_ATOMS;

@@ -492,7 +492,7 @@ def run_single_benchmark(w, steps, warmup, dist, sampler):
     hbm, hbm_src = hbm_peak()
     key = ("mtp16" if m["kind"] == "mtp" else "nep") + f"_{n}_efv"
     traffic, traffic_src = profiled_traffic(key)
-    roofline = {"kernel": "mtp_fwd_lanes + mtp_contract + mtp_force (the three E/F/V kernels of a call)" if m["kind"] == "mtp" else "nep_fast_kernel",
+    roofline = {"kernel": "mtp_fwd_atoms + mtp_contract_seg + mtp_force_atoms (the three E/F/V kernels of a call)" if m["kind"] == "mtp" else "nep_fast_kernel",
                 "bound": bound,
                 "achieved": achieved, "peak": peak_meas, "unit": "TFLOP/s", "frac": achieved / peak_meas,
                 "peak_source": "FMA-chain microbenchmark in this run (of measured)", "peak_nominal": peak_nom,
