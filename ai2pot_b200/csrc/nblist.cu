@@ -654,7 +654,7 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
 // predicate is the one of nb_build_kernel, line for line. Rows are padded by the whole warp afterwards, one row at a time, with
 // stores that run along the row.
 constexpr int NBL_WARPS = 4;
-constexpr int NBL_MIN_ATOMS = 400000;     // systems from this size on take this kernel
+constexpr int NBL_MIN_ATOMS = 220000;     // systems from this size on take this kernel
 template <typename T, typename TO>
 __global__ void __launch_bounds__(NBL_WARPS * 32)
 nb_build_lanes_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restrict__ bin_start,
@@ -1043,9 +1043,10 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
     // search window (known on the host: open axes always search NB_SUB bins)
     const int R2 = P.per[2] ? (int)std::ceil(P.rcut_m / (P.dplane[2] / P.nbh[2])) : NB_SUB;
     const bool zmerge = !P.per[2] || P.nbh[2] >= 2 * R2 + 1;
-    // Lanes = centres for large systems: far fewer instructions per atom, but every lane walks through memory
-    // on its own, which only pays once there are enough warps per SM to hide that latency (measured: 5 % faster
-    // at 1,048,576 atoms, 2-3 times slower at 13,824).
+    // Lanes = centres for large systems: far fewer instructions per atom, but every lane walks through memory on
+    // its own, which only pays once there are enough warps per SM to hide that latency. Measured time of the whole
+    // build, warp per centre / lane per centre (fp32, rcut 6, 29 neighbours): 55,296 atoms 0.087 / 0.126 ms,
+    // 186,624 atoms 0.234 / 0.236 ms, 256,000 atoms 0.280 / 0.265 ms, 780,448 atoms 0.769 / 0.618 ms.
     int min_atoms = NBL_MIN_ATOMS;
     if (const char *env = std::getenv("AI2B_NBL_MIN_ATOMS")) min_atoms = std::atoi(env);   // tuning knob, read per call
     if (zmerge && n >= min_atoms) {

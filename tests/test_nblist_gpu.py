@@ -211,7 +211,7 @@ def test_batched_build_ragged_triclinic_fractional(checkers, dt):
 
 @pytest.mark.parametrize("dt", [np.float64, np.float32])
 def test_lanes_as_centres_kernel_on_small_cases(checkers, dt, monkeypatch):
-    """Systems of 400,000 atoms and more take the kernel whose lanes are centre atoms (the full-size configs[4]
+    """Large systems (220,000 atoms and more) take the kernel whose lanes are centre atoms (the full-size configs[4]
     test runs it). AI2B_NBL_MIN_ATOMS = 0 sends every build with merged columns through it: triclinic cell with
     atoms outside it, open axes, fractional input, a centre range with bin reuse, truncated rows."""
     monkeypatch.setenv("AI2B_NBL_MIN_ATOMS", "0")
