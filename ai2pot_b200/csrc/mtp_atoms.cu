@@ -186,12 +186,15 @@ __device__ __forceinline__ int warp_max_int(int v)
 }
 
 // ---- forward --------------------------------------------------------------------------------------
-// shared memory: radial coefficients [ntypes^2][NMUS][CSP], staging [AT_CH][3 + NMUS][32]
-template <typename T, typename SIG, int CSP>
-__global__ void __launch_bounds__(AT_WARPS * 32, 3) mtp_fwd_atoms_kernel(const MtpProgramDev P, const MtpArgs<T> A)
+// DERIV = false: basic moments M -> A.Mb. DERIV = true (loss gradient, linearMtpLoss.h:331-389): their directional
+// derivatives D = sum_j p_ij . dM/dr_j along the pair weights p of the loss -> L.Db; per neighbour and monomial m
+// that is a_mu m + f_mu (q . grad m) with a_mu = f'_mu (p . u), q = (p - (p . u) u) / r.
+// shared memory: radial coefficients [ntypes^2][NMUS][CSP] (rows shifted), staging [AT_CH][NV][32], tile rows
+template <typename T, typename SIG, int CSP, bool DERIV>
+__global__ void __launch_bounds__(AT_WARPS * 32, DERIV ? 2 : 3) mtp_fwd_atoms_kernel(const MtpProgramDev P, const MtpArgs<T> A, const LossArgs<T> L)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    constexpr int NV = 3 + SIG::NMUS;
+    constexpr int NV = 3 + SIG::NMUS + (DERIV ? SIG::NMUS + 3 : 0);   // u, f [, a, q]
     constexpr int KD = SIG::KD;
     T *cf = reinterpret_cast<T *>(smem_raw);
     T *st = cf + A.ntypes * A.ntypes * cf_stride<SIG, CSP>();
@@ -207,7 +210,8 @@ __global__ void __launch_bounds__(AT_WARPS * 32, 3) mtp_fwd_atoms_kernel(const M
         at.set(A, tile * MTP_TILE + lane, ntot);
         const int nmax = warp_max_int(at.nn);      // the same in every warp of the block
         const size_t row = at.slot * A.umax;
-        T *out = A.Mb + (size_t)tile * A.nbp * MTP_TILE + lane;
+        const int nstruct = at.valid ? A.binum[at.b] : 1;
+        T *out = (DERIV ? L.Db : A.Mb) + (size_t)tile * A.nbp * MTP_TILE + lane;
         __syncthreads();     // the previous tile's rows are no longer read
         if (warp == 0) tr.describe(lane, row, (size_t)(at.types_b - A.types), at.nn);
         __syncthreads();
@@ -225,10 +229,21 @@ __global__ void __launch_bounds__(AT_WARPS * 32, 3) mtp_fwd_atoms_kernel(const M
                 for (int jj = warp; jj < cnt; jj += AT_WARPS) {   // this warp's slots of the round
                     PairEval<T, SIG, CSP> pe;
                     pe.fetch(A, tr, at.types_b, row, lane, j0 + jj, at.nn);
-                    pe.template compute<false>(A, cf, at.ti);
+                    pe.template compute<DERIV>(A, cf, at.ti);
                     T *s = st + (size_t)jj * NV * 32 + lane;
                     s[0] = pe.ux; s[32] = pe.uy; s[64] = pe.uz;
                     static_for<0, SIG::NMUS>([&](auto mm) { s[(3 + decltype(mm)::value) * 32] = pe.f[decltype(mm)::value]; });
+                    if constexpr (DERIV) {
+                        T px = T(0), py = T(0), pz = T(0);
+                        if (pe.act) pair_weight(A, L, at.b, nstruct, at.ci, pe.nj, pe.x, pe.y, pe.z, px, py, pz);
+                        const T ppar = px * pe.ux + py * pe.uy + pz * pe.uz;
+                        static_for<0, SIG::NMUS>([&](auto mm) {
+                            s[(3 + SIG::NMUS + decltype(mm)::value) * 32] = pe.fd[decltype(mm)::value] * ppar;
+                        });
+                        s[(3 + 2 * SIG::NMUS) * 32] = (px - ppar * pe.ux) * pe.rinv;
+                        s[(4 + 2 * SIG::NMUS) * 32] = (py - ppar * pe.uy) * pe.rinv;
+                        s[(5 + 2 * SIG::NMUS) * 32] = (pz - ppar * pe.uz) * pe.rinv;
+                    }
                 }
                 __syncthreads();
                 if constexpr (NACC > 0) {
@@ -237,18 +252,30 @@ __global__ void __launch_bounds__(AT_WARPS * 32, 3) mtp_fwd_atoms_kernel(const M
                         const T *s = st + (size_t)jj * NV * 32 + lane;
                         Powers<T, KD> pw;
                         pw.set(s[0], s[32], s[64]);
-                        T f[SIG::NMUS];
+                        T f[SIG::NMUS], a[SIG::NMUS], qx = T(0), qy = T(0), qz = T(0);
                         static_for<0, SIG::NMUS>([&](auto mm) { f[decltype(mm)::value] = s[(3 + decltype(mm)::value) * 32]; });
+                        if constexpr (DERIV) {
+                            static_for<0, SIG::NMUS>([&](auto mm) { a[decltype(mm)::value] = s[(3 + SIG::NMUS + decltype(mm)::value) * 32]; });
+                            qx = s[(3 + 2 * SIG::NMUS) * 32]; qy = s[(4 + 2 * SIG::NMUS) * 32]; qz = s[(5 + 2 * SIG::NMUS) * 32];
+                        }
                         static_for<0, KD + 1>([&](auto dd) {
                             constexpr int D = decltype(dd)::value;
                             if constexpr (SIG::group(D) == G) {
                                 static_for<0, ndeg(D)>([&](auto qq) {
                                     constexpr int Q = decltype(qq)::value;
                                     const T m = mono<T, KD, D, Q>(pw);
+                                    T dm = T(0);
+                                    if constexpr (DERIV) {   // q . grad of the monomial
+                                        constexpr Exp3 e = deg_exp(D, Q);
+                                        if constexpr (e.x > 0) dm = fma(qx * T(e.x), pw.x[e.x - 1] * pw.y[e.y] * pw.z[e.z], dm);
+                                        if constexpr (e.y > 0) dm = fma(qy * T(e.y), pw.x[e.x] * pw.y[e.y - 1] * pw.z[e.z], dm);
+                                        if constexpr (e.z > 0) dm = fma(qz * T(e.z), pw.x[e.x] * pw.y[e.y] * pw.z[e.z - 1], dm);
+                                    }
                                     static_for<0, SIG::cnt(D)>([&](auto mm) {
                                         constexpr int mu = decltype(mm)::value;
                                         constexpr int I = SIG::acc_off(D) + Q * SIG::cnt(D) + mu;
-                                        acc[I] = fma(f[mu], m, acc[I]);
+                                        if constexpr (DERIV) acc[I] = fma(a[mu], m, fma(f[mu], dm, acc[I]));
+                                        else acc[I] = fma(f[mu], m, acc[I]);
                                     });
                                 });
                             }
@@ -415,17 +442,21 @@ static bool sig_matches(const MtpProgramDev &P)
     return true;
 }
 
-// the template levels 10, 12, 14 and 16 of the reference's MTP_templates
+// the template levels 6 to 16 of the reference's MTP_templates
 using Sig16 = KSig<6, 4, 2, 0>;
 using Sig14 = KSig<5, 3, 1, 0>;
 using Sig12 = KSig<4, 2, 0, -1>;
 using Sig10 = KSig<3, 1, 0, -1>;
+using Sig08 = KSig<2, 0, -1, -1>;
+using Sig06 = KSig<1, 0, -1, -1>;
 
 #define AI2B_FOR_SIG(P, CALL)                \
     if (sig_matches<Sig16>(P)) { CALL(Sig16) } \
     if (sig_matches<Sig14>(P)) { CALL(Sig14) } \
     if (sig_matches<Sig12>(P)) { CALL(Sig12) } \
-    if (sig_matches<Sig10>(P)) { CALL(Sig10) }
+    if (sig_matches<Sig10>(P)) { CALL(Sig10) } \
+    if (sig_matches<Sig08>(P)) { CALL(Sig08) } \
+    if (sig_matches<Sig06>(P)) { CALL(Sig06) }
 
 constexpr int AT_CSP = 8;
 
@@ -440,19 +471,19 @@ bool mtp_atoms_supported(const MtpProgramDev &P, int ntypes, int cs, size_t elem
     return false;
 }
 
-template <typename T, typename SIG>
-static int launch_fwd_atoms(const MtpProgramDev &P, const MtpArgs<T> &A, cudaStream_t st)
+template <typename T, typename SIG, bool DERIV>
+static int launch_fwd_atoms(const MtpProgramDev &P, const MtpArgs<T> &A, const LossArgs<T> &L, cudaStream_t st)
 {
     const size_t ncf = (size_t)A.ntypes * A.ntypes * cf_stride<SIG, AT_CSP>();
-    const size_t smem = sizeof(T) * (ncf + (size_t)AT_CH * (3 + SIG::NMUS) * 32) + tile_rows_bytes<T>();
-    auto kern = mtp_fwd_atoms_kernel<T, SIG, AT_CSP>;
+    const size_t smem = sizeof(T) * (ncf + (size_t)AT_CH * (3 + SIG::NMUS + (DERIV ? SIG::NMUS + 3 : 0)) * 32) + tile_rows_bytes<T>();
+    auto kern = mtp_fwd_atoms_kernel<T, SIG, AT_CSP, DERIV>;
     static KernelSetup setup;
     int per_sm = 1;
     if (int rc = kernel_setup(setup, kern, smem, AT_WARPS * 32, &per_sm)) return rc;
     long tiles = ((long)A.B * A.npad + MTP_TILE - 1) / MTP_TILE;
     long blocks = (long)sm_count() * per_sm;
     if (blocks > tiles) blocks = tiles;
-    kern<<<(unsigned)blocks, AT_WARPS * 32, smem, st>>>(P, A);
+    kern<<<(unsigned)blocks, AT_WARPS * 32, smem, st>>>(P, A, L);
     AI2B_CUDA(cudaGetLastError());
     return AI2B_OK;
 }
@@ -477,9 +508,19 @@ static int launch_force_atoms(const MtpProgramDev &P, const MtpArgs<T> &A, cudaS
 template <typename T>
 int mtp_fwd_atoms(const MtpProgramDev &P, const MtpArgs<T> &A, cudaStream_t st)
 {
-#define AI2B_SIG_FWD(S) return launch_fwd_atoms<T, S>(P, A, st);
+#define AI2B_SIG_FWD(S) return launch_fwd_atoms<T, S, false>(P, A, LossArgs<T>{}, st);
     AI2B_FOR_SIG(P, AI2B_SIG_FWD)
 #undef AI2B_SIG_FWD
+    set_error("no lanes-as-atoms MTP kernel for these tables");
+    return AI2B_ERR_UNSUPPORTED;
+}
+
+template <typename T>
+int mtp_dfwd_atoms(const MtpProgramDev &P, const MtpArgs<T> &A, const LossArgs<T> &L, cudaStream_t st)
+{
+#define AI2B_SIG_DFWD(S) return launch_fwd_atoms<T, S, true>(P, A, L, st);
+    AI2B_FOR_SIG(P, AI2B_SIG_DFWD)
+#undef AI2B_SIG_DFWD
     set_error("no lanes-as-atoms MTP kernel for these tables");
     return AI2B_ERR_UNSUPPORTED;
 }
@@ -496,6 +537,8 @@ int mtp_force_atoms(const MtpProgramDev &P, const MtpArgs<T> &A, cudaStream_t st
 
 template int mtp_fwd_atoms<float>(const MtpProgramDev &, const MtpArgs<float> &, cudaStream_t);
 template int mtp_fwd_atoms<double>(const MtpProgramDev &, const MtpArgs<double> &, cudaStream_t);
+template int mtp_dfwd_atoms<float>(const MtpProgramDev &, const MtpArgs<float> &, const LossArgs<float> &, cudaStream_t);
+template int mtp_dfwd_atoms<double>(const MtpProgramDev &, const MtpArgs<double> &, const LossArgs<double> &, cudaStream_t);
 template int mtp_force_atoms<float, MODE_EFV>(const MtpProgramDev &, const MtpArgs<float> &, cudaStream_t);
 template int mtp_force_atoms<float, MODE_EF>(const MtpProgramDev &, const MtpArgs<float> &, cudaStream_t);
 template int mtp_force_atoms<double, MODE_EFV>(const MtpProgramDev &, const MtpArgs<double> &, cudaStream_t);

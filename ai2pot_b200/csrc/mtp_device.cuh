@@ -25,10 +25,41 @@ struct MtpArgs {
     int zero_outputs = 0;   // etot, force and virial are zeroed by the set-up launch
 };
 
+// Inputs and outputs of the loss-gradient path (mtp_loss.cu).
+template <typename T>
+struct LossArgs {
+    const T *e_ml, *e_dft, *f_ml, *f_dft, *v_ml, *v_dft;   // v_* NULL: energy + force loss
+    T *dcoeffs, *dlinear, *dbias;                           // [B,ncoef], [B,ns], [B,ntypes]
+    T *Db, *Xb;                                             // [atoms][nbp] workspace rows
+    T ew, fw, vw;
+    int ncoef;
+};
+
+// pair weight vector p of the loss gradient
+template <typename T>
+__device__ __forceinline__ void pair_weight(const MtpArgs<T> &A, const LossArgs<T> &L, int b, int n, int ci, int nj, T x, T y, T z,
+                                            T &px, T &py, T &pz)
+{
+    const T cf = T(2) * L.fw / T(3 * n);
+    const T *fm = L.f_ml + (size_t)b * (A.npad + A.nghost) * 3, *fd = L.f_dft + (size_t)b * A.npad * 3;
+    px = cf * ((fm[3 * ci + 0] - fd[3 * ci + 0]) - (fm[3 * nj + 0] - fd[3 * nj + 0]));
+    py = cf * ((fm[3 * ci + 1] - fd[3 * ci + 1]) - (fm[3 * nj + 1] - fd[3 * nj + 1]));
+    pz = cf * ((fm[3 * ci + 2] - fd[3 * ci + 2]) - (fm[3 * nj + 2] - fd[3 * nj + 2]));
+    if (L.v_ml) {
+        const T cv = T(2) * L.vw / T(9 * n);
+        const T *vm = L.v_ml + 9 * b, *vd = L.v_dft + 9 * b;
+        px -= cv * ((vm[0] - vd[0]) * x + (vm[1] - vd[1]) * y + (vm[2] - vd[2]) * z);
+        py -= cv * ((vm[3] - vd[3]) * x + (vm[4] - vd[4]) * y + (vm[5] - vd[5]) * z);
+        pz -= cv * ((vm[6] - vd[6]) * x + (vm[7] - vd[7]) * y + (vm[8] - vd[8]) * z);
+    }
+}
+
 // Lanes-as-atoms forward / force kernels (mtp_atoms.cu): available for the tables they are compiled for.
 bool mtp_atoms_supported(const MtpProgramDev &P, int ntypes, int cs, size_t elem, long atom_ids);
 template <typename T> int mtp_fwd_atoms(const MtpProgramDev &P, const MtpArgs<T> &A, cudaStream_t st);
 template <typename T, int MODE> int mtp_force_atoms(const MtpProgramDev &P, const MtpArgs<T> &A, cudaStream_t st);
+// directional derivatives of the basic moments along the loss gradient's pair weights -> L.Db (tiled)
+template <typename T> int mtp_dfwd_atoms(const MtpProgramDev &P, const MtpArgs<T> &A, const LossArgs<T> &L, cudaStream_t st);
 
 // exclusive prefix sum of binum -> prefix[0..B]; one block
 static __device__ __forceinline__ void prefix_binum_block(const int *__restrict__ binum, int B, int *__restrict__ prefix)

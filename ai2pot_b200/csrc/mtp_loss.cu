@@ -21,15 +21,6 @@
 
 namespace ai2b {
 
-template <typename T>
-struct LossArgs {
-    const T *e_ml, *e_dft, *f_ml, *f_dft, *v_ml, *v_dft;   // v_* NULL: energy + force loss
-    T *dcoeffs, *dlinear, *dbias;                           // [B,ncoef], [B,ns], [B,ntypes]
-    T *Db, *Xb;                                             // [atoms][nbp] workspace rows
-    T ew, fw, vw;
-    int ncoef;
-};
-
 // ---- loss and squared-error sums ---------------------------------------------------------------
 // one block per structure; se[0..2] accumulate sum dE^2 (of the energy per atom if e_per_atom: the NEP ops'
 // definition, nepLoss_cpu_launcher.h:300-345), sum dF^2, sum dV^2, se[3] the atom count
@@ -75,25 +66,6 @@ __global__ void mtp_rmse_kernel(T *__restrict__ rmse, const T *__restrict__ se, 
         rmse[0] = sqrt(se[0] / T(B));
         rmse[1] = sqrt(se[1] / (T(3) * se[3]));
         rmse[2] = sqrt(se[2] / T(9 * B));
-    }
-}
-
-// pair weight vector p of the loss gradient
-template <typename T>
-__device__ __forceinline__ void pair_weight(const MtpArgs<T> &A, const LossArgs<T> &L, int b, int n, int ci, int nj, T x, T y, T z,
-                                            T &px, T &py, T &pz)
-{
-    const T cf = T(2) * L.fw / T(3 * n);
-    const T *fm = L.f_ml + (size_t)b * (A.npad + A.nghost) * 3, *fd = L.f_dft + (size_t)b * A.npad * 3;
-    px = cf * ((fm[3 * ci + 0] - fd[3 * ci + 0]) - (fm[3 * nj + 0] - fd[3 * nj + 0]));
-    py = cf * ((fm[3 * ci + 1] - fd[3 * ci + 1]) - (fm[3 * nj + 1] - fd[3 * nj + 1]));
-    pz = cf * ((fm[3 * ci + 2] - fd[3 * ci + 2]) - (fm[3 * nj + 2] - fd[3 * nj + 2]));
-    if (L.v_ml) {
-        const T cv = T(2) * L.vw / T(9 * n);
-        const T *vm = L.v_ml + 9 * b, *vd = L.v_dft + 9 * b;
-        px -= cv * ((vm[0] - vd[0]) * x + (vm[1] - vd[1]) * y + (vm[2] - vd[2]) * z);
-        py -= cv * ((vm[3] - vd[3]) * x + (vm[4] - vd[4]) * y + (vm[5] - vd[5]) * z);
-        pz -= cv * ((vm[6] - vd[6]) * x + (vm[7] - vd[7]) * y + (vm[8] - vd[8]) * z);
     }
 }
 
@@ -249,8 +221,11 @@ __global__ void __launch_bounds__(MTP_CWARPS * 32, 1) mtp_loss_contract_kernel(c
     for (int idx = threadIdx.x; idx < TA * A.nbp; idx += nthreads) {
         const int at = idx / A.nbp, i = idx - at * A.nbp;
         if (i < P.nb && t0 + at < ntot) {
-            M[i * LD + at] = A.Mb[(size_t)(t0 + at) * A.nbp + i];
-            D[i * LD + at] = L.Db[(size_t)(t0 + at) * A.nbp + i];
+            const int t = t0 + at;
+            // rows per atom, or [tile of 32 atoms][row][32]
+            const size_t src = A.tiled ? ((size_t)(t >> 5) * A.nbp + i) * 32 + (t & 31) : (size_t)t * A.nbp + i;
+            M[i * LD + at] = A.Mb[src];
+            D[i * LD + at] = L.Db[src];
         }
     }
     __syncthreads();
@@ -503,7 +478,7 @@ static LossWs loss_ws_layout(const MtpProgramDev &P, int B, int npad, int ntypes
 {
     LossWs L;
     L.base = mtp_ws_layout(P, B, npad, ntypes, elem);
-    const size_t atoms = (size_t)(B > 0 ? B : 0) * (npad > 0 ? npad : 0);
+    const size_t atoms = ((size_t)(B > 0 ? B : 0) * (npad > 0 ? npad : 0) + 31) & ~size_t(31);   // whole tiles of 32 atoms
     L.db = L.base.total;
     L.xb = L.db + up256(atoms * nbasic_pad(P) * elem);
     L.total = L.xb + up256(atoms * nbasic_pad(P) * elem);
@@ -548,7 +523,14 @@ static int launch_loss_bwd_v(const ai2b_mtp_program *prog, MtpArgs<T> A, LossArg
     AI2B_CUDA(cudaGetLastError());
     const long atoms_upper = (long)A.B * A.npad;
     const long need = (atoms_upper + MTP_WARPS - 1) / MTP_WARPS;
-    {
+    // basic moments and their directional derivatives: the lanes-as-atoms kernels where they exist for these tables
+    bool atoms_path = false;
+    if constexpr (KD <= 6 && CSP == 8) atoms_path = mtp_atoms_supported(P, A.ntypes, A.cs, sizeof(T), (long)A.npad + A.nghost);
+    if (atoms_path) {
+        A.tiled = 1;
+        if (int rc = mtp_fwd_atoms<T>(P, A, st)) return rc;
+        if (int rc = mtp_dfwd_atoms<T>(P, A, L, st)) return rc;
+    } else {
         const size_t smem = sizeof(T) * (size_t)(2 * A.ndp + 2 * MTP_MAX_MU * 32) * MTP_WARPS;
         auto kern = mtp_loss_fwd_kernel<T, KD, CSP>;
         static KernelSetup setup;
