@@ -17,7 +17,6 @@
 // all three kernels read and write in full 256-byte rows.
 // The kernels are compiled per "signature" = the highest monomial degree of every radial function
 // (non-increasing, at most four functions); other tables take the warp-per-atom kernels.
-#include <cuda_pipeline.h>
 #include "mtp_device.cuh"
 #include "tile_rows.cuh"
 
