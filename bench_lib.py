@@ -371,11 +371,35 @@ def run_slab_benchmark(w, steps, warmup, dist, sampler):
         note = f"symmetric memory unavailable ({type(exc).__name__}): NCCL transport"
         dom = slab.SlabDomain(w["cell"], w["coords"], w["types"], w["rcut"], rank, world, dev, dist,
                               halo_cutoffs=2 if (schedule == "owner" and world > 1) else 1, transport="nccl")
-    step_obj = slab.SlabStep(dom, w["model"], w["umax"], dtype, schedule=schedule,
-                             tail_fraction=float(os.environ.get("AI2B_SLAB_TAIL", "0.25")))
-    e, f, v = step_obj.evaluate()
-    torch.cuda.synchronize()
-    step_obj.check_status()
+    def make_step(d):
+        return slab.SlabStep(d, w["model"], w["umax"], dtype, schedule=schedule, tail_fraction=float(os.environ.get("AI2B_SLAB_TAIL", "0.25")))
+
+    step_obj = make_step(dom)
+    # First step. A peer exchange that gave up on one rank (bounded waits: the kernels return, the status says where) must not
+    # leave the other ranks waiting in the next barrier: the ranks agree on the outcome and, if need be, all change to NCCL.
+    ok = 1
+    if dist is not None:
+        dist.barrier()      # the ranks enter their first exchange together (the waits are bounded to a few seconds)
+    try:
+        e, f, v = step_obj.evaluate()
+        torch.cuda.synchronize()
+        step_obj.check_status()
+    except RuntimeError as exc:
+        if dom.transport != "peer" or dist is None:
+            raise
+        ok = 0
+        note = f"peer exchange failed on rank {rank} ({exc}): NCCL transport"
+    if dist is not None and dom.transport == "peer":
+        agreed = torch.tensor([ok], dtype=torch.int32, device=dev)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        if int(agreed.item()) == 0:
+            note = note or "peer exchange failed on another rank: NCCL transport"
+            dom = slab.SlabDomain(w["cell"], w["coords"], w["types"], w["rcut"], rank, world, dev, dist,
+                                  halo_cutoffs=2 if (schedule == "owner" and world > 1) else 1, transport="nccl")
+            step_obj = make_step(dom)
+            e, f, v = step_obj.evaluate()
+            torch.cuda.synchronize()
+            step_obj.check_status()
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
     barrier = (lambda: dist.barrier()) if dist is not None else None
     sampler.start()
