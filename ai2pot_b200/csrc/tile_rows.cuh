@@ -55,34 +55,34 @@ struct TileRows {
                                           int umax)
     {
         const int lim = 3 * (umax < TR_SLOTS ? umax : TR_SLOTS);
-        constexpr int NP = 32 * 3 * TR_SLOTS / NT, NI = 32 * TR_SLOTS / NT;
-        static_assert(32 * 3 * TR_SLOTS % NT == 0 && 32 * TR_SLOTS % NT == 0, "block size must divide the tile");
+        constexpr int TP = 32 * 3 * TR_SLOTS, TI = 32 * TR_SLOTS;           // elements of the two copies
+        constexpr int NP = (TP + NT - 1) / NT, NI = (TI + NT - 1) / NT;     // per thread
         T v[NP];
         int nj[NI], w[NI];
 #pragma unroll
         for (int k = 0; k < NI; k++) {
-            const int e = threadIdx.x + k * NT, a = e >> 5, j = e & 31;
-            nj[k] = j < nn[a] ? firstneigh[row[a] + j] : -1;
+            const int e = threadIdx.x + k * NT, a = (e >> 5) & 31, j = e & 31;
+            nj[k] = (e < TI && j < nn[a]) ? firstneigh[row[a] + j] : -1;
         }
 #pragma unroll
         for (int k = 0; k < NP; k++) {
-            const int e = threadIdx.x + k * NT, a = e / (3 * TR_SLOTS), o = e - a * (3 * TR_SLOTS);
-            v[k] = o < lim ? rcs[row[a] * 3 + o] : T(0);
+            const int e = threadIdx.x + k * NT, a = (e / (3 * TR_SLOTS)) & 31, o = e % (3 * TR_SLOTS);
+            v[k] = (e < TP && o < lim) ? rcs[row[a] * 3 + o] : T(0);
         }
 #pragma unroll
         for (int k = 0; k < NI; k++) {
-            const int e = threadIdx.x + k * NT, a = e >> 5;
+            const int e = threadIdx.x + k * NT, a = (e >> 5) & 31;
             w[k] = nj[k] >= 0 ? (nj[k] | (types[tbase[a] + nj[k]] << TR_TYPE_SHIFT)) : 0;
         }
 #pragma unroll
         for (int k = 0; k < NP; k++) {
-            const int e = threadIdx.x + k * NT, a = e / (3 * TR_SLOTS), o = e - a * (3 * TR_SLOTS);
-            pos[a * TR_RS + o] = v[k];
+            const int e = threadIdx.x + k * NT, a = e / (3 * TR_SLOTS), o = e % (3 * TR_SLOTS);
+            if (e < TP) pos[a * TR_RS + o] = v[k];
         }
 #pragma unroll
         for (int k = 0; k < NI; k++) {
             const int e = threadIdx.x + k * NT, a = e >> 5, j = e & 31;
-            idx[a * TR_IS + j] = w[k];
+            if (e < TI) idx[a * TR_IS + j] = w[k];
         }
     }
 };
