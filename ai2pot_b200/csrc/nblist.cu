@@ -301,46 +301,55 @@ __global__ void nb_setup_periodic_kernel(NbGrid host_grid, NbGrid *__restrict__ 
     }
 }
 
-// exclusive scan by one block (grids of up to 64 K bins): bin_start and cursor. The counters of SCAN_ITEMS rounds
-// of the block-wide scan are loaded together (coalesced, all loads in flight at once) and the results stored
-// together, so the rounds themselves run out of registers.
-constexpr int SCAN_ITEMS = 16;
+// exclusive scan by one block (grids of up to 64 K bins): bin_start and cursor. Chunks of SCAN_BLOCK * SCAN_ITEMS
+// counters: loaded along the array into shared memory, every thread scans SCAN_ITEMS consecutive counters by itself
+// (rows padded by one word, so the threads' rows start in different banks), ONE block-wide scan of the thread totals,
+// and the results leave along the array again.
+constexpr int SCAN_ITEMS = 8;
 __global__ void __launch_bounds__(SCAN_BLOCK) nb_scan_small_kernel(const NbGrid *__restrict__ gp, const int *__restrict__ in, int *__restrict__ out,
                                                                   int *__restrict__ cursor)
 {
-    __shared__ int ws[2][32];
+    __shared__ int buf[SCAN_BLOCK * (SCAN_ITEMS + 1)];
+    __shared__ int ws[32];
     const int total = gp->total;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     int carry = 0;      // every thread keeps the running total
     for (int base = 0; base <= total; base += SCAN_BLOCK * SCAN_ITEMS) {
-        int v[SCAN_ITEMS];
 #pragma unroll
         for (int k = 0; k < SCAN_ITEMS; k++) {
-            const int i = base + k * SCAN_BLOCK + threadIdx.x;
-            v[k] = i < total ? in[i] : 0;
+            const int e = k * SCAN_BLOCK + threadIdx.x, i = base + e;
+            buf[(e / SCAN_ITEMS) * (SCAN_ITEMS + 1) + e % SCAN_ITEMS] = i < total ? in[i] : 0;
         }
+        __syncthreads();
+        int v[SCAN_ITEMS], sum = 0;
 #pragma unroll
         for (int k = 0; k < SCAN_ITEMS; k++) {
-            int inc = v[k];
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) { int n = __shfl_up_sync(FULL_MASK, inc, o); if (lane >= o) inc += n; }
-            if (lane == 31) ws[k & 1][warp] = inc;
-            __syncthreads();
-            int w = ws[k & 1][lane];                 // every warp scans the 32 warp totals itself
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) { int n = __shfl_up_sync(FULL_MASK, w, o); if (lane >= o) w += n; }
-            const int before = __shfl_sync(FULL_MASK, w, max(warp - 1, 0));
-            const int all = __shfl_sync(FULL_MASK, w, 31);
-            const int excl = carry + inc - v[k] + (warp > 0 ? before : 0);
-            v[k] = excl;
-            carry += all;
+            v[k] = sum;                                         // exclusive within the thread
+            sum += buf[threadIdx.x * (SCAN_ITEMS + 1) + k];
         }
+        int inc = sum;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { int n = __shfl_up_sync(FULL_MASK, inc, o); if (lane >= o) inc += n; }
+        if (lane == 31) ws[warp] = inc;
+        __syncthreads();
+        int w = ws[lane];                                       // every warp scans the 32 warp totals itself
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { int n = __shfl_up_sync(FULL_MASK, w, o); if (lane >= o) w += n; }
+        const int before = __shfl_sync(FULL_MASK, w, max(warp - 1, 0));
+        const int all = __shfl_sync(FULL_MASK, w, 31);
+        const int off = carry + inc - sum + (warp > 0 ? before : 0);
+#pragma unroll
+        for (int k = 0; k < SCAN_ITEMS; k++) buf[threadIdx.x * (SCAN_ITEMS + 1) + k] = off + v[k];
+        carry += all;
+        __syncthreads();
 #pragma unroll
         for (int k = 0; k < SCAN_ITEMS; k++) {
-            const int i = base + k * SCAN_BLOCK + threadIdx.x;
-            if (i <= total) out[i] = v[k];
-            if (i < total) cursor[i] = v[k];
+            const int e = k * SCAN_BLOCK + threadIdx.x, i = base + e;
+            const int r = buf[(e / SCAN_ITEMS) * (SCAN_ITEMS + 1) + e % SCAN_ITEMS];
+            if (i <= total) out[i] = r;
+            if (i < total) cursor[i] = r;
         }
+        __syncthreads();     // the buffer and the warp totals are reused by the next chunk
     }
 }
 
