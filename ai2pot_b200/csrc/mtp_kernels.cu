@@ -445,9 +445,12 @@ __global__ void __launch_bounds__(MTP_CWARPS * 32, 1) mtp_contract_kernel(const 
 // stride 33 keeps those transposing accesses spread over the banks), the next tile's rows travelling in
 // registers while the current tile is processed.
 // Shared memory: M[nm][33], E[nm][33] (not for descriptors), headers, rows, seeds, worker tables.
+constexpr int MTP_SEG_EWARPS = 8;   // warps that sum the site energies of a tile
 template <typename T>
 struct SegSmem {
     T *M, *E, *seed, *wsc;     // wsc[s] = lin[s] / q[s]; seed[m] = sum of wsc over the scalars mapped to moment m
+    int *mapo;                 // element offset of the moment of scalar s
+    T *ep;                     // [MTP_SEG_EWARPS][33] partial site energies
     int4 *hdr;
     int2 *row;
     int *wseg, *wrow;
@@ -458,12 +461,13 @@ __host__ __device__ inline size_t seg_smem_layout(const MtpProgramDev &P, unsign
     size_t o = 0;
     auto take = [&](size_t bytes) { size_t r = o; o += (bytes + 15) & ~size_t(15); return r; };
     const size_t oM = take(sizeof(T) * (size_t)P.nm * MTP_SEG_LD);
-    // the adjoint array also holds the per-worker partial site energies before the adjoint phases: at least one row per worker
-    const size_t oE = MODE == MODE_DESC ? oM : take(sizeof(T) * (size_t)(P.nm > MTP_SEG_WORKERS ? P.nm : MTP_SEG_WORKERS) * MTP_SEG_LD);
+    const size_t oE = MODE == MODE_DESC ? oM : take(sizeof(T) * (size_t)P.nm * MTP_SEG_LD);
     const size_t oh = take(sizeof(int4) * (size_t)P.nseg);
     const size_t orow = take(sizeof(int2) * (size_t)P.nseg_rows);
     const size_t os = take(sizeof(T) * (size_t)P.nm);
     const size_t osc = take(sizeof(T) * (size_t)P.ns);
+    const size_t omo = take(sizeof(int) * (size_t)P.ns);
+    const size_t oep = take(MODE == MODE_DESC ? 0 : sizeof(T) * MTP_SEG_EWARPS * MTP_SEG_LD);
     const size_t ow = take(sizeof(int) * (size_t)(2 * P.nlev) * (MTP_SEG_WORKERS + 1));
     const size_t owr = take(sizeof(int) * (size_t)(2 * P.nlev) * MTP_SEG_WORKERS);
     if (out) {
@@ -471,6 +475,8 @@ __host__ __device__ inline size_t seg_smem_layout(const MtpProgramDev &P, unsign
         out->hdr = reinterpret_cast<int4 *>(base + oh); out->row = reinterpret_cast<int2 *>(base + orow);
         out->seed = reinterpret_cast<T *>(base + os); out->wsc = reinterpret_cast<T *>(base + osc);
         out->wseg = reinterpret_cast<int *>(base + ow); out->wrow = reinterpret_cast<int *>(base + owr);
+        out->mapo = reinterpret_cast<int *>(base + omo);
+        out->ep = reinterpret_cast<T *>(base + oep);
     }
     return o;
 }
@@ -509,23 +515,28 @@ __device__ __forceinline__ void sts_val(unsigned a, float v) { asm volatile("st.
 template <typename T, bool SEEDED>
 __device__ __forceinline__ void seg_phase(int h, int hend, unsigned hdr, unsigned rp, unsigned seed, unsigned xl, unsigned yl, unsigned dl)
 {
+    constexpr unsigned ES = (unsigned)sizeof(T);
     T dsum = T(0);
     for (; h < hend; h++) {
+        // a worker's rows follow one another across its segments, so the first two row records are requested together
+        // with the header (they are simply not used if the segment is shorter), and inside a segment the next pair is
+        // requested before the current pair's products are formed
         const int4 hd = lds_int4(hdr + 16u * (unsigned)h);
+        int2 r0 = lds_int2(rp), r1 = lds_int2(rp + 8u);
         const int n = hd.y & 0x3fffffff;
         T acc0 = T(0), acc1 = T(0);
         const unsigned rend = rp + 8u * (unsigned)n;
 #pragma unroll 1
-        for (; rp + 8u < rend; rp += 16u) {
-            const int2 r0 = lds_int2(rp), r1 = lds_int2(rp + 8u);
-            const T x0 = lds_val(xl + (unsigned)r0.x * (unsigned)sizeof(T), T()), y0 = lds_val(yl + (unsigned)r0.y * (unsigned)sizeof(T), T());
-            const T x1 = lds_val(xl + (unsigned)r1.x * (unsigned)sizeof(T), T()), y1 = lds_val(yl + (unsigned)r1.y * (unsigned)sizeof(T), T());
+        while (rp + 8u < rend) {
+            const T x0 = lds_val(xl + (unsigned)r0.x * ES, T()), y0 = lds_val(yl + (unsigned)r0.y * ES, T());
+            const T x1 = lds_val(xl + (unsigned)r1.x * ES, T()), y1 = lds_val(yl + (unsigned)r1.y * ES, T());
+            rp += 16u;
+            r0 = lds_int2(rp); r1 = lds_int2(rp + 8u);
             acc0 = fma(x0, y0, acc0);
             acc1 = fma(x1, y1, acc1);
         }
         if (rp < rend) {
-            const int2 r0 = lds_int2(rp);
-            acc0 = fma(lds_val(xl + (unsigned)r0.x * (unsigned)sizeof(T), T()), lds_val(yl + (unsigned)r0.y * (unsigned)sizeof(T), T()), acc0);
+            acc0 = fma(lds_val(xl + (unsigned)r0.x * ES, T()), lds_val(yl + (unsigned)r0.y * ES, T()), acc0);
             rp += 8u;
         }
         const T mult = (T)__hiloint2double(hd.w, hd.z);
@@ -533,8 +544,8 @@ __device__ __forceinline__ void seg_phase(int h, int hend, unsigned hdr, unsigne
         dsum = (hd.y & (1 << 30)) ? mult * acc : fma(mult, acc, dsum);
         if (hd.y < 0) {                                  // bit 31: last segment of the moment
             T out = dsum;
-            if (SEEDED) out += lds_val(seed + (unsigned)(hd.x / MTP_SEG_LD) * (unsigned)sizeof(T), T());
-            sts_val(dl + (unsigned)hd.x * (unsigned)sizeof(T), out);
+            if (SEEDED) out += lds_val(seed + (unsigned)(hd.x / MTP_SEG_LD) * ES, T());
+            sts_val(dl + (unsigned)hd.x * ES, out);
         }
     }
 }
@@ -562,9 +573,13 @@ __global__ void __launch_bounds__(MTP_SEG_WORKERS * 32, 1) mtp_contract_seg_kern
         // adjoint seeds lin[s] / q[s] (linearMtp.h:292-295); a moment may serve several scalars
         for (int s = threadIdx.x; s < P.ns; s += NT) {
             const T w = A.lin[s] / A.qs[s];
+            const int m = P.map[s];
             S.wsc[s] = w;
-            atomicAdd(S.seed + P.map[s], w);
+            S.mapo[s] = m * MTP_SEG_LD;
+            atomicAdd(S.seed + m, w);
         }
+    } else {
+        for (int s = threadIdx.x; s < P.ns; s += NT) S.mapo[s] = P.map[s] * MTP_SEG_LD;
     }
 
     // basic-moment rows of a tile: warp w fetches atom w, lanes run over the row; fetched one tile ahead
@@ -593,8 +608,10 @@ __global__ void __launch_bounds__(MTP_SEG_WORKERS * 32, 1) mtp_contract_seg_kern
         seg_phase<T, decltype(seeded)::value>(h, hend, a_hdr, a_row + 8u * (unsigned)S.wrow[p * MTP_SEG_WORKERS + warp], a_seed, xl, yl, dl);
     };
 
+    __syncthreads();         // tables staged
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-        __syncthreads();     // tables staged / the previous tile's adjoints written and its moments no longer read
+        // (no barrier here: the last adjoint phase ended with one, after which the moments are no longer read, and the
+        // adjoint array is not written again before the barrier that follows the product phases)
         if (can_prefetch) {
 #pragma unroll
             for (int k = 0; k < MTP_PREF; k++) {
@@ -612,53 +629,63 @@ __global__ void __launch_bounds__(MTP_SEG_WORKERS * 32, 1) mtp_contract_seg_kern
         }
         __syncthreads();
 
+        // per-atom bookkeeping (lane = atom of the tile): its loads are in flight during the product phases
+        const int t = tile * MTP_TILE + lane;
+        const bool valid = t < ntot;
+        int b = 0;
+        size_t slot = 0;
+        T ebias = T(0);
+        if (valid) {
+            b = find_structure(A.prefix, A.B, t);
+            slot = (size_t)b * A.npad + (t - A.prefix[b]);
+            if (MODE != MODE_DESC && warp == 0) {
+                const int *types = A.types + (size_t)b * (A.npad + A.nghost);
+                ebias = A.bias[types[A.bilist[slot]]];
+            }
+        }
+
         for (int p = 0; p < P.nlev; p++) {
             run_phase(p, std::false_type{}, ml, ml, ml);
             __syncthreads();
         }
 
-        // per-atom bookkeeping (lane = atom of the tile)
-        const int t = tile * MTP_TILE + lane;
-        const bool valid = t < ntot;
-        int b = 0;
-        size_t slot = 0;
-        if (valid) {
-            b = find_structure(A.prefix, A.B, t);
-            slot = (size_t)b * A.npad + (t - A.prefix[b]);
-        }
         if (MODE == MODE_DESC) {
             if (valid)
-                for (int s = warp; s < P.ns; s += MTP_SEG_WORKERS) A.desc[slot * P.ns + s] = S.M[P.map[s] * MTP_SEG_LD + lane];
+                for (int s = warp; s < P.ns; s += MTP_SEG_WORKERS) A.desc[slot * P.ns + s] = S.M[S.mapo[s] + lane];
+            __syncthreads();     // the moments are overwritten by the next tile
             continue;
         }
 
-        // site energies (linearMtp.h:281-289): partial sums per warp in the (still unused) adjoint array
-        T es = T(0);
-        for (int s = warp; s < P.ns; s += MTP_SEG_WORKERS) es = fma(S.wsc[s], S.M[P.map[s] * MTP_SEG_LD + lane], es);
-        S.E[warp * MTP_SEG_LD + lane] = es;
-        __syncthreads();
-        if (warp == 0) {
-            T e = T(0);
-#pragma unroll 8
-            for (int k = 0; k < MTP_SEG_WORKERS; k++) e += S.E[k * MTP_SEG_LD + lane];
-            if (valid) {
-                const int *types = A.types + (size_t)b * (A.npad + A.nghost);
-                e += A.bias[types[A.bilist[slot]]];
-            } else {
-                e = T(0);
+        // site energies (linearMtp.h:281-289) by the first MTP_SEG_EWARPS warps, which meet at a barrier of their own;
+        // the other warps go on to the adjoints (they read the moments and write the adjoint array only)
+        if (warp < MTP_SEG_EWARPS) {
+            T es = T(0);
+            for (int s = warp; s < P.ns; s += MTP_SEG_EWARPS) es = fma(S.wsc[s], S.M[S.mapo[s] + lane], es);
+            S.ep[warp * MTP_SEG_LD + lane] = es;
+            asm volatile("bar.sync 1, %0;" ::"n"(MTP_SEG_EWARPS * 32) : "memory");
+            if (warp == 0) {
+                T e = ebias;
+#pragma unroll
+                for (int k = 0; k < MTP_SEG_EWARPS; k++) e += S.ep[k * MTP_SEG_LD + lane];
+                if (!valid) e = T(0);
+                // one atomic per structure present in these 32 atoms
+                const int key = valid ? b : -1;
+                const int key0 = __shfl_sync(FULL_MASK, key, 0);
+                if (__all_sync(FULL_MASK, key == key0 || key < 0)) {      // one structure: a plain warp sum
+                    const T tot = warp_sum(e);
+                    if (lane == 0 && key0 >= 0) atomicAdd(A.etot + key0, tot);
+                } else {
+                    T tot = T(0);
+                    int leader = MTP_TILE;
+                    for (int k = 0; k < MTP_TILE; k++) {
+                        const T ek = __shfl_sync(FULL_MASK, e, k);
+                        const int bk = __shfl_sync(FULL_MASK, key, k);
+                        if (bk == key) { tot += ek; leader = min(leader, k); }
+                    }
+                    if (valid && lane == leader) atomicAdd(A.etot + b, tot);
+                }
             }
-            // one atomic per structure present in these 32 atoms
-            const int key = valid ? b : -1;
-            T tot = T(0);
-            int leader = MTP_TILE;
-            for (int k = 0; k < MTP_TILE; k++) {
-                const T ek = __shfl_sync(FULL_MASK, e, k);
-                const int bk = __shfl_sync(FULL_MASK, key, k);
-                if (bk == key) { tot += ek; leader = min(leader, k); }
-            }
-            if (valid && lane == leader) atomicAdd(A.etot + b, tot);
         }
-        __syncthreads();
         // moments whose adjoint is only their seed
         for (int i = warp; i < P.nseg_init; i += MTP_SEG_WORKERS) {
             const int m = P.seg_init[i];
