@@ -126,8 +126,7 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_fast_kernel(const Ne
 
     // block prologue: zero-padded tables, 1/q_scaler, 3-body factors, descriptor index map.
     // The tables [coefficients | W0 rows | b0 | w1] are one contiguous run of shared memory; every
-    // thread first issues all of its (independent) global loads, then stores, so the block pays
-    // one memory round trip per 24 * blockDim elements instead of one per element.
+    // thread first issues all of its (independent) global loads of the coefficients, then stores.
     {
         T qsv = T(1);
         if (NET && (int)threadIdx.x < A.nd) qsv = A.qs[threadIdx.x];
@@ -159,20 +158,40 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_fast_kernel(const Ne
             if (pn >= A.nneu) return T(0);
             return i < n2 ? A.b0[t * A.nneu + pn] : A.w1[t * A.nneu + pn];
         };
-        constexpr int U = 24;
-        for (int i0 = threadIdx.x; i0 < nall; i0 += U * blockDim.x) {
+        // coefficients: through registers (the radial pass of the first atom needs them at once)
+        constexpr int U = 8;
+        for (int i0 = threadIdx.x; i0 < n0; i0 += U * blockDim.x) {
             T v[U];
 #pragma unroll
             for (int u = 0; u < U; u++) {
                 const int i = i0 + u * blockDim.x;
-                v[u] = i < nall ? load(i) : T(0);
+                v[u] = i < n0 ? load(i) : T(0);
             }
 #pragma unroll
             for (int u = 0; u < U; u++) {
                 const int i = i0 + u * blockDim.x;
-                if (i < nall) ctab_s[i] = v[u];
+                if (i < n0) ctab_s[i] = v[u];
             }
         }
+        // network tables: asynchronous copies straight into shared memory, awaited before the first atom's network
+        // (they travel during its radial and angular passes); padding entries are plain zero stores
+        for (int i = n0 + threadIdx.x; i < nall; i += blockDim.x) {
+            const T *src = nullptr;
+            if (i < n1) {
+                const int row = (i - n0) / NDP, k = (i - n0) % NDP;
+                int t, pn;
+                split(row, t, pn);
+                if (k < A.nd && pn < A.nneu) src = A.w0 + ((size_t)t * A.nneu + pn) * A.nd + k;
+            } else {
+                const int row = i < n2 ? i - n1 : i - n2;
+                int t, pn;
+                split(row, t, pn);
+                if (pn < A.nneu) src = (i < n2 ? A.b0 : A.w1) + t * A.nneu + pn;
+            }
+            if (src) __pipeline_memcpy_async(ctab_s + i, src, sizeof(T));
+            else ctab_s[i] = T(0);
+        }
+        __pipeline_commit();
         if (NET && threadIdx.x < NDP) iqs[threadIdx.x] = (int)threadIdx.x < A.nd ? T(1) / qsv : T(0);
     }
     if (threadIdx.x < NEP_NLM) {
@@ -368,6 +387,10 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_fast_kernel(const Ne
             __syncwarp(gmask);
         } else {
         // network on the scaled descriptors; rows and vectors are zero-padded to NDP
+        if (it == 0) {      // the network tables requested in the prologue have to be there now
+            __pipeline_wait_prior(0);
+            __syncthreads();
+        }
         for (int k = sub; k < A.nd; k += NEP_GROUP) Eq[k] = q[k] * iqs[k];
         __syncwarp(gmask);
         T es = T(0);

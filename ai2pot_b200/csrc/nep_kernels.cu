@@ -15,6 +15,7 @@
 //      angular g = sum_mu [ g'_mu P u + g_mu/r (G - (u.G) u) ],  P = sum_lm e_lm B_lm(u),
 //      G = sum_lm e_lm grad B_lm(u);  F_i += g, F_j -= g, V -= g (x) r
 #include "common.cuh"
+#include <cuda_pipeline.h>
 
 #include <cstring>
 #include <algorithm>
