@@ -17,6 +17,7 @@
 // all three kernels read and write in full 256-byte rows.
 // The kernels are compiled per "signature" = the highest monomial degree of every radial function
 // (non-increasing, at most four functions); other tables take the warp-per-atom kernels.
+#include <cuda_pipeline.h>
 #include "mtp_device.cuh"
 #include "tile_rows.cuh"
 
@@ -82,6 +83,9 @@ struct KSig {
 // pairs at the same offset, so consecutive rows are shifted by 16 bytes (4 banks) against one another.
 template <typename SIG, int CSP>
 __host__ __device__ constexpr int cf_stride() { return SIG::NMUS * CSP + 2; }
+// elements of the whole table, rounded so that what follows it in shared memory starts on a 16-byte boundary
+template <typename SIG, int CSP>
+__host__ __device__ constexpr int cf_elems(int ntypes) { return (ntypes * ntypes * cf_stride<SIG, CSP>() + 3) & ~3; }
 
 // One neighbour of this lane's atom: geometry and the radial functions of every mu (registers). The three steps
 // are separate so that the loads of several neighbours can be in flight together.
@@ -167,8 +171,12 @@ struct TileAtom {
         b = 0; ci = 0; nn = 0; ti = 0; slot = 0;
         types_b = A.types;
         if (valid) {
-            b = find_structure(A.prefix, A.B, t);
-            slot = (size_t)b * A.npad + (t - A.prefix[b]);
+            if (A.B > 1) {      // one structure: atom t is slot t, no look-ups
+                b = find_structure(A.prefix, A.B, t);
+                slot = (size_t)b * A.npad + (t - A.prefix[b]);
+            } else {
+                slot = (size_t)t;
+            }
             types_b = A.types + (size_t)b * (A.npad + A.nghost);
             ci = A.bilist[slot];
             nn = min(A.numneigh[slot], A.umax);
@@ -196,7 +204,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32, DERIV ? 2 : 3) mtp_fwd_atoms_ke
     constexpr int NV = 3 + SIG::NMUS + (DERIV ? SIG::NMUS + 3 : 0);   // u, f [, a, q]
     constexpr int KD = SIG::KD;
     T *cf = reinterpret_cast<T *>(smem_raw);
-    T *st = cf + A.ntypes * A.ntypes * cf_stride<SIG, CSP>();
+    T *st = cf + cf_elems<SIG, CSP>(A.ntypes);
     TileRows<T> tr;
     tr.bind(reinterpret_cast<unsigned char *>(st + (size_t)AT_CH * NV * 32));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -314,7 +322,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32, 3) mtp_force_atoms_kernel(const
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int KD = SIG::KD;
     T *cf = reinterpret_cast<T *>(smem_raw);
-    T *Es = cf + A.ntypes * A.ntypes * cf_stride<SIG, CSP>();
+    T *Es = cf + cf_elems<SIG, CSP>(A.ntypes);
     TileRows<T> tr;
     tr.bind(reinterpret_cast<unsigned char *>(Es + (size_t)SIG::NDENSE * 32));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -323,6 +331,14 @@ __global__ void __launch_bounds__(AT_WARPS * 32, 3) mtp_force_atoms_kernel(const
     const int ntiles = (ntot + MTP_TILE - 1) / MTP_TILE;
 
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        if (tile != (int)blockIdx.x) __syncthreads();     // the previous tile's adjoints are no longer read
+        {   // The contraction leaves the adjoints of a tile in dense monomial order, [dense][32 atoms] in one piece: they are
+            // requested here with asynchronous 16-byte copies and awaited only before the neighbour loop.
+            const T *ein = A.Eb + (size_t)tile * A.ndp * MTP_TILE;
+            constexpr int CH = 16 / (int)sizeof(T);
+            for (int c = threadIdx.x; c < SIG::NDENSE * 32 / CH; c += AT_WARPS * 32) __pipeline_memcpy_async(Es + c * CH, ein + c * CH, 16);
+            __pipeline_commit();
+        }
         TileAtom<T> at;
         at.set(A, tile * MTP_TILE + lane, ntot);
         const int nmax = warp_max_int(at.nn);
@@ -330,15 +346,9 @@ __global__ void __launch_bounds__(AT_WARPS * 32, 3) mtp_force_atoms_kernel(const
         T *frc = A.force + (size_t)at.b * (A.npad + A.nghost) * 3;
         __syncthreads();     // the previous tile's adjoints and rows are no longer read
         if (warp == 0) tr.describe(lane, row, (size_t)(at.types_b - A.types), at.nn);
-        {
-            const T *ein = A.Eb + (size_t)tile * A.nbp * MTP_TILE + lane;
-            for (int d = warp; d < SIG::NDENSE; d += AT_WARPS) {
-                const int r = P.dense_basic[d];
-                Es[d * 32 + lane] = r >= 0 ? ein[(size_t)r * MTP_TILE] : T(0);
-            }
-        }
         __syncthreads();
         tr.template stage<AT_WARPS * 32>(A.rcs, A.firstneigh, A.types, A.umax);
+        __pipeline_wait_prior(0);     // the adjoints requested at the top of the tile
         __syncthreads();
 
         T fcx = T(0), fcy = T(0), fcz = T(0);
@@ -473,7 +483,7 @@ bool mtp_atoms_supported(const MtpProgramDev &P, int ntypes, int cs, size_t elem
 template <typename T, typename SIG, bool DERIV>
 static int launch_fwd_atoms(const MtpProgramDev &P, const MtpArgs<T> &A, const LossArgs<T> &L, cudaStream_t st)
 {
-    const size_t ncf = (size_t)A.ntypes * A.ntypes * cf_stride<SIG, AT_CSP>();
+    const size_t ncf = (size_t)cf_elems<SIG, AT_CSP>(A.ntypes);
     const size_t smem = sizeof(T) * (ncf + (size_t)AT_CH * (3 + SIG::NMUS + (DERIV ? SIG::NMUS + 3 : 0)) * 32) + tile_rows_bytes<T>();
     auto kern = mtp_fwd_atoms_kernel<T, SIG, AT_CSP, DERIV>;
     static KernelSetup setup;
@@ -490,7 +500,7 @@ static int launch_fwd_atoms(const MtpProgramDev &P, const MtpArgs<T> &A, const L
 template <typename T, int MODE, typename SIG>
 static int launch_force_atoms(const MtpProgramDev &P, const MtpArgs<T> &A, cudaStream_t st)
 {
-    const size_t ncf = (size_t)A.ntypes * A.ntypes * cf_stride<SIG, AT_CSP>();
+    const size_t ncf = (size_t)cf_elems<SIG, AT_CSP>(A.ntypes);
     const size_t smem = sizeof(T) * (ncf + (size_t)SIG::NDENSE * 32) + tile_rows_bytes<T>();
     auto kern = mtp_force_atoms_kernel<T, MODE, SIG, AT_CSP>;
     static KernelSetup setup;

@@ -224,7 +224,9 @@ static inline MtpWs mtp_ws_layout(const MtpProgramDev &P, int B, int npad, int n
     L.cpad = up256(((size_t)(B > 0 ? B : 0) + 1) * sizeof(int));
     L.mb = L.cpad + up256((size_t)ntypes * ntypes * P.nmus * 16 * elem);
     L.eb = L.mb + up256(atoms * nbasic_pad(P) * elem);
-    L.total = L.eb + up256(atoms * nbasic_pad(P) * elem);
+    // the adjoints of a tile may be kept in dense monomial order (ndense >= basic moments)
+    const size_t erow = (size_t)(ndense_pad(P) > nbasic_pad(P) ? ndense_pad(P) : nbasic_pad(P));
+    L.total = L.eb + up256(atoms * erow * elem);
     return L;
 }
 

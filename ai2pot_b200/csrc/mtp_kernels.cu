@@ -451,6 +451,7 @@ struct SegSmem {
     T *M, *E, *seed, *wsc;     // wsc[s] = lin[s] / q[s]; seed[m] = sum of wsc over the scalars mapped to moment m
     int *mapo;                 // element offset of the moment of scalar s
     T *ep;                     // [MTP_SEG_EWARPS][33] partial site energies
+    int *db;                   // [ndense] element offset of the basic moment of dense index d (-1: none)
     int4 *hdr;
     int2 *row;
     int *wseg, *wrow;
@@ -468,6 +469,7 @@ __host__ __device__ inline size_t seg_smem_layout(const MtpProgramDev &P, unsign
     const size_t osc = take(sizeof(T) * (size_t)P.ns);
     const size_t omo = take(sizeof(int) * (size_t)P.ns);
     const size_t oep = take(MODE == MODE_DESC ? 0 : sizeof(T) * MTP_SEG_EWARPS * MTP_SEG_LD);
+    const size_t odb = take(MODE == MODE_DESC ? 0 : sizeof(int) * (size_t)P.ndense);
     const size_t ow = take(sizeof(int) * (size_t)(2 * P.nlev) * (MTP_SEG_WORKERS + 1));
     const size_t owr = take(sizeof(int) * (size_t)(2 * P.nlev) * MTP_SEG_WORKERS);
     if (out) {
@@ -477,6 +479,7 @@ __host__ __device__ inline size_t seg_smem_layout(const MtpProgramDev &P, unsign
         out->wseg = reinterpret_cast<int *>(base + ow); out->wrow = reinterpret_cast<int *>(base + owr);
         out->mapo = reinterpret_cast<int *>(base + omo);
         out->ep = reinterpret_cast<T *>(base + oep);
+        out->db = reinterpret_cast<int *>(base + odb);
     }
     return o;
 }
@@ -577,6 +580,10 @@ __global__ void __launch_bounds__(MTP_SEG_WORKERS * 32, 1) mtp_contract_seg_kern
             S.wsc[s] = w;
             S.mapo[s] = m * MTP_SEG_LD;
             atomicAdd(S.seed + m, w);
+        }
+        for (int d = threadIdx.x; d < P.ndense; d += NT) {
+            const int r = P.dense_basic[d];
+            S.db[d] = r >= 0 ? r * MTP_SEG_LD : -1;
         }
     } else {
         for (int s = threadIdx.x; s < P.ns; s += NT) S.mapo[s] = P.map[s] * MTP_SEG_LD;
@@ -699,9 +706,12 @@ __global__ void __launch_bounds__(MTP_SEG_WORKERS * 32, 1) mtp_contract_seg_kern
             __syncthreads();
         }
         // adjoints of the basic moments: whole rows of the tile, or back to per-atom rows (warp w writes atom w)
-        if (A.tiled) {
-            T *dstp = A.Eb + (size_t)tile * A.nbp * MTP_TILE + lane;
-            for (int i = warp; i < P.nb; i += MTP_SEG_WORKERS) dstp[(size_t)i * MTP_TILE] = S.E[i * MTP_SEG_LD + lane];
+        if (A.tiled) {      // in dense monomial order, the order the force kernel evaluates its polynomials in
+            T *dstp = A.Eb + (size_t)tile * A.ndp * MTP_TILE + lane;
+            for (int d = warp; d < P.ndense; d += MTP_SEG_WORKERS) {
+                const int o = S.db[d];
+                dstp[(size_t)d * MTP_TILE] = o >= 0 ? S.E[o + lane] : T(0);
+            }
         } else {
             const int t = tile * MTP_TILE + warp;
             if (t < ntot) {
