@@ -212,17 +212,28 @@ __global__ void __launch_bounds__(AT_WARPS * 32, DERIV ? 2 : 3) mtp_fwd_atoms_ke
     const int ntot = A.prefix[A.B];
     const int ntiles = (ntot + MTP_TILE - 1) / MTP_TILE;
 
+    const bool single = A.B == 1;      // one structure: a tile's rows are known from its index alone
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        if (single) {
+            if (tile != (int)blockIdx.x) __syncthreads();     // the previous tile's rows are no longer read
+            tr.template request<AT_WARPS * 32>(A.rcs, A.firstneigh, A.umax, (size_t)tile * MTP_TILE, (size_t)A.npad);
+        }
         TileAtom<T> at;
         at.set(A, tile * MTP_TILE + lane, ntot);
         const int nmax = warp_max_int(at.nn);      // the same in every warp of the block
         const size_t row = at.slot * A.umax;
         const int nstruct = at.valid ? A.binum[at.b] : 1;
         T *out = (DERIV ? L.Db : A.Mb) + (size_t)tile * A.nbp * MTP_TILE + lane;
-        __syncthreads();     // the previous tile's rows are no longer read
-        if (warp == 0) tr.describe(lane, row, (size_t)(at.types_b - A.types), at.nn);
-        __syncthreads();
-        tr.template stage<AT_WARPS * 32>(A.rcs, A.firstneigh, A.types, A.umax);
+        if (single) {
+            __pipeline_wait_prior(0);
+            __syncthreads();     // every thread's copies have arrived
+            tr.template complete<AT_WARPS * 32>(A.types, A.npad + A.nghost);
+        } else {
+            __syncthreads();     // the previous tile's rows are no longer read
+            if (warp == 0) tr.describe(lane, row, (size_t)(at.types_b - A.types), at.nn);
+            __syncthreads();
+            tr.template stage<AT_WARPS * 32>(A.rcs, A.firstneigh, A.types, A.umax);
+        }
 
         auto body = [&](auto gg) {
             constexpr int G = decltype(gg)::value;
@@ -329,9 +340,10 @@ __global__ void __launch_bounds__(AT_WARPS * 32, 3) mtp_force_atoms_kernel(const
     stage_coefficients<T, SIG, CSP>(A, cf);
     const int ntot = A.prefix[A.B];
     const int ntiles = (ntot + MTP_TILE - 1) / MTP_TILE;
+    const bool single = A.B == 1;      // one structure: a tile's rows are known from its index alone
 
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-        if (tile != (int)blockIdx.x) __syncthreads();     // the previous tile's adjoints are no longer read
+        if (tile != (int)blockIdx.x) __syncthreads();     // the previous tile's adjoints and rows are no longer read
         {   // The contraction leaves the adjoints of a tile in dense monomial order, [dense][32 atoms] in one piece: they are
             // requested here with asynchronous 16-byte copies and awaited only before the neighbour loop.
             const T *ein = A.Eb + (size_t)tile * A.ndp * MTP_TILE;
@@ -339,16 +351,23 @@ __global__ void __launch_bounds__(AT_WARPS * 32, 3) mtp_force_atoms_kernel(const
             for (int c = threadIdx.x; c < SIG::NDENSE * 32 / CH; c += AT_WARPS * 32) __pipeline_memcpy_async(Es + c * CH, ein + c * CH, 16);
             __pipeline_commit();
         }
+        if (single) tr.template request<AT_WARPS * 32>(A.rcs, A.firstneigh, A.umax, (size_t)tile * MTP_TILE, (size_t)A.npad);
         TileAtom<T> at;
         at.set(A, tile * MTP_TILE + lane, ntot);
         const int nmax = warp_max_int(at.nn);
         const size_t row = at.slot * A.umax;
         T *frc = A.force + (size_t)at.b * (A.npad + A.nghost) * 3;
-        __syncthreads();     // the previous tile's adjoints and rows are no longer read
-        if (warp == 0) tr.describe(lane, row, (size_t)(at.types_b - A.types), at.nn);
-        __syncthreads();
-        tr.template stage<AT_WARPS * 32>(A.rcs, A.firstneigh, A.types, A.umax);
-        __pipeline_wait_prior(0);     // the adjoints requested at the top of the tile
+        if (single) {
+            __pipeline_wait_prior(0);     // the adjoints and the rows requested at the top of the tile
+            __syncthreads();
+            tr.template complete<AT_WARPS * 32>(A.types, A.npad + A.nghost);
+        } else {
+            __syncthreads();     // the previous tile's rows are no longer read
+            if (warp == 0) tr.describe(lane, row, (size_t)(at.types_b - A.types), at.nn);
+            __syncthreads();
+            tr.template stage<AT_WARPS * 32>(A.rcs, A.firstneigh, A.types, A.umax);
+            __pipeline_wait_prior(0);     // the adjoints requested at the top of the tile
+        }
         __syncthreads();
 
         T fcx = T(0), fcy = T(0), fcz = T(0);

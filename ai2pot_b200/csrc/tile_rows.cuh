@@ -9,6 +9,7 @@
 //   idx[atom][TR_IS]   neighbour index | neighbour type << 26 (0 for empty slots)
 // Slots beyond TR_SLOTS (rows longer than 32 neighbours) are read from global memory by the caller.
 #pragma once
+#include <cuda_pipeline.h>
 #include "common.cuh"
 
 namespace ai2b {
@@ -22,7 +23,7 @@ constexpr int TR_INDEX_MASK = (1 << TR_TYPE_SHIFT) - 1;
 template <typename T>
 __host__ __device__ constexpr size_t tile_rows_bytes()
 {
-    return ((sizeof(T) * 32 * TR_RS + 15) & ~size_t(15)) + sizeof(int) * 32 * TR_IS + 32 * (2 * sizeof(long long) + sizeof(int)) + 16;
+    return ((sizeof(T) * 32 * TR_RS + 15) & ~size_t(15)) + 2 * sizeof(int) * 32 * TR_IS + 32 * (2 * sizeof(long long) + sizeof(int)) + 16;
 }
 
 template <typename T>
@@ -32,6 +33,7 @@ struct TileRows {
     long long *row;     // [32] first slot of the atom's row in the neighbour arrays (atom slot * umax)
     long long *tbase;   // [32] offset of the atom's structure in the type array
     int *nn;            // [32] neighbours of the atom (clamped to umax)
+    int *raw;           // [32][TR_IS] neighbour indices as copied, before their types are looked up (single-structure path)
 
     __device__ __forceinline__ void bind(unsigned char *mem)
     {
@@ -41,6 +43,7 @@ struct TileRows {
         tbase = row + 32;
         idx = reinterpret_cast<int *>(tbase + 32);
         nn = idx + 32 * TR_IS;
+        raw = nn + 32;
     }
     // one warp, lane = atom of the tile
     __device__ __forceinline__ void describe(int lane, size_t first_slot, size_t types_offset, int count)
@@ -83,6 +86,46 @@ struct TileRows {
         for (int k = 0; k < NI; k++) {
             const int e = threadIdx.x + k * NT, a = e >> 5, j = e & 31;
             if (e < TI) idx[a * TR_IS + j] = w[k];
+        }
+    }
+
+    // Single structure: atom a of the tile is slot first_slot + a, so its rows can be requested before anything about the
+    // atoms has been looked up. request() issues asynchronous copies straight into shared memory (no registers are held
+    // while the caller does its look-ups); complete(), after the caller's __pipeline_wait_prior(0) and a barrier, looks up
+    // the neighbours' types. Slots whose index is outside [0, ids) are empty (rows are padded with -1). Both are called
+    // by all NT threads; a barrier must follow complete().
+    template <int NT>
+    __device__ __forceinline__ void request(const T *__restrict__ rcs, const int *__restrict__ firstneigh, int umax, size_t first_slot,
+                                            size_t nslots)
+    {
+        const int lim = umax < TR_SLOTS ? umax : TR_SLOTS;
+        for (int e = threadIdx.x; e < 32 * 3 * TR_SLOTS; e += NT) {
+            const int a = e / (3 * TR_SLOTS), o = e % (3 * TR_SLOTS);
+            if (o < 3 * lim && first_slot + a < nslots) __pipeline_memcpy_async(pos + a * TR_RS + o, rcs + (first_slot + a) * umax * 3 + o, sizeof(T));
+        }
+        for (int e = threadIdx.x; e < 32 * TR_SLOTS; e += NT) {
+            const int a = e >> 5, j = e & 31;
+            if (j < lim && first_slot + a < nslots) __pipeline_memcpy_async(raw + a * TR_IS + j, firstneigh + (first_slot + a) * umax + j, sizeof(int));
+            else raw[a * TR_IS + j] = -1;
+        }
+        __pipeline_commit();
+    }
+    template <int NT>
+    __device__ __forceinline__ void complete(const int *__restrict__ types, int ids)
+    {
+        constexpr int NI = (32 * TR_SLOTS + NT - 1) / NT;
+        int nj[NI], w[NI];
+#pragma unroll
+        for (int k = 0; k < NI; k++) {
+            const int e = threadIdx.x + k * NT;
+            nj[k] = e < 32 * TR_SLOTS ? raw[(e >> 5) * TR_IS + (e & 31)] : -1;
+        }
+#pragma unroll
+        for (int k = 0; k < NI; k++) w[k] = (nj[k] >= 0 && nj[k] < ids) ? (nj[k] | (types[nj[k]] << TR_TYPE_SHIFT)) : 0;
+#pragma unroll
+        for (int k = 0; k < NI; k++) {
+            const int e = threadIdx.x + k * NT;
+            if (e < 32 * TR_SLOTS) idx[(e >> 5) * TR_IS + (e & 31)] = w[k];
         }
     }
 };
