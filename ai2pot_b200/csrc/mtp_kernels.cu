@@ -616,6 +616,13 @@ __global__ void __launch_bounds__(MTP_SEG_WORKERS * 32, 1) mtp_contract_seg_kern
     };
 
     __syncthreads();         // tables staged
+    if (MODE != MODE_DESC) {
+        // moments no product reads: their adjoint is their seed for every atom of every tile, written once
+        for (int i = warp; i < P.nseg_init; i += MTP_SEG_WORKERS) {
+            const int m = P.seg_init[i];
+            S.E[m * MTP_SEG_LD + lane] = S.seed[m];
+        }
+    }
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
         // (no barrier here: the last adjoint phase ended with one, after which the moments are no longer read, and the
         // adjoint array is not written again before the barrier that follows the product phases)
@@ -653,6 +660,9 @@ __global__ void __launch_bounds__(MTP_SEG_WORKERS * 32, 1) mtp_contract_seg_kern
 
         for (int p = 0; p < P.nlev; p++) {
             run_phase(p, std::false_type{}, ml, ml, ml);
+            // The sources of the deepest adjoint level feed only products of the last level, whose adjoints are their
+            // seeds: that level reads nothing the last product level writes and follows it without a barrier.
+            if (MODE != MODE_DESC && p == P.nlev - 1) run_phase(P.nlev, std::true_type{}, el, ml, el);
             __syncthreads();
         }
 
@@ -693,18 +703,12 @@ __global__ void __launch_bounds__(MTP_SEG_WORKERS * 32, 1) mtp_contract_seg_kern
                 }
             }
         }
-        // moments whose adjoint is only their seed
-        for (int i = warp; i < P.nseg_init; i += MTP_SEG_WORKERS) {
-            const int m = P.seg_init[i];
-            S.E[m * MTP_SEG_LD + lane] = S.seed[m];
-        }
-        __syncthreads();
-
-        // adjoints, deepest sources first: E[src] = seed + sum mult E[dst] M[other]
-        for (int p = P.nlev; p < 2 * P.nlev; p++) {
+        // the other adjoint levels, deepest sources first: E[src] = seed + sum mult E[dst] M[other]
+        for (int p = P.nlev + 1; p < 2 * P.nlev; p++) {
             run_phase(p, std::true_type{}, el, ml, el);
             __syncthreads();
         }
+        if (P.nlev < 2) __syncthreads();     // the energy warps still read the moments the next tile overwrites
         // adjoints of the basic moments: whole rows of the tile, or back to per-atom rows (warp w writes atom w)
         if (A.tiled) {      // in dense monomial order, the order the force kernel evaluates its polynomials in
             T *dstp = A.Eb + (size_t)tile * A.ndp * MTP_TILE + lane;
