@@ -112,6 +112,11 @@ def test_properties_full_size():
     # second run is bit-for-bit repeatable in energy up to atomic ordering
     e2, f2, v2 = capi.mtp_efv(prog, md, nbd)
     assert util.relerr(e2.cpu().numpy(), e) < 1e-12 and util.relerr(f2.cpu().numpy(), f) < 1e-12
+    # outputs are overwritten, whatever they held (the set-up launch zeroes them: there are no memsets)
+    dirty = tuple(torch.full_like(x, float("nan")) for x in (e2, f2, v2))
+    e3, f3, v3 = capi.mtp_efv(prog, md, nbd, out=dirty)
+    assert util.relerr(e3.cpu().numpy(), e) < 1e-12 and util.relerr(f3.cpu().numpy(), f) < 1e-12
+    assert util.relerr(v3.cpu().numpy(), v) < 1e-12
 
 
 def test_errors():

@@ -142,9 +142,14 @@ def test_ragged_batch(checkers):
         lists.append((nn, fn, rc, ty))
     nb = synth.pad_batch(lists, 3, 160)
     model = synth.nep_model(3, rng)
-    (e, f, v), *_ = _run(model, nb)
+    (e, f, v), md, nbd = _run(model, nb)
     er, fr, vr = chk.nep_efv(model, nb)
     assert util.relerr(e, er) < 1e-5 and util.relerr(f, fr) < 1e-5 and util.relerr(v, vr) < 1e-5
+    # outputs are overwritten, whatever they held (one zeroing launch ahead of the kernel, no memsets)
+    e0, f0, v0 = capi.nep_efv(md, nbd)
+    dirty = tuple(torch.full_like(x, float("nan")) for x in (e0, f0, v0))
+    e3, f3, v3 = capi.nep_efv(md, nbd, out=dirty)
+    assert util.relerr(e3.cpu().numpy(), er) < 1e-5 and util.relerr(f3.cpu().numpy(), fr) < 1e-5 and util.relerr(v3.cpu().numpy(), vr) < 1e-5
 
 
 def test_g4_full_size_properties():
