@@ -446,11 +446,20 @@ __global__ void __launch_bounds__(AT_WARPS * 32, 3) mtp_force_atoms_kernel(const
             // one atomic per component when the 32 atoms belong to one structure, else one per atom
             const int b0 = __shfl_sync(FULL_MASK, at.b, 0);
             const bool uniform = __all_sync(FULL_MASK, !at.valid || at.b == b0);
-            if (uniform) {
+            if (uniform) {      // (the same decision in every warp of the block: they share the tile's atoms)
+                // the block's four partial sums are combined first: a quarter of the atomics on these nine addresses
+                __shared__ T vred[AT_WARPS][9];
 #pragma unroll
                 for (int k = 0; k < 9; k++) {
                     const T s = warp_sum(vir[k]);
-                    if (lane == 0) atomicAdd(A.virial + 9 * b0 + k, s);
+                    if (lane == 0) vred[warp][k] = s;
+                }
+                __syncthreads();
+                if (threadIdx.x < 9) {
+                    T s = T(0);
+#pragma unroll
+                    for (int w = 0; w < AT_WARPS; w++) s += vred[w][threadIdx.x];
+                    atomicAdd(A.virial + 9 * b0 + threadIdx.x, s);
                 }
             } else if (at.valid && warp < at.nn) {
 #pragma unroll
