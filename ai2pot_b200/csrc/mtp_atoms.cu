@@ -208,8 +208,15 @@ __global__ void __launch_bounds__(AT_WARPS * 32, DERIV ? 2 : 3) mtp_fwd_atoms_ke
     TileRows<T> tr;
     tr.bind(reinterpret_cast<unsigned char *>(st + (size_t)AT_CH * NV * 32));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (!DERIV && A.zero_outputs == 2) {      // no set-up launch: this first kernel of the call zeroes the outputs
+        const size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x, step = (size_t)gridDim.x * blockDim.x;
+        const size_t nf = 3 * (size_t)A.B * (A.npad + A.nghost);
+        for (size_t i = i0; i < nf; i += step) A.force[i] = T(0);
+        if (i0 < (size_t)A.B) A.etot[i0] = T(0);
+        if (A.virial && i0 < 9 * (size_t)A.B) A.virial[i0] = T(0);
+    }
     stage_coefficients<T, SIG, CSP>(A, cf);
-    const int ntot = A.prefix[A.B];
+    const int ntot = total_atoms(A);
     const int ntiles = (ntot + MTP_TILE - 1) / MTP_TILE;
 
     const bool single = A.B == 1;      // one structure: a tile's rows are known from its index alone
@@ -338,7 +345,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32, 3) mtp_force_atoms_kernel(const
     tr.bind(reinterpret_cast<unsigned char *>(Es + (size_t)SIG::NDENSE * 32));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     stage_coefficients<T, SIG, CSP>(A, cf);
-    const int ntot = A.prefix[A.B];
+    const int ntot = total_atoms(A);
     const int ntiles = (ntot + MTP_TILE - 1) / MTP_TILE;
     const bool single = A.B == 1;      // one structure: a tile's rows are known from its index alone
 
@@ -383,11 +390,13 @@ __global__ void __launch_bounds__(AT_WARPS * 32, 3) mtp_force_atoms_kernel(const
             T X[KD + 1], Y[KD + 1], Z[KD + 1], dX[KD + 1], dY[KD + 1], dZ[KD + 1];
             X[0] = Y[0] = Z[0] = T(1);
             dX[0] = dY[0] = dZ[0] = T(0);
+            if constexpr (KD >= 1) { X[1] = pe.ux; Y[1] = pe.uy; Z[1] = pe.uz; }
 #pragma unroll
-            for (int k = 1; k <= KD; k++) {
-                X[k] = X[k - 1] * pe.ux; Y[k] = Y[k - 1] * pe.uy; Z[k] = Z[k - 1] * pe.uz;
-                dX[k] = T(k) * X[k - 1]; dY[k] = T(k) * Y[k - 1]; dZ[k] = T(k) * Z[k - 1];
+            for (int k = 2; k <= KD; k++) {      // u^k = u^(k/2) u^(k - k/2): short chains of dependent products
+                X[k] = X[k / 2] * X[k - k / 2]; Y[k] = Y[k / 2] * Y[k - k / 2]; Z[k] = Z[k / 2] * Z[k - k / 2];
             }
+#pragma unroll
+            for (int k = 1; k <= KD; k++) { dX[k] = T(k) * X[k - 1]; dY[k] = T(k) * Y[k - 1]; dZ[k] = T(k) * Z[k - 1]; }
             T gx = T(0), gy = T(0), gz = T(0);
             static_for<0, SIG::NMUS>([&](auto mm) {
                 constexpr int mu = decltype(mm)::value;

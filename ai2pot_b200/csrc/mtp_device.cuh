@@ -22,7 +22,7 @@ struct MtpArgs {
     int B, npad, ntypes, umax, nghost, cs, ndp, nbp;
     T scaling, rmax, rmin;
     int tiled = 0;
-    int zero_outputs = 0;   // etot, force and virial are zeroed by the set-up launch
+    int zero_outputs = 0;   // 1: etot, force and virial are zeroed by the set-up launch; 2: by the forward kernel (no set-up launch)
 };
 
 // Inputs and outputs of the loss-gradient path (mtp_loss.cu).
@@ -144,6 +144,10 @@ static const T *mtp_prepare(const int *binum, int B, int *prefix, const T *coeff
     mtp_prep_kernel<T><<<1 + pad_blocks + (unsigned)zb, 256, 0, st>>>(binum, B, prefix, coeffs, cpad, rows, cs, csp, pad_blocks, Z);
     return pad ? cpad : coeffs;
 }
+
+// Atoms of the call. A single structure needs no offset table (the set-up launch that writes it may then be left out).
+template <typename T>
+__device__ __forceinline__ int total_atoms(const MtpArgs<T> &A) { return A.B == 1 ? A.binum[0] : A.prefix[A.B]; }
 
 // structure index of flat atom t: largest b with prefix[b] <= t
 __device__ __forceinline__ int find_structure(const int *__restrict__ prefix, int B, int t)

@@ -561,7 +561,7 @@ __global__ void __launch_bounds__(MTP_SEG_WORKERS * 32, 1) mtp_contract_seg_kern
     SegSmem<T> S;
     seg_smem_layout<T, MODE>(P, smem_raw, &S);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int ntot = A.prefix[A.B];
+    const int ntot = total_atoms(A);
     const int ntiles = (ntot + MTP_TILE - 1) / MTP_TILE;
     if ((int)blockIdx.x >= ntiles) return;
 
@@ -650,8 +650,12 @@ __global__ void __launch_bounds__(MTP_SEG_WORKERS * 32, 1) mtp_contract_seg_kern
         size_t slot = 0;
         T ebias = T(0);
         if (valid) {
-            b = find_structure(A.prefix, A.B, t);
-            slot = (size_t)b * A.npad + (t - A.prefix[b]);
+            if (A.B > 1) {
+                b = find_structure(A.prefix, A.B, t);
+                slot = (size_t)b * A.npad + (t - A.prefix[b]);
+            } else {
+                slot = (size_t)t;
+            }
             if (MODE != MODE_DESC && warp == 0) {
                 const int *types = A.types + (size_t)b * (A.npad + A.nghost);
                 ebias = A.bias[types[A.bilist[slot]]];
@@ -965,17 +969,24 @@ static int launch_mtp_v(const ai2b_mtp_program *prog, MtpArgs<T> A, void *ws, cu
         Z.p[1] = A.force; Z.n[1] = 3 * (size_t)A.B * (A.npad + A.nghost);
         if (A.virial) { Z.p[2] = A.virial; Z.n[2] = 9 * (size_t)A.B; }
     }
-    A.coeffs_pad = mtp_prepare<T>(A.binum, A.B, prefix, A.coeffs, cpad, A.ntypes * A.ntypes * P.nmus, A.cs, CSP, st, Z);
-    AI2B_CUDA(cudaGetLastError());
-
-    const long atoms_upper = (long)A.B * A.npad;
-    const long need = (atoms_upper + MTP_WARPS - 1) / MTP_WARPS;
-    bool fwd_done = false;
     // lanes-as-atoms forward and force kernels around the segment contraction, where all three apply
     bool atoms_path = false;
     if constexpr (KD <= 6 && CSP == 8)
         atoms_path = mtp_atoms_supported(P, A.ntypes, A.cs, sizeof(T), (long)A.npad + A.nghost) && P.nseg > 0 &&
                      seg_smem_layout<T, MODE>(P, nullptr, nullptr) <= 226 * 1024;
+    const bool need_pad = A.cs != CSP || (reinterpret_cast<size_t>(A.coeffs) % (2 * sizeof(T))) != 0;
+    if (atoms_path && A.B == 1 && !need_pad) {
+        // one structure, coefficient rows usable as they are: no set-up launch; the forward kernel zeroes the outputs
+        A.coeffs_pad = A.coeffs;
+        if (A.zero_outputs) A.zero_outputs = 2;
+    } else {
+        A.coeffs_pad = mtp_prepare<T>(A.binum, A.B, prefix, A.coeffs, cpad, A.ntypes * A.ntypes * P.nmus, A.cs, CSP, st, Z);
+        AI2B_CUDA(cudaGetLastError());
+    }
+
+    const long atoms_upper = (long)A.B * A.npad;
+    const long need = (atoms_upper + MTP_WARPS - 1) / MTP_WARPS;
+    bool fwd_done = false;
     if (atoms_path) {
         A.tiled = 1;
         if (int rc = mtp_fwd_atoms<T>(P, A, st)) return rc;

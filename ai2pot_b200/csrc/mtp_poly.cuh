@@ -52,14 +52,16 @@ __device__ __forceinline__ void mtp_radial_basis(T r, T rmax, T rmin, T scaling,
 template <typename T, int KD>
 struct Powers {
     T x[KD + 1], y[KD + 1], z[KD + 1];
+    // u^k = u^(k/2) * u^(k - k/2): the longest chain of dependent products has log2(KD) + 1 links instead of KD
     __device__ __forceinline__ void set(T ux, T uy, T uz)
     {
         x[0] = y[0] = z[0] = T(1);
+        if constexpr (KD >= 1) { x[1] = ux; y[1] = uy; z[1] = uz; }
 #pragma unroll
-        for (int k = 1; k <= KD; k++) {
-            x[k] = x[k - 1] * ux;
-            y[k] = y[k - 1] * uy;
-            z[k] = z[k - 1] * uz;
+        for (int k = 2; k <= KD; k++) {
+            x[k] = x[k / 2] * x[k - k / 2];
+            y[k] = y[k / 2] * y[k - k / 2];
+            z[k] = z[k / 2] * z[k - k / 2];
         }
     }
 };

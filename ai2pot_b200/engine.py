@@ -69,7 +69,9 @@ class Evaluator:
         return self.graph_out
 
     # kernels of this library launched by one compute() on a fully periodic cell (memsets not counted):
-    # neighbour build = set-up, count, scan, fill, build; MTP = set-up, forward, contraction, force;
-    # NEP = one kernel (single structure, up to 8 radial / angular functions)
+    # neighbour build = set-up, count, scan, fill, build; MTP = forward, contraction, force (plus a set-up launch when the
+    # radial coefficient rows have to be padded to eight entries); NEP = zeroing of the outputs + one kernel
     def launches_per_step(self):
-        return 5 + (4 if self.kind == "mtp" else 1)
+        if self.kind == "mtp":
+            return 5 + 3 + (0 if int(self.model["chebyshev_size"]) == 8 else 1)
+        return 5 + 2
