@@ -26,9 +26,11 @@ class Evaluator:
                               bilist=torch.arange(n, dtype=torch.int32, device=dev)[None].contiguous(),
                               btypes=torch.from_numpy(np.ascontiguousarray(types, np.int32)).to(dev)[None].contiguous(),
                               ntypes=int(model["ntypes"]), nghost=0)
-        self.out = (torch.empty(1, dtype=dtype, device=dev), torch.empty(1, n, 3, dtype=dtype, device=dev),
-                    torch.empty(1, 9, dtype=dtype, device=dev))
+        # E, virial and forces in one piece, [E | virial (9) | pad | forces (3 n)], so that a host reads them with one copy
+        self.outbuf = torch.empty(16 + 3 * n, dtype=dtype, device=dev)
+        self.out = (self.outbuf[0:1], self.outbuf[16:].view(1, n, 3), self.outbuf[1:10].view(1, 9))
         self.status = None
+        self.graph = self.graph_io = None
 
     def build_list(self, coords):
         nn, fn, rcs, status = self.builder.build(self.cell, coords, self.rcut, self.umax)
@@ -67,6 +69,27 @@ class Evaluator:
     def replay(self):
         self.graph.replay()
         return self.graph_out
+
+    def capture_io(self, coords, host_coords, host_out):
+        """One CUDA graph for a whole call as a host sees it: pinned host positions -> device, neighbour build, E/F/V,
+        results -> pinned host buffer `host_out` (laid out like `outbuf`: E, virial 1..9, forces from element 16).
+        replay_io() then costs one graph launch. Returns False if the capture is refused."""
+        self.graph_io = None
+        try:
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                coords.copy_(host_coords, non_blocking=True)
+                self.compute(coords)
+                host_out.copy_(self.outbuf, non_blocking=True)
+            self.graph_io = g
+        except Exception:
+            self.graph_io = None
+            torch.cuda.synchronize()
+        return self.graph_io is not None
+
+    def replay_io(self):
+        self.graph_io.replay()
 
     # kernels of this library launched by one compute() on a fully periodic cell (memsets not counted):
     # neighbour build = set-up, count, scan, fill, build; MTP = forward, contraction, force (plus a set-up launch when the
