@@ -310,16 +310,25 @@ extern "C" int ai2b_mtp_program_create(int nm, int nb, const int *basic, int nt,
             if (!is_source[m] && (is_mapped[m] || m < nb)) seg_init.push_back(m);
         struct Row { int x, y, mult; };
         auto emit_phase = [&](const std::vector<std::pair<int, std::vector<Row>>> &moments) {
-            // longest processing time first over the workers; cost = rows + one per segment
+            // longest processing time first over the workers; a segment (rows of one multiplier) costs about as much as
+            // two and a half of its rows (header, multiplier, final store)
+            std::vector<long> cost(moments.size());
+            for (size_t i = 0; i < moments.size(); i++) {
+                std::vector<int> mults;
+                for (const Row &r : moments[i].second) mults.push_back(r.mult);
+                std::sort(mults.begin(), mults.end());
+                const long nseg = (long)(std::unique(mults.begin(), mults.end()) - mults.begin());
+                cost[i] = 2 * (long)moments[i].second.size() + 5 * nseg;
+            }
             std::vector<size_t> order(moments.size());
             for (size_t i = 0; i < order.size(); i++) order[i] = i;
-            std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) { return moments[a].second.size() > moments[b].second.size(); });
+            std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) { return cost[a] > cost[b]; });
             std::vector<std::vector<size_t>> mine(MTP_SEG_WORKERS);
             std::vector<long> load(MTP_SEG_WORKERS, 0);
             for (size_t i : order) {
                 int w = (int)(std::min_element(load.begin(), load.end()) - load.begin());
                 mine[w].push_back(i);
-                load[w] += (long)moments[i].second.size() + 2;
+                load[w] += cost[i];
             }
             for (int w = 0; w < MTP_SEG_WORKERS; w++) {
                 seg_wseg.push_back((int)seg_hdr.size());
