@@ -135,6 +135,8 @@ __device__ __forceinline__ T warp_xreduce(T (&v)[N], int lane)
 
 __device__ __forceinline__ double gsqrt(double x) { return sqrt(x); }
 __device__ __forceinline__ float gsqrt(float x) { return sqrtf(x); }
+__device__ __forceinline__ double grsqrt(double x) { return rsqrt(x); }
+__device__ __forceinline__ float grsqrt(float x) { return rsqrtf(x); }
 
 // number of monomials x^a y^b z^c with a+b+c <= k, and of exact degree d
 __host__ __device__ constexpr int ncan(int k) { return k < 0 ? 0 : (k + 1) * (k + 2) * (k + 3) / 6; }

@@ -122,16 +122,20 @@ struct PairEval {
             lookup(types_b);
         }
     }
+    // inv_range = 1 / (rmax - rmin), computed once per thread
     template <bool DERIV>
-    __device__ __forceinline__ void compute(const MtpArgs<T> &A, const T *cf, int ti)
+    __device__ __forceinline__ void compute(const MtpArgs<T> &A, const T *cf, int ti, T inv_range)
     {
         using V2 = typename Vec2<T>::type;
-        const T r = gsqrt(x * x + y * y + z * z);
+        // 1 / r from the reciprocal square root (one special-function sequence instead of a square root and a division)
+        const T r2 = x * x + y * y + z * z;
+        const T ri = r2 > T(0) ? grsqrt(r2) : T(0);
+        const T r = r2 * ri;
         act = act && (r <= A.rmax) && (r > T(0));
-        rinv = act ? T(1) / r : T(0);
+        rinv = act ? ri : T(0);
         ux = x * rinv; uy = y * rinv; uz = z * rinv;
         T q[CSP], dq[CSP];
-        mtp_radial_basis<T, CSP>(act ? r : A.rmax, A.rmax, A.rmin, A.scaling, q, dq);
+        mtp_radial_basis<T, CSP>(act ? r : A.rmax, A.rmax, A.rmin, A.scaling, q, dq, inv_range);
         const T *crow = cf + (size_t)(ti * A.ntypes + (act ? tj : 0)) * cf_stride<SIG, CSP>();
         static_for<0, SIG::NMUS>([&](auto mm) {
             constexpr int m = decltype(mm)::value;
@@ -220,6 +224,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32, DERIV ? 2 : 3) mtp_fwd_atoms_ke
     const int ntiles = (ntot + MTP_TILE - 1) / MTP_TILE;
 
     const bool single = A.B == 1;      // one structure: a tile's rows are known from its index alone
+    const T inv_range = T(1) / (A.rmax - A.rmin);
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
         if (single) {
             if (tile != (int)blockIdx.x) __syncthreads();     // the previous tile's rows are no longer read
@@ -254,7 +259,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32, DERIV ? 2 : 3) mtp_fwd_atoms_ke
                 for (int jj = warp; jj < cnt; jj += AT_WARPS) {   // this warp's slots of the round
                     PairEval<T, SIG, CSP> pe;
                     pe.fetch(A, tr, at.types_b, row, lane, j0 + jj, at.nn);
-                    pe.template compute<DERIV>(A, cf, at.ti);
+                    pe.template compute<DERIV>(A, cf, at.ti, inv_range);
                     T *s = st + (size_t)jj * NV * 32 + lane;
                     s[0] = pe.ux; s[32] = pe.uy; s[64] = pe.uz;
                     static_for<0, SIG::NMUS>([&](auto mm) { s[(3 + decltype(mm)::value) * 32] = pe.f[decltype(mm)::value]; });
@@ -348,6 +353,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32, 3) mtp_force_atoms_kernel(const
     const int ntot = total_atoms(A);
     const int ntiles = (ntot + MTP_TILE - 1) / MTP_TILE;
     const bool single = A.B == 1;      // one structure: a tile's rows are known from its index alone
+    const T inv_range = T(1) / (A.rmax - A.rmin);
 
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
         if (tile != (int)blockIdx.x) __syncthreads();     // the previous tile's adjoints and rows are no longer read
@@ -385,7 +391,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32, 3) mtp_force_atoms_kernel(const
         for (int j = warp; j < nmax; j += AT_WARPS) {
             PairEval<T, SIG, CSP> pe;
             pe.fetch(A, tr, at.types_b, row, lane, j, at.nn);
-            pe.template compute<true>(A, cf, at.ti);
+            pe.template compute<true>(A, cf, at.ti, inv_range);
             // powers of the unit vector and their derivatives k u^(k-1)
             T X[KD + 1], Y[KD + 1], Z[KD + 1], dX[KD + 1], dY[KD + 1], dZ[KD + 1];
             X[0] = Y[0] = Z[0] = T(1);

@@ -19,10 +19,10 @@ template <> struct Vec2<float> { using type = float2; };
 // Q_xi = s(r) T_xi(u), Q'_xi = s' T_xi + s T'_xi  (source/descriptor/mtpr/include/basis.h:155-181,
 // 352-380, 621-637), scaled by `scaling`. CSP >= chebyshev_size entries are produced; the ones
 // past chebyshev_size meet zero coefficients (the coefficient rows are zero-padded to CSP).
+// (inv = 1 / (rmax - rmin): the same for every pair of a call, so callers in a pair loop pass it in)
 template <typename T, int CSP>
-__device__ __forceinline__ void mtp_radial_basis(T r, T rmax, T rmin, T scaling, T (&q)[CSP], T (&dq)[CSP])
+__device__ __forceinline__ void mtp_radial_basis(T r, T rmax, T rmin, T scaling, T (&q)[CSP], T (&dq)[CSP], T inv)
 {
-    const T inv = T(1) / (rmax - rmin);
     const T w = (r - rmin) * inv;
     T s = T(0), ds = T(0);
     if (r >= rmin && r < rmax) {
@@ -47,6 +47,12 @@ __device__ __forceinline__ void mtp_radial_basis(T r, T rmax, T rmin, T scaling,
         q[xi] = s * t;
         dq[xi] = ds * t + s * (d * uc);
     }
+}
+
+template <typename T, int CSP>
+__device__ __forceinline__ void mtp_radial_basis(T r, T rmax, T rmin, T scaling, T (&q)[CSP], T (&dq)[CSP])
+{
+    mtp_radial_basis<T, CSP>(r, rmax, rmin, scaling, q, dq, T(1) / (rmax - rmin));
 }
 
 template <typename T, int KD>
