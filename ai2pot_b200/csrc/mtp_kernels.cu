@@ -1,15 +1,14 @@
 // Linear MTP: energy, force, virial and descriptors on sm_100a, as three kernels per call.
 //
-//   mtp_fwd_kernel      one warp per atom, lanes = neighbours: r, unit vector, radial functions
-//                       f_mu, dense basic-moment sums per mu (compile-time monomials + warp
-//                       transpose-reduce) -> Mb[atom][dense] in the workspace
-//   mtp_contract_kernel one block per tile of atoms, LANES = ATOMS: the product rows and the
-//                       adjoint sweep run out of shared memory with the row tables uniform across
-//                       the warp (no divergence, no per-lane table loads); site energies;
-//                       adjoints of the basic moments -> Eb[atom][dense] (or the descriptors)
-//   mtp_force_kernel    one warp per atom, lanes = neighbours: adjoints -> polynomial coefficient
-//                       quadruples in shared memory, evaluated per neighbour with their gradient;
-//                       pair force g = f' P u + f/r (G - (u.G) u); F_i += g, F_j -= g, V -= g (x) r
+// Tables of the reference's template levels 6 to 16 (monomial degree <= 6, four radial functions at most):
+//   mtp_fwd_atoms_kernel    (mtp_atoms.cu) lanes = atoms, basic moments in registers -> Mb[tile][basic row][32 atoms]
+//   mtp_contract_seg_kernel lanes = atoms, one tile of 32 atoms per block at a time: the product rows and the adjoint
+//                           sweep run out of shared memory, every moment owned by one warp; site energies; adjoints
+//                           of the basic moments -> Eb[tile][dense monomial][32 atoms] (or the descriptors)
+//   mtp_force_atoms_kernel  (mtp_atoms.cu) lanes = atoms: polynomial of every radial function and its gradient per
+//                           neighbour; pair force g = f' P u + f/r (G - (u.G) u); F_i += g, F_j -= g, V -= g (x) r
+// Other tables (levels 18 and 20, or more than 32 atom types) take the warp-per-atom kernels of this file with rows per
+// atom in the workspace: mtp_fwd_lanes_kernel / mtp_fwd_kernel, mtp_contract_kernel (flat row streams), mtp_force_kernel.
 //
 // Reference semantics: source/descriptor/mtpr/include/mtpBasis.h:400-534, linearMtp.h:190-352.
 #include "mtp_device.cuh"
@@ -441,9 +440,9 @@ __global__ void __launch_bounds__(MTP_CWARPS * 32, 1) mtp_contract_kernel(const 
 // compiled into segments (mtp_program.cuh): a header {moment, row count, multiplier} followed by rows of
 // two element offsets, every moment owned by one warp, so a row is one 8-byte broadcast load, two address
 // adds, two operand loads and one FMA, and a moment is finished with a plain store. Tiles of 32 atoms;
-// the per-atom rows of the workspace are transposed into [moment][atom] on the way in and out (row
-// stride 33 keeps those transposing accesses spread over the banks), the next tile's rows travelling in
-// registers while the current tile is processed.
+// the workspace holds them tile by tile ([tile][row][32 atoms]; per-atom rows from the warp-per-atom forward
+// kernels are transposed on the way in and out, row stride 33 keeps those accesses spread over the banks),
+// the next tile's rows travelling in registers while the current tile is processed.
 // Shared memory: M[nm][33], E[nm][33] (not for descriptors), headers, rows, seeds, worker tables.
 constexpr int MTP_SEG_EWARPS = 8;   // warps that sum the site energies of a tile
 template <typename T>
