@@ -17,6 +17,7 @@
 // for centres next to a periodic face) instead of 125 bins. The padded row is written once, by
 // the same warp.
 #include "common.cuh"
+#include <cooperative_groups.h>
 
 #include <cmath>
 #include <cstdlib>
@@ -351,6 +352,61 @@ __global__ void __launch_bounds__(SCAN_BLOCK) nb_scan_small_kernel(const NbGrid 
         }
         __syncthreads();     // the buffer and the warp totals are reused by the next chunk
     }
+}
+
+// The same scan by a cluster of SCAN_CLUSTER blocks (grids of up to SCAN_CLUSTER * SCAN_BLOCK * SCAN_ITEMS bins): every
+// block scans one chunk, the block totals are read from the other blocks' shared memory.
+constexpr int SCAN_CLUSTER = 4;
+__global__ void __cluster_dims__(SCAN_CLUSTER, 1, 1) __launch_bounds__(SCAN_BLOCK)
+nb_scan_cluster_kernel(const NbGrid *__restrict__ gp, const int *__restrict__ in, int *__restrict__ out, int *__restrict__ cursor)
+{
+    namespace cg = cooperative_groups;
+    __shared__ int buf[SCAN_BLOCK * (SCAN_ITEMS + 1)];
+    __shared__ int ws[32];
+    __shared__ int block_total;
+    cg::cluster_group cl = cg::this_cluster();
+    const int rank = (int)cl.block_rank();
+    const int total = gp->total;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int base = rank * SCAN_BLOCK * SCAN_ITEMS;
+#pragma unroll
+    for (int k = 0; k < SCAN_ITEMS; k++) {
+        const int e = k * SCAN_BLOCK + threadIdx.x, i = base + e;
+        buf[(e / SCAN_ITEMS) * (SCAN_ITEMS + 1) + e % SCAN_ITEMS] = i < total ? in[i] : 0;
+    }
+    __syncthreads();
+    int v[SCAN_ITEMS], sum = 0;
+#pragma unroll
+    for (int k = 0; k < SCAN_ITEMS; k++) {
+        v[k] = sum;
+        sum += buf[threadIdx.x * (SCAN_ITEMS + 1) + k];
+    }
+    int inc = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { int n = __shfl_up_sync(FULL_MASK, inc, o); if (lane >= o) inc += n; }
+    if (lane == 31) ws[warp] = inc;
+    __syncthreads();
+    int w = ws[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { int n = __shfl_up_sync(FULL_MASK, w, o); if (lane >= o) w += n; }
+    const int before = __shfl_sync(FULL_MASK, w, max(warp - 1, 0));
+    if (threadIdx.x == 0) block_total = __shfl_sync(FULL_MASK, w, 31);
+    else (void)__shfl_sync(FULL_MASK, w, 31);
+    cl.sync();
+    int carry = 0;
+    for (int r = 0; r < rank; r++) carry += *cl.map_shared_rank(&block_total, r);
+    const int off = carry + inc - sum + (warp > 0 ? before : 0);
+#pragma unroll
+    for (int k = 0; k < SCAN_ITEMS; k++) buf[threadIdx.x * (SCAN_ITEMS + 1) + k] = off + v[k];
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < SCAN_ITEMS; k++) {
+        const int e = k * SCAN_BLOCK + threadIdx.x, i = base + e;
+        const int r = buf[(e / SCAN_ITEMS) * (SCAN_ITEMS + 1) + e % SCAN_ITEMS];
+        if (i <= total) out[i] = r;
+        if (i < total) cursor[i] = r;
+    }
+    cl.sync();      // no block leaves while another may still read its total
 }
 
 // pass 2: atoms into bin order: position (type T) + {original index, wrap}
@@ -1027,7 +1083,9 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
         const int ncount = (int)prod + 1;
         nb_setup_periodic_kernel<<<(ncount + 255) / 256, 256, 0, st>>>(hg, grid, count, ncount, d_status);
         nb_count_kernel<T><<<nblk, tb, 0, st>>>(P, grid, pos, ainfo, count);
-        if (ncount <= 64 * SCAN_BLOCK) {
+        if (ncount <= SCAN_CLUSTER * SCAN_BLOCK * SCAN_ITEMS) {
+            nb_scan_cluster_kernel<<<SCAN_CLUSTER, SCAN_BLOCK, 0, st>>>(grid, count, start, cursor);
+        } else if (ncount <= 64 * SCAN_BLOCK) {
             nb_scan_small_kernel<<<1, SCAN_BLOCK, 0, st>>>(grid, count, start, cursor);
         } else {   // large grids: block-parallel scan
             const int sblk = (ncount + SCAN_BLOCK - 1) / SCAN_BLOCK;
