@@ -138,6 +138,33 @@ __device__ __forceinline__ float gsqrt(float x) { return sqrtf(x); }
 __device__ __forceinline__ double grsqrt(double x) { return rsqrt(x); }
 __device__ __forceinline__ float grsqrt(float x) { return rsqrtf(x); }
 
+// Chained launches (programmatic dependent launch). The launches of one evaluation form a chain on one stream, each
+// kernel reading what the one before it wrote. launch_chained() lets the blocks of a kernel become resident while the
+// kernel before it is still draining: they run whatever does not depend on earlier kernels (staging of model tables),
+// then chain_wait() holds them until every earlier kernel of the stream has completed and its writes are visible.
+// chain_release() in a kernel says that the next kernel of the chain may be made resident as soon as all blocks of
+// this one have started. Rules: a kernel launched with launch_chained() executes chain_wait() in every thread before
+// its first access to memory that another kernel writes or reads (so completion stays transitive along the chain);
+// in a kernel launched the ordinary way both calls do nothing.
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(static_cast<Args &&>(args))...);
+}
+
 // number of monomials x^a y^b z^c with a+b+c <= k, and of exact degree d
 __host__ __device__ constexpr int ncan(int k) { return k < 0 ? 0 : (k + 1) * (k + 2) * (k + 3) / 6; }
 __host__ __device__ constexpr int ndeg(int d) { return (d + 1) * (d + 2) / 2; }

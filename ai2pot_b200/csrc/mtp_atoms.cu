@@ -212,6 +212,9 @@ __global__ void __launch_bounds__(AT_WARPS * 32, DERIV ? 2 : 3) mtp_fwd_atoms_ke
     TileRows<T> tr;
     tr.bind(reinterpret_cast<unsigned char *>(st + (size_t)AT_CH * NV * 32));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    stage_coefficients<T, SIG, CSP>(A, cf);   // model constants: staged while the kernel before this one drains
+    chain_wait();
+    chain_release();
     if (!DERIV && A.zero_outputs == 2) {      // no set-up launch: this first kernel of the call zeroes the outputs
         const size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x, step = (size_t)gridDim.x * blockDim.x;
         const size_t nf = 3 * (size_t)A.B * (A.npad + A.nghost);
@@ -219,7 +222,6 @@ __global__ void __launch_bounds__(AT_WARPS * 32, DERIV ? 2 : 3) mtp_fwd_atoms_ke
         if (i0 < (size_t)A.B) A.etot[i0] = T(0);
         if (A.virial && i0 < 9 * (size_t)A.B) A.virial[i0] = T(0);
     }
-    stage_coefficients<T, SIG, CSP>(A, cf);
     const int ntot = total_atoms(A);
     const int ntiles = (ntot + MTP_TILE - 1) / MTP_TILE;
 
@@ -349,7 +351,9 @@ __global__ void __launch_bounds__(AT_WARPS * 32, 3) mtp_force_atoms_kernel(const
     TileRows<T> tr;
     tr.bind(reinterpret_cast<unsigned char *>(Es + (size_t)SIG::NDENSE * 32));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    stage_coefficients<T, SIG, CSP>(A, cf);
+    stage_coefficients<T, SIG, CSP>(A, cf);   // model constants: staged while the contraction drains
+    chain_wait();
+    chain_release();
     const int ntot = total_atoms(A);
     const int ntiles = (ntot + MTP_TILE - 1) / MTP_TILE;
     const bool single = A.B == 1;      // one structure: a tile's rows are known from its index alone
@@ -535,8 +539,7 @@ static int launch_fwd_atoms(const MtpProgramDev &P, const MtpArgs<T> &A, const L
     long tiles = ((long)A.B * A.npad + MTP_TILE - 1) / MTP_TILE;
     long blocks = (long)sm_count() * per_sm;
     if (blocks > tiles) blocks = tiles;
-    kern<<<(unsigned)blocks, AT_WARPS * 32, smem, st>>>(P, A, L);
-    AI2B_CUDA(cudaGetLastError());
+    AI2B_CUDA(launch_chained(kern, (unsigned)blocks, AT_WARPS * 32, smem, st, P, A, L));
     return AI2B_OK;
 }
 
@@ -552,8 +555,7 @@ static int launch_force_atoms(const MtpProgramDev &P, const MtpArgs<T> &A, cudaS
     long tiles = ((long)A.B * A.npad + MTP_TILE - 1) / MTP_TILE;
     long blocks = (long)sm_count() * per_sm;
     if (blocks > tiles) blocks = tiles;
-    kern<<<(unsigned)blocks, AT_WARPS * 32, smem, st>>>(P, A);
-    AI2B_CUDA(cudaGetLastError());
+    AI2B_CUDA(launch_chained(kern, (unsigned)blocks, AT_WARPS * 32, smem, st, P, A));
     return AI2B_OK;
 }
 

@@ -604,6 +604,8 @@ __global__ void __launch_bounds__(MTP_SEG_WORKERS * 32, 1) mtp_contract_seg_kern
             }
         }
     };
+    chain_wait();        // everything above reads the program's tables and the model only
+    chain_release();
     if (can_prefetch) fetch(blockIdx.x);
     // shared-window addresses of this lane's columns and of the tables
     const unsigned ml = (unsigned)__cvta_generic_to_shared(S.M + lane), el = (unsigned)__cvta_generic_to_shared(S.E + lane);
@@ -932,8 +934,7 @@ static int dispatch_contract(const MtpProgramDev &P, const MtpArgs<T> &A, long a
             if (int rc = kernel_setup(setup, kern, smem)) return rc;
             long tiles = (atoms_upper + MTP_TILE - 1) / MTP_TILE;
             if (tiles > sm_count()) tiles = sm_count();      // persistent: one block per SM walks over the tiles
-            kern<<<(unsigned)tiles, MTP_SEG_WORKERS * 32, smem, st>>>(P, A);
-            AI2B_CUDA(cudaGetLastError());
+            AI2B_CUDA(launch_chained(kern, (unsigned)tiles, MTP_SEG_WORKERS * 32, smem, st, P, A));
             return AI2B_OK;
         }
     }

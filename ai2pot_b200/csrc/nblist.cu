@@ -211,6 +211,8 @@ template <typename T>
 __global__ void nb_count_kernel(NbParams<T> P, NbGrid *gp, const T *__restrict__ pos,
                                 int4 *__restrict__ ainfo, int *__restrict__ bin_count)
 {
+    chain_wait();
+    chain_release();
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= P.n) return;
     const NbGrid g = *gp;
@@ -294,6 +296,8 @@ __global__ void nb_scan3_kernel(const NbGrid *__restrict__ gp, int *__restrict__
 // resets the status words and writes the grid description
 __global__ void nb_setup_periodic_kernel(NbGrid host_grid, NbGrid *__restrict__ g, int *__restrict__ count, int ncount, int *__restrict__ status)
 {
+    chain_wait();
+    chain_release();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < ncount) count[i] = 0;
     if (i == 0) {
@@ -310,6 +314,8 @@ constexpr int SCAN_ITEMS = 8;
 __global__ void __launch_bounds__(SCAN_BLOCK) nb_scan_small_kernel(const NbGrid *__restrict__ gp, const int *__restrict__ in, int *__restrict__ out,
                                                                   int *__restrict__ cursor)
 {
+    chain_wait();
+    chain_release();
     __shared__ int buf[SCAN_BLOCK * (SCAN_ITEMS + 1)];
     __shared__ int ws[32];
     const int total = gp->total;
@@ -360,6 +366,8 @@ constexpr int SCAN_CLUSTER = 4;
 __global__ void __cluster_dims__(SCAN_CLUSTER, 1, 1) __launch_bounds__(SCAN_BLOCK)
 nb_scan_cluster_kernel(const NbGrid *__restrict__ gp, const int *__restrict__ in, int *__restrict__ out, int *__restrict__ cursor)
 {
+    chain_wait();
+    chain_release();
     namespace cg = cooperative_groups;
     __shared__ int buf[SCAN_BLOCK * (SCAN_ITEMS + 1)];
     __shared__ int ws[32];
@@ -415,6 +423,8 @@ __global__ void nb_fill_kernel(NbParams<T> P, const T *__restrict__ pos, const i
                                int *__restrict__ cursor, typename Vec4<T>::type *__restrict__ spos, int4 *__restrict__ sinfo,
                                float4 *__restrict__ sposw, int4 *__restrict__ sbin, const NbGrid *__restrict__ gp)
 {
+    chain_wait();
+    chain_release();
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= P.n) return;
     const int4 a = ainfo[i];
@@ -452,6 +462,8 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
                 const int4 *__restrict__ sinfo, const float4 *__restrict__ sposw, const int4 *__restrict__ sbin, int *__restrict__ numneigh,
                 int *__restrict__ firstneigh, TO *__restrict__ rcs, int *__restrict__ status)
 {
+    chain_wait();
+    chain_release();
     __shared__ int s_start[NB_WARPS][32], s_pre[NB_WARPS][33], s_shift[NB_WARPS][32];
     __shared__ float4 s_sv[NB_WARPS][32];      // image shift of a table entry as a single-precision vector
     // candidate c of the current group of bins -> its atom (bin order) and its bin's slot, filled by the
@@ -727,6 +739,8 @@ nb_build_lanes_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *_
                       const float4 *__restrict__ sposw, const int4 *__restrict__ sbin, int *__restrict__ numneigh,
                       int *__restrict__ firstneigh, TO *__restrict__ rcs, int *__restrict__ status)
 {
+    chain_wait();
+    chain_release();
     const NbGrid g = *gp;
     const bool packed = g.bigwrap == 0;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -1081,12 +1095,12 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
         // bins, bin-ordered positions and (for fractional input) Cartesian positions are in the workspace already
     } else if (small_grid) {
         const int ncount = (int)prod + 1;
-        nb_setup_periodic_kernel<<<(ncount + 255) / 256, 256, 0, st>>>(hg, grid, count, ncount, d_status);
-        nb_count_kernel<T><<<nblk, tb, 0, st>>>(P, grid, pos, ainfo, count);
+        AI2B_CUDA(launch_chained(nb_setup_periodic_kernel, (ncount + 255) / 256, 256, 0, st, hg, grid, count, ncount, d_status));
+        AI2B_CUDA(launch_chained(nb_count_kernel<T>, nblk, tb, 0, st, P, grid, pos, ainfo, count));
         if (ncount <= SCAN_CLUSTER * SCAN_BLOCK * SCAN_ITEMS) {
-            nb_scan_cluster_kernel<<<SCAN_CLUSTER, SCAN_BLOCK, 0, st>>>(grid, count, start, cursor);
+            AI2B_CUDA(launch_chained(nb_scan_cluster_kernel, SCAN_CLUSTER, SCAN_BLOCK, 0, st, grid, count, start, cursor));
         } else if (ncount <= 64 * SCAN_BLOCK) {
-            nb_scan_small_kernel<<<1, SCAN_BLOCK, 0, st>>>(grid, count, start, cursor);
+            AI2B_CUDA(launch_chained(nb_scan_small_kernel, 1, SCAN_BLOCK, 0, st, grid, count, start, cursor));
         } else {   // large grids: block-parallel scan
             const int sblk = (ncount + SCAN_BLOCK - 1) / SCAN_BLOCK;
             nb_scan1_kernel<<<sblk, SCAN_BLOCK, 0, st>>>(grid, count, start, bsum);
@@ -1104,7 +1118,7 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
         nb_scan2_kernel<<<1, SCAN_BLOCK, 0, st>>>(grid, bsum);
         nb_scan3_kernel<<<sblk, SCAN_BLOCK, 0, st>>>(grid, start, bsum, cursor);
     }
-    if (!reuse_bins) nb_fill_kernel<T><<<nblk, tb, 0, st>>>(P, pos, ainfo, cursor, spos, sinfo, sposw, sbin, grid);
+    if (!reuse_bins) AI2B_CUDA(launch_chained(nb_fill_kernel<T>, nblk, tb, 0, st, P, pos, ainfo, cursor, spos, sinfo, sposw, sbin, grid));
     const int sms = sm_count();
     // the bins of a column along the third axis form one range unless that axis is periodic and shorter than the
     // search window (known on the host: open axes always search NB_SUB bins)
@@ -1119,15 +1133,14 @@ static int nblist_build(int n, int ncentre, const T *h_cell, const T *d_coords, 
     if (zmerge && n >= min_atoms) {
         long blocks = ((long)n + 32 * NBL_WARPS - 1) / (32 * NBL_WARPS);
         if (blocks > (long)sms * 16) blocks = (long)sms * 16;
-        nb_build_lanes_kernel<T, TO><<<(unsigned)blocks, NBL_WARPS * 32, 0, st>>>(P, grid, start, spos, sinfo, sposw, sbin, d_numneigh, d_firstneigh,
-                                                                               d_rcs, d_status);
-        AI2B_CUDA(cudaGetLastError());
+        AI2B_CUDA(launch_chained(nb_build_lanes_kernel<T, TO>, (unsigned)blocks, NBL_WARPS * 32, 0, st, P, grid, start, spos, sinfo, sposw, sbin,
+                                 d_numneigh, d_firstneigh, d_rcs, d_status));
         return AI2B_OK;
     }
     long blocks = ((long)n + NB_WARPS - 1) / NB_WARPS;
     if (blocks > (long)sms * 8) blocks = (long)sms * 8;
-    nb_build_kernel<T, TO><<<(unsigned)blocks, NB_WARPS * 32, 0, st>>>(P, grid, start, ainfo, spos, sinfo, sposw, sbin, d_numneigh, d_firstneigh, d_rcs, d_status);
-    AI2B_CUDA(cudaGetLastError());
+    AI2B_CUDA(launch_chained(nb_build_kernel<T, TO>, (unsigned)blocks, NB_WARPS * 32, 0, st, P, grid, start, ainfo, spos, sinfo, sposw, sbin, d_numneigh,
+                             d_firstneigh, d_rcs, d_status));
     return AI2B_OK;
 }
 

@@ -208,6 +208,8 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_fast_kernel(const Ne
     // descriptors and their adjoints are read as NDP-long vectors: the padding stays zero
     for (int i = threadIdx.x; i < NEP_APB * 2 * NDP; i += blockDim.x) atoms_s[(size_t)(i / (2 * NDP)) * per_atom + i % (2 * NDP)] = T(0);
     __syncthreads();
+    chain_wait();        // the prologue read the model only: it ran while the kernel before this one drained
+    chain_release();
 
     const int ntot = A.B == 1 ? A.binum[0] : A.prefix[A.B];
     const int ngroups = gridDim.x * NEP_APB;

@@ -189,6 +189,8 @@ __global__ void nep_pad_coeffs_kernel(const T *__restrict__ c, T *__restrict__ o
 template <typename T>
 __global__ void nep_zero_kernel(T *__restrict__ a, size_t na, T *__restrict__ b, size_t nb, T *__restrict__ c, size_t nc)
 {
+    chain_wait();
+    chain_release();
     const size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x, step = (size_t)gridDim.x * blockDim.x;
     for (size_t i = i0; i < na; i += step) a[i] = T(0);
     for (size_t i = i0; i < nb; i += step) b[i] = T(0);
@@ -201,8 +203,7 @@ static int nep_zero_outputs(T *etot, size_t ne, T *force, size_t nf, T *virial, 
     if (n == 0) return AI2B_OK;
     size_t blocks = (n + 4 * 256 - 1) / (4 * 256);
     if (blocks > 4096) blocks = 4096;
-    nep_zero_kernel<T><<<(unsigned)blocks, 256, 0, st>>>(etot, ne, force, nf, virial, virial ? nv : 0);
-    AI2B_CUDA(cudaGetLastError());
+    AI2B_CUDA(launch_chained(nep_zero_kernel<T>, (unsigned)blocks, 256, 0, st, etot, ne, force, nf, virial, virial ? nv : size_t(0)));
     return AI2B_OK;
 }
 
@@ -561,8 +562,7 @@ static int launch_nep_fast(const NepArgs<T> &A, const T *coeffs, cudaStream_t st
     long blocks = 0;
     int rc = nep_grid((const void *)kern, smem, A.B, A.npad, &blocks);
     if (rc != AI2B_OK) return rc;
-    kern<<<(unsigned)blocks, NEP_WARPS * 32, smem, st>>>(A, coeffs);
-    AI2B_CUDA(cudaGetLastError());
+    AI2B_CUDA(launch_chained(kern, (unsigned)blocks, NEP_WARPS * 32, smem, st, A, coeffs));
     *done = true;
     return AI2B_OK;
 }
