@@ -212,9 +212,9 @@ __global__ void __launch_bounds__(AT_WARPS * 32, DERIV ? 2 : 3) mtp_fwd_atoms_ke
     TileRows<T> tr;
     tr.bind(reinterpret_cast<unsigned char *>(st + (size_t)AT_CH * NV * 32));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    chain_release();
     stage_coefficients<T, SIG, CSP>(A, cf);   // model constants: staged while the kernel before this one drains
     chain_wait();
-    chain_release();
     if (!DERIV && A.zero_outputs == 2) {      // no set-up launch: this first kernel of the call zeroes the outputs
         const size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x, step = (size_t)gridDim.x * blockDim.x;
         const size_t nf = 3 * (size_t)A.B * (A.npad + A.nghost);
@@ -351,9 +351,9 @@ __global__ void __launch_bounds__(AT_WARPS * 32, 3) mtp_force_atoms_kernel(const
     TileRows<T> tr;
     tr.bind(reinterpret_cast<unsigned char *>(Es + (size_t)SIG::NDENSE * 32));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    chain_release();
     stage_coefficients<T, SIG, CSP>(A, cf);   // model constants: staged while the contraction drains
     chain_wait();
-    chain_release();
     const int ntot = total_atoms(A);
     const int ntiles = (ntot + MTP_TILE - 1) / MTP_TILE;
     const bool single = A.B == 1;      // one structure: a tile's rows are known from its index alone

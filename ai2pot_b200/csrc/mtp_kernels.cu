@@ -560,9 +560,13 @@ __global__ void __launch_bounds__(MTP_SEG_WORKERS * 32, 1) mtp_contract_seg_kern
     SegSmem<T> S;
     seg_smem_layout<T, MODE>(P, smem_raw, &S);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    chain_release();
     const int ntot = total_atoms(A);
     const int ntiles = (ntot + MTP_TILE - 1) / MTP_TILE;
-    if ((int)blockIdx.x >= ntiles) return;
+    if ((int)blockIdx.x >= ntiles) {
+        chain_wait();        // every block waits, so that this kernel never completes before the one it follows
+        return;
+    }
 
     // tables, staged once per block
     for (int i = threadIdx.x; i < P.nseg; i += NT) S.hdr[i] = P.seg_hdr[i];
@@ -605,7 +609,6 @@ __global__ void __launch_bounds__(MTP_SEG_WORKERS * 32, 1) mtp_contract_seg_kern
         }
     };
     chain_wait();        // everything above reads the program's tables and the model only
-    chain_release();
     if (can_prefetch) fetch(blockIdx.x);
     // shared-window addresses of this lane's columns and of the tables
     const unsigned ml = (unsigned)__cvta_generic_to_shared(S.M + lane), el = (unsigned)__cvta_generic_to_shared(S.E + lane);

@@ -211,8 +211,8 @@ template <typename T>
 __global__ void nb_count_kernel(NbParams<T> P, NbGrid *gp, const T *__restrict__ pos,
                                 int4 *__restrict__ ainfo, int *__restrict__ bin_count)
 {
-    chain_wait();
     chain_release();
+    chain_wait();
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= P.n) return;
     const NbGrid g = *gp;
@@ -296,8 +296,8 @@ __global__ void nb_scan3_kernel(const NbGrid *__restrict__ gp, int *__restrict__
 // resets the status words and writes the grid description
 __global__ void nb_setup_periodic_kernel(NbGrid host_grid, NbGrid *__restrict__ g, int *__restrict__ count, int ncount, int *__restrict__ status)
 {
-    chain_wait();
     chain_release();
+    chain_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < ncount) count[i] = 0;
     if (i == 0) {
@@ -314,8 +314,8 @@ constexpr int SCAN_ITEMS = 8;
 __global__ void __launch_bounds__(SCAN_BLOCK) nb_scan_small_kernel(const NbGrid *__restrict__ gp, const int *__restrict__ in, int *__restrict__ out,
                                                                   int *__restrict__ cursor)
 {
-    chain_wait();
     chain_release();
+    chain_wait();
     __shared__ int buf[SCAN_BLOCK * (SCAN_ITEMS + 1)];
     __shared__ int ws[32];
     const int total = gp->total;
@@ -366,8 +366,8 @@ constexpr int SCAN_CLUSTER = 4;
 __global__ void __cluster_dims__(SCAN_CLUSTER, 1, 1) __launch_bounds__(SCAN_BLOCK)
 nb_scan_cluster_kernel(const NbGrid *__restrict__ gp, const int *__restrict__ in, int *__restrict__ out, int *__restrict__ cursor)
 {
-    chain_wait();
     chain_release();
+    chain_wait();
     namespace cg = cooperative_groups;
     __shared__ int buf[SCAN_BLOCK * (SCAN_ITEMS + 1)];
     __shared__ int ws[32];
@@ -423,8 +423,8 @@ __global__ void nb_fill_kernel(NbParams<T> P, const T *__restrict__ pos, const i
                                int *__restrict__ cursor, typename Vec4<T>::type *__restrict__ spos, int4 *__restrict__ sinfo,
                                float4 *__restrict__ sposw, int4 *__restrict__ sbin, const NbGrid *__restrict__ gp)
 {
-    chain_wait();
     chain_release();
+    chain_wait();
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= P.n) return;
     const int4 a = ainfo[i];
@@ -462,8 +462,8 @@ nb_build_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *__restr
                 const int4 *__restrict__ sinfo, const float4 *__restrict__ sposw, const int4 *__restrict__ sbin, int *__restrict__ numneigh,
                 int *__restrict__ firstneigh, TO *__restrict__ rcs, int *__restrict__ status)
 {
-    chain_wait();
     chain_release();
+    chain_wait();
     __shared__ int s_start[NB_WARPS][32], s_pre[NB_WARPS][33], s_shift[NB_WARPS][32];
     __shared__ float4 s_sv[NB_WARPS][32];      // image shift of a table entry as a single-precision vector
     // candidate c of the current group of bins -> its atom (bin order) and its bin's slot, filled by the
@@ -739,8 +739,8 @@ nb_build_lanes_kernel(NbParams<T> P, const NbGrid *__restrict__ gp, const int *_
                       const float4 *__restrict__ sposw, const int4 *__restrict__ sbin, int *__restrict__ numneigh,
                       int *__restrict__ firstneigh, TO *__restrict__ rcs, int *__restrict__ status)
 {
-    chain_wait();
     chain_release();
+    chain_wait();
     const NbGrid g = *gp;
     const bool packed = g.bigwrap == 0;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

@@ -99,6 +99,7 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_fast_kernel(const Ne
     __shared__ T c3w_s[NEP_NLM];     // (2 - delta_m0) * C_lm
     __shared__ unsigned char pm_mu[NDP], pm_l[NDP];   // angular descriptor p -> (mu, l)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    chain_release();
     const int sub = lane & (NEP_GROUP - 1), grp = lane / NEP_GROUP;
     const int slot_in_block = warp * NEP_APW + grp;
     const unsigned gmask_shift = grp * NEP_GROUP;
@@ -208,8 +209,7 @@ __global__ void __launch_bounds__(NEP_WARPS * 32, MINB) nep_fast_kernel(const Ne
     // descriptors and their adjoints are read as NDP-long vectors: the padding stays zero
     for (int i = threadIdx.x; i < NEP_APB * 2 * NDP; i += blockDim.x) atoms_s[(size_t)(i / (2 * NDP)) * per_atom + i % (2 * NDP)] = T(0);
     __syncthreads();
-    chain_wait();        // the prologue read the model only: it ran while the kernel before this one drained
-    chain_release();
+    chain_wait();        // the prologue read the model only: it ran while the kernels before this one drained
 
     const int ntot = A.B == 1 ? A.binum[0] : A.prefix[A.B];
     const int ngroups = gridDim.x * NEP_APB;

@@ -189,8 +189,8 @@ __global__ void nep_pad_coeffs_kernel(const T *__restrict__ c, T *__restrict__ o
 template <typename T>
 __global__ void nep_zero_kernel(T *__restrict__ a, size_t na, T *__restrict__ b, size_t nb, T *__restrict__ c, size_t nc)
 {
-    chain_wait();
     chain_release();
+    chain_wait();
     const size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x, step = (size_t)gridDim.x * blockDim.x;
     for (size_t i = i0; i < na; i += step) a[i] = T(0);
     for (size_t i = i0; i < nb; i += step) b[i] = T(0);
