@@ -54,7 +54,7 @@ def fp32_parity(case, name, got, r32, r64, tol=1e-5):
         d_cuda32 = CUDA fp32 result   <-> fp32 CPU checker
     Required: the CUDA result is within `tol` of the fp64 value, or at least as close to it as the CPU code's own
     fp32 result is; and it is within tol + d_cpu64 of the fp32 CPU result. The distances are printed and appended
-    to gpurun_out/parity_fp32_distances.jsonl."""
+    to the record file (_FP32_RECORD, one JSON object per line)."""
     import json
     d_cuda64, d_cpu64, d_cuda32 = relerr(got, r64), relerr(r32, r64), relerr(got, r32)
     rec = dict(case=case, tensor=name, cuda_vs_fp64=d_cuda64, cpu32_vs_fp64=d_cpu64, cuda_vs_cpu32=d_cuda32)
