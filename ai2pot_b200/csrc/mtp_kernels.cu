@@ -10,6 +10,9 @@
 // Other tables (levels 18 and 20, or more than 32 atom types) take the warp-per-atom kernels of this file with rows per
 // atom in the workspace: mtp_fwd_lanes_kernel / mtp_fwd_kernel, mtp_contract_kernel (flat row streams), mtp_force_kernel.
 //
+// The three lanes-as-atoms kernels are launched as a chain (launch_chained() in common.cuh): each stages its model
+// tables while the kernel before it drains, then waits for it.
+//
 // Reference semantics: source/descriptor/mtpr/include/mtpBasis.h:400-534, linearMtp.h:190-352.
 #include "mtp_device.cuh"
 #include <cuda_pipeline.h>

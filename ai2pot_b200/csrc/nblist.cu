@@ -15,7 +15,8 @@
 // that follow one another along the third axis are contiguous in bin order, so the 5 bins of a
 // column are ONE range of atoms: the warp's table holds 25 ranges (plus the wrapped remainders
 // for centres next to a periodic face) instead of 125 bins. The padded row is written once, by
-// the same warp.
+// the same warp. The launches of one build (set-up, count, scan, fill, build) go out as a chain
+// (launch_chained() in common.cuh), so each becomes resident while the one before it drains.
 #include "common.cuh"
 #include <cooperative_groups.h>
 
