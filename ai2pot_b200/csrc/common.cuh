@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 #include "../../include/ai2pot_b200.h"
@@ -145,7 +146,8 @@ __device__ __forceinline__ float grsqrt(float x) { return rsqrtf(x); }
 // chain_release() in a kernel says that the next kernel of the chain may be made resident as soon as all blocks of
 // this one have started. Rules: a kernel launched with launch_chained() executes chain_wait() in every thread before
 // its first access to memory that another kernel writes or reads (so completion stays transitive along the chain);
-// in a kernel launched the ordinary way both calls do nothing.
+// in a kernel launched the ordinary way both calls do nothing. With AI2B_CHAIN=0 in the environment launch_chained() launches the
+// ordinary way.
 __device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
@@ -161,7 +163,8 @@ inline cudaError_t launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block,
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
-    cfg.numAttrs = 1;
+    const char *env = std::getenv("AI2B_CHAIN");          // AI2B_CHAIN=0: ordinary launches (a switch for debugging), read per launch
+    cfg.numAttrs = (env && env[0] == '0') ? 0 : 1;
     return cudaLaunchKernelEx(&cfg, kern, KArgs(static_cast<Args &&>(args))...);
 }
 

@@ -70,3 +70,18 @@ def test_replay_equals_eager_and_checker(kind, checkers):
         torch.cuda.synchronize()
         got = (h_out[0:1].numpy(), h_out[16:16 + 3 * n].numpy().reshape(1, n, 3), h_out[1:10].numpy().reshape(1, 9))
         _close(got, eager[k], tol)
+
+
+@pytest.mark.parametrize("kind", ["mtp", "nep"])
+def test_ordinary_launches_give_the_same(kind, monkeypatch):
+    """AI2B_CHAIN=0 switches the chained launches off: same numbers either way."""
+    w, dt, tol = _workload(kind, 8)
+    ev = engine.Evaluator(w["model"], w["cell"], w["types"], w["rcut"], w["umax"], dt)
+    coords = torch.from_numpy(np.ascontiguousarray(w["coords"])).to(dt).cuda()
+    chained = _host(ev.compute(coords))
+    monkeypatch.setenv("AI2B_CHAIN", "0")
+    plain = _host(ev.compute(coords))
+    monkeypatch.delenv("AI2B_CHAIN")
+    again = _host(ev.compute(coords))
+    _close(plain, chained, tol)
+    _close(again, chained, tol)
